@@ -1,0 +1,368 @@
+#!/usr/bin/env python3
+"""Placement-plan benchmark.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one placement plan for one decode step of the headline workload:
+40 layers (80 KV buffers of 512 MiB), 256 requests, a 262,144-slot pool, and per
+(layer, request) touched sets of the newest 128 slots plus 2048 Zipf(1.1)
+history draws -- 22.3 M int64 slot ids (178 MB) per step.  Two different
+batches alternate, so every step re-reads more than the L2 holds and every
+plan has real evictions and additions.
+
+`value`  device time per step, slot ids already in HBM (CUDA events on the
+         launching stream, max over ranks)
+`e2e`    the same plan through the host-buffer C-ABI call: pinned host ids are
+         copied to the device, planned, and the range list is copied back
+--impl reference  times the CPU restatement of the reference's Python path on
+         the host cores (a bounded sample of layers per step, scaled up)
+
+Prints one JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import multiprocessing as mp
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "placement_plan_us_per_decode_step"
+UNIT = "us/step"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def make_workload(name: str, seed: int):
+    from retarget_b200 import workloads
+    if name == "target":
+        return workloads.target_step(seed)
+    if name == "sparse":
+        return workloads.sparse_feedback(seed)
+    if name == "full_refresh":
+        return workloads.full_refresh(seed)
+    if name == "tp_shard":
+        return workloads.tp_shard(seed)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def algorithmic_bytes(batch, n_ranges: int) -> int:
+    """Bytes one step must move: every slot id once, the group offsets, the
+    resident words read and written, the ranges and the result record."""
+    G = batch.layout.n_groups
+    return 8 * batch.n_idx + 8 * (G + 1) + 2 * 4 * 32 * G + 24 * n_ranges + 64
+
+
+def workload_config(batch, extra=None) -> dict:
+    lay = batch.layout
+    cfg = {"workload": batch.name, "layers": lay.layers, "kv_buffers": lay.n_buffers,
+           "alloc_bytes": lay.alloc_bytes, "pool_slots": lay.pool_slots,
+           "bytes_per_slot": lay.bytes_per_slot, "uvm_block_bytes": lay.block_bytes,
+           "bitmaps": lay.n_groups, "blocks_per_bitmap": lay.n_blocks,
+           "budget_blocks": batch.budget_blocks, "slot_ids_per_step": batch.n_idx,
+           "slot_id_bytes_per_step": 8 * batch.n_idx, "index_dtype": "int64"}
+    cfg.update(extra or {})
+    return cfg
+
+
+# --------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons, power = [], [], set(), []
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0])); smax.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------
+# CPU arms (oracle ports; the only place this file touches oracle/)
+# --------------------------------------------------------------------------
+_CPU = {}
+
+
+def _cpu_layer(args):
+    """Worker: the literal reference chain on one layer of one batch."""
+    which, layer, resident_blocks = args
+    from oracle import compose
+    import dataclasses
+    b = _CPU["batches"][which]
+    lay = dataclasses.replace(b.layout, layers=1, shared_bitmap=True)
+    lo, hi = int(b.group_off[layer]), int(b.group_off[layer + 1])
+    ro = b.req_off
+    k0, k1 = np.searchsorted(ro, lo, "left"), np.searchsorted(ro, hi, "right")
+    from retarget_b200.workloads import SlotBatch
+    one = SlotBatch(lay, b.slots[lo:hi], np.array([0, hi - lo], np.int64), ro[k0:k1] - lo,
+                    b.budget_blocks)
+    resident = [set(resident_blocks)]
+    t = time.perf_counter()
+    out, _ = compose.plan_step(one, resident, evict=True, literal=True)
+    return time.perf_counter() - t, len(out), layer, sorted(resident[0])
+
+
+def cpu_python_port(batches, sample_layers: int, procs: int, steps: int, warmup: int):
+    """Times the Python restatement of the reference path on `sample_layers`
+    layers per step (spread over `procs` processes) and scales to all layers.
+    Returns per-step seconds for the whole workload."""
+    L = batches[0].layout.n_groups
+    _CPU["batches"] = batches
+    resident = {}
+    layers = list(range(min(sample_layers, L)))
+    ctx = mp.get_context("fork")
+    times = []
+    with ctx.Pool(procs) as pool:
+        for step in range(warmup + steps):
+            t = time.perf_counter()
+            res = pool.map(_cpu_layer, [(step % 2, l, resident.get(l, ())) for l in layers],
+                           chunksize=1)
+            dt = time.perf_counter() - t
+            for _, _, layer, blocks in res:
+                resident[layer] = blocks
+            if step >= warmup:
+                times.append(dt * L / len(layers))
+    return times
+
+
+def cpu_c_port(batches, reps: int):
+    from oracle import c_oracle
+    co = c_oracle.COracle(batches[0].layout)
+    threads = min(co.max_threads, os.cpu_count() or 1)
+    times = []
+    for i in range(reps + 1):
+        b = batches[i % 2]
+        t = time.perf_counter()
+        co.step(b.slots, b.group_off, b.budget_blocks, True, threads)
+        if i:
+            times.append(time.perf_counter() - t)
+    return statistics.median(times), threads
+
+
+def run_reference(args):
+    """The reference arm: CPU only, rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    batches = [make_workload(args.workload, 0), make_workload(args.workload, 1)]
+    cores = os.cpu_count() or 1
+    L = batches[0].layout.n_groups
+    sample = min(L, max(1, cores))
+    times = cpu_python_port(batches, sample, min(cores, sample), args.steps, args.warmup)
+    per_step = statistics.mean(times)
+    us = per_step * 1e6
+    sample_text = (f"{sample} of {L} layers per step through the Python restatement of "
+                   f"encode_runs->blocks->target_blocks->choose->blocksv, {min(cores, sample)} "
+                   f"processes, scaled x{L / sample:.2f}")
+    line = {"impl": "reference", "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
+            "data": "synthetic", "config": workload_config(batches[0]),
+            "cpu_baseline": {"value": us, "unit": UNIT, "cores": min(cores, sample), "kind": "port",
+                             "sample": sample_text},
+            "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from retarget_b200 import capi
+    from retarget_b200.planner import DevicePlanner, result_from_tensor
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    batches = [make_workload(args.workload, 0), make_workload(args.workload, 1)]
+    lay = batches[0].layout
+    # CPU baseline first: its worker processes are forked before CUDA is initialised
+    cpu_lines = {}
+    if rank == 0 and world == 1 and not args.no_cpu:
+        sample = 2
+        L = lay.n_groups
+        py = cpu_python_port(batches, sample, 1, 2, 1)
+        c_s, c_threads = cpu_c_port(batches, 3)
+        cpu_lines["cpu_baseline"] = {
+            "value": statistics.mean(py) * 1e6, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"{min(sample, L)} of {L} layers per step through the Python restatement of "
+                      f"the reference chain, 1 process, scaled x{L / min(sample, L):.0f}"}
+        cpu_lines["cpu_baseline_native"] = {
+            "value": c_s * 1e6, "unit": UNIT, "cores": c_threads, "kind": "port",
+            "sample": "full step, C restatement with OpenMP over layers"}
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; retarget_b200 has no CPU path to fall back to")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    flags = capi.RT_PLAN_EVICT | (capi.RT_PLAN_NO_TMA if args.no_tma else 0)
+    planner = DevicePlanner(lay, local, max_indices=max(b.n_idx for b in batches) + 8,
+                            max_ranges=1 << 16)
+    d_slots = [torch.from_numpy(b.slots).to(dev) for b in batches]
+    h_slots = [torch.from_numpy(b.slots).pin_memory() for b in batches]
+    d_out = torch.zeros((1 << 16) * 24, dtype=torch.uint8, device=dev)
+    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream()
+    K, W = args.steps, args.warmup
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def device_step(i):
+        b = batches[i % 2]
+        planner.step_device(d_slots[i % 2], b.group_off, b.budget_blocks, flags, d_out, d_res,
+                            stream.cuda_stream)
+
+    for i in range(W):
+        device_step(i)
+    torch.cuda.synchronize()
+    n_ranges = result_from_tensor(d_res)["n_ranges"]
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(K + 1)]
+    barrier()
+    ev[0].record(stream)
+    for i in range(K):
+        device_step(W + i)
+        ev[i + 1].record(stream)
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[K])
+    per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(K)]
+    last = result_from_tensor(d_res)
+    if last["flags"]:
+        raise SystemExit(f"bench.py: planner reported flags {last['flags']}")
+
+    # end to end through the host-buffer call: pinned ids -> device -> plan -> ranges on the host
+    out_host = np.empty(1 << 16, dtype=capi.RANGE_DTYPE)
+    e2e_ranges = 0
+    for i in range(W):
+        planner.step_host(h_slots[i % 2].numpy(), batches[i % 2].group_off,
+                          batches[i % 2].budget_blocks, flags, out=out_host)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(K):
+        b = batches[(W + i) % 2]
+        got, res = planner.step_host(h_slots[(W + i) % 2].numpy(), b.group_off, b.budget_blocks,
+                                     flags, out=out_host)
+        e2e_ranges = res.n_ranges
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / K
+    clocks = sampler.stop() if sampler else None
+
+    t = torch.tensor([total_ms / K, e2e_s * 1e3, statistics.mean(per_launch_ms)],
+                     dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step, e2e_ms, launch_ms = (float(x) for x in t.cpu())
+
+    if rank == 0:
+        peaks_path = ROOT / "MEASURED_PEAKS.json"
+        if peaks_path.exists():
+            peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured"
+        else:
+            peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+        bytes_step = algorithmic_bytes(batches[0], n_ranges)
+        achieved = bytes_step / (launch_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": ms_per_step * 1e3, "unit": UNIT, "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+            "config": workload_config(batches[0], {
+                "parallelism": f"{world} independent per-GPU planners (one KV shard each), no collective on the data path",
+                "l2": "178 MB of ids per step (> 126 MB L2); two batches alternate",
+                "staging": "ld.global 128-bit" if args.no_tma else "cp.async.bulk (TMA) -> shared",
+                "evict": True}),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": PROFILED_TRAFFIC_BYTES,
+                         "peak_source": peak_src, "algorithmic_bytes_per_launch": bytes_step,
+                         "launch_ms": launch_ms, "kernel": "scan_plan_tma_kernel" if not args.no_tma else "scan_plan_kernel"},
+            "e2e": {"value": e2e_ms * 1e3, "unit": UNIT,
+                    "h2d_bytes_per_step": 8 * batches[0].n_idx,
+                    "d2h_bytes_per_step": 24 * e2e_ranges + 64},
+            "gpu_launches": K,
+            "clocks": clocks,
+            "slot_scan_gbs_aggregate": world * achieved,
+            "plans_per_s_aggregate": world / (ms_per_step * 1e-3),
+            "ranges_per_step": n_ranges,
+        }
+        if cpu_lines:
+            line.update(cpu_lines)
+        print(json.dumps(line), flush=True)
+    planner.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes per launch of the scan kernel from the ncu capture summarised under
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until captured.
+PROFILED_TRAFFIC_BYTES = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="target",
+                    choices=["target", "sparse", "full_refresh", "tp_shard"])
+    ap.add_argument("--no-tma", action="store_true", help="stage ids with plain 128-bit loads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

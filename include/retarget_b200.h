@@ -1,0 +1,265 @@
+/*
+ * retarget_b200 -- C ABI of the B200-native KV-cache placement planner.
+ *
+ * Plain C, no CUDA or framework types in any signature: device pointers are
+ * `const void *` / typed pointers to device memory, streams are passed as
+ * `void *` (a cudaStream_t / CUstream; NULL = the plan's own stream).
+ *
+ * Every function returns an `int` status: 0 (RT_OK) on success, a negative
+ * `rt_status` otherwise; `rt_strerror()` turns it into text.  Where the
+ * reference reports a specific message or socket error string the same text is
+ * returned.  Nothing throws, nothing calls back, the caller owns every buffer
+ * it passes in.  A plan handle may be used from one thread at a time.
+ *
+ * Each entry point names the reference code it stands in for (paths relative
+ * to the reference project root).
+ */
+#ifndef RETARGET_B200_H
+#define RETARGET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RT_ABI_VERSION 1
+#define RT_MAX_GROUPS 128u      /* bitmaps per plan (one per layer at most)          */
+#define RT_MAX_BLOCKS 1024u     /* bits per bitmap: the 256-hex-digit mask limit,    */
+                                /* select.cpp:24155                                  */
+#define RT_MAX_BUFFERS 1024u    /* cache allocations per plan                        */
+#define RT_BITMAP_WORDS 32u     /* RT_MAX_BLOCKS / 32                                */
+#define RT_DST_CPU (-1)         /* CU_DEVICE_CPU                                     */
+#define RT_INITIAL UINT64_MAX   /* "no previous window", experiments/cache_window.py:16 */
+
+typedef enum rt_status {
+    RT_OK = 0,
+    RT_ERR_INVALID_ARGUMENT = -1,
+    RT_ERR_NO_DEVICE = -2,          /* CUDA runtime/driver unusable: there is no CPU fallback */
+    RT_ERR_CUDA = -3,               /* a CUDA call failed; rt_last_cuda_error() has the code  */
+    RT_ERR_OUT_OF_MEMORY = -4,
+    RT_ERR_CAPACITY = -5,           /* more indices / ranges than the plan was created for    */
+    RT_ERR_ALIGNMENT = -6,          /* slot array not 16-byte aligned                         */
+    RT_ERR_SLOT_RANGE = -7,         /* a slot id above capacity (the reference asserts)       */
+    RT_ERR_BUSY = -8,
+    RT_ERR_NOT_RUNNING = -9,
+    RT_ERR_IO = -10,
+    RT_ERR_PLAN = -11,              /* plan command rejected; text from rt_uvm_command reply  */
+    /* experiments/cache_window.py:31-50, one code per message, in check order */
+    RT_ERR_SPEC_POSITIVE = -20,
+    RT_ERR_SPEC_TRAILING = -21,
+    RT_ERR_SPEC_PAGE = -22,
+    RT_ERR_SPEC_MULTIPLE = -23,
+    RT_ERR_SPEC_EXCEEDS = -24,
+    RT_ERR_SPEC_INTERVAL = -25,
+    RT_ERR_SPEC_MODE = -26,
+    RT_ERR_COMPLETED_COUNT = -27,   /* experiments/cache_window.py:53-54 */
+    /* experiments/slot_placement.py:60-64 */
+    RT_ERR_BUDGET_DIVISIBLE = -28,
+    RT_ERR_BLOCK_PAGE = -29
+} rt_status;
+
+const char *rt_strerror(int status);
+int rt_abi_version(void);
+/* Last cudaError_t / CUresult seen by the calling thread (0 if none). */
+int rt_last_cuda_error(void);
+
+/* ------------------------------------------------------------------ */
+/* Window policy: host arithmetic                                      */
+/* ------------------------------------------------------------------ */
+
+/* experiments/cache_window.py:19-29 (CacheWindowSpec fields) */
+typedef struct rt_window_spec {
+    uint64_t allocation_bytes;
+    uint64_t allocation_count;
+    uint64_t bytes_per_token;
+    uint64_t width_tokens;
+    uint64_t lookahead_tokens;
+    uint64_t quantum_tokens;
+    double min_update_seconds;
+    int32_t idle_only;       /* 0 / 1 */
+    int32_t update_mode;     /* 0 incremental, 1 initial_only, 2 full_cache */
+} rt_window_spec;
+
+/* CacheWindowSpec.__post_init__, experiments/cache_window.py:31-50.
+ * On RT_ERR_SPEC_POSITIVE *bad_field (optional) gets the index of the
+ * offending field in declaration order. */
+int rt_window_spec_check(const rt_window_spec *spec, int *bad_field);
+
+/* CacheWindowSpec.window, experiments/cache_window.py:52-63. */
+int rt_window(const rt_window_spec *spec, double completed_tokens, uint64_t out[2]);
+
+/* interval_difference, experiments/cache_window.py:66-68.
+ * Writes up to two (lo, hi) pairs to out[4]; returns the pair count. */
+int rt_interval_difference(const uint64_t a[2], const uint64_t b[2], uint64_t out[4]);
+
+/* requested_gpu_bytes / requested_cpu_bytes of a window plan,
+ * experiments/cache_window.py:122-131.  `other_bytes` is the total size of the
+ * non-cache allocations (only counted for a full plan). */
+int rt_window_accounting(const rt_window_spec *spec, uint64_t n_cache, uint64_t other_bytes,
+                         const uint64_t old_window[2], const uint64_t new_window[2],
+                         int full, int refresh, uint64_t *gpu_bytes, uint64_t *cpu_bytes);
+
+/* SlotPlacementController.__init__ budget rule, experiments/slot_placement.py:60-64. */
+int rt_slot_budget(const rt_window_spec *spec, uint64_t block_tokens, uint64_t *budget_blocks);
+
+/* encode_mask, experiments/slot_placement.py:47-51: lower-case hex of the OR of
+ * (1 << block), no leading zeros, "0" when empty.  Returns the string length. */
+int rt_encode_mask(const uint32_t *blocks, size_t n, char *out, size_t cap);
+
+/* encode_runs, experiments/kv_audit/kv_audit_probe.py:23-32: half-open runs of
+ * consecutive values, order and repeats preserved.  runs_out holds
+ * (begin, end) pairs; *n_runs gets the count even when cap_runs is too small
+ * (then RT_ERR_CAPACITY is returned). */
+int rt_encode_runs(const int64_t *values, size_t n, int64_t *runs_out, size_t cap_runs,
+                   size_t *n_runs);
+
+/* ------------------------------------------------------------------ */
+/* Plan-command expansion: host, no GPU                                 */
+/* ------------------------------------------------------------------ */
+
+/* One registry entry, select.cpp:23770-23778 (ctx and pointer omitted). */
+typedef struct rt_alloc_info {
+    uint64_t id;
+    uint64_t bytes;
+    int32_t device;
+    int32_t concurrent;
+} rt_alloc_info;
+
+/* One migration request, select.cpp:23779-23784. */
+typedef struct rt_id_range {
+    uint64_t id;
+    uint64_t offset;
+    uint64_t bytes;
+    int32_t dst;          /* device ordinal or RT_DST_CPU */
+    int32_t reserved;
+} rt_id_range;
+
+/* The plan half of uvm_command, select.cpp:24099-24309: parses one command line
+ * (prefetch / target / targetv / retarget / windowv / windowfullv / blocksv)
+ * against a registry snapshot and writes the ranges it would queue, in queue
+ * order.  On rejection returns RT_ERR_PLAN and *error points at the socket's
+ * error string (static storage).  `page` is the host page size (0 = ask the OS). */
+int rt_expand_command(const rt_alloc_info *registry, size_t n_alloc, uint64_t generation,
+                      const char *line, uint64_t page, rt_id_range *out, size_t cap,
+                      size_t *n_out, const char **error);
+
+/* ------------------------------------------------------------------ */
+/* Device planner                                                       */
+/* ------------------------------------------------------------------ */
+
+/* One emitted range: buffer = index of the cache allocation in registry order. */
+typedef struct rt_range {
+    uint32_t buffer;
+    int32_t dst;          /* device ordinal or RT_DST_CPU */
+    uint64_t offset;
+    uint64_t bytes;
+} rt_range;
+
+/* KV geometry the planner works on.  All cache allocations have alloc_bytes;
+ * bitmap g covers the buffers whose buffer_group entry is g (NULL: one bitmap
+ * for all buffers).  Valid slot ids are 1..capacity_slots
+ * (experiments/slot_feedback.py:27-28,39-43). */
+typedef struct rt_layout {
+    uint32_t n_buffers;
+    uint32_t n_groups;
+    uint64_t alloc_bytes;
+    uint32_t bytes_per_slot;
+    uint32_t block_bytes;
+    uint64_t capacity_slots;
+    const uint32_t *buffer_group;
+    int32_t dst_device;   /* ordinal written into GPU-bound ranges */
+    int32_t reserved;
+} rt_layout;
+
+#define RT_PLAN_EVICT   1u   /* also emit resident-but-not-wanted blocks, CPU-bound, first */
+#define RT_PLAN_DRY_RUN 2u   /* do not commit the wanted set as the new resident set       */
+#define RT_PLAN_NO_TMA  4u   /* stage the slot table with plain 128-bit loads             */
+
+#define RT_RESULT_OVERFLOW   1u   /* more ranges than `cap`; the first cap were written */
+#define RT_RESULT_SLOT_RANGE 2u   /* some slot id was above capacity                    */
+#define RT_RESULT_TIMEOUT    4u   /* a bounded device-side wait gave up                 */
+
+typedef struct rt_plan_result {
+    uint32_t n_ranges;        /* total emitted (may exceed cap, see flags)  */
+    uint32_t n_cpu_ranges;    /* the first n_cpu_ranges move to the CPU      */
+    uint32_t flags;
+    uint32_t blocks_touched;  /* distinct blocks seen, summed over bitmaps   */
+    uint32_t blocks_desired;  /* after the budget cut                        */
+    uint32_t blocks_added;
+    uint32_t blocks_evicted;
+    uint32_t reserved;
+    uint64_t invalid_slots;   /* ids above capacity                          */
+    uint64_t ignored_slots;   /* ids below 1 (dropped, as the reference does)*/
+    uint64_t gpu_bytes;       /* requested_gpu_bytes, experiments/slot_placement.py:154 */
+    uint64_t cpu_bytes;
+} rt_plan_result;
+
+typedef struct rt_plan rt_plan;
+
+/* Creates the planner state on `device`: resident bitmaps (all clear), scratch,
+ * a side stream, a device staging buffer for max_indices slot ids and a pinned
+ * host buffer for max_ranges ranges (both only used by the host-buffer call).
+ * Fails with RT_ERR_NO_DEVICE when no usable GPU is present. */
+int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices,
+                   uint32_t max_ranges, rt_plan **out);
+int rt_plan_destroy(rt_plan *plan);
+
+/* Resident ("committed") bitmaps, n_groups x RT_BITMAP_WORDS uint32 words, bit b
+ * of a bitmap = block b.  Stands in for SlotPlacementController.committed,
+ * experiments/slot_placement.py:65,150-153. */
+int rt_plan_set_resident(rt_plan *plan, const uint32_t *words);
+int rt_plan_get_resident(rt_plan *plan, uint32_t *words);
+
+/* One planning step over slot ids that are already in device memory.
+ *
+ *   d_slots      int64 slot ids, 16-byte aligned; group g owns
+ *                d_slots[group_off[g] .. group_off[g+1])
+ *   group_off    HOST array of n_groups+1 ascending offsets
+ *   budget       keep at most this many blocks per bitmap
+ *   out/result   device or mapped-pinned memory; written by the kernel
+ *
+ * Replaces, per bitmap: encode_runs (kv_audit_probe.py:23-32) ->
+ * SlotFeedback.blocks (slot_feedback.py:35-46) -> read stamps (:72-74) ->
+ * publish/target_blocks (slot_feedback.py:81-85, slot_placement.py:37-44) ->
+ * choose (slot_placement.py:83-94) -> encode_mask + blocksv expansion
+ * (slot_placement.py:47-51, select.cpp:24147-24195).
+ * Asynchronous on `stream`. */
+int rt_plan_step_device(rt_plan *plan, const int64_t *d_slots, const int64_t *group_off,
+                        uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                        rt_plan_result *result, void *stream);
+
+/* Same step from HOST memory: copies the slot ids to the device, plans, copies
+ * the ranges back and waits.  This is the call a scheduler makes when the slot
+ * table lives on the host, as in kv_audit_probe.py:54-105. */
+int rt_plan_step(rt_plan *plan, const int64_t *h_slots, const int64_t *group_off,
+                 uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                 rt_plan_result *result);
+
+/* Padded request table (the serving engine's req_to_token layout): row r holds
+ * lens[r] valid ids in d_table[r*stride ..]; one bitmap for all buffers
+ * (n_groups must be 1).  d_lens is a DEVICE int32 array. */
+int rt_plan_step_table(rt_plan *plan, const int64_t *d_table, const int32_t *d_lens,
+                       uint32_t n_rows, uint64_t stride, uint32_t budget, uint32_t flags,
+                       rt_range *out, uint32_t cap, rt_plan_result *result, void *stream);
+
+/* Scan only: OR of touched blocks per bitmap into d_bitmaps
+ * (n_groups x RT_BITMAP_WORDS words, overwritten).  slot_feedback.py:35-46. */
+int rt_scan_slots(rt_plan *plan, const int64_t *d_slots, const int64_t *group_off,
+                  uint32_t *d_bitmaps, rt_plan_result *result, void *stream);
+
+/* Diff + budget + coalesce only, from wanted bitmaps already on the device.
+ * With the resident set holding the old window and d_want the new one this
+ * yields the windowv symmetric difference (select.cpp:24231-24240) for
+ * block-aligned windows. */
+int rt_plan_from_bitmaps(rt_plan *plan, const uint32_t *d_want, uint32_t budget, uint32_t flags,
+                         rt_range *out, uint32_t cap, rt_plan_result *result, void *stream);
+
+/* Waits for everything queued on the plan's own stream. */
+int rt_plan_sync(rt_plan *plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RETARGET_B200_H */

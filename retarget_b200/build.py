@@ -1,0 +1,106 @@
+"""Builds the native libraries in-tree with nvcc / g++ (sm_100a only).
+
+    python -m retarget_b200.build            # build what is out of date
+    python -m retarget_b200.build --force
+
+Outputs (next to this file, ignored by git):
+    libretarget_b200.so     C ABI: planner kernels, host policy, UVM server
+    libretarget_preload.so  LD_PRELOAD library: driver-API hooks around the same server
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+ROOT = PKG.parent
+CSRC = PKG / "csrc"
+INCLUDE = ROOT / "include"
+OBJ = ROOT / "build" / "obj"
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC,-Wall", f"-I{INCLUDE}", f"-I{CSRC}"]
+CXX_FLAGS = ["-O2", "-g", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-pthread",
+             f"-I{INCLUDE}", f"-I{CSRC}"]
+
+CORE_CU = ["plan_kernels.cu", "plan_capi.cu"]
+CORE_CPP = ["host_policy.cpp", "uvm_plan.cpp"]
+OPTIONAL_CORE_CPP = ["uvm_server.cpp", "prefetch_exec.cpp", "driver_api.cpp"]
+OPTIONAL_CORE_CU = ["feedback_kernels.cu", "paged_reader.cu", "noalloc_scan.cu"]
+PRELOAD_CPP = ["preload_hooks.cpp"]
+
+
+def nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found: the CUDA toolkit is required to build retarget_b200")
+
+
+def cuda_include() -> str:
+    return str(Path(nvcc()).resolve().parent.parent / "include")
+
+
+def _stale(target: Path, deps) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(Path(d).stat().st_mtime > t for d in deps)
+
+
+def _run(cmd):
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode:
+        sys.stderr.write(" ".join(map(str, cmd)) + "\n" + proc.stdout + proc.stderr)
+        raise RuntimeError(f"build step failed: {cmd[0]} {cmd[-1]}")
+    return proc.stdout + proc.stderr
+
+
+def build(force: bool = False, verbose: bool = False) -> dict:
+    OBJ.mkdir(parents=True, exist_ok=True)
+    headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
+    objs = []
+    log = []
+    cu = CORE_CU + [f for f in OPTIONAL_CORE_CU if (CSRC / f).exists()]
+    cpp = CORE_CPP + [f for f in OPTIONAL_CORE_CPP if (CSRC / f).exists()]
+    for name in cu:
+        src, obj = CSRC / name, OBJ / (name + ".o")
+        if force or _stale(obj, [src, *headers]):
+            log.append(_run([nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []),
+                             "-c", str(src), "-o", str(obj)]))
+        objs.append(obj)
+    for name in cpp:
+        src, obj = CSRC / name, OBJ / (name + ".o")
+        if force or _stale(obj, [src, *headers]):
+            log.append(_run(["g++", *CXX_FLAGS, f"-I{cuda_include()}", "-c", str(src), "-o", str(obj)]))
+        objs.append(obj)
+    core = PKG / "libretarget_b200.so"
+    if force or _stale(core, objs):
+        _run([nvcc(), "-shared", "-o", str(core), *map(str, objs),
+              "-cudart", "static", "-Xlinker", "--no-undefined", "-lpthread", "-ldl", "-lrt"])
+    out = {"core": core}
+    pre_srcs = [CSRC / f for f in PRELOAD_CPP if (CSRC / f).exists()]
+    if pre_srcs:
+        pre_objs = []
+        for src in pre_srcs:
+            obj = OBJ / (src.name + ".o")
+            if force or _stale(obj, [src, *headers]):
+                _run(["g++", *CXX_FLAGS, f"-I{cuda_include()}", "-c", str(src), "-o", str(obj)])
+            pre_objs.append(obj)
+        pre = PKG / "libretarget_preload.so"
+        if force or _stale(pre, pre_objs + objs):
+            _run([nvcc(), "-shared", "-o", str(pre), *map(str, pre_objs), *map(str, objs),
+                  "-cudart", "static", "-lpthread", "-ldl", "-lrt"])
+        out["preload"] = pre
+    if verbose:
+        print("".join(log))
+    return out
+
+
+if __name__ == "__main__":
+    built = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    for k, v in built.items():
+        print(k, v)

@@ -1,0 +1,367 @@
+// C ABI of the device planner: plan handles, argument checks, launches.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "plan_device.cuh"
+#include "rt_internal.h"
+
+namespace rt {
+cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, int grid,
+                             cudaStream_t stream);
+cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid, cudaStream_t stream);
+cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream_t stream);
+cudaError_t scan_plan_occupancy(int *plain_blocks_per_sm, int *tma_blocks_per_sm);
+}  // namespace rt
+
+struct rt_plan {
+    rt_layout layout;
+    int device = 0;
+    int sm_count = 0;
+    int plain_blocks_per_sm = 1;
+    int tma_blocks_per_sm = 1;
+    uint32_t n_blocks = 0;
+    uint32_t block_tokens = 0;
+    int shift = -1;
+    cudaStream_t stream = nullptr;
+    rt::GroupScratch *d_groups = nullptr;
+    rt::GlobalScratch *d_global = nullptr;
+    uint32_t *d_resident = nullptr;
+    uint32_t *d_buffer_group = nullptr;
+    long long *d_stage = nullptr;      // host-buffer call: slot ids land here
+    uint64_t max_indices = 0;
+    rt_range *h_out = nullptr;         // pinned + mapped: the kernel writes ranges here
+    rt_plan_result *h_result = nullptr;
+    uint32_t max_ranges = 0;
+};
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver || e == cudaErrorInitializationError)
+        return RT_ERR_NO_DEVICE;
+    if (e == cudaErrorMemoryAllocation) return RT_ERR_OUT_OF_MEMORY;
+    return RT_ERR_CUDA;
+}
+
+#define RT_CUDA(call)                                  \
+    do {                                               \
+        cudaError_t e__ = (call);                      \
+        if (e__ != cudaSuccess) return cuda_fail(e__); \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int device) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        ok = cudaSetDevice(device) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_t flags,
+                    rt_range *out, uint32_t cap, rt_plan_result *result) {
+    p.groups = pl->d_groups;
+    p.global = pl->d_global;
+    p.resident = pl->d_resident;
+    p.buffer_group = pl->d_buffer_group;
+    p.bitmaps_out = nullptr;
+    p.out = out;
+    p.result = result;
+    p.cap = cap;
+    p.n_buffers = pl->layout.n_buffers;
+    p.n_groups = pl->layout.n_groups;
+    p.n_blocks = pl->n_blocks;
+    p.budget = budget;
+    p.flags = flags;
+    p.dst_device = pl->layout.dst_device;
+    p.scan_only = 0;
+    p.alloc_bytes = pl->layout.alloc_bytes;
+    p.block_bytes = pl->layout.block_bytes;
+}
+
+// CSR work-unit table.  Every group gets at least one unit so that its tail
+// runs even when it has no ids this step.
+int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const int64_t *d_slots,
+                       const int64_t *group_off) {
+    const uint32_t G = pl->layout.n_groups;
+    a.slots = reinterpret_cast<const long long *>(d_slots);
+    a.lens = nullptr;
+    a.stride = 0;
+    a.units_per_row = 0;
+    a.n_groups = (int)G;
+    a.capacity = pl->layout.capacity_slots;
+    a.block_tokens = pl->block_tokens;
+    a.shift = pl->shift;
+    long long units = 0;
+    for (uint32_t g = 0; g < G; ++g) {
+        long long lo = group_off[g], hi = group_off[g + 1];
+        if (lo < 0 || hi < lo) return RT_ERR_INVALID_ARGUMENT;
+        a.group_off[g] = lo;
+        a.unit_first[g] = (int)units;
+        long long span = hi - (lo & ~1LL);
+        long long n = (span + rt::kChunkElems - 1) / rt::kChunkElems;
+        units += n > 0 ? n : 1;
+        if (units > 0x7fffffffLL) return RT_ERR_CAPACITY;
+    }
+    a.group_off[G] = group_off[G];
+    a.unit_first[G] = (int)units;
+    a.n_units = (int)units;
+    if ((reinterpret_cast<uintptr_t>(d_slots) & 15u) && group_off[G] > 0) return RT_ERR_ALIGNMENT;
+    return RT_OK;
+}
+
+int grid_for(const rt_plan *pl, int units, bool tma) {
+    long long slots = (long long)pl->sm_count * (tma ? pl->tma_blocks_per_sm : pl->plain_blocks_per_sm);
+    return (int)(units < slots ? units : slots);
+}
+
+bool want_tma(uint32_t flags) {
+    if (flags & RT_PLAN_NO_TMA) return false;
+    static const bool env_off = [] {
+        const char *s = getenv("RT_NO_TMA");
+        return s && *s == '1';
+    }();
+    return !env_off;
+}
+
+}  // namespace
+
+namespace rt {
+int last_cuda_error_get() { return g_last_cuda_error; }
+void last_cuda_error_set(int e) { g_last_cuda_error = e; }
+}  // namespace rt
+
+extern "C" {
+
+int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, uint32_t max_ranges,
+                   rt_plan **out) {
+    if (!layout || !out) return RT_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    const rt_layout &L = *layout;
+    if (!L.n_buffers || L.n_buffers > RT_MAX_BUFFERS || !L.n_groups || L.n_groups > RT_MAX_GROUPS ||
+        !L.alloc_bytes || !L.bytes_per_slot || !L.block_bytes || L.block_bytes > L.alloc_bytes ||
+        L.block_bytes % L.bytes_per_slot || !L.capacity_slots || L.capacity_slots > 0xfffffffeull)
+        return RT_ERR_INVALID_ARGUMENT;
+    uint64_t n_blocks = L.alloc_bytes / L.block_bytes + (L.alloc_bytes % L.block_bytes != 0);
+    uint32_t block_tokens = L.block_bytes / L.bytes_per_slot;
+    if (n_blocks > RT_MAX_BLOCKS || L.capacity_slots / block_tokens >= n_blocks)
+        return RT_ERR_INVALID_ARGUMENT;
+    if (L.buffer_group)
+        for (uint32_t j = 0; j < L.n_buffers; ++j)
+            if (L.buffer_group[j] >= L.n_groups) return RT_ERR_INVALID_ARGUMENT;
+    if (!L.buffer_group && L.n_groups != 1) return RT_ERR_INVALID_ARGUMENT;
+
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (device < 0 || device >= count) return RT_ERR_NO_DEVICE;
+    DeviceGuard guard(device);
+    if (!guard.ok) return RT_ERR_NO_DEVICE;
+
+    rt_plan *pl = new (std::nothrow) rt_plan();
+    if (!pl) return RT_ERR_OUT_OF_MEMORY;
+    pl->layout = L;
+    pl->layout.buffer_group = nullptr;
+    pl->device = device;
+    pl->n_blocks = (uint32_t)n_blocks;
+    pl->block_tokens = block_tokens;
+    pl->shift = -1;
+    if ((block_tokens & (block_tokens - 1)) == 0) {
+        int s = 0;
+        while ((1u << s) != block_tokens) ++s;
+        pl->shift = s;
+    }
+    pl->max_indices = max_indices;
+    pl->max_ranges = max_ranges;
+    int status = RT_OK;
+    auto fail = [&](cudaError_t err) { status = cuda_fail(err); };
+    do {
+        if ((e = cudaDeviceGetAttribute(&pl->sm_count, cudaDevAttrMultiProcessorCount, device))) { fail(e); break; }
+        if ((e = rt::scan_plan_occupancy(&pl->plain_blocks_per_sm, &pl->tma_blocks_per_sm))) { fail(e); break; }
+        if (pl->plain_blocks_per_sm < 1) pl->plain_blocks_per_sm = 1;
+        if (pl->tma_blocks_per_sm < 1) pl->tma_blocks_per_sm = 1;
+        if ((e = cudaStreamCreateWithFlags(&pl->stream, cudaStreamNonBlocking))) { fail(e); break; }
+        size_t gbytes = sizeof(rt::GroupScratch) * L.n_groups;
+        if ((e = cudaMalloc(&pl->d_groups, gbytes))) { fail(e); break; }
+        if ((e = cudaMemset(pl->d_groups, 0, gbytes))) { fail(e); break; }
+        if ((e = cudaMalloc(&pl->d_global, sizeof(rt::GlobalScratch)))) { fail(e); break; }
+        if ((e = cudaMemset(pl->d_global, 0, sizeof(rt::GlobalScratch)))) { fail(e); break; }
+        size_t rbytes = sizeof(uint32_t) * rt::kWords * L.n_groups;
+        if ((e = cudaMalloc(&pl->d_resident, rbytes))) { fail(e); break; }
+        if ((e = cudaMemset(pl->d_resident, 0, rbytes))) { fail(e); break; }
+        std::vector<uint32_t> bg(L.n_buffers, 0u);
+        if (L.buffer_group) memcpy(bg.data(), L.buffer_group, sizeof(uint32_t) * L.n_buffers);
+        if ((e = cudaMalloc(&pl->d_buffer_group, sizeof(uint32_t) * L.n_buffers))) { fail(e); break; }
+        if ((e = cudaMemcpy(pl->d_buffer_group, bg.data(), sizeof(uint32_t) * L.n_buffers,
+                            cudaMemcpyHostToDevice))) { fail(e); break; }
+        if (max_indices) {
+            // +2 ids of slack so a 16-byte load at the very end stays in bounds
+            if ((e = cudaMalloc(&pl->d_stage, sizeof(long long) * (max_indices + 2)))) { fail(e); break; }
+        }
+        if ((e = cudaHostAlloc(&pl->h_out, sizeof(rt_range) * (max_ranges ? max_ranges : 1),
+                               cudaHostAllocMapped))) { fail(e); break; }
+        if ((e = cudaHostAlloc(&pl->h_result, sizeof(rt_plan_result), cudaHostAllocMapped))) { fail(e); break; }
+        if ((e = cudaDeviceSynchronize())) { fail(e); break; }
+    } while (0);
+    if (status != RT_OK) {
+        rt_plan_destroy(pl);
+        return status;
+    }
+    *out = pl;
+    return RT_OK;
+}
+
+int rt_plan_destroy(rt_plan *pl) {
+    if (!pl) return RT_OK;
+    DeviceGuard guard(pl->device);
+    if (pl->stream) {
+        cudaStreamSynchronize(pl->stream);
+        cudaStreamDestroy(pl->stream);
+    }
+    cudaFree(pl->d_groups);
+    cudaFree(pl->d_global);
+    cudaFree(pl->d_resident);
+    cudaFree(pl->d_buffer_group);
+    cudaFree(pl->d_stage);
+    if (pl->h_out) cudaFreeHost(pl->h_out);
+    if (pl->h_result) cudaFreeHost(pl->h_result);
+    delete pl;
+    return RT_OK;
+}
+
+int rt_plan_set_resident(rt_plan *pl, const uint32_t *words) {
+    if (!pl || !words) return RT_ERR_INVALID_ARGUMENT;
+    DeviceGuard guard(pl->device);
+    size_t bytes = sizeof(uint32_t) * rt::kWords * pl->layout.n_groups;
+    RT_CUDA(cudaMemcpyAsync(pl->d_resident, words, bytes, cudaMemcpyHostToDevice, pl->stream));
+    RT_CUDA(cudaStreamSynchronize(pl->stream));
+    return RT_OK;
+}
+
+int rt_plan_get_resident(rt_plan *pl, uint32_t *words) {
+    if (!pl || !words) return RT_ERR_INVALID_ARGUMENT;
+    DeviceGuard guard(pl->device);
+    size_t bytes = sizeof(uint32_t) * rt::kWords * pl->layout.n_groups;
+    RT_CUDA(cudaMemcpyAsync(words, pl->d_resident, bytes, cudaMemcpyDeviceToHost, pl->stream));
+    RT_CUDA(cudaStreamSynchronize(pl->stream));
+    return RT_OK;
+}
+
+int rt_plan_step_device(rt_plan *pl, const int64_t *d_slots, const int64_t *group_off,
+                        uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                        rt_plan_result *result, void *stream) {
+    if (!pl || !group_off || !result || (!out && cap)) return RT_ERR_INVALID_ARGUMENT;
+    if (!d_slots && group_off[pl->layout.n_groups] > 0) return RT_ERR_INVALID_ARGUMENT;
+    DeviceGuard guard(pl->device);
+    rt::ScanArgs a;
+    int st = fill_scan_args_csr(pl, a, d_slots, group_off);
+    if (st != RT_OK) return st;
+    rt::PlanArgs p;
+    fill_plan_args(pl, p, budget, flags, out, cap, result);
+    cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
+    bool tma = want_tma(flags);
+    int grid = grid_for(pl, a.n_units, tma);
+    RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s) : rt::launch_scan_plan(a, p, false, grid, s));
+    return RT_OK;
+}
+
+int rt_plan_step(rt_plan *pl, const int64_t *h_slots, const int64_t *group_off, uint32_t budget,
+                 uint32_t flags, rt_range *out, uint32_t cap, rt_plan_result *result) {
+    if (!pl || !group_off || !result || (!out && cap)) return RT_ERR_INVALID_ARGUMENT;
+    const uint32_t G = pl->layout.n_groups;
+    int64_t n = group_off[G];
+    if (n < 0 || (uint64_t)n > pl->max_indices || group_off[0] < 0) return RT_ERR_CAPACITY;
+    if (n && !h_slots) return RT_ERR_INVALID_ARGUMENT;
+    DeviceGuard guard(pl->device);
+    if (n) RT_CUDA(cudaMemcpyAsync(pl->d_stage, h_slots, sizeof(long long) * (size_t)n,
+                                   cudaMemcpyHostToDevice, pl->stream));
+    uint32_t dev_cap = cap < pl->max_ranges ? cap : pl->max_ranges;
+    int st = rt_plan_step_device(pl, reinterpret_cast<const int64_t *>(pl->d_stage), group_off, budget,
+                                 flags, pl->h_out, dev_cap, pl->h_result, pl->stream);
+    if (st != RT_OK) return st;
+    RT_CUDA(cudaStreamSynchronize(pl->stream));
+    *result = *pl->h_result;
+    uint32_t n_copy = result->n_ranges < dev_cap ? result->n_ranges : dev_cap;
+    if (n_copy) memcpy(out, pl->h_out, sizeof(rt_range) * n_copy);
+    if (result->flags & RT_RESULT_SLOT_RANGE) return RT_ERR_SLOT_RANGE;
+    if (result->flags & RT_RESULT_OVERFLOW) return RT_ERR_CAPACITY;
+    return RT_OK;
+}
+
+int rt_plan_step_table(rt_plan *pl, const int64_t *d_table, const int32_t *d_lens, uint32_t n_rows,
+                       uint64_t stride, uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                       rt_plan_result *result, void *stream) {
+    if (!pl || !result || (!out && cap) || pl->layout.n_groups != 1) return RT_ERR_INVALID_ARGUMENT;
+    if (!n_rows || !stride || !d_table || !d_lens) return RT_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(d_table) & 15u) return RT_ERR_ALIGNMENT;
+    DeviceGuard guard(pl->device);
+    rt::ScanArgs a;
+    memset(&a, 0, sizeof(a));
+    a.slots = reinterpret_cast<const long long *>(d_table);
+    a.lens = d_lens;
+    a.stride = (long long)stride;
+    // a row may start on an odd index: one more unit covers the shifted tail
+    long long per_row = ((long long)stride + 1 + rt::kChunkElems - 1) / rt::kChunkElems;
+    long long units = per_row * n_rows;
+    if (units > 0x7fffffffLL) return RT_ERR_CAPACITY;
+    a.units_per_row = (int)per_row;
+    a.n_units = (int)units;
+    a.n_groups = 1;
+    a.capacity = pl->layout.capacity_slots;
+    a.block_tokens = pl->block_tokens;
+    a.shift = pl->shift;
+    rt::PlanArgs p;
+    fill_plan_args(pl, p, budget, flags, out, cap, result);
+    cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
+    RT_CUDA(rt::launch_scan_plan(a, p, true, grid_for(pl, a.n_units, false), s));
+    return RT_OK;
+}
+
+int rt_scan_slots(rt_plan *pl, const int64_t *d_slots, const int64_t *group_off, uint32_t *d_bitmaps,
+                  rt_plan_result *result, void *stream) {
+    if (!pl || !group_off || !result || !d_bitmaps) return RT_ERR_INVALID_ARGUMENT;
+    DeviceGuard guard(pl->device);
+    rt::ScanArgs a;
+    int st = fill_scan_args_csr(pl, a, d_slots, group_off);
+    if (st != RT_OK) return st;
+    rt::PlanArgs p;
+    fill_plan_args(pl, p, 0, 0, nullptr, 0, result);
+    p.scan_only = 1;
+    p.bitmaps_out = d_bitmaps;
+    cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
+    bool tma = want_tma(0);
+    int grid = grid_for(pl, a.n_units, tma);
+    RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s) : rt::launch_scan_plan(a, p, false, grid, s));
+    return RT_OK;
+}
+
+int rt_plan_from_bitmaps(rt_plan *pl, const uint32_t *d_want, uint32_t budget, uint32_t flags,
+                         rt_range *out, uint32_t cap, rt_plan_result *result, void *stream) {
+    if (!pl || !d_want || !result || (!out && cap)) return RT_ERR_INVALID_ARGUMENT;
+    DeviceGuard guard(pl->device);
+    rt::PlanArgs p;
+    fill_plan_args(pl, p, budget, flags, out, cap, result);
+    cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
+    RT_CUDA(rt::launch_plan_tail(d_want, p, s));
+    return RT_OK;
+}
+
+int rt_plan_sync(rt_plan *pl) {
+    if (!pl) return RT_ERR_INVALID_ARGUMENT;
+    DeviceGuard guard(pl->device);
+    RT_CUDA(cudaStreamSynchronize(pl->stream));
+    return RT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,69 @@
+// Device-side data structures shared by the planner kernels.
+#pragma once
+#include <stdint.h>
+
+#include "retarget_b200.h"
+
+namespace rt {
+
+constexpr int kWords = RT_BITMAP_WORDS;      // 32 x 32 bits = RT_MAX_BLOCKS
+constexpr int kMaxRuns = RT_MAX_BLOCKS / 2;  // alternating bits give the most runs
+constexpr int kScanThreads = 256;
+constexpr int kUnroll = 4;                   // independent 16-byte loads per thread
+constexpr int kChunkElems = kScanThreads * 2 * kUnroll;   // 2048 slot ids = 16 KiB
+
+// Per-bitmap working state.  Self-cleaning: the warp that consumes `want` and
+// `units_done` zeroes them again, so back-to-back launches need no memset.
+struct GroupScratch {
+    uint32_t want[kWords];        // OR of touched blocks, filled with atomicOr
+    uint32_t units_done;          // arrival counter of scanned work units
+    uint32_t n_runs[2];           // [0] CPU-bound (evict)  [1] GPU-bound (add)
+    uint32_t touched, desired, added, evicted;
+    uint32_t pad;
+    uint16_t run_begin[2][kMaxRuns];
+    uint16_t run_end[2][kMaxRuns];
+};
+
+struct GlobalScratch {
+    unsigned long long invalid_slots;
+    unsigned long long ignored_slots;
+    uint32_t groups_done;
+    uint32_t error_flags;
+};
+
+// Kernel arguments, passed by value (about 1.7 KiB): no per-step upload.
+struct ScanArgs {
+    const long long *slots;
+    const int *lens;                          // table mode: valid ids per row
+    long long group_off[RT_MAX_GROUPS + 1];   // CSR mode
+    int unit_first[RT_MAX_GROUPS + 1];        // CSR mode: first work unit of each group
+    long long stride;                         // table mode
+    int units_per_row;                        // table mode
+    int n_units;                              // work units of kChunkElems ids each
+    int n_groups;
+    unsigned long long capacity;              // largest valid slot id
+    uint32_t block_tokens;
+    int shift;                                // log2(block_tokens) or -1
+};
+
+struct PlanArgs {
+    GroupScratch *groups;
+    GlobalScratch *global;
+    uint32_t *resident;                       // n_groups x kWords
+    const uint32_t *buffer_group;             // n_buffers
+    uint32_t *bitmaps_out;                    // scan-only: n_groups x kWords (or null)
+    rt_range *out;
+    rt_plan_result *result;
+    uint32_t cap;
+    uint32_t n_buffers;
+    uint32_t n_groups;
+    uint32_t n_blocks;
+    uint32_t budget;
+    uint32_t flags;
+    int32_t dst_device;
+    int scan_only;
+    unsigned long long alloc_bytes;
+    unsigned long long block_bytes;
+};
+
+}  // namespace rt

@@ -1,0 +1,274 @@
+"""GPU parity: the CUDA planner, called through the C ABI, against the CPU
+oracle on the same seeded inputs.  Integer work: every comparison is exact."""
+import dataclasses
+
+import numpy as np
+import pytest
+
+from oracle import compose
+from oracle import ref_policy as rp
+from oracle import uvm_expand as ux
+from retarget_b200 import capi, workloads
+from retarget_b200.planner import (DevicePlanner, blocks_to_bitmap, ranges_from_tensor,
+                                   ranges_to_tuples, result_from_tensor)
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+MODES = [pytest.param(0, id="tma"), pytest.param(capi.RT_PLAN_NO_TMA, id="ld128")]
+
+
+def random_batch(rng, *, layers, pool_slots, bytes_per_slot, shared, n_req, max_len, budget,
+                 block_bytes=2 << 20, junk=False):
+    lay = workloads.Layout(layers, bytes_per_slot, pool_slots, block_bytes, shared)
+    G = lay.n_groups
+    chunks, lens = [], []
+    for g in range(G):
+        for r in range(n_req):
+            n = int(rng.integers(0, max_len + 1))
+            kind = rng.integers(0, 3)
+            if kind == 0:      # paged, consecutive within a page
+                pages = rng.integers(0, max(1, pool_slots // 16), -(-n // 16))
+                s = (pages[:, None] * 16 + np.arange(16)).reshape(-1)[:n]
+            elif kind == 1:    # one long consecutive run
+                start = int(rng.integers(0, max(1, pool_slots - n)))
+                s = np.arange(start, start + n)
+            else:              # random with repeats
+                s = rng.integers(1, pool_slots, n)
+            s = np.clip(s, 0, lay.capacity).astype(np.int64)
+            if junk and n:
+                k = rng.integers(0, n, max(1, n // 50))
+                s[k] = rng.choice([0, -1, -5, -(1 << 40)], len(k))
+            chunks.append(s)
+            lens.append(n)
+    slots = np.concatenate(chunks) if chunks else np.zeros(0, np.int64)
+    req_off = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    group_off = req_off[::n_req].copy() if n_req else np.zeros(G + 1, np.int64)
+    return workloads.SlotBatch(lay, slots.astype(np.int64), group_off, req_off, budget, "random")
+
+
+def run_steps(batches, *, evict, flags, literal=True):
+    """Feeds the same sequence of batches to the device planner (host-buffer
+    entry point) and to the oracle; compares every step."""
+    lay = batches[0].layout
+    planner = DevicePlanner(lay, 0, max_indices=max(b.n_idx for b in batches) + 8, max_ranges=1 << 16)
+    resident = [set() for _ in range(lay.n_groups)]
+    f = flags | (capi.RT_PLAN_EVICT if evict else 0)
+    for step, b in enumerate(batches):
+        want, info = compose.plan_step(b, resident, evict=evict, literal=literal)
+        got, res = planner.step_host(b.slots, b.group_off, b.budget_blocks, f)
+        assert ranges_to_tuples(got) == want, f"step {step}"
+        assert res.n_ranges == len(want)
+        assert res.n_cpu_ranges == sum(1 for r in want if r[1] == ux.CPU)
+        assert res.blocks_added == info["blocks_added"]
+        assert res.blocks_evicted == info["blocks_evicted"]
+        assert res.gpu_bytes == sum(r[3] for r in want if r[1] != ux.CPU)
+        assert res.cpu_bytes == sum(r[3] for r in want if r[1] == ux.CPU)
+        assert res.invalid_slots == 0
+        assert [sorted(s) for s in resident] == planner.get_resident(), f"step {step}"
+    planner.close()
+
+
+@pytest.mark.parametrize("flags", MODES)
+@pytest.mark.parametrize("evict", [True, False])
+def test_random_small_multi_step(flags, evict):
+    rng = np.random.default_rng(42)
+    shapes = [
+        dict(layers=3, pool_slots=8192, bytes_per_slot=2048, shared=False, n_req=5, max_len=700, budget=3),
+        dict(layers=2, pool_slots=65536, bytes_per_slot=2048, shared=True, n_req=9, max_len=5000, budget=16),
+        dict(layers=4, pool_slots=262144, bytes_per_slot=256, shared=False, n_req=3, max_len=9000, budget=8),
+        # 1024 blocks of 4 KiB: the widest bitmap the protocol allows
+        dict(layers=2, pool_slots=8192, bytes_per_slot=512, shared=False, n_req=6, max_len=3000,
+             budget=300, block_bytes=4096),
+        # 6 slots per block (not a power of two), 1001 blocks, the last one partial
+        dict(layers=2, pool_slots=6001, bytes_per_slot=2048, shared=False, n_req=4, max_len=2500,
+             budget=40, block_bytes=12288),
+    ]
+    for shape in shapes:
+        batches = [random_batch(rng, junk=(k == 2), **shape) for k in range(4)]
+        # vary the budget between steps as a scheduler would
+        batches[3] = dataclasses.replace(batches[3], budget_blocks=max(1, shape["budget"] // 2))
+        run_steps(batches, evict=evict, flags=flags)
+
+
+@pytest.mark.parametrize("flags", MODES)
+def test_ragged_and_empty_inputs(flags):
+    rng = np.random.default_rng(7)
+    lay = workloads.Layout(4, 2048, 32768, shared_bitmap=False)
+    # groups: empty, one id at an odd offset, a few ids, empty
+    slots = np.array([77, 5000, 5001, 5002, 31000, 1, 1], dtype=np.int64)
+    b0 = workloads.SlotBatch(lay, slots, np.array([0, 0, 1, 7, 7], np.int64),
+                             np.array([0, 0, 1, 7, 7], np.int64), 2)
+    empty = workloads.SlotBatch(lay, np.zeros(0, np.int64), np.zeros(5, np.int64),
+                                np.zeros(5, np.int64), 2)
+    zero_budget = dataclasses.replace(b0, budget_blocks=0)
+    big = random_batch(rng, layers=4, pool_slots=32768, bytes_per_slot=2048, shared=False,
+                       n_req=3, max_len=4099, budget=50)
+    run_steps([b0, empty, b0, zero_budget, big, empty], evict=True, flags=flags)
+
+
+@pytest.mark.parametrize("flags", MODES)
+def test_full_refresh_config(flags):
+    """40 layers, 65,536-slot pool, 64 requests, 25 % budget: literal oracle."""
+    b = workloads.full_refresh(0)
+    assert b.layout.n_blocks == 64 and b.budget_blocks == 16 and b.layout.n_buffers == 80
+    b2 = workloads.full_refresh(1)
+    run_steps([b, b, b2], evict=True, flags=flags)
+
+
+@pytest.mark.parametrize("flags", MODES)
+def test_tp_shard_config(flags):
+    """48 layers, one KV head per rank (256 B slots), 262,144-slot pool."""
+    b = workloads.tp_shard(0)
+    assert b.layout.n_blocks == 32 and b.layout.block_tokens == 8192 and b.layout.n_buffers == 96
+    run_steps([b, workloads.tp_shard(3)], evict=True, flags=flags, literal=False)
+
+
+def test_sparse_feedback_config_reduced_literal():
+    """Per-layer touched sets (newest 128 + 2048 Zipf draws), 4 layers through
+    the literal reference chain."""
+    b = workloads.sparse_feedback(0, layers=4, requests=32)
+    assert b.layout.n_groups == 4 and b.layout.n_blocks == 128 and b.budget_blocks == 19
+    run_steps([b, workloads.sparse_feedback(1, layers=4, requests=32)], evict=True, flags=0)
+
+
+@pytest.mark.parametrize("flags", MODES)
+def test_sparse_feedback_config_full(flags):
+    """Full 40-layer, 128-request case (11.1 M ids)."""
+    b = workloads.sparse_feedback(0)
+    assert b.n_idx == 128 * 40 * 2176
+    run_steps([b, b], evict=True, flags=flags, literal=False)
+
+
+def test_device_resident_entry_points_agree():
+    """step_device (ids already in HBM), the padded-table entry point and the
+    scan-only + from-bitmaps pair all give the host-buffer call's answer."""
+    b = workloads.full_refresh(2)
+    lay = b.layout
+    dev = torch.device("cuda:0")
+    resident0 = [set(range(3, 9))]
+    want, _ = compose.plan_step(b, [set(resident0[0])], evict=True)
+    d_slots = torch.from_numpy(b.slots).to(dev)
+    d_out = torch.zeros(4096 * 24, dtype=torch.uint8, device=dev)
+    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def fresh():
+        p = DevicePlanner(lay, 0, max_indices=0)
+        p.set_resident(resident0)
+        return p
+
+    p = fresh()
+    p.step_device(d_slots, b.group_off, b.budget_blocks, capi.RT_PLAN_EVICT, d_out, d_res, stream)
+    torch.cuda.synchronize()
+    res = result_from_tensor(d_res)
+    assert ranges_to_tuples(ranges_from_tensor(d_out, res["n_ranges"])) == want
+    p.close()
+
+    # padded [requests, stride] table with an odd stride
+    lens = np.diff(b.req_off).astype(np.int32)
+    stride = int(lens.max()) + 3
+    table = np.full((len(lens), stride), -7, dtype=np.int64)
+    for r, n in enumerate(lens):
+        table[r, :n] = b.slots[b.req_off[r]:b.req_off[r + 1]]
+    p = fresh()
+    p.step_table(torch.from_numpy(table).to(dev), torch.from_numpy(lens).to(dev), b.budget_blocks,
+                 capi.RT_PLAN_EVICT, d_out, d_res, stream)
+    torch.cuda.synchronize()
+    res = result_from_tensor(d_res)
+    assert ranges_to_tuples(ranges_from_tensor(d_out, res["n_ranges"])) == want
+    assert res["ignored_slots"] == 0          # padding is never read
+    p.close()
+
+    # scan only, then diff + coalesce from the bitmap
+    p = fresh()
+    d_bits = torch.zeros(32, dtype=torch.int32, device=dev)
+    p.scan(d_slots, b.group_off, d_bits, d_res, stream)
+    torch.cuda.synchronize()
+    touched = compose.group_blocks_fast(b.slots, lay)
+    assert np.array_equal(d_bits.cpu().numpy().view(np.uint32), blocks_to_bitmap(touched))
+    assert result_from_tensor(d_res)["blocks_touched"] == len(touched)
+    p.from_bitmaps(d_bits, b.budget_blocks, capi.RT_PLAN_EVICT, d_out, d_res, stream)
+    torch.cuda.synchronize()
+    res = result_from_tensor(d_res)
+    assert ranges_to_tuples(ranges_from_tensor(d_out, res["n_ranges"])) == want
+    p.close()
+
+
+def test_window_plan_from_bitmaps_matches_window_command():
+    """A block-aligned window held as a bitmap: resident = old window, wanted =
+    new window gives exactly the windowv symmetric difference."""
+    lay = workloads.Layout(40, 2048, 65536)
+    spec = rp.WindowSpec(lay.alloc_bytes, lay.n_buffers, 2048, 16384, 8192, 1024)
+    dev = torch.device("cuda:0")
+    d_out = torch.zeros(4096 * 24, dtype=torch.uint8, device=dev)
+    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
+    p = DevicePlanner(lay, 0)
+    old = None
+    for completed in (100, 9000, 9100, 30000, 12, 1 << 30):
+        new, want = compose.window_step(spec, lay, completed, old)
+        if old is None:
+            # first plan: everything outside the window to the CPU, window to the GPU
+            p.set_resident([set(range(lay.n_blocks))])
+        want_bits = torch.from_numpy(
+            blocks_to_bitmap(compose.window_blocks(*new, lay.block_bytes)).view(np.int32)).to(dev)
+        p.from_bitmaps(want_bits, capi.RT_MAX_BLOCKS, capi.RT_PLAN_EVICT, d_out, d_res)
+        p.sync()
+        res = result_from_tensor(d_res)
+        got = ranges_to_tuples(ranges_from_tensor(d_out, res["n_ranges"]))
+        if old is None:
+            # the command also re-sends the window itself; the bitmap diff only moves what changes
+            want = [r for r in want if r[1] == ux.CPU]
+        assert got == want, completed
+        old = new
+    p.close()
+
+
+def test_slot_above_capacity_is_reported():
+    lay = workloads.Layout(2, 2048, 8192)
+    slots = np.array([5, 8191, 8192, 1 << 40, 9], dtype=np.int64)
+    p = DevicePlanner(lay, 0, max_indices=16)
+    with pytest.raises(capi.RtError) as e:
+        p.step_host(slots, np.array([0, 5], np.int64), 4)
+    assert e.value.status == capi.RT_ERR_SLOT_RANGE
+    got, res = p.step_host(slots, np.array([0, 5], np.int64), 4, raise_on_slot_range=False)
+    assert res.invalid_slots == 2 and res.flags & capi.RT_RESULT_SLOT_RANGE
+    # counters are clean again on the next step
+    got, res = p.step_host(slots[:2], np.array([0, 2], np.int64), 4)
+    assert res.invalid_slots == 0 and res.flags == 0
+    p.close()
+
+
+def test_range_capacity_overflow_is_reported():
+    lay = workloads.Layout(8, 2048, 65536, shared_bitmap=True)
+    # every second block touched: 32 runs x 16 buffers
+    slots = (np.arange(0, 64, 2, dtype=np.int64) * 1024 + 5)
+    p = DevicePlanner(lay, 0, max_indices=64, max_ranges=100)
+    with pytest.raises(capi.RtError) as e:
+        p.step_host(slots, np.array([0, len(slots)], np.int64), 64)
+    assert e.value.status == capi.RT_ERR_CAPACITY
+    p.close()
+
+
+def test_headline_step_properties():
+    """At the benchmark's full size (40 layers x 256 requests, 262,144 slots)
+    the answer is checked through the vectorised oracle and size-independent
+    properties: idempotence, sorted non-overlapping ranges, byte accounting."""
+    b = workloads.target_step(0)
+    lay = b.layout
+    p = DevicePlanner(lay, 0, max_indices=b.n_idx + 8)
+    resident = [set() for _ in range(lay.n_groups)]
+    want, _ = compose.plan_step(b, resident, literal=False)
+    got, res = p.step_host(b.slots, b.group_off, b.budget_blocks, capi.RT_PLAN_EVICT)
+    assert ranges_to_tuples(got) == want
+    assert res.gpu_bytes == int(got["bytes"].sum()) and res.cpu_bytes == 0
+    for j in range(lay.n_buffers):
+        mine = got[got["buffer"] == j]
+        ends = mine["offset"] + mine["bytes"]
+        assert np.all(mine["offset"][1:] > ends[:-1])        # sorted, coalesced, disjoint
+        assert np.all(ends <= lay.alloc_bytes)
+        assert mine["bytes"].sum() <= b.budget_blocks * lay.block_bytes
+    again, res2 = p.step_host(b.slots, b.group_off, b.budget_blocks, capi.RT_PLAN_EVICT)
+    assert len(again) == 0 and res2.blocks_added == 0 and res2.blocks_evicted == 0
+    p.close()
