@@ -248,7 +248,9 @@ def run_ours(args):
     h_slots = [torch.from_numpy(b.slots).pin_memory() for b in batches]
     d_out = torch.zeros((1 << 16) * 24, dtype=torch.uint8, device=dev)
     d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
-    stream = torch.cuda.current_stream()
+    # a stream of our own: handle 0 would select the planner's internal stream
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
     K, W = args.steps, args.warmup
 
     def barrier():

@@ -3,7 +3,9 @@
  *
  * Plain C, no CUDA or framework types in any signature: device pointers are
  * `const void *` / typed pointers to device memory, streams are passed as
- * `void *` (a cudaStream_t / CUstream; NULL = the plan's own stream).
+ * `void *` (a cudaStream_t / CUstream).  NULL selects the plan's own
+ * non-blocking stream, NOT the legacy default stream; pass cudaStreamLegacy or
+ * cudaStreamPerThread to name those.
  *
  * Every function returns an `int` status: 0 (RT_OK) on success, a negative
  * `rt_status` otherwise; `rt_strerror()` turns it into text.  Where the

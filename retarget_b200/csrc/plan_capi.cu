@@ -11,6 +11,7 @@
 #include "rt_internal.h"
 
 namespace rt {
+void division_magic(uint32_t d, uint32_t *magic, uint32_t *shift);
 cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, int grid,
                              cudaStream_t stream);
 cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid, cudaStream_t stream);
@@ -27,6 +28,7 @@ struct rt_plan {
     uint32_t n_blocks = 0;
     uint32_t block_tokens = 0;
     int shift = -1;
+    uint32_t magic = 0, magic_shift = 0;
     cudaStream_t stream = nullptr;
     rt::GroupScratch *d_groups = nullptr;
     rt::GlobalScratch *d_global = nullptr;
@@ -103,6 +105,8 @@ int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const int64_t *d_slot
     a.capacity = pl->layout.capacity_slots;
     a.block_tokens = pl->block_tokens;
     a.shift = pl->shift;
+    a.magic = pl->magic;
+    a.magic_shift = pl->magic_shift;
     long long units = 0;
     for (uint32_t g = 0; g < G; ++g) {
         long long lo = group_off[g], hi = group_off[g + 1];
@@ -138,6 +142,21 @@ bool want_tma(uint32_t flags) {
 }  // namespace
 
 namespace rt {
+// Multiplier and shift for dividing any 32-bit n by d (d not a power of two):
+//   q = mulhi(n, magic);  n / d == (((n - q) >> 1) + q) >> shift
+// This is the round-up method with a 33-bit multiplier whose top bit is
+// folded into the add (Granlund & Montgomery; the "branch-free" libdivide form).
+void division_magic(uint32_t d, uint32_t *magic, uint32_t *shift) {
+    uint32_t k = 31;
+    while (!(d >> k)) --k;                       // floor(log2 d)
+    const uint64_t two_k = 1ull << (32 + k);
+    uint64_t m = two_k / d, rem = two_k % d;     // floor(2^(32+k) / d)
+    m *= 2;
+    uint64_t twice = rem * 2;
+    if (twice >= d) m += 1;
+    *magic = (uint32_t)(m + 1);
+    *shift = k;
+}
 int last_cuda_error_get() { return g_last_cuda_error; }
 void last_cuda_error_set(int e) { g_last_cuda_error = e; }
 }  // namespace rt
@@ -181,6 +200,8 @@ int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, ui
         int s = 0;
         while ((1u << s) != block_tokens) ++s;
         pl->shift = s;
+    } else {
+        rt::division_magic(block_tokens, &pl->magic, &pl->magic_shift);
     }
     pl->max_indices = max_indices;
     pl->max_ranges = max_ranges;
@@ -321,6 +342,8 @@ int rt_plan_step_table(rt_plan *pl, const int64_t *d_table, const int32_t *d_len
     a.capacity = pl->layout.capacity_slots;
     a.block_tokens = pl->block_tokens;
     a.shift = pl->shift;
+    a.magic = pl->magic;
+    a.magic_shift = pl->magic_shift;
     rt::PlanArgs p;
     fill_plan_args(pl, p, budget, flags, out, cap, result);
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;

@@ -44,6 +44,8 @@ struct ScanArgs {
     unsigned long long capacity;              // largest valid slot id
     uint32_t block_tokens;
     int shift;                                // log2(block_tokens) or -1
+    uint32_t magic;                           // exact division by block_tokens when it is not
+    uint32_t magic_shift;                     //   a power of two: see block_of()
 };
 
 struct PlanArgs {

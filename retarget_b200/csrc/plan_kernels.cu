@@ -44,121 +44,177 @@ __device__ __forceinline__ uint32_t lowest_bits(uint32_t x, uint32_t k) {
 }
 
 // --------------------------------------------------------------------------
-// scan: mark one slot id in the CTA's shared bitmap
+// CTA-scope barriers.  The TMA kernel keeps a producer warp out of the
+// consumers' barriers, so those go through a named barrier of kThreads threads.
 // --------------------------------------------------------------------------
+template <int kBar, int kThreads>
+__device__ __forceinline__ void cta_sync() {
+    if (kBar == 0) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"n"(kBar), "n"(kThreads) : "memory");
+}
+
+template <int kBar, int kThreads>
+__device__ __forceinline__ bool cta_or(bool pred) {
+    if (kBar == 0) return __syncthreads_or(pred);
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %1, 0;\n\t"
+        "bar.red.or.pred q, %2, %3, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)pred), "n"(kBar), "n"(kThreads)
+        : "memory");
+    return r != 0;
+}
+
+// --------------------------------------------------------------------------
+// scan: mark slot ids in the CTA's shared block map
+// --------------------------------------------------------------------------
+// The map is one BYTE per block (1 KiB for 1024 blocks).  Marking a block is a
+// single plain shared store of 1: idempotent, so it needs no read, no atomic
+// and no branch.  (A bit map with test + atomicOr cost ~39 instructions per id
+// in measurement and left the kernel issue-bound at a third of HBM speed.)  The
+// bytes are folded into 32-bit words with warp ballots when the CTA leaves a
+// bitmap.
 struct ScanCounters {
     uint32_t invalid;    // id above capacity
     uint32_t ignored;    // id below 1
 };
 
-__device__ __forceinline__ void mark_slot(long long s, const ScanArgs &a, uint32_t *s_bits,
+// slot -> block.  Power-of-two block sizes shift; others use an exact
+// multiply-shift division (round-up magic with the 33-bit "add" fix-up, valid
+// for every 32-bit numerator), so no hardware-emulated divide sits in the loop.
+template <bool kPow2>
+__device__ __forceinline__ uint32_t block_of(uint32_t slot, const ScanArgs &a) {
+    if (kPow2) return slot >> a.shift;
+    uint32_t q = __umulhi(slot, a.magic);
+    return (((slot - q) >> 1) + q) >> a.magic_shift;
+}
+
+// Exact classification of one id (slow path).
+template <bool kPow2>
+__device__ __forceinline__ void mark_slot(long long s, const ScanArgs &a, uint8_t *s_map,
                                           ScanCounters &c) {
-    // valid ids are 1..capacity: one unsigned compare covers both ends
     unsigned long long u = (unsigned long long)(s - 1);
-    if (u < a.capacity) {
-        uint32_t v = (uint32_t)s;
-        uint32_t blk = a.shift >= 0 ? (v >> a.shift) : (v / a.block_tokens);
-        uint32_t w = blk >> 5, bit = 1u << (blk & 31);
-        // Bitmaps saturate after the first few ids: test with a plain
-        // shared load and only fall into the atomic when the bit is new.  Lanes
-        // that need the same word elect one leader for a single atomicOr.
-        if (!(s_bits[w] & bit)) {
-            uint32_t active = __activemask();
-            uint32_t peers = __match_any_sync(active, w);
-            uint32_t bits = __reduce_or_sync(peers, bit);
-            if ((uint32_t)(__ffs(peers) - 1) == (threadIdx.x & 31u)) atomicOr(&s_bits[w], bits);
+    if (u < a.capacity) s_map[block_of<kPow2>((uint32_t)s, a)] = 1;
+    else if (s < 1) ++c.ignored;
+    else ++c.invalid;
+}
+
+constexpr uint32_t kAllIds = (1u << (2 * kUnroll)) - 1u;
+
+// 2*kUnroll ids held as kUnroll 16-byte pairs, all of them real ids.
+template <bool kPow2>
+__device__ __forceinline__ void mark_full(const longlong2 (&v)[kUnroll], const ScanArgs &a,
+                                          uint8_t *s_map, ScanCounters &c) {
+    // Fast path: every id is 1..capacity (< 2^32), tested with 32-bit
+    // arithmetic; the high words are OR-ed and checked once.
+    uint32_t hi_or = 0;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+        hi_or |= (uint32_t)((unsigned long long)v[u].x >> 32) | (uint32_t)((unsigned long long)v[u].y >> 32);
+    if (hi_or == 0) {
+        const uint32_t cap = (uint32_t)a.capacity;
+        bool bad = false;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint32_t x = (uint32_t)v[u].x, y = (uint32_t)v[u].y;
+            bool okx = x - 1u < cap, oky = y - 1u < cap;
+            bad |= !okx | !oky;
+            if (okx) s_map[block_of<kPow2>(x, a)] = 1;
+            if (oky) s_map[block_of<kPow2>(y, a)] = 1;
         }
-    } else if (s < 1) {
-        ++c.ignored;
-    } else {
-        ++c.invalid;
+        if (!bad) return;
+        // some id was 0 or above capacity: recount exactly below (stores repeat harmlessly)
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        mark_slot<kPow2>(v[u].x, a, s_map, c);
+        mark_slot<kPow2>(v[u].y, a, s_map, c);
     }
 }
 
-// One work unit: kChunkElems ids starting at the even index e0, of which
-// [begin, end) belong to the unit's group.  Every thread holds kUnroll 16-byte
-// pairs; bit 2u / 2u+1 of `mask` says whether v[u].x / v[u].y is a real id.
+// Same with a validity mask: bit 2u / 2u+1 says whether v[u].x / v[u].y is real.
+template <bool kPow2>
+__device__ __forceinline__ void mark_masked(const longlong2 (&v)[kUnroll], uint32_t mask,
+                                            const ScanArgs &a, uint8_t *s_map, ScanCounters &c) {
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        if (mask & (1u << (2 * u))) mark_slot<kPow2>(v[u].x, a, s_map, c);
+        if (mask & (2u << (2 * u))) mark_slot<kPow2>(v[u].y, a, s_map, c);
+    }
+}
+
+// One work unit as registers: kChunkElems ids starting at the even index e0, of
+// which [begin, end) belong to the unit's group.
 struct Chunk {
     longlong2 v[kUnroll];
     uint32_t mask;
 };
 
-__device__ __forceinline__ void load_chunk(const long long *slots, long long e0, long long begin,
+// `mine` points at this thread's first pair of the unit (slots + e0 + 2*tid).
+__device__ __forceinline__ void load_chunk(const long long *mine, long long e0, long long begin,
                                            long long end, Chunk &ch) {
-    const int tid = threadIdx.x;
     if (e0 >= begin && e0 + kChunkElems <= end) {
         // interior: kUnroll independent, fully coalesced 128-bit loads per thread
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
-            ch.v[u] = __ldcs(reinterpret_cast<const longlong2 *>(
-                slots + e0 + 2 * (u * kScanThreads + tid)));
-        ch.mask = (1u << (2 * kUnroll)) - 1u;
+            ch.v[u] = __ldcs(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
+        ch.mask = kAllIds;
     } else {
         ch.mask = 0;
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            long long i = e0 + 2 * (u * kScanThreads + tid);
+            long long i = e0 + 2 * (u * kScanThreads + (int)threadIdx.x);
             ch.v[u].x = ch.v[u].y = 0;
-            if (i >= begin && i < end) { ch.v[u].x = __ldcs(slots + i); ch.mask |= 1u << (2 * u); }
+            if (i >= begin && i < end) {
+                ch.v[u].x = __ldcs(mine + 2 * u * kScanThreads);
+                ch.mask |= 1u << (2 * u);
+            }
             if (i + 1 >= begin && i + 1 < end) {
-                ch.v[u].y = __ldcs(slots + i + 1);
+                ch.v[u].y = __ldcs(mine + 2 * u * kScanThreads + 1);
                 ch.mask |= 2u << (2 * u);
             }
         }
     }
 }
 
-__device__ __forceinline__ void mark_chunk(const Chunk &ch, const ScanArgs &a, uint32_t *s_bits,
+template <bool kPow2>
+__device__ __forceinline__ void mark_chunk(const Chunk &ch, const ScanArgs &a, uint8_t *s_map,
                                            ScanCounters &c) {
-    if (ch.mask == (1u << (2 * kUnroll)) - 1u) {
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            mark_slot(ch.v[u].x, a, s_bits, c);
-            mark_slot(ch.v[u].y, a, s_bits, c);
-        }
-    } else {
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            if (ch.mask & (1u << (2 * u))) mark_slot(ch.v[u].x, a, s_bits, c);
-            if (ch.mask & (2u << (2 * u))) mark_slot(ch.v[u].y, a, s_bits, c);
-        }
-    }
+    if (ch.mask == kAllIds) mark_full<kPow2>(ch.v, a, s_map, c);
+    else mark_masked<kPow2>(ch.v, ch.mask, a, s_map, c);
 }
 
-// Where work unit q lives.  `g` is a running hint (units are visited in
-// ascending order), advanced past every group that ends before q.
-struct UnitPos {
-    uint32_t g;
-    long long e0, begin, end;
+// The part of bitmap g that falls to a CTA owning work units [q_begin, q_end).
+struct GroupSpan {
+    int q_lo, q_hi;          // units of this group handled here
+    int units_in_group;
+    long long lo, hi;        // the group's ids
+    long long e0;            // even start index of unit q_lo
 };
 
-template <bool kTable>
-__device__ __forceinline__ UnitPos locate_unit(const ScanArgs &a, int q, uint32_t g_hint) {
-    UnitPos u;
-    long long lo, hi;
-    int k;
-    if (kTable) {
-        int row = q / a.units_per_row;
-        k = q - row * a.units_per_row;
-        int len = a.lens[row];
-        if (len < 0) len = 0;
-        if ((long long)len > a.stride) len = (int)a.stride;
-        lo = (long long)row * a.stride;
-        hi = lo + len;
-        u.g = 0;
-    } else {
-        uint32_t g = g_hint;
-        while (q >= a.unit_first[g + 1]) ++g;
-        k = q - a.unit_first[g];
-        lo = a.group_off[g];
-        hi = a.group_off[g + 1];
-        u.g = g;
+__device__ __forceinline__ GroupSpan group_span(const ScanArgs &a, uint32_t g, int q_begin, int q_end) {
+    GroupSpan s;
+    const int uf = a.unit_first[g], ul = a.unit_first[g + 1];
+    s.q_lo = q_begin > uf ? q_begin : uf;
+    s.q_hi = q_end < ul ? q_end : ul;
+    s.units_in_group = ul - uf;
+    s.lo = a.group_off[g];
+    s.hi = a.group_off[g + 1];
+    s.e0 = (s.lo & ~1LL) + (long long)(s.q_lo - uf) * kChunkElems;
+    return s;
+}
+
+__device__ __forceinline__ uint32_t first_group(const ScanArgs &a, int q) {
+    // last group whose first unit is <= q
+    int gl = 0, gh = a.n_groups;
+    while (gh - gl > 1) {
+        int mid = (gl + gh) >> 1;
+        if (a.unit_first[mid] <= q) gl = mid; else gh = mid;
     }
-    u.e0 = (lo & ~1LL) + (long long)k * kChunkElems;
-    u.end = u.e0 + kChunkElems < hi ? u.e0 + kChunkElems : hi;
-    u.begin = u.e0 > lo ? u.e0 : lo;
-    if (u.begin > u.end) u.begin = u.end;
-    return u;
+    return (uint32_t)gl;
 }
 
 // --------------------------------------------------------------------------
@@ -234,13 +290,14 @@ struct FinalizeShared {
     unsigned long long bytes[2];
 };
 
+template <int kBar>
 __device__ void finalize(const PlanArgs &p, FinalizeShared &sh) {
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t nthr = blockDim.x, nwarp = nthr >> 5;
+    const uint32_t nthr = kScanThreads, nwarp = nthr >> 5;
     const uint32_t items = p.scan_only ? 0 : 2 * p.n_buffers;
     if (tid < 4) sh.stats[tid] = 0;
     if (tid < 2) sh.bytes[tid] = 0;
-    __syncthreads();
+    cta_sync<kBar, kScanThreads>();
     // group statistics
     for (uint32_t g = tid; g < p.n_groups; g += nthr) {
         const GroupScratch &gs = p.groups[g];      // written by other CTAs: read through L2
@@ -263,7 +320,7 @@ __device__ void finalize(const PlanArgs &p, FinalizeShared &sh) {
     }
     uint32_t incl = warp_inclusive_sum(local, lane);
     if (lane == 31) sh.warp_tot[warp] = incl;
-    __syncthreads();
+    cta_sync<kBar, kScanThreads>();
     uint32_t base = 0;
     for (uint32_t w = 0; w < warp; ++w) base += sh.warp_tot[w];
     uint32_t total = 0;
@@ -279,7 +336,7 @@ __device__ void finalize(const PlanArgs &p, FinalizeShared &sh) {
         }
     }
     if (tid == 0) sh.off[items] = total;
-    __syncthreads();
+    cta_sync<kBar, kScanThreads>();
     const uint32_t n_cpu = items ? sh.off[p.n_buffers] : 0;
     unsigned long long my_bytes[2] = {0, 0};
     for (uint32_t r = tid; r < total; r += nthr) {
@@ -308,7 +365,7 @@ __device__ void finalize(const PlanArgs &p, FinalizeShared &sh) {
     }
     if (my_bytes[0]) atomicAdd(&sh.bytes[0], my_bytes[0]);
     if (my_bytes[1]) atomicAdd(&sh.bytes[1], my_bytes[1]);
-    __syncthreads();
+    cta_sync<kBar, kScanThreads>();
     if (tid == 0) {
         GlobalScratch &gl = *p.global;
         rt_plan_result res;
@@ -342,16 +399,17 @@ struct HandoverShared {
     int role;      // 0 nothing, 1 run the group's tail, 2 tail + finalize
 };
 
+template <int kBar>
 __device__ __forceinline__ void retire_units(const PlanArgs &p, uint32_t g, uint32_t count,
                                              uint32_t units_in_group, HandoverShared &hs,
                                              FinalizeShared &fs) {
     __threadfence();
-    __syncthreads();
+    cta_sync<kBar, kScanThreads>();
     if (threadIdx.x == 0) {
         uint32_t prev = atomicAdd(&p.groups[g].units_done, count);
         hs.role = prev + count == units_in_group;
     }
-    __syncthreads();
+    cta_sync<kBar, kScanThreads>();
     if (!hs.role) return;
     __threadfence();
     if (threadIdx.x < 32) {
@@ -366,17 +424,18 @@ __device__ __forceinline__ void retire_units(const PlanArgs &p, uint32_t g, uint
             hs.role = prev + 1 == p.n_groups ? 2 : 1;
         }
     }
-    __syncthreads();
+    cta_sync<kBar, kScanThreads>();
     if (hs.role == 2) {
         __threadfence();
-        finalize(p, fs);
+        finalize<kBar>(p, fs);
     }
-    __syncthreads();
+    cta_sync<kBar, kScanThreads>();
 }
 
+template <int kBar>
 __device__ __forceinline__ void flush_counters(const PlanArgs &p, ScanCounters &c) {
     // rare path: any thread of the CTA saw an id outside 1..capacity
-    if (__syncthreads_or(c.invalid | c.ignored)) {
+    if (cta_or<kBar, kScanThreads>((c.invalid | c.ignored) != 0)) {
         uint32_t inv = warp_sum(c.invalid), ign = warp_sum(c.ignored);
         if ((threadIdx.x & 31) == 0) {
             if (inv) atomicAdd(&p.global->invalid_slots, (unsigned long long)inv);
@@ -386,93 +445,127 @@ __device__ __forceinline__ void flush_counters(const PlanArgs &p, ScanCounters &
     }
 }
 
+__device__ __forceinline__ void clear_map(uint8_t *s_map) {
+    reinterpret_cast<uint32_t *>(s_map)[threadIdx.x] = 0;      // 256 threads x 4 bytes
+}
+
+// Byte map -> 32-bit words by ballot, OR-ed into the bitmap's global words.
+// Call between two CTA barriers.
+__device__ __forceinline__ void flush_map(const PlanArgs &p, uint32_t g, const uint8_t *s_map) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kPerWarp = kWords / (kScanThreads / 32);
+#pragma unroll
+    for (int k = 0; k < kPerWarp; ++k) {
+        uint32_t word = warp * kPerWarp + k;
+        uint32_t bits = __ballot_sync(0xffffffffu, s_map[word * 32 + lane] != 0);
+        if (lane == 0 && bits) atomicOr(&p.groups[g].want[word], bits);
+    }
+}
+
+// The CTA leaves bitmap g after `count` work units: publish, hand over, reset.
+template <int kBar>
+__device__ __forceinline__ void leave_group(const ScanArgs &a, const PlanArgs &p, uint32_t g,
+                                            uint32_t count, uint32_t units_in_group, uint8_t *s_map,
+                                            ScanCounters &c, HandoverShared &hs, FinalizeShared &fs) {
+    cta_sync<kBar, kScanThreads>();
+    flush_map(p, g, s_map);
+    flush_counters<kBar>(p, c);
+    retire_units<kBar>(p, g, count, units_in_group, hs, fs);
+    clear_map(s_map);
+    cta_sync<kBar, kScanThreads>();
+}
+
 // --------------------------------------------------------------------------
-// kernel: plain 128-bit loads, register double buffering
+// kernel: CSR input, plain 128-bit loads, register double buffering
 // --------------------------------------------------------------------------
-// CSR input: every CTA owns one contiguous span of work units, keeps its shared
-// bitmap across the units of a group and hands over once per (CTA, group).
-// Table input: units are dealt round-robin (rows have ragged lengths) and all
-// belong to bitmap 0.
-template <bool kTable>
+// Every CTA owns one contiguous span of work units, walks it bitmap by bitmap,
+// keeps its shared block map across the units of a bitmap and hands over once
+// per (CTA, bitmap).  Inside a bitmap the next unit's loads are issued before
+// the current unit is marked.
+template <bool kPow2>
 __global__ void __launch_bounds__(kScanThreads)
 scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
-    __shared__ uint32_t s_bits[kWords];
+    __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
     __shared__ FinalizeShared fs;
+    const int q_begin = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
+    const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
+    if (q_begin >= q_end) return;
     ScanCounters c = {0, 0};
-    int q, q_end, q_step;
-    if (kTable) {
-        q = blockIdx.x; q_end = a.n_units; q_step = gridDim.x;
-    } else {
-        q = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
-        q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
-        q_step = 1;
-    }
-    if (q >= q_end) return;
-    if (threadIdx.x < kWords) s_bits[threadIdx.x] = 0;
-    uint32_t g0 = 0;
-    if (!kTable) {
-        // last group whose first unit is <= q
-        int gl = 0, gh = a.n_groups;
-        while (gh - gl > 1) {
-            int mid = (gl + gh) >> 1;
-            if (a.unit_first[mid] <= q) gl = mid; else gh = mid;
-        }
-        g0 = gl;
-    }
-    UnitPos cur = locate_unit<kTable>(a, q, g0);
-    Chunk ch;
-    load_chunk(a.slots, cur.e0, cur.begin, cur.end, ch);
+    clear_map(s_map);
     __syncthreads();
-    uint32_t units_done = 0;
-    for (;;) {
-        int qn = q + q_step;
-        UnitPos nxt = cur;
-        Chunk chn;
-        chn.mask = 0;
-        if (qn < q_end) {                       // next unit's loads fly while this one is marked
-            nxt = locate_unit<kTable>(a, qn, cur.g);
-            load_chunk(a.slots, nxt.e0, nxt.begin, nxt.end, chn);
-        }
-        mark_chunk(ch, a, s_bits, c);
-        ++units_done;
-        bool last = qn >= q_end;
-        if (last || nxt.g != cur.g) {
-            uint32_t in_group = kTable ? (uint32_t)a.n_units
-                                       : (uint32_t)(a.unit_first[cur.g + 1] - a.unit_first[cur.g]);
-            __syncthreads();
-            if (threadIdx.x < kWords && s_bits[threadIdx.x])
-                atomicOr(&p.groups[cur.g].want[threadIdx.x], s_bits[threadIdx.x]);
-            flush_counters(p, c);
-            retire_units(p, cur.g, units_done, in_group, hs, fs);
-            units_done = 0;
-            if (threadIdx.x < kWords) s_bits[threadIdx.x] = 0;
-            __syncthreads();
-        }
-        if (last) break;
-        q = qn;
-        cur = nxt;
+    for (uint32_t g = first_group(a, q_begin);; ++g) {
+        const GroupSpan sp = group_span(a, g, q_begin, q_end);
+        const long long begin = sp.lo, end = sp.hi;
+        long long e0 = sp.e0;
+        const long long *mine = a.slots + e0 + 2 * (int)threadIdx.x;
+        Chunk ch;
+        load_chunk(mine, e0, begin, end, ch);
+        for (int q = sp.q_lo; q < sp.q_hi; ++q) {
+            Chunk nx;
+            nx.mask = 0;
+            if (q + 1 < sp.q_hi) load_chunk(mine + kChunkElems, e0 + kChunkElems, begin, end, nx);
+            mark_chunk<kPow2>(ch, a, s_map, c);
+            mine += kChunkElems;
+            e0 += kChunkElems;
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) ch.v[u] = chn.v[u];
-        ch.mask = chn.mask;
+            for (int u = 0; u < kUnroll; ++u) ch.v[u] = nx.v[u];
+            ch.mask = nx.mask;
+        }
+        leave_group<0>(a, p, g, (uint32_t)(sp.q_hi - sp.q_lo), (uint32_t)sp.units_in_group, s_map, c, hs, fs);
+        if (sp.q_hi >= q_end) break;
     }
+}
+
+// --------------------------------------------------------------------------
+// kernel: padded [rows, stride] table (the serving engine's req_to_token)
+// --------------------------------------------------------------------------
+// Rows are ragged, so work units are dealt round-robin; all ids belong to
+// bitmap 0 and the CTA hands over once.
+template <bool kPow2>
+__global__ void __launch_bounds__(kScanThreads)
+scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
+    __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
+    __shared__ HandoverShared hs;
+    __shared__ FinalizeShared fs;
+    if ((int)blockIdx.x >= a.n_units) return;
+    ScanCounters c = {0, 0};
+    clear_map(s_map);
+    __syncthreads();
+    uint32_t units = 0;
+    for (int q = blockIdx.x; q < a.n_units; q += gridDim.x) {
+        const int row = q / a.units_per_row, k = q - row * a.units_per_row;
+        long long len = a.lens[row];
+        if (len < 0) len = 0;
+        if (len > a.stride) len = a.stride;
+        const long long lo = (long long)row * a.stride, hi = lo + len;
+        const long long e0 = (lo & ~1LL) + (long long)k * kChunkElems;
+        ++units;
+        if (e0 >= hi) continue;                                  // past the row's valid ids
+        Chunk ch;
+        load_chunk(a.slots + e0 + 2 * (int)threadIdx.x, e0, lo, hi, ch);
+        mark_chunk<kPow2>(ch, a, s_map, c);
+    }
+    leave_group<0>(a, p, 0, units, (uint32_t)a.n_units, s_map, c, hs, fs);
 }
 
 // --------------------------------------------------------------------------
 // kernel: slot ids staged through shared memory with bulk async copies (TMA)
 // --------------------------------------------------------------------------
-// One elected thread keeps kStages 16 KiB copies in flight per CTA
-// (cp.async.bulk global -> shared, completion counted on an mbarrier); all
-// threads then read their ids from shared memory with conflict-free 128-bit
-// loads.  Registers hold no staging data, so the bytes in flight per SM are set
-// by shared memory (kStages x 16 KiB per CTA), not by occupancy.
+// A producer warp keeps kStages 16 KiB copies in flight per CTA
+// (cp.async.bulk global -> shared, completion counted on a "full" mbarrier);
+// eight consumer warps read their ids from shared memory with conflict-free
+// 128-bit loads and hand each stage back through an "empty" mbarrier, so no
+// CTA-wide barrier sits in the streaming loop.  Registers hold no staging
+// data: the bytes in flight per SM are set by shared memory (kStages x 16 KiB
+// per CTA), not by occupancy.
 //
 // Every wait on an mbarrier is bounded; when the bound is hit the CTA records
 // RT_RESULT_TIMEOUT, skips the unit and still retires it, so the grid always
 // drains.
 constexpr int kStages = 4;
 constexpr int kStageBytes = kChunkElems * 8;
-constexpr uint32_t kWaitLimit = 1u << 24;
+constexpr uint32_t kWaitLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_addr(const void *ptr) {
     return (uint32_t)__cvta_generic_to_shared(ptr);
@@ -487,11 +580,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
+// try_wait suspends the thread in hardware for a bounded time before it
+// reports "not yet", so the polling loop issues few instructions.
 __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_addr(bar)), "r"(parity)
@@ -511,125 +606,134 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
         : "memory");
 }
 
-__global__ void __launch_bounds__(kScanThreads)
+// Threads 0..255 consume; warp 8 is the producer (lane 0 issues the copies).
+constexpr int kTmaThreads = kScanThreads + 32;
+constexpr int kConsumerBar = 1;
+
+// Ids [e0, copy_end) of a unit travel by bulk copy: whole 16-byte pairs only,
+// never past the last whole pair of the array.
+__device__ __forceinline__ long long copy_end_of(long long e0, long long hi, long long copy_limit) {
+    long long end = e0 + kChunkElems < hi ? e0 + kChunkElems : hi;
+    end = (end + 1) & ~1LL;
+    return end < copy_limit ? end : copy_limit;
+}
+
+template <bool kPow2>
+__global__ void __launch_bounds__(kTmaThreads)
 scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
     extern __shared__ __align__(128) unsigned char stage_mem[];
-    __shared__ __align__(8) uint64_t full_bar[kStages];
-    __shared__ uint32_t s_bits[kWords];
+    __shared__ __align__(8) uint64_t full_bar[kStages];    // copy landed (tx bytes)
+    __shared__ __align__(8) uint64_t empty_bar[kStages];   // all consumer warps done with the stage
+    __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
     __shared__ FinalizeShared fs;
     const int tid = threadIdx.x;
     const int q_begin = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
     const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
     if (q_begin >= q_end) return;
-    const long long copy_limit = a.group_off[a.n_groups] & ~1LL;   // whole 16-byte pairs only
+    const long long copy_limit = a.group_off[a.n_groups] & ~1LL;
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kScanThreads / 32);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < kWords) s_bits[tid] = 0;
-    uint32_t g0;
-    {
-        int gl = 0, gh = a.n_groups;
-        while (gh - gl > 1) {
-            int mid = (gl + gh) >> 1;
-            if (a.unit_first[mid] <= q_begin) gl = mid; else gh = mid;
-        }
-        g0 = gl;
-    }
+    if (tid < kScanThreads) clear_map(s_map);
+    const uint32_t g0 = first_group(a, q_begin);
     __syncthreads();
 
-    // producer state (thread 0 only)
-    int q_issue = q_begin;
-    uint32_t g_issue = g0;
-    auto issue = [&](int stage) {
-        UnitPos u = locate_unit<false>(a, q_issue, g_issue);
-        g_issue = u.g;
-        long long hi = (u.end + 1) & ~1LL;
-        if (hi > copy_limit) hi = copy_limit;
-        long long n = hi - u.e0;
-        if (n > 0) {
-            mbar_expect_tx(&full_bar[stage], (uint32_t)(n * 8));
-            bulk_load(stage_mem + stage * kStageBytes, a.slots + u.e0, (uint32_t)(n * 8), &full_bar[stage]);
-        } else {
-            mbar_arrive(&full_bar[stage]);
-        }
-        ++q_issue;
-    };
-    if (tid == 0)
-        for (int s = 0; s < kStages && q_issue < q_end; ++s) issue(s);
-
-    ScanCounters c = {0, 0};
-    uint32_t units_done = 0, g_cur = g0;
-    bool gave_up = false;
-    for (int q = q_begin; q < q_end; ++q) {
-        const int i = q - q_begin;
-        const int stage = i % kStages;
-        const uint32_t parity = (uint32_t)(i / kStages) & 1u;
-        UnitPos u = locate_unit<false>(a, q, g_cur);
-        if (u.g != g_cur) {
-            // the CTA crosses into the next bitmap: hand the finished one over
-            __syncthreads();
-            if (tid < kWords && s_bits[tid]) atomicOr(&p.groups[g_cur].want[tid], s_bits[tid]);
-            flush_counters(p, c);
-            retire_units(p, g_cur, units_done, (uint32_t)(a.unit_first[g_cur + 1] - a.unit_first[g_cur]),
-                         hs, fs);
-            units_done = 0;
-            if (tid < kWords) s_bits[tid] = 0;
-            __syncthreads();
-            g_cur = u.g;
-        }
-        long long copied_to = (u.end + 1) & ~1LL;
-        if (copied_to > copy_limit) copied_to = copy_limit;
-        bool ok = mbar_wait_bounded(&full_bar[stage], parity);
-        if (ok) {
-            const longlong2 *src = reinterpret_cast<const longlong2 *>(stage_mem + stage * kStageBytes);
-            const bool interior = u.e0 >= u.begin && u.e0 + kChunkElems <= u.end;
-            longlong2 v[kUnroll];
-            if (interior) {
-#pragma unroll
-                for (int k = 0; k < kUnroll; ++k) v[k] = src[k * kScanThreads + tid];
-#pragma unroll
-                for (int k = 0; k < kUnroll; ++k) {
-                    mark_slot(v[k].x, a, s_bits, c);
-                    mark_slot(v[k].y, a, s_bits, c);
-                }
-            } else {
-#pragma unroll
-                for (int k = 0; k < kUnroll; ++k) {
-                    long long idx = u.e0 + 2 * (k * kScanThreads + tid);
-                    if (idx < copied_to) {
-                        longlong2 w = src[k * kScanThreads + tid];
-                        if (idx >= u.begin && idx < u.end) mark_slot(w.x, a, s_bits, c);
-                        if (idx + 1 >= u.begin && idx + 1 < u.end) mark_slot(w.y, a, s_bits, c);
-                    } else if (idx >= u.begin && idx < u.end) {
-                        // odd last id of the whole array: not part of any 16-byte pair
-                        mark_slot(__ldcs(a.slots + idx), a, s_bits, c);
+    if (tid >= kScanThreads) {
+        // ---- producer warp: keeps up to kStages copies in flight ----
+        if (tid == kScanThreads) {
+            int i = 0;
+            bool alive = true;
+            for (uint32_t g = g0; alive; ++g) {
+                const GroupSpan sp = group_span(a, g, q_begin, q_end);
+                long long e0 = sp.e0;
+                for (int q = sp.q_lo; q < sp.q_hi; ++q, ++i, e0 += kChunkElems) {
+                    const int stage = i % kStages, round = i / kStages;
+                    if (round > 0 && !mbar_wait_bounded(&empty_bar[stage], (uint32_t)(round - 1) & 1u)) {
+                        atomicOr(&p.global->error_flags, RT_RESULT_TIMEOUT);
+                        alive = false;
+                        break;
+                    }
+                    const long long n = copy_end_of(e0, sp.hi, copy_limit) - e0;
+                    if (n > 0) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        mbar_expect_tx(&full_bar[stage], (uint32_t)(n * 8));
+                        bulk_load(stage_mem + stage * kStageBytes, a.slots + e0, (uint32_t)(n * 8),
+                                  &full_bar[stage]);
+                    } else {
+                        mbar_arrive(&full_bar[stage]);
                     }
                 }
+                if (sp.q_hi >= q_end) break;
             }
-        } else {
-            gave_up = true;
         }
-        ++units_done;
-        __syncthreads();                     // everyone is done reading this stage
-        if (tid == 0 && q_issue < q_end) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            issue(stage);
+        return;
+    }
+
+    // ---- consumer warps ----
+    ScanCounters c = {0, 0};
+    bool gave_up = false;
+    int i = 0;
+    for (uint32_t g = g0;; ++g) {
+        const GroupSpan sp = group_span(a, g, q_begin, q_end);
+        long long e0 = sp.e0;
+        for (int q = sp.q_lo; q < sp.q_hi; ++q, ++i, e0 += kChunkElems) {
+            const int stage = i % kStages;
+            const uint32_t parity = (uint32_t)(i / kStages) & 1u;
+            const longlong2 *src =
+                reinterpret_cast<const longlong2 *>(stage_mem + stage * kStageBytes) + tid;
+            const bool landed = mbar_wait_bounded(&full_bar[stage], parity);
+            longlong2 v[kUnroll];
+            uint32_t mask = 0;
+            if (landed) {
+                if (e0 >= sp.lo && e0 + kChunkElems <= sp.hi) {
+#pragma unroll
+                    for (int k = 0; k < kUnroll; ++k) v[k] = src[k * kScanThreads];
+                    mask = kAllIds;
+                } else {
+                    const long long copied_to = copy_end_of(e0, sp.hi, copy_limit);
+                    const long long end = e0 + kChunkElems < sp.hi ? e0 + kChunkElems : sp.hi;
+#pragma unroll
+                    for (int k = 0; k < kUnroll; ++k) {
+                        long long idx = e0 + 2 * (k * kScanThreads + tid);
+                        v[k].x = v[k].y = 0;
+                        if (idx < copied_to) {
+                            v[k] = src[k * kScanThreads];
+                            if (idx >= sp.lo && idx < end) mask |= 1u << (2 * k);
+                            if (idx + 1 >= sp.lo && idx + 1 < end) mask |= 2u << (2 * k);
+                        } else if (idx >= sp.lo && idx < end) {
+                            // odd last id of the whole array: not part of any 16-byte pair
+                            v[k].x = __ldcs(a.slots + idx);
+                            mask |= 1u << (2 * k);
+                        }
+                    }
+                }
+            } else {
+                gave_up = true;
+            }
+            // the ids are in registers: give the stage back before marking
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&empty_bar[stage]);
+            if (mask == kAllIds) mark_full<kPow2>(v, a, s_map, c);
+            else mark_masked<kPow2>(v, mask, a, s_map, c);
         }
+        leave_group<kConsumerBar>(a, p, g, (uint32_t)(sp.q_hi - sp.q_lo), (uint32_t)sp.units_in_group,
+                                  s_map, c, hs, fs);
+        if (sp.q_hi >= q_end) break;
     }
     if (gave_up) {
         if ((tid & 31) == 0) atomicOr(&p.global->error_flags, RT_RESULT_TIMEOUT);
-        // give copies that may still be in flight one more bounded chance to land
+        // copies that never signalled may still be in flight: give them one more
+        // bounded chance to land before the CTA's shared memory is released
         for (int s = 0; s < kStages; ++s) {
             int uses = (q_end - q_begin - s + kStages - 1) / kStages;
             if (uses > 0) mbar_wait_bounded(&full_bar[s], (uint32_t)(uses - 1) & 1u);
         }
     }
-    __syncthreads();
-    if (tid < kWords && s_bits[tid]) atomicOr(&p.groups[g_cur].want[tid], s_bits[tid]);
-    flush_counters(p, c);
-    retire_units(p, g_cur, units_done, (uint32_t)(a.unit_first[g_cur + 1] - a.unit_first[g_cur]), hs, fs);
 }
 
 // --------------------------------------------------------------------------
@@ -643,7 +747,7 @@ plan_tail_kernel(const uint32_t *want, const __grid_constant__ PlanArgs p) {
         group_tail(p, g, want[g * kWords + lane], lane);
     __threadfence();
     __syncthreads();
-    finalize(p, fs);
+    finalize<0>(p, fs);
 }
 
 // --------------------------------------------------------------------------
@@ -651,10 +755,14 @@ plan_tail_kernel(const uint32_t *want, const __grid_constant__ PlanArgs p) {
 // --------------------------------------------------------------------------
 cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, int grid,
                              cudaStream_t stream) {
-    if (table)
-        scan_plan_kernel<true><<<grid, kScanThreads, 0, stream>>>(a, p);
-    else
-        scan_plan_kernel<false><<<grid, kScanThreads, 0, stream>>>(a, p);
+    const bool pow2 = a.shift >= 0;
+    if (table) {
+        if (pow2) scan_table_kernel<true><<<grid, kScanThreads, 0, stream>>>(a, p);
+        else scan_table_kernel<false><<<grid, kScanThreads, 0, stream>>>(a, p);
+    } else {
+        if (pow2) scan_plan_kernel<true><<<grid, kScanThreads, 0, stream>>>(a, p);
+        else scan_plan_kernel<false><<<grid, kScanThreads, 0, stream>>>(a, p);
+    }
     return cudaGetLastError();
 }
 
@@ -664,19 +772,25 @@ cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream
 }
 
 cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid, cudaStream_t stream) {
-    scan_plan_tma_kernel<<<grid, kScanThreads, kStages * kStageBytes, stream>>>(a, p);
+    if (a.shift >= 0)
+        scan_plan_tma_kernel<true><<<grid, kTmaThreads, kStages * kStageBytes, stream>>>(a, p);
+    else
+        scan_plan_tma_kernel<false><<<grid, kTmaThreads, kStages * kStageBytes, stream>>>(a, p);
     return cudaGetLastError();
 }
 
 cudaError_t scan_plan_occupancy(int *plain_blocks_per_sm, int *tma_blocks_per_sm) {
-    cudaError_t e = cudaFuncSetAttribute(scan_plan_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kStages * kStageBytes);
+    cudaError_t e = cudaFuncSetAttribute(scan_plan_tma_kernel<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * kStageBytes);
     if (e != cudaSuccess) return e;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(plain_blocks_per_sm, scan_plan_kernel<false>,
+    e = cudaFuncSetAttribute(scan_plan_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kStages * kStageBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(plain_blocks_per_sm, scan_plan_kernel<true>,
                                                       kScanThreads, 0);
     if (e != cudaSuccess) return e;
-    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(tma_blocks_per_sm, scan_plan_tma_kernel,
-                                                         kScanThreads, kStages * kStageBytes);
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(tma_blocks_per_sm, scan_plan_tma_kernel<true>,
+                                                         kTmaThreads, kStages * kStageBytes);
 }
 
 }  // namespace rt

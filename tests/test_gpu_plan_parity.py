@@ -152,7 +152,9 @@ def test_device_resident_entry_points_agree():
     d_slots = torch.from_numpy(b.slots).to(dev)
     d_out = torch.zeros(4096 * 24, dtype=torch.uint8, device=dev)
     d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
-    stream = torch.cuda.current_stream().cuda_stream
+    side = torch.cuda.Stream(device=dev)        # the caller's own stream
+    stream = side.cuda_stream
+    torch.cuda.synchronize()
 
     def fresh():
         p = DevicePlanner(lay, 0, max_indices=0)
