@@ -261,6 +261,54 @@ int rt_plan_from_bitmaps(rt_plan *plan, const uint32_t *d_want, uint32_t budget,
 /* Waits for everything queued on the plan's own stream. */
 int rt_plan_sync(rt_plan *plan);
 
+/* ------------------------------------------------------------------ */
+/* UVM control server + prefetch executor (process-wide singleton)      */
+/* ------------------------------------------------------------------ */
+
+/* Stands in for the UVM block of the reference preload library,
+ * select.cpp:23750-24446: allocation registry, the text protocol of the control
+ * socket (same commands, replies and error strings), one migration job at a
+ * time executed by a worker thread.  Differences are confined to HOW the job
+ * runs: persistent side streams instead of a stream created and destroyed per
+ * chunk, several chunks in flight, one wait per batch. */
+typedef struct rt_uvm_config {
+    const char *socket_path;   /* NULL: /tmp/select-uvm-<uid>-<pid>.sock, select.cpp:24416 */
+    uint64_t chunk_bytes;      /* 0: SELECT_UVM_CHUNK_MB (1..256) or 16 MiB, select.cpp:23853 */
+    uint64_t batch_bytes;      /* bytes issued between two waits; 0: 256 MiB             */
+    uint32_t streams;          /* side streams per context; 0: 4                         */
+    int32_t listen;            /* 0: no socket, commands only through rt_uvm_command     */
+} rt_uvm_config;
+
+int rt_uvm_start(const rt_uvm_config *config);
+int rt_uvm_stop(void);
+
+/* Registry, select.cpp:24724-24761 (insert) and 23871-23913 (remove).  Every
+ * change bumps the allocation generation.  ctx may be NULL (current context). */
+int rt_uvm_register(uint64_t ptr, uint64_t bytes, void *ctx, int device, int concurrent,
+                    uint64_t *id);
+int rt_uvm_unregister_ptr(uint64_t ptr);
+int rt_uvm_unregister_ctx(void *ctx);
+int rt_uvm_unregister_device(int device);
+
+/* One protocol line in, one JSON reply line out (without the newline); exactly
+ * what a socket client would get, select.cpp:24045-24327.  Returns the reply
+ * length, or RT_ERR_CAPACITY. */
+int rt_uvm_command(const char *line, char *reply, size_t cap);
+
+/* Queues ranges produced by the device planner as one job: ranges[i].buffer
+ * indexes buffer_ids (allocation ids in registry order).  No reference
+ * counterpart: it skips the text round trip of blocksv/windowv, the job itself
+ * is what select.cpp:23990-24024 runs.  RT_ERR_BUSY while a job is in flight. */
+int rt_uvm_submit_ranges(const rt_range *ranges, size_t n, const uint64_t *buffer_ids,
+                         size_t n_ids, uint64_t *job_id);
+
+/* Blocks until job_id has completed (or timeout_s passed: RT_ERR_BUSY).
+ * *cuda_error gets the job's CUresult. */
+int rt_uvm_wait(uint64_t job_id, double timeout_s, int *cuda_error);
+
+/* Path the listener is bound to ("" when not listening).  Returns its length. */
+int rt_uvm_socket_path(char *out, size_t cap);
+
 #ifdef __cplusplus
 }
 #endif

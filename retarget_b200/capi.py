@@ -11,8 +11,11 @@ from pathlib import Path
 
 import numpy as np
 
+import os
+
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "libretarget_b200.so"
+# RETARGET_B200_LIB selects another build of the same library (e.g. an experimental variant)
+LIB_PATH = Path(os.environ.get("RETARGET_B200_LIB") or PKG / "libretarget_b200.so")
 
 RT_MAX_GROUPS = 128
 RT_MAX_BLOCKS = 1024

@@ -16,7 +16,8 @@ cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, i
                              cudaStream_t stream);
 cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid, cudaStream_t stream);
 cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream_t stream);
-cudaError_t scan_plan_occupancy(int *plain_blocks_per_sm, int *tma_blocks_per_sm);
+cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plain_blocks_per_sm,
+                                int *tma_blocks_per_sm);
 }  // namespace rt
 
 struct rt_plan {
@@ -33,7 +34,7 @@ struct rt_plan {
     rt::GroupScratch *d_groups = nullptr;
     rt::GlobalScratch *d_global = nullptr;
     uint32_t *d_resident = nullptr;
-    uint32_t *d_buffer_group = nullptr;
+    uint8_t buffer_group[RT_MAX_BUFFERS] = {0};
     long long *d_stage = nullptr;      // host-buffer call: slot ids land here
     uint64_t max_indices = 0;
     rt_range *h_out = nullptr;         // pinned + mapped: the kernel writes ranges here
@@ -76,7 +77,8 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
     p.groups = pl->d_groups;
     p.global = pl->d_global;
     p.resident = pl->d_resident;
-    p.buffer_group = pl->d_buffer_group;
+    memcpy(p.buffer_group, pl->buffer_group, sizeof(p.buffer_group));
+    p.n_units = 0;
     p.bitmaps_out = nullptr;
     p.out = out;
     p.result = result;
@@ -209,7 +211,8 @@ int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, ui
     auto fail = [&](cudaError_t err) { status = cuda_fail(err); };
     do {
         if ((e = cudaDeviceGetAttribute(&pl->sm_count, cudaDevAttrMultiProcessorCount, device))) { fail(e); break; }
-        if ((e = rt::scan_plan_occupancy(&pl->plain_blocks_per_sm, &pl->tma_blocks_per_sm))) { fail(e); break; }
+        if ((e = rt::scan_plan_occupancy(L.n_groups, L.n_buffers, &pl->plain_blocks_per_sm,
+                                         &pl->tma_blocks_per_sm))) { fail(e); break; }
         if (pl->plain_blocks_per_sm < 1) pl->plain_blocks_per_sm = 1;
         if (pl->tma_blocks_per_sm < 1) pl->tma_blocks_per_sm = 1;
         if ((e = cudaStreamCreateWithFlags(&pl->stream, cudaStreamNonBlocking))) { fail(e); break; }
@@ -221,11 +224,8 @@ int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, ui
         size_t rbytes = sizeof(uint32_t) * rt::kWords * L.n_groups;
         if ((e = cudaMalloc(&pl->d_resident, rbytes))) { fail(e); break; }
         if ((e = cudaMemset(pl->d_resident, 0, rbytes))) { fail(e); break; }
-        std::vector<uint32_t> bg(L.n_buffers, 0u);
-        if (L.buffer_group) memcpy(bg.data(), L.buffer_group, sizeof(uint32_t) * L.n_buffers);
-        if ((e = cudaMalloc(&pl->d_buffer_group, sizeof(uint32_t) * L.n_buffers))) { fail(e); break; }
-        if ((e = cudaMemcpy(pl->d_buffer_group, bg.data(), sizeof(uint32_t) * L.n_buffers,
-                            cudaMemcpyHostToDevice))) { fail(e); break; }
+        if (L.buffer_group)
+            for (uint32_t j = 0; j < L.n_buffers; ++j) pl->buffer_group[j] = (uint8_t)L.buffer_group[j];
         if (max_indices) {
             // +2 ids of slack so a 16-byte load at the very end stays in bounds
             if ((e = cudaMalloc(&pl->d_stage, sizeof(long long) * (max_indices + 2)))) { fail(e); break; }
@@ -253,7 +253,6 @@ int rt_plan_destroy(rt_plan *pl) {
     cudaFree(pl->d_groups);
     cudaFree(pl->d_global);
     cudaFree(pl->d_resident);
-    cudaFree(pl->d_buffer_group);
     cudaFree(pl->d_stage);
     if (pl->h_out) cudaFreeHost(pl->h_out);
     if (pl->h_result) cudaFreeHost(pl->h_result);
@@ -290,6 +289,7 @@ int rt_plan_step_device(rt_plan *pl, const int64_t *d_slots, const int64_t *grou
     if (st != RT_OK) return st;
     rt::PlanArgs p;
     fill_plan_args(pl, p, budget, flags, out, cap, result);
+    p.n_units = (uint32_t)a.n_units;
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
     bool tma = want_tma(flags);
     int grid = grid_for(pl, a.n_units, tma);
@@ -346,6 +346,7 @@ int rt_plan_step_table(rt_plan *pl, const int64_t *d_table, const int32_t *d_len
     a.magic_shift = pl->magic_shift;
     rt::PlanArgs p;
     fill_plan_args(pl, p, budget, flags, out, cap, result);
+    p.n_units = (uint32_t)a.n_units;
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
     RT_CUDA(rt::launch_scan_plan(a, p, true, grid_for(pl, a.n_units, false), s));
     return RT_OK;
@@ -360,6 +361,7 @@ int rt_scan_slots(rt_plan *pl, const int64_t *d_slots, const int64_t *group_off,
     if (st != RT_OK) return st;
     rt::PlanArgs p;
     fill_plan_args(pl, p, 0, 0, nullptr, 0, result);
+    p.n_units = (uint32_t)a.n_units;
     p.scan_only = 1;
     p.bitmaps_out = d_bitmaps;
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;

@@ -12,26 +12,20 @@ constexpr int kScanThreads = 256;
 constexpr int kUnroll = 4;                   // independent 16-byte loads per thread
 constexpr int kChunkElems = kScanThreads * 2 * kUnroll;   // 2048 slot ids = 16 KiB
 
-// Per-bitmap working state.  Self-cleaning: the warp that consumes `want` and
-// `units_done` zeroes them again, so back-to-back launches need no memset.
+// Per-bitmap accumulation words, filled with atomicOr by the scan.  The tail
+// zeroes them after reading, so back-to-back launches need no memset.
 struct GroupScratch {
-    uint32_t want[kWords];        // OR of touched blocks, filled with atomicOr
-    uint32_t units_done;          // arrival counter of scanned work units
-    uint32_t n_runs[2];           // [0] CPU-bound (evict)  [1] GPU-bound (add)
-    uint32_t touched, desired, added, evicted;
-    uint32_t pad;
-    uint16_t run_begin[2][kMaxRuns];
-    uint16_t run_end[2][kMaxRuns];
+    uint32_t want[kWords];
 };
 
 struct GlobalScratch {
     unsigned long long invalid_slots;
     unsigned long long ignored_slots;
-    uint32_t groups_done;
+    uint32_t units_done;          // arrival counter of scanned work units
     uint32_t error_flags;
 };
 
-// Kernel arguments, passed by value (about 1.7 KiB): no per-step upload.
+// Kernel arguments, passed by value (about 1.7 KiB + 1.1 KiB): no per-step upload.
 struct ScanArgs {
     const long long *slots;
     const int *lens;                          // table mode: valid ids per row
@@ -52,7 +46,6 @@ struct PlanArgs {
     GroupScratch *groups;
     GlobalScratch *global;
     uint32_t *resident;                       // n_groups x kWords
-    const uint32_t *buffer_group;             // n_buffers
     uint32_t *bitmaps_out;                    // scan-only: n_groups x kWords (or null)
     rt_range *out;
     rt_plan_result *result;
@@ -64,8 +57,10 @@ struct PlanArgs {
     uint32_t flags;
     int32_t dst_device;
     int scan_only;
+    uint32_t n_units;                         // work units of this launch (scan kernels)
     unsigned long long alloc_bytes;
     unsigned long long block_bytes;
+    uint8_t buffer_group[RT_MAX_BUFFERS];     // bitmap of every buffer, registry order
 };
 
 }  // namespace rt

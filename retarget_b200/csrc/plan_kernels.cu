@@ -16,57 +16,9 @@
 #include <cuda_runtime.h>
 
 #include "plan_device.cuh"
+#include "plan_tail.cuh"
 
 namespace rt {
-
-// --------------------------------------------------------------------------
-// small warp helpers
-// --------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t warp_inclusive_sum(uint32_t v, uint32_t lane) {
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        uint32_t n = __shfl_up_sync(0xffffffffu, v, d);
-        if (lane >= (uint32_t)d) v += n;
-    }
-    return v;
-}
-
-__device__ __forceinline__ uint32_t warp_sum(uint32_t v) {
-    return __reduce_add_sync(0xffffffffu, v);
-}
-
-// Lowest `k` set bits of x.
-__device__ __forceinline__ uint32_t lowest_bits(uint32_t x, uint32_t k) {
-    if (k >= (uint32_t)__popc(x)) return x;
-    if (k == 0) return 0;
-    uint32_t pos = __fns(x, 0, (int)k + 1);      // position of the (k+1)-th set bit
-    return x & ((1u << pos) - 1u);
-}
-
-// --------------------------------------------------------------------------
-// CTA-scope barriers.  The TMA kernel keeps a producer warp out of the
-// consumers' barriers, so those go through a named barrier of kThreads threads.
-// --------------------------------------------------------------------------
-template <int kBar, int kThreads>
-__device__ __forceinline__ void cta_sync() {
-    if (kBar == 0) __syncthreads();
-    else asm volatile("bar.sync %0, %1;" ::"n"(kBar), "n"(kThreads) : "memory");
-}
-
-template <int kBar, int kThreads>
-__device__ __forceinline__ bool cta_or(bool pred) {
-    if (kBar == 0) return __syncthreads_or(pred);
-    uint32_t r;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.u32 p, %1, 0;\n\t"
-        "bar.red.or.pred q, %2, %3, p;\n\t"
-        "selp.u32 %0, 1, 0, q;\n\t}"
-        : "=r"(r)
-        : "r"((uint32_t)pred), "n"(kBar), "n"(kThreads)
-        : "memory");
-    return r != 0;
-}
 
 // --------------------------------------------------------------------------
 // scan: mark slot ids in the CTA's shared block map
@@ -108,26 +60,25 @@ constexpr uint32_t kAllIds = (1u << (2 * kUnroll)) - 1u;
 template <bool kPow2>
 __device__ __forceinline__ void mark_full(const longlong2 (&v)[kUnroll], const ScanArgs &a,
                                           uint8_t *s_map, ScanCounters &c) {
-    // Fast path: every id is 1..capacity (< 2^32), tested with 32-bit
-    // arithmetic; the high words are OR-ed and checked once.
-    uint32_t hi_or = 0;
+    // Fast path: one test for the whole batch.  Every id must be 1..capacity
+    // (< 2^32): the high words are OR-ed, and the largest (id - 1) -- an id of 0
+    // wraps to 2^32 - 1 -- is compared with the capacity once.  Then the stores
+    // run unconditionally.
+    uint32_t hi_or = 0, worst = 0;
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
+    for (int u = 0; u < kUnroll; ++u) {
         hi_or |= (uint32_t)((unsigned long long)v[u].x >> 32) | (uint32_t)((unsigned long long)v[u].y >> 32);
-    if (hi_or == 0) {
-        const uint32_t cap = (uint32_t)a.capacity;
-        bool bad = false;
+        worst = max(worst, max((uint32_t)v[u].x - 1u, (uint32_t)v[u].y - 1u));
+    }
+    if (hi_or == 0 && worst < (uint32_t)a.capacity) {
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            uint32_t x = (uint32_t)v[u].x, y = (uint32_t)v[u].y;
-            bool okx = x - 1u < cap, oky = y - 1u < cap;
-            bad |= !okx | !oky;
-            if (okx) s_map[block_of<kPow2>(x, a)] = 1;
-            if (oky) s_map[block_of<kPow2>(y, a)] = 1;
+            s_map[block_of<kPow2>((uint32_t)v[u].x, a)] = 1;
+            s_map[block_of<kPow2>((uint32_t)v[u].y, a)] = 1;
         }
-        if (!bad) return;
-        // some id was 0 or above capacity: recount exactly below (stores repeat harmlessly)
+        return;
     }
+    // some id is 0, negative or above capacity: classify each one exactly
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
         mark_slot<kPow2>(v[u].x, a, s_map, c);
@@ -218,219 +169,11 @@ __device__ __forceinline__ uint32_t first_group(const ScanArgs &a, int q) {
 }
 
 // --------------------------------------------------------------------------
-// tail: one warp turns a bitmap into evict/add run lists
+// hand-over between the scan and the tail
 // --------------------------------------------------------------------------
-__device__ __forceinline__ void emit_runs(uint32_t m, uint32_t lane, uint16_t *run_begin,
-                                          uint16_t *run_end, uint32_t *n_runs) {
-    uint32_t prev_top = __shfl_up_sync(0xffffffffu, m, 1) >> 31;
-    uint32_t next_low = __shfl_down_sync(0xffffffffu, m, 1) & 1u;
-    if (lane == 0) prev_top = 0;
-    if (lane == 31) next_low = 0;
-    uint32_t starts = m & ~((m << 1) | prev_top);
-    uint32_t lasts = m & ~((m >> 1) | (next_low << 31));
-    uint32_t sb = warp_inclusive_sum(__popc(starts), lane);
-    uint32_t eb = warp_inclusive_sum(__popc(lasts), lane);
-    uint32_t total = __shfl_sync(0xffffffffu, sb, 31);
-    sb -= __popc(starts);
-    eb -= __popc(lasts);
-    while (starts) {
-        uint32_t b = __ffs(starts) - 1;
-        starts &= starts - 1;
-        run_begin[sb++] = (uint16_t)(lane * 32 + b);
-    }
-    while (lasts) {
-        uint32_t b = __ffs(lasts) - 1;
-        lasts &= lasts - 1;
-        run_end[eb++] = (uint16_t)(lane * 32 + b + 1);
-    }
-    if (lane == 0) *n_runs = total;
-}
-
-// `raw` = this lane's word of the touched bitmap.
-__device__ void group_tail(const PlanArgs &p, uint32_t g, uint32_t raw, uint32_t lane) {
-    GroupScratch &gs = p.groups[g];
-    // bits at or above n_blocks cannot be produced by valid ids; drop them anyway
-    uint32_t lo_bit = lane * 32;
-    uint32_t valid = p.n_blocks >= lo_bit + 32 ? 0xffffffffu
-                     : (p.n_blocks > lo_bit ? ((1u << (p.n_blocks - lo_bit)) - 1u) : 0u);
-    raw &= valid;
-    uint32_t touched = warp_sum(__popc(raw));
-    if (p.scan_only) {
-        if (p.bitmaps_out) p.bitmaps_out[g * kWords + lane] = raw;
-        if (lane == 0) {
-            gs.touched = touched; gs.desired = 0; gs.added = 0; gs.evicted = 0;
-            gs.n_runs[0] = 0; gs.n_runs[1] = 0;
-        }
-        return;
-    }
-    // budget cut: lowest block ids first (one event => all stamps tie, and ties
-    // rank by ascending block id)
-    uint32_t before = warp_inclusive_sum(__popc(raw), lane) - __popc(raw);
-    uint32_t keep = p.budget > before ? p.budget - before : 0;
-    uint32_t desired = lowest_bits(raw, keep);
-    uint32_t res = p.resident[g * kWords + lane];
-    uint32_t add = desired & ~res;
-    uint32_t evict = (p.flags & RT_PLAN_EVICT) ? (res & ~desired) : 0u;
-    if (!(p.flags & RT_PLAN_DRY_RUN)) p.resident[g * kWords + lane] = desired;
-    emit_runs(evict, lane, gs.run_begin[0], gs.run_end[0], &gs.n_runs[0]);
-    emit_runs(add, lane, gs.run_begin[1], gs.run_end[1], &gs.n_runs[1]);
-    uint32_t n_des = warp_sum(__popc(desired));
-    uint32_t n_add = warp_sum(__popc(add));
-    uint32_t n_ev = warp_sum(__popc(evict));
-    if (lane == 0) { gs.touched = touched; gs.desired = n_des; gs.added = n_add; gs.evicted = n_ev; }
-}
-
-// --------------------------------------------------------------------------
-// finalize: the whole CTA lays the ranges out in queue order
-// --------------------------------------------------------------------------
-struct FinalizeShared {
-    uint32_t off[2 * RT_MAX_BUFFERS + 1];
-    uint32_t warp_tot[kScanThreads / 32];
-    uint32_t stats[4];
-    unsigned long long bytes[2];
-};
-
-template <int kBar>
-__device__ void finalize(const PlanArgs &p, FinalizeShared &sh) {
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t nthr = kScanThreads, nwarp = nthr >> 5;
-    const uint32_t items = p.scan_only ? 0 : 2 * p.n_buffers;
-    if (tid < 4) sh.stats[tid] = 0;
-    if (tid < 2) sh.bytes[tid] = 0;
-    cta_sync<kBar, kScanThreads>();
-    // group statistics
-    for (uint32_t g = tid; g < p.n_groups; g += nthr) {
-        const GroupScratch &gs = p.groups[g];      // written by other CTAs: read through L2
-        atomicAdd(&sh.stats[0], __ldcg(&gs.touched));
-        atomicAdd(&sh.stats[1], __ldcg(&gs.desired));
-        atomicAdd(&sh.stats[2], __ldcg(&gs.added));
-        atomicAdd(&sh.stats[3], __ldcg(&gs.evicted));
-    }
-    // exclusive prefix sum of run counts over (phase, buffer)
-    const uint32_t per = (items + nthr - 1) / nthr;
-    const uint32_t first = tid * per;
-    uint32_t local = 0;
-    for (uint32_t k = 0; k < per; ++k) {
-        uint32_t i = first + k;
-        if (i < items) {
-            uint32_t phase = i >= p.n_buffers;
-            uint32_t j = i - phase * p.n_buffers;
-            local += __ldcg(&p.groups[p.buffer_group[j]].n_runs[phase]);
-        }
-    }
-    uint32_t incl = warp_inclusive_sum(local, lane);
-    if (lane == 31) sh.warp_tot[warp] = incl;
-    cta_sync<kBar, kScanThreads>();
-    uint32_t base = 0;
-    for (uint32_t w = 0; w < warp; ++w) base += sh.warp_tot[w];
-    uint32_t total = 0;
-    for (uint32_t w = 0; w < nwarp; ++w) total += sh.warp_tot[w];
-    uint32_t run = base + incl - local;
-    for (uint32_t k = 0; k < per; ++k) {
-        uint32_t i = first + k;
-        if (i < items) {
-            sh.off[i] = run;
-            uint32_t phase = i >= p.n_buffers;
-            uint32_t j = i - phase * p.n_buffers;
-            run += __ldcg(&p.groups[p.buffer_group[j]].n_runs[phase]);
-        }
-    }
-    if (tid == 0) sh.off[items] = total;
-    cta_sync<kBar, kScanThreads>();
-    const uint32_t n_cpu = items ? sh.off[p.n_buffers] : 0;
-    unsigned long long my_bytes[2] = {0, 0};
-    for (uint32_t r = tid; r < total; r += nthr) {
-        // last item whose offset is <= r
-        uint32_t lo = 0, hi = items;
-        while (hi - lo > 1) {
-            uint32_t mid = (lo + hi) >> 1;
-            if (sh.off[mid] <= r) lo = mid; else hi = mid;
-        }
-        uint32_t phase = lo >= p.n_buffers;
-        uint32_t j = lo - phase * p.n_buffers;
-        const GroupScratch &gs = p.groups[p.buffer_group[j]];
-        uint32_t k = r - sh.off[lo];
-        unsigned long long b = (unsigned long long)__ldcg(&gs.run_begin[phase][k]) * p.block_bytes;
-        unsigned long long e = (unsigned long long)__ldcg(&gs.run_end[phase][k]) * p.block_bytes;
-        if (e > p.alloc_bytes) e = p.alloc_bytes;       // final partial block, select.cpp:24188
-        my_bytes[phase] += e - b;
-        if (r < p.cap) {
-            rt_range out;
-            out.buffer = j;
-            out.dst = phase ? p.dst_device : RT_DST_CPU;
-            out.offset = b;
-            out.bytes = e - b;
-            p.out[r] = out;
-        }
-    }
-    if (my_bytes[0]) atomicAdd(&sh.bytes[0], my_bytes[0]);
-    if (my_bytes[1]) atomicAdd(&sh.bytes[1], my_bytes[1]);
-    cta_sync<kBar, kScanThreads>();
-    if (tid == 0) {
-        GlobalScratch &gl = *p.global;
-        rt_plan_result res;
-        res.n_ranges = total;
-        res.n_cpu_ranges = n_cpu;
-        unsigned long long invalid = *(volatile unsigned long long *)&gl.invalid_slots;
-        uint32_t eflags = *(volatile uint32_t *)&gl.error_flags;
-        res.flags = (total > p.cap ? RT_RESULT_OVERFLOW : 0u) | (invalid ? RT_RESULT_SLOT_RANGE : 0u) | eflags;
-        res.blocks_touched = sh.stats[0];
-        res.blocks_desired = sh.stats[1];
-        res.blocks_added = sh.stats[2];
-        res.blocks_evicted = sh.stats[3];
-        res.reserved = 0;
-        res.invalid_slots = invalid;
-        res.ignored_slots = *(volatile unsigned long long *)&gl.ignored_slots;
-        res.cpu_bytes = sh.bytes[0];
-        res.gpu_bytes = sh.bytes[1];
-        *p.result = res;
-        // leave the scratch clean for the next launch
-        gl.invalid_slots = 0;
-        gl.ignored_slots = 0;
-        gl.groups_done = 0;
-        gl.error_flags = 0;
-        __threadfence_system();
-    }
-}
-
-// Hand-over after a CTA's bits for bitmap g reached the global words.  Returns after the
-// CTA has done whatever stage fell to it.
 struct HandoverShared {
-    int role;      // 0 nothing, 1 run the group's tail, 2 tail + finalize
+    int last;      // this CTA retired the last work unit of the launch
 };
-
-template <int kBar>
-__device__ __forceinline__ void retire_units(const PlanArgs &p, uint32_t g, uint32_t count,
-                                             uint32_t units_in_group, HandoverShared &hs,
-                                             FinalizeShared &fs) {
-    __threadfence();
-    cta_sync<kBar, kScanThreads>();
-    if (threadIdx.x == 0) {
-        uint32_t prev = atomicAdd(&p.groups[g].units_done, count);
-        hs.role = prev + count == units_in_group;
-    }
-    cta_sync<kBar, kScanThreads>();
-    if (!hs.role) return;
-    __threadfence();
-    if (threadIdx.x < 32) {
-        uint32_t lane = threadIdx.x;
-        uint32_t raw = atomicExch(&p.groups[g].want[lane], 0u);   // consume + clean
-        if (lane == 0) p.groups[g].units_done = 0;
-        group_tail(p, g, raw, lane);
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) {
-            uint32_t prev = atomicAdd(&p.global->groups_done, 1u);
-            hs.role = prev + 1 == p.n_groups ? 2 : 1;
-        }
-    }
-    cta_sync<kBar, kScanThreads>();
-    if (hs.role == 2) {
-        __threadfence();
-        finalize<kBar>(p, fs);
-    }
-    cta_sync<kBar, kScanThreads>();
-}
 
 template <int kBar>
 __device__ __forceinline__ void flush_counters(const PlanArgs &p, ScanCounters &c) {
@@ -462,17 +205,32 @@ __device__ __forceinline__ void flush_map(const PlanArgs &p, uint32_t g, const u
     }
 }
 
-// The CTA leaves bitmap g after `count` work units: publish, hand over, reset.
+// The CTA leaves bitmap g: publish its bits and counters, start a clean map.
 template <int kBar>
-__device__ __forceinline__ void leave_group(const ScanArgs &a, const PlanArgs &p, uint32_t g,
-                                            uint32_t count, uint32_t units_in_group, uint8_t *s_map,
-                                            ScanCounters &c, HandoverShared &hs, FinalizeShared &fs) {
+__device__ __forceinline__ void leave_group(const PlanArgs &p, uint32_t g, uint8_t *s_map,
+                                            ScanCounters &c) {
     cta_sync<kBar, kScanThreads>();
     flush_map(p, g, s_map);
     flush_counters<kBar>(p, c);
-    retire_units<kBar>(p, g, count, units_in_group, hs, fs);
     clear_map(s_map);
     cta_sync<kBar, kScanThreads>();
+}
+
+// The CTA is done with its `count` work units.  Whoever brings the launch-wide
+// counter to the total runs the tail; nobody waits for anybody.
+template <int kBar>
+__device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, HandoverShared &hs,
+                                           unsigned char *tail_mem) {
+    __threadfence();                      // this CTA's atomicOr / atomicAdd before the arrival
+    cta_sync<kBar, kScanThreads>();
+    if (threadIdx.x == 0) {
+        uint32_t prev = atomicAdd(&p.global->units_done, count);
+        hs.last = prev + count == p.n_units;
+    }
+    cta_sync<kBar, kScanThreads>();
+    if (!hs.last) return;
+    __threadfence();
+    plan_tail<kBar>(p, &p.groups[0].want[0], true, tail_mem);
 }
 
 // --------------------------------------------------------------------------
@@ -485,9 +243,9 @@ __device__ __forceinline__ void leave_group(const ScanArgs &a, const PlanArgs &p
 template <bool kPow2>
 __global__ void __launch_bounds__(kScanThreads)
 scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
+    extern __shared__ __align__(16) unsigned char tail_mem[];
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
-    __shared__ FinalizeShared fs;
     const int q_begin = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
     const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
     if (q_begin >= q_end) return;
@@ -496,25 +254,57 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
     __syncthreads();
     for (uint32_t g = first_group(a, q_begin);; ++g) {
         const GroupSpan sp = group_span(a, g, q_begin, q_end);
-        const long long begin = sp.lo, end = sp.hi;
+        int q = sp.q_lo;
         long long e0 = sp.e0;
         const long long *mine = a.slots + e0 + 2 * (int)threadIdx.x;
-        Chunk ch;
-        load_chunk(mine, e0, begin, end, ch);
-        for (int q = sp.q_lo; q < sp.q_hi; ++q) {
-            Chunk nx;
-            nx.mask = 0;
-            if (q + 1 < sp.q_hi) load_chunk(mine + kChunkElems, e0 + kChunkElems, begin, end, nx);
+        // ragged first unit of the bitmap (odd start index)
+        if (q < sp.q_hi && e0 < sp.lo) {
+            Chunk ch;
+            load_chunk(mine, e0, sp.lo, sp.hi, ch);
             mark_chunk<kPow2>(ch, a, s_map, c);
-            mine += kChunkElems;
-            e0 += kChunkElems;
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) ch.v[u] = nx.v[u];
-            ch.mask = nx.mask;
+            ++q; e0 += kChunkElems; mine += kChunkElems;
         }
-        leave_group<0>(a, p, g, (uint32_t)(sp.q_hi - sp.q_lo), (uint32_t)sp.units_in_group, s_map, c, hs, fs);
+        // whole units: two register sets alternate, so the loads of one unit are
+        // in flight while the other is marked, with no copies between them
+        int n_whole = (int)((sp.hi - e0) / kChunkElems);
+        if (n_whole > sp.q_hi - q) n_whole = sp.q_hi - q;
+        if (n_whole > 0) {
+            longlong2 va[kUnroll], vb[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u)
+                va[u] = __ldcs(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
+            int left = n_whole;
+            while (left >= 2) {
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u)
+                    vb[u] = __ldcs(reinterpret_cast<const longlong2 *>(mine + kChunkElems + 2 * u * kScanThreads));
+                mark_full<kPow2>(va, a, s_map, c);
+                mine += 2 * kChunkElems;
+                left -= 2;
+                if (left > 0) {
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u)
+                        va[u] = __ldcs(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
+                }
+                mark_full<kPow2>(vb, a, s_map, c);
+            }
+            if (left == 1) {
+                mark_full<kPow2>(va, a, s_map, c);
+                mine += kChunkElems;
+            }
+            q += n_whole;
+            e0 += (long long)n_whole * kChunkElems;
+        }
+        // ragged last unit
+        if (q < sp.q_hi) {
+            Chunk ch;
+            load_chunk(mine, e0, sp.lo, sp.hi, ch);
+            mark_chunk<kPow2>(ch, a, s_map, c);
+        }
+        leave_group<0>(p, g, s_map, c);
         if (sp.q_hi >= q_end) break;
     }
+    finish_cta<0>(p, (uint32_t)(q_end - q_begin), hs, tail_mem);
 }
 
 // --------------------------------------------------------------------------
@@ -525,9 +315,9 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
 template <bool kPow2>
 __global__ void __launch_bounds__(kScanThreads)
 scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
+    extern __shared__ __align__(16) unsigned char tail_mem[];
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
-    __shared__ FinalizeShared fs;
     if ((int)blockIdx.x >= a.n_units) return;
     ScanCounters c = {0, 0};
     clear_map(s_map);
@@ -546,7 +336,8 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
         load_chunk(a.slots + e0 + 2 * (int)threadIdx.x, e0, lo, hi, ch);
         mark_chunk<kPow2>(ch, a, s_map, c);
     }
-    leave_group<0>(a, p, 0, units, (uint32_t)a.n_units, s_map, c, hs, fs);
+    leave_group<0>(p, 0, s_map, c);
+    finish_cta<0>(p, units, hs, tail_mem);
 }
 
 // --------------------------------------------------------------------------
@@ -563,7 +354,10 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
 // Every wait on an mbarrier is bounded; when the bound is hit the CTA records
 // RT_RESULT_TIMEOUT, skips the unit and still retires it, so the grid always
 // drains.
-constexpr int kStages = 4;
+#ifndef RT_STAGES
+#define RT_STAGES 4
+#endif
+constexpr int kStages = RT_STAGES;
 constexpr int kStageBytes = kChunkElems * 8;
 constexpr uint32_t kWaitLimit = 1u << 20;
 
@@ -626,7 +420,6 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
     __shared__ __align__(8) uint64_t empty_bar[kStages];   // all consumer warps done with the stage
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
-    __shared__ FinalizeShared fs;
     const int tid = threadIdx.x;
     const int q_begin = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
     const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
@@ -721,8 +514,7 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
             if (mask == kAllIds) mark_full<kPow2>(v, a, s_map, c);
             else mark_masked<kPow2>(v, mask, a, s_map, c);
         }
-        leave_group<kConsumerBar>(a, p, g, (uint32_t)(sp.q_hi - sp.q_lo), (uint32_t)sp.units_in_group,
-                                  s_map, c, hs, fs);
+        leave_group<kConsumerBar>(p, g, s_map, c);
         if (sp.q_hi >= q_end) break;
     }
     if (gave_up) {
@@ -734,20 +526,17 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
             if (uses > 0) mbar_wait_bounded(&full_bar[s], (uint32_t)(uses - 1) & 1u);
         }
     }
+    // every stage has been consumed: the staging memory now serves the tail
+    finish_cta<kConsumerBar>(p, (uint32_t)(q_end - q_begin), hs, stage_mem);
 }
 
 // --------------------------------------------------------------------------
 // kernel: wanted bitmaps given, no scan
 // --------------------------------------------------------------------------
 __global__ void __launch_bounds__(kScanThreads)
-plan_tail_kernel(const uint32_t *want, const __grid_constant__ PlanArgs p) {
-    __shared__ FinalizeShared fs;
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (uint32_t g = warp; g < p.n_groups; g += blockDim.x >> 5)
-        group_tail(p, g, want[g * kWords + lane], lane);
-    __threadfence();
-    __syncthreads();
-    finalize<0>(p, fs);
+plan_tail_kernel(uint32_t *want, const __grid_constant__ PlanArgs p) {
+    extern __shared__ __align__(16) unsigned char tail_mem[];
+    plan_tail<0>(p, want, false, tail_mem);
 }
 
 // --------------------------------------------------------------------------
@@ -756,18 +545,20 @@ plan_tail_kernel(const uint32_t *want, const __grid_constant__ PlanArgs p) {
 cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, int grid,
                              cudaStream_t stream) {
     const bool pow2 = a.shift >= 0;
+    const size_t smem = tail_smem_bytes(p.n_groups, p.n_buffers);
     if (table) {
-        if (pow2) scan_table_kernel<true><<<grid, kScanThreads, 0, stream>>>(a, p);
-        else scan_table_kernel<false><<<grid, kScanThreads, 0, stream>>>(a, p);
+        if (pow2) scan_table_kernel<true><<<grid, kScanThreads, smem, stream>>>(a, p);
+        else scan_table_kernel<false><<<grid, kScanThreads, smem, stream>>>(a, p);
     } else {
-        if (pow2) scan_plan_kernel<true><<<grid, kScanThreads, 0, stream>>>(a, p);
-        else scan_plan_kernel<false><<<grid, kScanThreads, 0, stream>>>(a, p);
+        if (pow2) scan_plan_kernel<true><<<grid, kScanThreads, smem, stream>>>(a, p);
+        else scan_plan_kernel<false><<<grid, kScanThreads, smem, stream>>>(a, p);
     }
     return cudaGetLastError();
 }
 
 cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream_t stream) {
-    plan_tail_kernel<<<1, kScanThreads, 0, stream>>>(want, p);
+    plan_tail_kernel<<<1, kScanThreads, tail_smem_bytes(p.n_groups, p.n_buffers), stream>>>(
+        const_cast<uint32_t *>(want), p);
     return cudaGetLastError();
 }
 
@@ -779,18 +570,30 @@ cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid,
     return cudaGetLastError();
 }
 
-cudaError_t scan_plan_occupancy(int *plain_blocks_per_sm, int *tma_blocks_per_sm) {
-    cudaError_t e = cudaFuncSetAttribute(scan_plan_tma_kernel<true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kStages * kStageBytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(scan_plan_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kStages * kStageBytes);
-    if (e != cudaSuccess) return e;
+// Opt in to the dynamic shared memory the kernels need and report how many CTAs
+// of each streaming kernel fit on one SM for this plan's geometry.
+cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plain_blocks_per_sm,
+                                int *tma_blocks_per_sm) {
+    const int tail = (int)tail_smem_bytes(n_groups, n_buffers);
+    const int tma = kStages * kStageBytes;
+    cudaError_t e;
+#define RT_SET_SMEM(kernel, bytes)                                                           \
+    if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes)) != \
+        cudaSuccess)                                                                         \
+        return e;
+    RT_SET_SMEM(scan_plan_tma_kernel<true>, tma)
+    RT_SET_SMEM(scan_plan_tma_kernel<false>, tma)
+    RT_SET_SMEM(scan_plan_kernel<true>, tail)
+    RT_SET_SMEM(scan_plan_kernel<false>, tail)
+    RT_SET_SMEM(scan_table_kernel<true>, tail)
+    RT_SET_SMEM(scan_table_kernel<false>, tail)
+    RT_SET_SMEM(plan_tail_kernel, tail)
+#undef RT_SET_SMEM
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(plain_blocks_per_sm, scan_plan_kernel<true>,
-                                                      kScanThreads, 0);
+                                                      kScanThreads, tail);
     if (e != cudaSuccess) return e;
     return cudaOccupancyMaxActiveBlocksPerMultiprocessor(tma_blocks_per_sm, scan_plan_tma_kernel<true>,
-                                                         kTmaThreads, kStages * kStageBytes);
+                                                         kTmaThreads, tma);
 }
 
 }  // namespace rt

@@ -1,0 +1,579 @@
+// UVM control server: allocation registry, protocol handler, migration worker.
+//
+// Lock order: life -> state.  `life` serialises allocation lifetime events
+// (alloc / free / context teardown) against one in-flight batch of prefetches;
+// `state` guards the registry and the counters and is never held across a CUDA
+// call.  `status` and `list` take `state` only, so they never wait for a
+// migration.
+#include <errno.h>
+#include <poll.h>
+#include <pthread.h>
+#include <sys/socket.h>
+#include <sys/stat.h>
+#include <sys/un.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <condition_variable>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "driver_api.h"
+#include "rt_internal.h"
+#include "uvm_plan.h"
+
+namespace rt {
+namespace {
+
+struct Allocation {
+    uint64_t id;
+    CUdeviceptr ptr;
+    uint64_t bytes;
+    CUcontext ctx;
+    int device;
+    int concurrent;
+};
+
+struct Server {
+    std::mutex life;
+    std::mutex state;
+    std::condition_variable wake;        // worker: a job arrived / stop
+    std::condition_variable done;        // waiters: a job completed
+    std::vector<Allocation> allocations; // insertion order == id order
+    uint64_t next_id = 0, managed_bytes = 0, generation = 0;
+    uint64_t job_id = 0, completed_job = 0, job_bytes = 0, cpu_bytes = 0, gpu_bytes = 0;
+    int last_error = 0;
+    bool busy = false, stop = false, running = false;
+    std::vector<rt_id_range> job;
+    uint64_t chunk = 16ull << 20, batch = 256ull << 20, page = 4096;
+    uint32_t n_streams = 4;
+    std::thread worker, listener;
+    int listen_fd = -1, client_fd = -1;
+    std::string socket_path;
+    dev_t socket_dev = 0;
+    ino_t socket_ino = 0;
+    pid_t owner = 0;
+    // side streams, per context, owned by the worker thread
+    std::map<CUcontext, std::vector<CUstream>> streams;
+};
+
+Server g;
+
+uint64_t saturating_add(uint64_t a, uint64_t b) { return b > UINT64_MAX - a ? UINT64_MAX : a + b; }
+
+std::vector<rt_alloc_info> snapshot_locked() {
+    std::vector<rt_alloc_info> out;
+    out.reserve(g.allocations.size());
+    for (const Allocation &a : g.allocations) out.push_back({a.id, a.bytes, a.device, a.concurrent});
+    return out;
+}
+
+// ---------------------------------------------------------------------------
+// executor: one job = ranges in queue order; CPU-bound ranges come first in
+// every plan and must have landed before the first GPU-bound one is issued.
+// ---------------------------------------------------------------------------
+struct Pending {
+    uint64_t bytes;
+    int dst;
+};
+
+CUresult streams_for(const DriverApi &api, CUcontext ctx, std::vector<CUstream> **out) {
+    auto it = g.streams.find(ctx);
+    if (it == g.streams.end()) {
+        std::vector<CUstream> made;
+        for (uint32_t i = 0; i < g.n_streams; ++i) {
+            CUstream s = nullptr;
+            CUresult r = api.stream_create(&s, CU_STREAM_NON_BLOCKING);
+            if (r != CUDA_SUCCESS) {
+                for (CUstream m : made) api.stream_destroy(m);
+                return r;
+            }
+            made.push_back(s);
+        }
+        it = g.streams.emplace(ctx, std::move(made)).first;
+    }
+    *out = &it->second;
+    return CUDA_SUCCESS;
+}
+
+// Issues up to `batch` bytes starting at (*range, *done) and waits for them.
+// Holds `life` for the whole batch so that no allocation can be freed under a
+// queued prefetch.
+CUresult run_batch(const DriverApi &api, const std::vector<rt_id_range> &job, size_t *range,
+                   uint64_t *done_in_range) {
+    std::lock_guard<std::mutex> life(g.life);
+    std::vector<Pending> pending;
+    std::vector<CUstream> used;
+    CUcontext current = nullptr;
+    bool have_ctx = false;
+    CUresult result = CUDA_SUCCESS;
+    uint64_t issued = 0;
+    const int batch_dst_is_cpu = job[*range].dst < 0;
+    uint32_t rr = 0;
+    while (*range < job.size() && issued < g.batch && result == CUDA_SUCCESS) {
+        const rt_id_range &r = job[*range];
+        if ((r.dst < 0) != batch_dst_is_cpu) break;      // phase boundary: wait first
+        CUdeviceptr ptr = 0;
+        CUcontext ctx = nullptr;
+        bool found = false, stopping;
+        {
+            std::lock_guard<std::mutex> st(g.state);
+            for (const Allocation &a : g.allocations)
+                if (a.id == r.id) { ptr = a.ptr + r.offset + *done_in_range; ctx = a.ctx; found = true; break; }
+            stopping = g.stop;
+        }
+        if (stopping) { result = CUDA_ERROR_DEINITIALIZED; break; }
+        if (!found) { result = CUDA_ERROR_INVALID_VALUE; break; }
+        if (have_ctx && ctx != current) break;            // one context per batch
+        if (!have_ctx) {
+            result = api.ctx_set_current(ctx);
+            if (result != CUDA_SUCCESS) break;
+            current = ctx;
+            have_ctx = true;
+        }
+        std::vector<CUstream> *streams = nullptr;
+        result = streams_for(api, ctx, &streams);
+        if (result != CUDA_SUCCESS) break;
+        uint64_t bytes = r.bytes - *done_in_range;
+        if (bytes > g.chunk) bytes = g.chunk;
+        CUstream s = (*streams)[rr++ % streams->size()];
+        result = api.prefetch(ptr, bytes, r.dst, s);
+        if (result != CUDA_SUCCESS) break;
+        bool seen = false;
+        for (CUstream u : used) seen |= u == s;
+        if (!seen) used.push_back(s);
+        pending.push_back({bytes, r.dst});
+        issued += bytes;
+        *done_in_range += bytes;
+        if (*done_in_range == r.bytes) { ++*range; *done_in_range = 0; }
+    }
+    for (CUstream s : used) {
+        CUresult r = api.stream_synchronize(s);
+        if (result == CUDA_SUCCESS) result = r;
+    }
+    if (have_ctx) {
+        // the worker owns its thread's context binding; never leave one behind
+        CUresult r = api.ctx_set_current(nullptr);
+        if (result == CUDA_SUCCESS) result = r;
+    }
+    if (result == CUDA_SUCCESS) {
+        std::lock_guard<std::mutex> st(g.state);
+        for (const Pending &p : pending) {
+            g.job_bytes = saturating_add(g.job_bytes, p.bytes);
+            uint64_t &side = p.dst < 0 ? g.cpu_bytes : g.gpu_bytes;
+            side = saturating_add(side, p.bytes);
+        }
+    }
+    return result;
+}
+
+void worker_main() {
+    const DriverApi *api = driver_api();
+    std::unique_lock<std::mutex> st(g.state);
+    for (;;) {
+        g.wake.wait(st, [] { return g.busy || g.stop; });
+        if (g.stop && !g.busy) break;
+        std::vector<rt_id_range> job;
+        job.swap(g.job);
+        st.unlock();
+        CUresult result = api ? CUDA_SUCCESS : CUDA_ERROR_NOT_INITIALIZED;
+        size_t range = 0;
+        uint64_t done_in_range = 0;
+        while (result == CUDA_SUCCESS && range < job.size())
+            result = run_batch(*api, job, &range, &done_in_range);
+        st.lock();
+        g.last_error = (int)result;
+        g.completed_job = g.job_id;
+        g.busy = false;
+        g.done.notify_all();
+        if (g.stop) break;
+    }
+}
+
+}  // namespace
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// protocol: one line in, one JSON line out (select.cpp:24045-24327)
+// ---------------------------------------------------------------------------
+std::string error_reply(const char *error) {
+    return std::string("{\"ok\":false,\"error\":\"") + error + "\"}";
+}
+
+std::string status_reply_locked() {
+    char buf[640];
+    snprintf(buf, sizeof(buf),
+             "{\"ok\":true,\"pid\":%ld,\"managed_bytes\":%llu,\"allocation_count\":%llu,"
+             "\"allocation_generation\":%llu,\"busy\":%s,\"job_id\":%llu,"
+             "\"completed_job\":%llu,\"last_error\":%d,"
+             "\"completed_cpu_bytes\":%llu,\"completed_gpu_bytes\":%llu,\"job_completed_bytes\":%llu}",
+             (long)g.owner, (unsigned long long)g.managed_bytes,
+             (unsigned long long)g.allocations.size(), (unsigned long long)g.generation,
+             g.busy ? "true" : "false", (unsigned long long)g.job_id,
+             (unsigned long long)g.completed_job, g.last_error, (unsigned long long)g.cpu_bytes,
+             (unsigned long long)g.gpu_bytes, (unsigned long long)g.job_bytes);
+    return buf;
+}
+
+std::string list_reply_locked() {
+    std::string out = "{\"ok\":true,\"allocation_generation\":" + std::to_string(g.generation) +
+                      ",\"allocations\":[";
+    bool first = true;
+    for (const Allocation &a : g.allocations) {
+        char item[128];
+        snprintf(item, sizeof(item), "%s{\"id\":%llu,\"bytes\":%llu,\"device\":%d}", first ? "" : ",",
+                 (unsigned long long)a.id, (unsigned long long)a.bytes, a.device);
+        out += item;
+        first = false;
+    }
+    return out + "]}";
+}
+
+bool single_word(const char *line, const char *word) {
+    while (*line == ' ' || *line == '\t' || *line == '\r') ++line;
+    size_t n = strlen(word);
+    if (strncmp(line, word, n)) return false;
+    line += n;
+    while (*line == ' ' || *line == '\t' || *line == '\r') ++line;
+    return !*line;
+}
+
+// Accepts the job under `state` (caller holds it): the admission checks of
+// select.cpp:24131-24135 in their order.
+const char *admit_locked(std::vector<rt_id_range> &ranges, uint64_t *accepted) {
+    const DriverApi *api = driver_api();
+    if (g.busy) return "busy";
+    if (g.stop) return "stopping";
+    if (!g.running || !api || !api->can_prefetch()) return "not_supported";
+    if (g.job_id == UINT64_MAX) return "job_id_exhausted";
+    (void)ranges;
+    (void)accepted;
+    return nullptr;
+}
+
+void publish_locked(std::vector<rt_id_range> &ranges, uint64_t *accepted) {
+    g.job.swap(ranges);
+    g.busy = true;
+    g.job_bytes = 0;
+    g.last_error = 0;
+    *accepted = ++g.job_id;
+    g.wake.notify_one();
+}
+
+std::string handle_line(const char *line) {
+    if (single_word(line, "status")) {
+        std::lock_guard<std::mutex> st(g.state);
+        return status_reply_locked();
+    }
+    if (single_word(line, "list")) {
+        std::lock_guard<std::mutex> st(g.state);
+        return list_reply_locked();
+    }
+    // Syntax errors are reported before the admission checks, plan errors after
+    // them, exactly as the reference orders them: parse once against an empty
+    // registry to classify.
+    std::vector<rt_id_range> ranges;
+    {
+        std::vector<rt_id_range> scratch;
+        const char *syntax = expand_plan_line(nullptr, 0, 0, line, g.page, scratch);
+        if (syntax && !strcmp(syntax, "invalid_command")) return error_reply("invalid_command");
+    }
+    uint64_t accepted = 0;
+    {
+        std::lock_guard<std::mutex> st(g.state);
+        if (const char *why = admit_locked(ranges, &accepted)) return error_reply(why);
+        std::vector<rt_alloc_info> reg = snapshot_locked();
+        if (const char *why = expand_plan_line(reg.data(), reg.size(), g.generation, line, g.page, ranges))
+            return error_reply(why);
+        publish_locked(ranges, &accepted);
+    }
+    return "{\"ok\":true,\"job_id\":" + std::to_string(accepted) + "}";
+}
+
+// ---------------------------------------------------------------------------
+// socket listener (select.cpp:24330-24376): one command per connection
+// ---------------------------------------------------------------------------
+void send_all(int fd, const std::string &text) {
+    const char *s = text.data();
+    size_t left = text.size();
+    while (left) {
+        ssize_t n = send(fd, s, left, MSG_NOSIGNAL);
+        if (n < 0 && errno == EINTR) continue;
+        if (n <= 0) return;
+        s += n;
+        left -= (size_t)n;
+    }
+}
+
+void listener_main() {
+    for (;;) {
+        struct pollfd pfd = {g.listen_fd, POLLIN, 0};
+        int ready = poll(&pfd, 1, 200);
+        {
+            std::lock_guard<std::mutex> st(g.state);
+            if (g.stop) break;
+        }
+        if (ready <= 0 || !(pfd.revents & POLLIN)) continue;
+        int fd = accept4(g.listen_fd, nullptr, nullptr, SOCK_CLOEXEC);
+        if (fd < 0) continue;
+        bool stopping;
+        {
+            std::lock_guard<std::mutex> st(g.state);
+            g.client_fd = fd;
+            stopping = g.stop;
+        }
+        struct ucred peer;
+        socklen_t size = sizeof(peer);
+        if (!stopping && getsockopt(fd, SOL_SOCKET, SO_PEERCRED, &peer, &size) == 0 &&
+            size == sizeof(peer) && peer.uid == getuid()) {
+            // a partial line cannot hold the listener for more than a second
+            struct timeval timeout = {1, 0};
+            setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &timeout, sizeof(timeout));
+            setsockopt(fd, SOL_SOCKET, SO_SNDTIMEO, &timeout, sizeof(timeout));
+            char line[512];
+            size_t used = 0;
+            bool complete = false, invalid = false;
+            while (used + 1 < sizeof(line)) {
+                char c;
+                ssize_t n = recv(fd, &c, 1, 0);
+                if (n < 0 && errno == EINTR) continue;
+                if (n != 1) break;
+                if (c == '\n') { complete = true; break; }
+                if (!c) { invalid = true; break; }
+                line[used++] = c;
+            }
+            line[used] = 0;
+            send_all(fd, (complete && !invalid ? handle_line(line) : error_reply("invalid_line")) + "\n");
+        }
+        {
+            std::lock_guard<std::mutex> st(g.state);
+            g.client_fd = -1;
+            close(fd);
+        }
+    }
+}
+
+void unlink_owned_socket() {
+    struct stat st;
+    if (g.socket_ino && lstat(g.socket_path.c_str(), &st) == 0 && S_ISSOCK(st.st_mode) &&
+        st.st_uid == getuid() && st.st_dev == g.socket_dev && st.st_ino == g.socket_ino)
+        unlink(g.socket_path.c_str());
+    g.socket_ino = 0;
+}
+
+int open_socket(const char *path) {
+    struct sockaddr_un address = {};
+    address.sun_family = AF_UNIX;
+    char def[sizeof(address.sun_path)];
+    if (!path) {
+        snprintf(def, sizeof(def), "/tmp/select-uvm-%lu-%ld.sock", (unsigned long)getuid(), (long)getpid());
+        path = def;
+    }
+    if (strlen(path) >= sizeof(address.sun_path)) return RT_ERR_INVALID_ARGUMENT;
+    strcpy(address.sun_path, path);
+    int fd = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC | SOCK_NONBLOCK, 0);
+    if (fd < 0) return RT_ERR_IO;
+    // never remove a path that already exists, even if it looks stale
+    if (bind(fd, (struct sockaddr *)&address, sizeof(address)) != 0) { close(fd); return RT_ERR_IO; }
+    g.socket_path = path;
+    struct stat st;
+    if (lstat(path, &st) != 0) { close(fd); return RT_ERR_IO; }
+    g.socket_dev = st.st_dev;
+    g.socket_ino = st.st_ino;
+    if (chmod(path, 0600) != 0 || listen(fd, 16) != 0) {
+        close(fd);
+        unlink_owned_socket();
+        return RT_ERR_IO;
+    }
+    g.listen_fd = fd;
+    return RT_OK;
+}
+
+}  // namespace
+}  // namespace rt
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+using rt::g;
+
+extern "C" {
+
+int rt_uvm_start(const rt_uvm_config *config) {
+    std::lock_guard<std::mutex> life(g.life);
+    {
+        std::lock_guard<std::mutex> st(g.state);
+        if (g.running) return RT_ERR_BUSY;
+    }
+    rt_uvm_config cfg = {};
+    if (config) cfg = *config;
+    uint64_t chunk = cfg.chunk_bytes;
+    if (!chunk) {
+        // SELECT_UVM_CHUNK_MB: 1..256, default 16 MiB (select.cpp:23794,23853-23856)
+        chunk = 16ull << 20;
+        uint64_t mb = 0;
+        const char *s = getenv("SELECT_UVM_CHUNK_MB");
+        if (s && rt::parse_u64(s, strlen(s), &mb) && mb >= 1 && mb <= 256) chunk = mb << 20;
+    }
+    long page = sysconf(_SC_PAGESIZE);
+    g.page = page > 0 ? (uint64_t)page : 4096;
+    g.chunk = chunk;
+    g.batch = cfg.batch_bytes ? cfg.batch_bytes : (256ull << 20);
+    if (g.batch < g.chunk) g.batch = g.chunk;
+    g.n_streams = cfg.streams ? cfg.streams : 4;
+    g.owner = getpid();
+    g.stop = false;
+    g.listen_fd = -1;
+    g.socket_path.clear();
+    if (cfg.listen) {
+        int st = rt::open_socket(cfg.socket_path);
+        if (st != RT_OK) return st;
+    }
+    g.worker = std::thread(rt::worker_main);
+    if (g.listen_fd >= 0) g.listener = std::thread(rt::listener_main);
+    std::lock_guard<std::mutex> st(g.state);
+    g.running = true;
+    return RT_OK;
+}
+
+int rt_uvm_stop(void) {
+    {
+        std::lock_guard<std::mutex> st(g.state);
+        if (!g.running) return RT_ERR_NOT_RUNNING;
+        g.stop = true;
+        if (g.client_fd >= 0) shutdown(g.client_fd, SHUT_RDWR);
+        g.wake.notify_all();
+    }
+    if (g.listener.joinable()) g.listener.join();
+    if (g.worker.joinable()) g.worker.join();
+    if (g.listen_fd >= 0) close(g.listen_fd);
+    g.listen_fd = -1;
+    rt::unlink_owned_socket();
+    std::lock_guard<std::mutex> life(g.life);
+    std::lock_guard<std::mutex> st(g.state);
+    g.running = false;
+    g.busy = false;
+    g.job.clear();
+    g.streams.clear();       // streams die with their contexts / the process
+    g.done.notify_all();
+    return RT_OK;
+}
+
+int rt_uvm_register(uint64_t ptr, uint64_t bytes, void *ctx, int device, int concurrent, uint64_t *id) {
+    if (!bytes) return RT_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> life(g.life);
+    std::lock_guard<std::mutex> st(g.state);
+    rt::Allocation a = {++g.next_id, (CUdeviceptr)ptr, bytes, (CUcontext)ctx, device, concurrent};
+    g.allocations.push_back(a);
+    g.managed_bytes += bytes;
+    ++g.generation;
+    if (id) *id = a.id;
+    return RT_OK;
+}
+
+static int remove_where(bool (*match)(const rt::Allocation &, const void *), const void *key) {
+    std::lock_guard<std::mutex> life(g.life);
+    std::lock_guard<std::mutex> st(g.state);
+    size_t kept = 0, removed = 0;
+    for (size_t i = 0; i < g.allocations.size(); ++i) {
+        if (match(g.allocations[i], key)) {
+            g.managed_bytes -= g.allocations[i].bytes;
+            ++removed;
+        } else {
+            g.allocations[kept++] = g.allocations[i];
+        }
+    }
+    g.allocations.resize(kept);
+    if (removed) ++g.generation;
+    return (int)removed;
+}
+
+int rt_uvm_unregister_ptr(uint64_t ptr) {
+    return remove_where([](const rt::Allocation &a, const void *k) { return a.ptr == *(const CUdeviceptr *)k; },
+                        &ptr);
+}
+
+int rt_uvm_unregister_ctx(void *ctx) {
+    int n = remove_where([](const rt::Allocation &a, const void *k) { return (const void *)a.ctx == k; }, ctx);
+    std::lock_guard<std::mutex> life(g.life);
+    g.streams.erase((CUcontext)ctx);
+    return n;
+}
+
+int rt_uvm_unregister_device(int device) {
+    // conservative, like the reference (select.cpp:23894-23913): everything on
+    // the device goes, explicit-context records included
+    int n = remove_where([](const rt::Allocation &a, const void *k) { return a.device == *(const int *)k; },
+                         &device);
+    std::lock_guard<std::mutex> life(g.life);
+    g.streams.clear();
+    return n;
+}
+
+int rt_uvm_command(const char *line, char *reply, size_t cap) {
+    if (!line || !reply || !cap) return RT_ERR_INVALID_ARGUMENT;
+    std::string text;
+    if (strlen(line) >= 512 || strchr(line, '\n')) text = rt::error_reply("invalid_line");
+    else text = rt::handle_line(line);
+    if (text.size() + 1 > cap) return RT_ERR_CAPACITY;
+    memcpy(reply, text.c_str(), text.size() + 1);
+    return (int)text.size();
+}
+
+int rt_uvm_submit_ranges(const rt_range *ranges, size_t n, const uint64_t *buffer_ids, size_t n_ids,
+                         uint64_t *job_id) {
+    if ((!ranges && n) || (!buffer_ids && n_ids) || !job_id) return RT_ERR_INVALID_ARGUMENT;
+    std::vector<rt_id_range> job;
+    job.reserve(n);
+    for (size_t i = 0; i < n; ++i) {
+        if (ranges[i].buffer >= n_ids) return RT_ERR_INVALID_ARGUMENT;
+        if (!ranges[i].bytes) continue;
+        job.push_back({buffer_ids[ranges[i].buffer], ranges[i].offset, ranges[i].bytes, ranges[i].dst, 0});
+    }
+    std::lock_guard<std::mutex> st(g.state);
+    uint64_t accepted = 0;
+    if (const char *why = rt::admit_locked(job, &accepted))
+        return !strcmp(why, "busy") ? RT_ERR_BUSY : RT_ERR_NOT_RUNNING;
+    // the same bounds the text commands enforce, against the live registry
+    for (const rt_id_range &r : job) {
+        const rt::Allocation *a = nullptr;
+        for (const rt::Allocation &x : g.allocations)
+            if (x.id == r.id) { a = &x; break; }
+        if (!a || r.offset >= a->bytes || r.bytes > a->bytes - r.offset || r.offset % g.page ||
+            (r.bytes % g.page && r.bytes != a->bytes - r.offset) || !a->concurrent)
+            return RT_ERR_INVALID_ARGUMENT;
+    }
+    rt::publish_locked(job, &accepted);
+    *job_id = accepted;
+    return RT_OK;
+}
+
+int rt_uvm_wait(uint64_t job_id, double timeout_s, int *cuda_error) {
+    std::unique_lock<std::mutex> st(g.state);
+    auto ready = [&] { return !g.running || (!g.busy && g.completed_job >= job_id); };
+    if (timeout_s < 0) {
+        g.done.wait(st, ready);
+    } else if (!g.done.wait_for(st, std::chrono::duration<double>(timeout_s), ready)) {
+        return RT_ERR_BUSY;
+    }
+    if (!g.running) return RT_ERR_NOT_RUNNING;
+    if (cuda_error) *cuda_error = g.last_error;
+    return g.last_error ? RT_ERR_CUDA : RT_OK;
+}
+
+int rt_uvm_socket_path(char *out, size_t cap) {
+    if (!out || !cap) return RT_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> st(g.state);
+    if (g.socket_path.size() + 1 > cap) return RT_ERR_CAPACITY;
+    memcpy(out, g.socket_path.c_str(), g.socket_path.size() + 1);
+    return (int)g.socket_path.size();
+}
+
+}  // extern "C"
