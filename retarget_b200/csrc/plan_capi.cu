@@ -128,7 +128,20 @@ int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const int64_t *d_slot
 }
 
 int grid_for(const rt_plan *pl, int units, bool tma) {
-    long long slots = (long long)pl->sm_count * (tma ? pl->tma_blocks_per_sm : pl->plain_blocks_per_sm);
+    int per_sm = tma ? pl->tma_blocks_per_sm : pl->plain_blocks_per_sm;
+    // RT_CTAS_PER_SM caps the resident CTAs per SM (tuning aid)
+    static const int cap = [] {
+        const char *s = getenv("RT_CTAS_PER_SM");
+        return s ? atoi(s) : 0;
+    }();
+    if (cap > 0 && cap < per_sm) per_sm = cap;
+    // RT_GRID_WAVES launches that many waves of CTAs instead of one (tuning aid)
+    static const int waves = [] {
+        const char *s = getenv("RT_GRID_WAVES");
+        int w = s ? atoi(s) : 0;
+        return w > 0 ? w : 1;
+    }();
+    long long slots = (long long)pl->sm_count * per_sm * (tma ? 1 : waves);
     return (int)(units < slots ? units : slots);
 }
 

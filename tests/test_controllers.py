@@ -1,0 +1,134 @@
+"""The scheduler-facing controllers replayed against logs recorded from the
+reference controllers (same metrics, same clock, same registry): every command
+line, every gate decision and every accounting field must match."""
+import json
+
+import pytest
+
+from retarget_b200 import cache_window as cw
+from retarget_b200 import slot_placement as sp
+from retarget_b200.control import ControlError, UvmStatus
+
+
+class RecordingUvm:
+    def __init__(self, allocations, generation):
+        self.allocs, self.generation, self.commands, self.job = allocations, generation, [], 0
+
+    def _status(self):
+        return UvmStatus(1234, sum(a["bytes"] for a in self.allocs), len(self.allocs), self.generation,
+                         False, self.job, self.job, 0, 0, 0, 0)
+
+    def wait_idle(self, timeout=0):
+        return self._status()
+
+    def _allocation_snapshot(self):
+        return self.generation, [dict(a) for a in self.allocs]
+
+    def command(self, line):
+        self.commands.append(line)
+        self.job += 1
+        return {"ok": True, "job_id": self.job}
+
+    def _wait_job(self, job_id, timeout=0):
+        return self._status()
+
+
+def _strip(result):
+    if result is None:
+        return None
+    result = dict(result)
+    result.pop("audit_plan_committed_monotonic_s", None)
+    result.pop("status", None)
+    return result
+
+
+def test_spec_validation_matches_reference(golden):
+    for kw, message in golden["window"]["rejected"]:
+        with pytest.raises(ValueError) as e:
+            cw.CacheWindowSpec(**kw)
+        assert str(e.value) == message
+    spec = cw.CacheWindowSpec(448790528, 80, 2048)
+    for text, message in golden["window"]["bad_counts"]:
+        with pytest.raises(ValueError) as e:
+            spec.window(float(text))
+        assert str(e.value) == message
+    for name, block in golden["window"]["windows"].items():
+        s = cw.CacheWindowSpec(**block["spec"])
+        for c, want in block["cases"]:
+            assert list(s.window(c)) == want
+    for a, b, want in golden["window"]["interval_difference"]:
+        assert [list(p) for p in cw.interval_difference(tuple(a), tuple(b))] == want
+    for blocks, want in golden["runs"]["encode_mask"]:
+        assert sp.encode_mask(blocks) == want
+    with pytest.raises(ValueError, match="block_tokens"):
+        sp.SlotPlacementSpec(block_tokens=0)
+    with pytest.raises(ValueError, match="refresh_seconds"):
+        sp.SlotPlacementSpec(refresh_seconds=float("inf"))
+
+
+def test_window_controller_replay(golden):
+    for mode, block in golden["window_controller"].items():
+        ctl = cw.CacheWindowController(cw.CacheWindowSpec(**block["spec"]))
+        uvm = RecordingUvm(block["allocations"], block["generation"])
+        for step in block["log"]:
+            note = step.get("note")
+            if note == "signature changed":
+                uvm.allocs = [dict(a, id=a["id"] + 100) for a in block["allocations"]]
+            if note == "layout mismatch":
+                uvm.allocs = block["allocations"][:-3]
+                with pytest.raises(ControlError) as e:
+                    ctl.update(uvm, metrics, 40.0, initial=True)
+                assert str(e.value) == step["error"]
+                continue
+            metrics, now = step["metrics"], step["now"]
+            if step["due"] is not None:
+                assert ctl.due(metrics, now) == step["due"], (mode, now)
+            before = len(uvm.commands)
+            got = ctl.update(uvm, metrics, now, initial=step["initial"])
+            assert uvm.commands[before:] == step["commands"], (mode, now)
+            assert _strip(got) == step["result"], (mode, now)
+            assert (list(ctl.current) if ctl.current else None) == step["current"]
+
+
+def test_placement_controller_replay(golden, tmp_path, monkeypatch):
+    block = golden["placement_controller"]
+    monkeypatch.setenv("RETARGET_SLOT_FEEDBACK_DIR", str(tmp_path))
+    clock = {"now": 0.0}
+
+    class Scripted:
+        @staticmethod
+        def monotonic():
+            return clock["now"]
+    monkeypatch.setattr(sp, "time", Scripted)
+    ctl = sp.SlotPlacementController(cw.CacheWindowSpec(**block["cache_spec"]),
+                                     sp.SlotPlacementSpec(**block["slot_spec"]), block["pid"])
+    n_cache = block["cache_spec"]["allocation_count"]
+    ctl.signature = tuple((a["id"], a["bytes"], a["device"]) for a in block["allocations"][:n_cache])
+    ctl.epoch = 1
+    uvm = RecordingUvm(block["allocations"], block["generation"])
+    keys = ("desired_blocks", "gpu_blocks", "committed_blocks", "requested_gpu_bytes",
+            "requested_cpu_bytes", "feedback_epoch", "allocation_generation")
+    for step in block["log"]:
+        clock["now"] = step["now"]
+        (tmp_path / f"{block['pid']}.json").write_text(json.dumps(step["snapshot"]))
+        metrics = {"sglang:prompt_tokens_total": 0.0, "sglang:generation_tokens_total": 0.0}
+        assert ctl.due(metrics, step["now"]) == step["due"]
+        before = len(uvm.commands)
+        got = ctl.update(uvm, metrics, step["now"])
+        assert uvm.commands[before:] == step["commands"]
+        assert (None if got is None else {k: got[k] for k in keys}) == step["result"]
+        assert {str(k): v[0] for k, v in ctl.committed.items()} == step["committed_versions"]
+    # the same controller fed by a callable instead of the file drop
+    ctl2 = sp.SlotPlacementController(cw.CacheWindowSpec(**block["cache_spec"]),
+                                      sp.SlotPlacementSpec(**block["slot_spec"]), block["pid"],
+                                      snapshot_source=lambda now: block["log"][0]["snapshot"])
+    assert ctl2.choose(ctl2.snapshot(50.0), 50.0) == ([3, 7, 9, 12], [3, 7])
+
+
+def test_budget_rules():
+    with pytest.raises(ValueError, match="KV budget must be divisible by block_tokens"):
+        sp.SlotPlacementController(cw.CacheWindowSpec(16 * 2097152, 4, 2048, 4096, 1024, 1024),
+                                   sp.SlotPlacementSpec(block_tokens=3000), 1, snapshot_source=lambda n: None)
+    with pytest.raises(ValueError, match="slot blocks must be page aligned"):
+        sp.SlotPlacementController(cw.CacheWindowSpec(16 * 2097152, 4, 4, 4096, 1024, 1024),
+                                   sp.SlotPlacementSpec(block_tokens=512), 1, snapshot_source=lambda n: None)
