@@ -9,7 +9,10 @@ namespace rt {
 constexpr int kWords = RT_BITMAP_WORDS;      // 32 x 32 bits = RT_MAX_BLOCKS
 constexpr int kMaxRuns = RT_MAX_BLOCKS / 2;  // alternating bits give the most runs
 constexpr int kScanThreads = 256;
-constexpr int kUnroll = 4;                   // independent 16-byte loads per thread
+#ifndef RT_UNROLL
+#define RT_UNROLL 4
+#endif
+constexpr int kUnroll = RT_UNROLL;                   // independent 16-byte loads per thread
 constexpr int kChunkElems = kScanThreads * 2 * kUnroll;   // 2048 slot ids = 16 KiB
 
 // Per-bitmap accumulation words, filled with atomicOr by the scan.  The tail

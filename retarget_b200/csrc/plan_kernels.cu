@@ -18,6 +18,11 @@
 #include "plan_device.cuh"
 #include "plan_tail.cuh"
 
+// Streaming load of slot ids: read once, never reused.
+#ifndef RT_LOAD
+#define RT_LOAD(ptr) __ldcs(ptr)
+#endif
+
 namespace rt {
 
 // --------------------------------------------------------------------------
@@ -111,7 +116,7 @@ __device__ __forceinline__ void load_chunk(const long long *mine, long long e0, 
         // interior: kUnroll independent, fully coalesced 128-bit loads per thread
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
-            ch.v[u] = __ldcs(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
+            ch.v[u] = RT_LOAD(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
         ch.mask = kAllIds;
     } else {
         ch.mask = 0;
@@ -120,11 +125,11 @@ __device__ __forceinline__ void load_chunk(const long long *mine, long long e0, 
             long long i = e0 + 2 * (u * kScanThreads + (int)threadIdx.x);
             ch.v[u].x = ch.v[u].y = 0;
             if (i >= begin && i < end) {
-                ch.v[u].x = __ldcs(mine + 2 * u * kScanThreads);
+                ch.v[u].x = RT_LOAD(mine + 2 * u * kScanThreads);
                 ch.mask |= 1u << (2 * u);
             }
             if (i + 1 >= begin && i + 1 < end) {
-                ch.v[u].y = __ldcs(mine + 2 * u * kScanThreads + 1);
+                ch.v[u].y = RT_LOAD(mine + 2 * u * kScanThreads + 1);
                 ch.mask |= 2u << (2 * u);
             }
         }
@@ -272,19 +277,19 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
             longlong2 va[kUnroll], vb[kUnroll];
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u)
-                va[u] = __ldcs(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
+                va[u] = RT_LOAD(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
             int left = n_whole;
             while (left >= 2) {
 #pragma unroll
                 for (int u = 0; u < kUnroll; ++u)
-                    vb[u] = __ldcs(reinterpret_cast<const longlong2 *>(mine + kChunkElems + 2 * u * kScanThreads));
+                    vb[u] = RT_LOAD(reinterpret_cast<const longlong2 *>(mine + kChunkElems + 2 * u * kScanThreads));
                 mark_full<kPow2>(va, a, s_map, c);
                 mine += 2 * kChunkElems;
                 left -= 2;
                 if (left > 0) {
 #pragma unroll
                     for (int u = 0; u < kUnroll; ++u)
-                        va[u] = __ldcs(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
+                        va[u] = RT_LOAD(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
                 }
                 mark_full<kPow2>(vb, a, s_map, c);
             }
@@ -359,6 +364,9 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
 #endif
 constexpr int kStages = RT_STAGES;
 constexpr int kStageBytes = kChunkElems * 8;
+// the staging ring is reused as the tail's working memory once streaming is over
+static_assert((size_t)kStages * kStageBytes >= tail_smem_bytes(RT_MAX_GROUPS, RT_MAX_BUFFERS),
+              "staging ring too small to host the plan tail");
 constexpr uint32_t kWaitLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_addr(const void *ptr) {
@@ -500,7 +508,7 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
                             if (idx + 1 >= sp.lo && idx + 1 < end) mask |= 2u << (2 * k);
                         } else if (idx >= sp.lo && idx < end) {
                             // odd last id of the whole array: not part of any 16-byte pair
-                            v[k].x = __ldcs(a.slots + idx);
+                            v[k].x = RT_LOAD(a.slots + idx);
                             mask |= 1u << (2 * k);
                         }
                     }

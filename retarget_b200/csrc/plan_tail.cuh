@@ -73,11 +73,10 @@ struct TailShared {
     uint16_t *stage;             // [kTailWarps][2][kMaxRuns] run begin / end per warp
 };
 
-__host__ __device__ inline size_t tail_smem_bytes(uint32_t n_groups, uint32_t n_buffers) {
-    size_t words = 4 + 4 + kTailWarps + 2 * (size_t)n_groups + (2 * (size_t)n_buffers + 1) +
-                   2 * (size_t)kWords * n_groups;
-    size_t bytes = words * 4 + (size_t)kTailWarps * 2 * kMaxRuns * 2;
-    return (bytes + 15) & ~(size_t)15;
+__host__ __device__ constexpr size_t tail_smem_bytes(uint32_t n_groups, uint32_t n_buffers) {
+    return ((4 + 4 + kTailWarps + 2 * (size_t)n_groups + (2 * (size_t)n_buffers + 1) +
+             2 * (size_t)kWords * n_groups) * 4 +
+            (size_t)kTailWarps * 2 * kMaxRuns * 2 + 15) & ~(size_t)15;
 }
 
 __device__ __forceinline__ TailShared carve_tail(unsigned char *raw, uint32_t n_groups, uint32_t n_buffers) {
