@@ -177,7 +177,9 @@ typedef struct rt_layout {
 
 #define RT_PLAN_EVICT   1u   /* also emit resident-but-not-wanted blocks, CPU-bound, first */
 #define RT_PLAN_DRY_RUN 2u   /* do not commit the wanted set as the new resident set       */
-#define RT_PLAN_NO_TMA  4u   /* stage the slot table with plain 128-bit loads             */
+#define RT_PLAN_TMA     4u   /* stage ids through shared memory with bulk async copies     */
+                             /* (default: register-staged 128-bit loads, which measured    */
+                             /* faster at the sizes a decode step produces)                */
 
 #define RT_RESULT_OVERFLOW   1u   /* more ranges than `cap`; the first cap were written */
 #define RT_RESULT_SLOT_RANGE 2u   /* some slot id was above capacity                    */

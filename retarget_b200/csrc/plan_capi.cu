@@ -146,12 +146,11 @@ int grid_for(const rt_plan *pl, int units, bool tma) {
 }
 
 bool want_tma(uint32_t flags) {
-    if (flags & RT_PLAN_NO_TMA) return false;
-    static const bool env_off = [] {
-        const char *s = getenv("RT_NO_TMA");
+    static const bool env_on = [] {
+        const char *s = getenv("RT_USE_TMA");
         return s && *s == '1';
     }();
-    return !env_off;
+    return (flags & RT_PLAN_TMA) || env_on;
 }
 
 }  // namespace

@@ -577,3 +577,111 @@ int rt_uvm_socket_path(char *out, size_t cap) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// driver-call wrappers for the preload hooks
+// ---------------------------------------------------------------------------
+#include "uvm_server.h"
+
+namespace rt {
+
+CUresult uvm_tracked_alloc(CUdeviceptr *dptr, size_t bytes, unsigned int flags) {
+    const DriverApi *api = driver_api();
+    if (!api || !api->mem_alloc_managed) return CUDA_ERROR_NOT_SUPPORTED;
+    if (!dptr || !bytes) return CUDA_ERROR_INVALID_VALUE;
+    Allocation a = {};
+    std::lock_guard<std::mutex> life(g.life);
+    CUresult result = api->ctx_get_current ? api->ctx_get_current(&a.ctx) : CUDA_ERROR_NOT_SUPPORTED;
+    if (result == CUDA_SUCCESS && !a.ctx) result = CUDA_ERROR_INVALID_CONTEXT;
+    if (result == CUDA_SUCCESS)
+        result = api->ctx_get_device ? api->ctx_get_device(&a.device) : CUDA_ERROR_NOT_SUPPORTED;
+    if (result == CUDA_SUCCESS)
+        result = api->device_get_attribute
+                     ? api->device_get_attribute(&a.concurrent, CU_DEVICE_ATTRIBUTE_CONCURRENT_MANAGED_ACCESS,
+                                                 a.device)
+                     : CUDA_ERROR_NOT_SUPPORTED;
+    {
+        std::lock_guard<std::mutex> st(g.state);
+        if (result == CUDA_SUCCESS && (g.next_id == UINT64_MAX || bytes > UINT64_MAX - g.managed_bytes))
+            result = CUDA_ERROR_OUT_OF_MEMORY;
+    }
+    if (result == CUDA_SUCCESS) result = api->mem_alloc_managed(dptr, bytes, flags);
+    if (result != CUDA_SUCCESS) return result;
+    a.ptr = *dptr;
+    a.bytes = bytes;
+    std::lock_guard<std::mutex> st(g.state);
+    a.id = ++g.next_id;
+    g.allocations.push_back(a);
+    g.managed_bytes += bytes;
+    ++g.generation;
+    return CUDA_SUCCESS;
+}
+
+static uint64_t forget_locked(bool (*match)(const Allocation &, const void *), const void *key) {
+    std::lock_guard<std::mutex> st(g.state);
+    size_t kept = 0;
+    uint64_t removed = 0;
+    for (size_t i = 0; i < g.allocations.size(); ++i) {
+        if (match(g.allocations[i], key)) {
+            g.managed_bytes -= g.allocations[i].bytes;
+            ++removed;
+        } else {
+            g.allocations[kept++] = g.allocations[i];
+        }
+    }
+    g.allocations.resize(kept);
+    if (removed) ++g.generation;
+    return removed;
+}
+
+CUresult uvm_tracked_free(CUdeviceptr dptr) {
+    const DriverApi *api = driver_api();
+    if (!api || !api->mem_free) return CUDA_ERROR_NOT_SUPPORTED;
+    std::lock_guard<std::mutex> life(g.life);
+    CUresult result = api->mem_free(dptr);
+    if (result == CUDA_SUCCESS)
+        forget_locked([](const Allocation &a, const void *k) { return a.ptr == *(const CUdeviceptr *)k; }, &dptr);
+    return result;
+}
+
+CUresult uvm_tracked_ctx_destroy(CUcontext ctx) {
+    const DriverApi *api = driver_api();
+    if (!api || !api->ctx_destroy) return CUDA_ERROR_NOT_SUPPORTED;
+    std::lock_guard<std::mutex> life(g.life);
+    CUresult result = api->ctx_destroy(ctx);
+    if (result == CUDA_SUCCESS && ctx) {
+        forget_locked([](const Allocation &a, const void *k) { return (const void *)a.ctx == k; }, ctx);
+        g.streams.erase(ctx);                // they went away with the context
+    }
+    return result;
+}
+
+CUresult uvm_tracked_primary(CUdevice device, CUresult (*real)(CUdevice), const char *name) {
+    if (!real) return CUDA_ERROR_NOT_SUPPORTED;
+    uint64_t removed = 0;
+    CUresult result;
+    {
+        std::lock_guard<std::mutex> life(g.life);
+        result = real(device);
+        if (result == CUDA_SUCCESS) {
+            removed = forget_locked([](const Allocation &a, const void *k) { return a.device == *(const int *)k; },
+                                    &device);
+            g.streams.clear();
+        }
+    }
+    if (removed)
+        fprintf(stderr,
+                "retarget_b200 UVM: %s succeeded on device %d; conservatively dropped %llu allocation "
+                "records (a release may leave the context alive).\n",
+                name, device, (unsigned long long)removed);
+    return result;
+}
+
+void uvm_fork_child() {
+    // no mutex and no CUDA call is safe here; the path still belongs to the parent
+    if (g.listen_fd >= 0) close(g.listen_fd);
+    if (g.client_fd >= 0) close(g.client_fd);
+    g.listen_fd = g.client_fd = -1;
+}
+
+}  // namespace rt

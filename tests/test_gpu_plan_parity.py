@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 torch = pytest.importorskip("torch")
 
-MODES = [pytest.param(0, id="tma"), pytest.param(capi.RT_PLAN_NO_TMA, id="ld128")]
+MODES = [pytest.param(0, id="ld128"), pytest.param(capi.RT_PLAN_TMA, id="tma")]
 
 
 def random_batch(rng, *, layers, pool_slots, bytes_per_slot, shared, n_req, max_len, budget,
