@@ -263,6 +263,32 @@ int rt_plan_from_bitmaps(rt_plan *plan, const uint32_t *d_want, uint32_t budget,
 /* Waits for everything queued on the plan's own stream. */
 int rt_plan_sync(rt_plan *plan);
 
+/* Scan for callers that must not allocate: no plan handle, no cudaMalloc /
+ * cudaFree or any other allocating call.  (No counterpart in the reference; it
+ * exists for this library's own use inside a serving process, see below.)
+ *
+ * Code that runs inside the preload library cannot allocate device memory
+ * without disturbing what it manages -- the allocation would go through the
+ * library's own cuMemAlloc hook, become a registered managed allocation and
+ * bump the generation that plans are validated against -- and a process whose
+ * device memory belongs entirely to the serving engine's pool has nothing left
+ * to allocate from.  For them the scan's working memory is a static device
+ * array of 8.25 KiB inside the library (held by every GPU that loads it), which
+ * limits a call to RT_STATIC_MAX_GROUPS bitmaps; more is refused with
+ * RT_ERR_CAPACITY.  The number of slot ids is not limited.
+ *
+ * Same result as rt_scan_slots: d_bitmaps gets n_groups x RT_BITMAP_WORDS words,
+ * d_result the counters (blocks_touched, invalid_slots, ignored_slots, flags).
+ * Runs on the calling thread's current device, asynchronously on `stream`
+ * (NULL here is the legacy default stream).  The first call on a device also
+ * looks up the array's device address; make that first call before any stream
+ * capture.  All calls on a device share the array: calls that overlap on the GPU
+ * race, so keep them on one stream or otherwise serialised. */
+#define RT_STATIC_MAX_GROUPS 64u
+int rt_scan_slots_static(const int64_t *d_slots, const int64_t *group_off, uint32_t n_groups,
+                         uint64_t capacity_slots, uint32_t block_tokens, uint32_t n_blocks,
+                         uint32_t *d_bitmaps, rt_plan_result *d_result, void *stream);
+
 /* ------------------------------------------------------------------ */
 /* UVM control server + prefetch executor (process-wide singleton)      */
 /* ------------------------------------------------------------------ */

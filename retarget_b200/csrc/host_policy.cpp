@@ -32,7 +32,7 @@ const char *rt_strerror(int status) {
         case RT_ERR_NO_DEVICE: return "no usable CUDA device (this library has no CPU fallback)";
         case RT_ERR_CUDA: return "CUDA call failed";
         case RT_ERR_OUT_OF_MEMORY: return "out of memory";
-        case RT_ERR_CAPACITY: return "more indices or ranges than the plan was created for";
+        case RT_ERR_CAPACITY: return "more slot ids, ranges or bitmaps than the plan (or the static scratch) can hold";
         case RT_ERR_ALIGNMENT: return "slot array must be 16-byte aligned";
         case RT_ERR_SLOT_RANGE: return "slot beyond capacity";
         case RT_ERR_BUSY: return "busy";
