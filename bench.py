@@ -212,7 +212,7 @@ def run_reference(args):
 # --------------------------------------------------------------------------
 def run_ours(args):
     import torch
-    import torch.distributed as dist
+    from retarget_b200.multirank import Ranks
     from retarget_b200 import capi
     from retarget_b200.planner import DevicePlanner, result_from_tensor
 
@@ -239,8 +239,7 @@ def run_ours(args):
         raise SystemExit("bench.py: no CUDA device; retarget_b200 has no CPU path to fall back to")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    ranks = Ranks("nccl").start(dev)
     flags = capi.RT_PLAN_EVICT | (capi.RT_PLAN_TMA if args.tma else 0)
     planner = DevicePlanner(lay, local, max_indices=max(b.n_idx for b in batches) + 8,
                             max_ranges=1 << 16)
@@ -254,8 +253,7 @@ def run_ours(args):
     K, W = args.steps, args.warmup
 
     def barrier():
-        if world > 1:
-            dist.barrier()
+        ranks.barrier()
         torch.cuda.synchronize()
 
     def device_step(i):
@@ -301,11 +299,11 @@ def run_ours(args):
     e2e_s = (time.perf_counter() - t0) / K
     clocks = sampler.stop() if sampler else None
 
-    t = torch.tensor([total_ms / K, e2e_s * 1e3, statistics.mean(per_launch_ms)],
-                     dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step, e2e_ms, launch_ms = (float(x) for x in t.cpu())
+    ms_per_step, e2e_ms, launch_ms = ranks.max_over_ranks(
+        [total_ms / K, e2e_s * 1e3, statistics.mean(per_launch_ms)])
+    # every rank planned from the same slot table: the plans must agree
+    plan = out_host[:e2e_ranges]          # dst names the rank's own GPU; the rest must agree
+    plans_agree = ranks.same_everywhere(b"".join(plan[k].tobytes() for k in ("buffer", "offset", "bytes")))
 
     if rank == 0:
         peaks_path = ROOT / "MEASURED_PEAKS.json"
@@ -336,13 +334,13 @@ def run_ours(args):
             "slot_scan_gbs_aggregate": world * achieved,
             "plans_per_s_aggregate": world / (ms_per_step * 1e-3),
             "ranges_per_step": n_ranges,
+            "plans_agree_across_ranks": plans_agree,
         }
         if cpu_lines:
             line.update(cpu_lines)
         print(json.dumps(line), flush=True)
     planner.close()
-    if world > 1:
-        dist.destroy_process_group()
+    ranks.stop()
 
 
 # DRAM bytes per launch of the scan kernel from the ncu capture summarised under
