@@ -290,6 +290,64 @@ int rt_scan_slots_static(const int64_t *d_slots, const int64_t *group_off, uint3
                          uint32_t *d_bitmaps, rt_plan_result *d_result, void *stream);
 
 /* ------------------------------------------------------------------ */
+/* Slot-feedback state in GPU memory                                    */
+/* ------------------------------------------------------------------ */
+
+/* Device-resident twin of SlotFeedback (experiments/slot_feedback.py:10-96):
+ * per-slot generation counters, per-block version / last-read / last-write
+ * stamps and the sampled free-list head, updated straight from the serving
+ * engine's device tensors -- no pinned copy, no run encoding on the host, no
+ * JSON file.  Bound to a plan with ONE bitmap (the reference plans one mask for
+ * all allocations); the plan's resident words are the committed set. */
+typedef struct rt_feedback rt_feedback;
+
+int rt_feedback_create(rt_plan *plan, rt_feedback **out);
+int rt_feedback_destroy(rt_feedback *fb);
+
+/* allocator_clear: SlotFeedback.reset, slot_feedback.py:25-33 (also forgets the
+ * committed set, as the controller does on a new epoch, slot_placement.py:123-124). */
+int rt_feedback_reset(rt_feedback *fb, void *stream);
+
+/* alloc event, slot_feedback.py:52-70: generations += 1 per allocated slot,
+ * version = max generation and write stamp for every touched block; the free
+ * head is replaced by d_free_head (first n_free <= 4096 free slots) or, when
+ * d_free_head is NULL, loses the slots just allocated. */
+int rt_feedback_alloc(rt_feedback *fb, const int64_t *d_slots, uint64_t n, const int64_t *d_free_head,
+                      uint32_t n_free, double t, void *stream);
+
+/* attention event, slot_feedback.py:71-75: read stamps, then write stamps. */
+int rt_feedback_attention(rt_feedback *fb, const int64_t *d_read, uint64_t n_read,
+                          const int64_t *d_write, uint64_t n_write, double t, void *stream);
+
+/* Copies the state to the host (any pointer may be NULL): n_blocks versions and
+ * stamps (-inf = never), up to 4096 free-head slot ids.  This is the content of
+ * the snapshot file of slot_feedback.py:86-91 before ranking.  Synchronous. */
+int rt_feedback_snapshot(rt_feedback *fb, int32_t *versions, double *read_seen, double *write_seen,
+                         int64_t *free_head, uint32_t *n_free, uint64_t *epoch,
+                         uint64_t *invalid_slots);
+
+/* experiments/slot_placement.py:18-26, the fields the plan uses. */
+typedef struct rt_feedback_policy {
+    uint32_t budget;                 /* width_tokens / block_tokens, slot_placement.py:60 */
+    uint32_t max_blocks_per_update;
+    uint32_t flags;                  /* RT_PLAN_EVICT */
+    uint32_t reserved;
+    double active_seconds;
+    double refresh_seconds;
+} rt_feedback_policy;
+
+/* Ranks the blocks on the device (active reads, active writes, free-list head,
+ * history by recency; ties by ascending block id), cuts at the budget, keeps
+ * the blocks that are new / re-versioned / due for refresh up to
+ * max_blocks_per_update, commits them and emits their ranges:
+ * publish + target_blocks + choose + encode_mask + blocksv expansion,
+ * slot_feedback.py:81-85, slot_placement.py:37-51,83-94,150-153,
+ * select.cpp:24147-24195.  `at` is the time of the last event (30 s horizon),
+ * `now` the planning time.  Asynchronous on `stream`. */
+int rt_feedback_plan(rt_feedback *fb, const rt_feedback_policy *policy, double at, double now,
+                     rt_range *out, uint32_t cap, rt_plan_result *result, void *stream);
+
+/* ------------------------------------------------------------------ */
 /* UVM control server + prefetch executor (process-wide singleton)      */
 /* ------------------------------------------------------------------ */
 

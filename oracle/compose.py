@@ -144,3 +144,59 @@ def window_step(spec, layout, completed, old, *, full=False, refresh=False, devi
                            full_refresh=refresh and not first)
     ids = {a["id"]: k for k, a in enumerate(reg)}
     return new, [(ids[i], dst, off, n) for i, off, n, dst in got]
+
+
+class FeedbackSession:
+    """The reference's event-driven slot path on the CPU: SlotFeedback state ->
+    publish -> target_blocks -> choose -> blocksv, with the controller's
+    committed bookkeeping (commit time = planning time) and the eviction glue."""
+
+    def __init__(self, layout, spec: rp.SlotSpec, budget: int, *, evict=True, device=0):
+        assert layout.n_groups == 1
+        self.layout, self.spec, self.budget, self.evict, self.device = layout, spec, budget, evict, device
+        self.fb = rp.FeedbackState(block_tokens=layout.block_tokens, publish_seconds=1e18)
+        self.fb.reset(layout.capacity)
+        self.committed = {}
+        self.sequence = 0
+        self.at = -float("inf")
+        self.reg = registry_for(layout, device)
+
+    def _row(self, kind, t, **fields):
+        self.sequence += 1
+        self.at = t
+        return dict(event=kind, monotonic_s=t, sequence=self.sequence, **fields)
+
+    def clear(self, t):
+        self.fb.consume(self._row("allocator_clear", t, allocator_size=self.layout.capacity))
+        self.committed = {}
+
+    def alloc(self, slots, free_head, t):
+        row = self._row("alloc", t, slot_runs=rp.encode_runs(np.asarray(slots).tolist()),
+                        allocator_size=self.layout.capacity)
+        if free_head is not None:
+            row["free_head_runs"] = rp.encode_runs(np.asarray(free_head).tolist())
+        self.fb.consume(row)
+
+    def attention(self, read, write, t):
+        self.fb.consume(self._row("attention", t, read_runs=rp.encode_runs(np.asarray(read).tolist()),
+                                  write_runs=rp.encode_runs(np.asarray(write).tolist())))
+
+    def snapshot(self):
+        return self.fb.publish(self.at)
+
+    def plan(self, now):
+        lay = self.layout
+        snap = self.snapshot()
+        desired, selected = rp.choose(snap, self.spec, self.budget, self.committed, now)
+        evicted = (set(self.committed) - set(desired)) if self.evict else set()
+        self.committed = rp.retain_committed(self.committed, desired, selected, snap["block_versions"], now)
+        out = []
+        for chosen, dst in ((evicted, ux.CPU), (set(selected), self.device)):
+            if not chosen:
+                continue
+            for j in range(lay.n_buffers):
+                got = ux.expand_blocks([dict(self.reg[j])], 0, gen=0, alloc_bytes=lay.alloc_bytes, count=1,
+                                       block_bytes=lay.block_bytes, mask=rp.encode_mask(chosen))
+                out += [(j, dst, off, n) for _, off, n, _ in got]
+        return out, dict(desired=desired, selected=selected, evicted=sorted(evicted),
+                         committed=sorted(self.committed))

@@ -1,0 +1,519 @@
+// Slot-feedback state kept in GPU memory, and the recency-ranked block plan.
+//
+// Stands in for experiments/slot_feedback.py (per-slot generation counters,
+// per-block version / last-read / last-write stamps, free-list head) and for
+// the ranking + selection of experiments/slot_placement.py:37-44,83-94, so that
+// the serving engine's index tensors never leave the device: no pinned copy,
+// no Python loop per slot, no JSON file per 50 ms.
+//
+// One bitmap (the reference plans one mask for all KV allocations).  Events are
+// small (at most a few hundred thousand ids), so these kernels favour simplicity
+// over streaming tricks; the bulk scan of the planner is a different kernel.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <new>
+
+#include "plan_device.cuh"
+#include "plan_tail.cuh"
+#include "rt_internal.h"
+
+namespace rt {
+
+constexpr int kFreeHeadMax = 4096;     // the probe samples the first 4096 free slots
+constexpr int kRankThreads = 1024;     // one thread per block id
+
+struct FeedbackState {
+    int32_t *generations;      // [capacity + 1]
+    int32_t *versions;         // [n_blocks]
+    double *read_seen;         // [n_blocks], -inf = never
+    double *write_seen;        // [n_blocks]
+    int32_t *commit_version;   // [n_blocks], valid where `resident` has the bit
+    double *commit_time;       // [n_blocks]
+    long long *free_head;      // [kFreeHeadMax] slot ids, queue order
+    int32_t *free_count;       // [1]
+    uint32_t *event_blocks;    // [kWords] scratch: blocks touched by the current event
+    uint32_t *slot_marks;      // [(capacity + 32) / 32] scratch: slots of the current alloc event
+    unsigned long long *bad;   // [2] invalid / ignored ids seen so far
+};
+
+struct Geometry {
+    unsigned long long capacity;
+    uint32_t block_tokens;
+    int shift;
+    uint32_t magic, magic_shift;
+    uint32_t n_blocks;
+};
+
+__device__ __forceinline__ uint32_t block_of_slot(uint32_t slot, const Geometry &g) {
+    if (g.shift >= 0) return slot >> g.shift;
+    uint32_t q = __umulhi(slot, g.magic);
+    return (((slot - q) >> 1) + q) >> g.magic_shift;
+}
+
+// ids of one event -> event_blocks words; for allocations also generations[id] += 1
+// (once per occurrence, like `generations[begin:end] += 1` over order-preserving
+// runs) and a mark per slot for the free-head filter.
+__global__ void __launch_bounds__(256)
+feedback_mark_kernel(const long long *ids, long long n, Geometry geo, FeedbackState st, int alloc) {
+    __shared__ uint8_t s_map[RT_MAX_BLOCKS];
+    reinterpret_cast<uint32_t *>(s_map)[threadIdx.x] = 0;
+    __syncthreads();
+    uint32_t invalid = 0, ignored = 0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        long long s = ids[i];
+        if ((unsigned long long)(s - 1) < geo.capacity) {
+            uint32_t v = (uint32_t)s;
+            s_map[block_of_slot(v, geo)] = 1;
+            if (alloc) {
+                atomicAdd(&st.generations[v], 1);
+                atomicOr(&st.slot_marks[v >> 5], 1u << (v & 31));
+            }
+        } else if (s < 1) {
+            if (alloc && s == 0) atomicOr(&st.slot_marks[0], 1u);   // only matters to the free-head filter
+            ++ignored;
+        } else {
+            ++invalid;
+        }
+    }
+    __syncthreads();
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        uint32_t word = warp * 4 + k;
+        uint32_t bits = __ballot_sync(0xffffffffu, s_map[word * 32 + lane] != 0);
+        if (lane == 0 && bits) atomicOr(&st.event_blocks[word], bits);
+    }
+    uint32_t inv = warp_sum(invalid), ign = warp_sum(ignored);
+    if (lane == 0) {
+        if (inv) atomicAdd(&st.bad[0], (unsigned long long)inv);
+        if (ign) atomicAdd(&st.bad[1], (unsigned long long)ign);
+    }
+}
+
+// Stamps the blocks of the current event and clears the event words.
+//   kind 0: read_seen = t        (slot_feedback.py:72-73)
+//   kind 1: write_seen = t       (slot_feedback.py:74-75)
+//   kind 2: versions[b] = max(generations[b*T .. (b+1)*T)), write_seen = t   (:59-62)
+__global__ void __launch_bounds__(256)
+feedback_stamp_kernel(Geometry geo, FeedbackState st, int kind, double t) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t b = warp; b < geo.n_blocks; b += blockDim.x >> 5) {
+        if (!((st.event_blocks[b >> 5] >> (b & 31)) & 1u)) continue;      // uniform over the warp
+        if (kind == 2) {
+            unsigned long long lo = (unsigned long long)b * geo.block_tokens;
+            unsigned long long hi = lo + geo.block_tokens;
+            if (hi > geo.capacity + 1) hi = geo.capacity + 1;
+            int best = 0;
+            for (unsigned long long s = lo + lane; s < hi; s += 32) best = max(best, st.generations[s]);
+            best = __reduce_max_sync(0xffffffffu, best);
+            if (lane == 0) { st.versions[b] = best; st.write_seen[b] = t; }
+        } else if (lane == 0) {
+            (kind == 0 ? st.read_seen : st.write_seen)[b] = t;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < kWords) st.event_blocks[threadIdx.x] = 0;
+}
+
+// Free-list head.  replace = 1: the event carried a fresh head (slot_feedback.py:63-64).
+// replace = 0: drop the slots this event allocated from the known head, keeping the
+// order (slot_feedback.py:65-70).  One CTA; the head is at most 4096 entries.
+__global__ void __launch_bounds__(1024)
+feedback_free_head_kernel(FeedbackState st, const long long *fresh, int n_fresh, int replace,
+                          unsigned long long capacity) {
+    __shared__ int s_warp[32];
+    __shared__ int s_base;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (replace) {
+        int n = n_fresh < kFreeHeadMax ? n_fresh : kFreeHeadMax;
+        for (int i = tid; i < n; i += blockDim.x) st.free_head[i] = fresh[i];
+        if (tid == 0) *st.free_count = n;
+        return;
+    }
+    const int n = *st.free_count;
+    if (tid == 0) s_base = 0;
+    __syncthreads();
+    for (int start = 0; start < n; start += blockDim.x) {
+        int i = start + tid;
+        long long slot = i < n ? st.free_head[i] : 0;
+        bool keep = i < n;
+        if (keep && (unsigned long long)slot <= capacity)
+            keep = !((st.slot_marks[(uint32_t)slot >> 5] >> ((uint32_t)slot & 31)) & 1u);
+        uint32_t mask = __ballot_sync(0xffffffffu, keep);
+        if (lane == 0) s_warp[warp] = __popc(mask);
+        __syncthreads();
+        int before = s_base;
+        for (int w = 0; w < warp; ++w) before += s_warp[w];
+        int pos = before + __popc(mask & ((1u << lane) - 1u));
+        __syncthreads();                       // everyone has read its slot before anyone writes
+        if (keep) st.free_head[pos] = slot;
+        __syncthreads();
+        if (tid == 0) {
+            int total = 0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += s_warp[w];
+            s_base += total;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) *st.free_count = s_base;
+}
+
+// Clears the per-slot marks of an alloc event (second pass over the same ids).
+__global__ void __launch_bounds__(256)
+feedback_unmark_kernel(const long long *ids, long long n, unsigned long long capacity, FeedbackState st) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        long long s = ids[i];
+        if ((unsigned long long)s <= capacity) st.slot_marks[(uint32_t)s >> 5] = 0;
+    }
+}
+
+
+// --------------------------------------------------------------------------
+// ranking + selection: one CTA, one thread per block id
+// --------------------------------------------------------------------------
+struct RankPolicy {
+    uint32_t budget;
+    uint32_t max_blocks;       // max_blocks_per_update
+    uint32_t flags;            // RT_PLAN_EVICT, RT_PLAN_DRY_RUN
+    double at;                 // time of the snapshot (30 s horizon), slot_feedback.py:82-85
+    double now;
+    double commit;             // stamp given to newly committed blocks
+    double active_seconds;
+    double refresh_seconds;
+};
+
+struct RankKey {
+    uint32_t cls;              // 0 active read, 1 active write, 2 free-list head, 3 history, 7 unranked
+    unsigned long long tkey;   // sortable image of -t (0 where time does not matter)
+    uint32_t aux;              // class 2: position in the free head; class 3: 0 read entry, 1 write entry
+};
+
+// Doubles -> unsigned integers with the same order.
+__device__ __forceinline__ unsigned long long ordered_bits(double x) {
+    unsigned long long u = (unsigned long long)__double_as_longlong(x);
+    return (u >> 63) ? ~u : (u | 0x8000000000000000ull);
+}
+
+__device__ __forceinline__ bool key_less(const RankKey &a, uint32_t ia, const RankKey &b, uint32_t ib) {
+    if (a.cls != b.cls) return a.cls < b.cls;
+    if (a.tkey != b.tkey) return a.tkey < b.tkey;
+    if (a.aux != b.aux) return a.aux < b.aux;
+    return ia < ib;
+}
+
+// sets: [0..31] evict words, [32..63] add words (read by the plan tail in
+// explicit mode).  counts: [0] desired [1] added [2] evicted.
+__global__ void __launch_bounds__(kRankThreads)
+feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *resident, uint32_t *sets,
+                     uint32_t *counts) {
+    __shared__ RankKey s_key[kRankThreads];
+    __shared__ uint16_t s_idx[kRankThreads];
+    __shared__ int s_free_pos[kRankThreads];
+    __shared__ uint32_t s_warp[32];
+    __shared__ uint8_t s_sel[kRankThreads], s_des[kRankThreads];
+    const uint32_t b = threadIdx.x, lane = b & 31, warp = b >> 5;
+    s_free_pos[b] = 0x7fffffff;
+    __syncthreads();
+    const int n_free = *st.free_count;
+    for (int i = b; i < n_free; i += kRankThreads) {
+        long long slot = st.free_head[i];
+        if (slot >= 0) {
+            unsigned long long blk = geo.shift >= 0 ? ((unsigned long long)slot >> geo.shift)
+                                                    : ((unsigned long long)slot / geo.block_tokens);
+            if (blk < kRankThreads) atomicMin(&s_free_pos[blk], i);
+        }
+    }
+    __syncthreads();
+    const bool real = b < geo.n_blocks;
+    const double r = real ? st.read_seen[b] : -INFINITY, w = real ? st.write_seen[b] : -INFINITY;
+    const bool recent_r = isfinite(r) && pol.at - r <= 30.0, recent_w = isfinite(w) && pol.at - w <= 30.0;
+    const bool active_r = recent_r && pol.now - r <= pol.active_seconds;
+    const bool active_w = recent_w && pol.now - w <= pol.active_seconds;
+    RankKey k;
+    k.cls = 7; k.tkey = 0; k.aux = 0;
+    if (active_r) { k.cls = 0; k.tkey = ordered_bits(-r); }
+    else if (active_w) { k.cls = 1; k.tkey = ordered_bits(-w); }
+    else if (s_free_pos[b] != 0x7fffffff) { k.cls = 2; k.aux = (uint32_t)s_free_pos[b]; }
+    else if (recent_r || recent_w) {
+        // first of the block's entries in reads+writes sorted by -t (stable: reads first)
+        const bool use_r = recent_r && (!recent_w || r >= w);
+        k.cls = 3; k.tkey = ordered_bits(-(use_r ? r : w)); k.aux = use_r ? 0u : 1u;
+    }
+    s_key[b] = k;
+    s_idx[b] = (uint16_t)b;
+    __syncthreads();
+    // bitonic sort of block ids by key
+    for (uint32_t size = 2; size <= kRankThreads; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            uint32_t partner = b ^ stride;
+            if (partner > b) {
+                uint32_t ia = s_idx[b], ib = s_idx[partner];
+                bool up = (b & size) == 0;
+                bool swap = up ? key_less(s_key[ib], ib, s_key[ia], ia) : key_less(s_key[ia], ia, s_key[ib], ib);
+                if (swap) { s_idx[b] = (uint16_t)ib; s_idx[partner] = (uint16_t)ia; }
+            }
+            __syncthreads();
+        }
+    }
+    // position b of the sorted order holds block `blk`
+    const uint32_t blk = s_idx[b];
+    const RankKey kb = s_key[blk];
+    const bool desired = kb.cls != 7 && b < pol.budget;
+    const bool held = (resident[blk >> 5] >> (blk & 31)) & 1u;
+    bool todo = false;
+    if (desired) {
+        const double rb = st.read_seen[blk], wb = st.write_seen[blk];
+        const bool act = (isfinite(rb) && pol.at - rb <= 30.0 && pol.now - rb <= pol.active_seconds) ||
+                         (isfinite(wb) && pol.at - wb <= 30.0 && pol.now - wb <= pol.active_seconds);
+        todo = !held || st.commit_version[blk] != st.versions[blk] ||
+               (pol.now - st.commit_time[blk] >= pol.refresh_seconds && act);
+    }
+    // first max_blocks of `todo` in rank order
+    uint32_t mask = __ballot_sync(0xffffffffu, todo);
+    if (lane == 0) s_warp[warp] = __popc(mask);
+    __syncthreads();
+    uint32_t before = __popc(mask & ((1u << lane) - 1u));
+    for (uint32_t wv = 0; wv < warp; ++wv) before += s_warp[wv];
+    const bool selected = todo && before < pol.max_blocks;
+    s_sel[blk] = selected;
+    s_des[blk] = desired;
+    if (selected && !(pol.flags & RT_PLAN_DRY_RUN)) {
+        st.commit_version[blk] = st.versions[blk];
+        st.commit_time[blk] = pol.commit;
+    }
+    __syncthreads();
+    // back to block-id order: thread b speaks for block b, warp = bitmap word
+    const bool sel_b = s_sel[b], des_b = s_des[b];
+    const bool held_b = (resident[b >> 5] >> (b & 31)) & 1u;
+    const bool evict_b = (pol.flags & RT_PLAN_EVICT) && held_b && !des_b;
+    const uint32_t add_word = __ballot_sync(0xffffffffu, sel_b);
+    const uint32_t evict_word = __ballot_sync(0xffffffffu, evict_b);
+    const uint32_t keep_word = __ballot_sync(0xffffffffu, (held_b && des_b) || sel_b);
+    const uint32_t des_word = __ballot_sync(0xffffffffu, des_b);
+    __syncthreads();
+    if (lane == 0) {
+        sets[warp] = evict_word;
+        sets[kWords + warp] = add_word;
+        if (!(pol.flags & RT_PLAN_DRY_RUN)) resident[warp] = keep_word;
+        atomicAdd(&counts[0], __popc(des_word));
+        atomicAdd(&counts[1], __popc(add_word));
+        atomicAdd(&counts[2], __popc(evict_word));
+    }
+}
+
+}  // namespace rt
+
+// --------------------------------------------------------------------------
+// C ABI
+// --------------------------------------------------------------------------
+#include "plan_internal.h"
+
+struct rt_feedback {
+    rt_plan *plan = nullptr;
+    rt::PlanView view;
+    rt::Geometry geo;
+    rt::FeedbackState st;
+    uint32_t *d_sets = nullptr;       // [2 * kWords] evict | add
+    uint32_t *d_counts = nullptr;     // [4]
+    uint64_t epoch = 0;
+    void *block = nullptr;            // one allocation behind all state arrays
+    size_t block_bytes = 0;
+};
+
+namespace {
+
+int fb_fail(cudaError_t e) {
+    rt::last_cuda_error_set((int)e);
+    return e == cudaErrorMemoryAllocation ? RT_ERR_OUT_OF_MEMORY : RT_ERR_CUDA;
+}
+#define FB_CUDA(call)                                \
+    do {                                             \
+        cudaError_t e__ = (call);                    \
+        if (e__ != cudaSuccess) return fb_fail(e__); \
+    } while (0)
+
+struct FbDevice {
+    int prev = -1;
+    explicit FbDevice(int d) { cudaGetDevice(&prev); cudaSetDevice(d); }
+    ~FbDevice() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// -inf stamps, zero everything else
+__global__ void feedback_clear_kernel(rt::FeedbackState st, uint32_t n_blocks) {
+    for (uint32_t b = threadIdx.x; b < n_blocks; b += blockDim.x) {
+        st.read_seen[b] = -INFINITY;
+        st.write_seen[b] = -INFINITY;
+        st.commit_time[b] = -INFINITY;
+    }
+}
+
+int clear_state(rt_feedback *fb, cudaStream_t s) {
+    FB_CUDA(cudaMemsetAsync(fb->block, 0, fb->block_bytes, s));
+    feedback_clear_kernel<<<1, 256, 0, s>>>(fb->st, fb->geo.n_blocks);
+    FB_CUDA(cudaGetLastError());
+    FB_CUDA(cudaMemsetAsync(fb->view.d_resident, 0, sizeof(uint32_t) * rt::kWords, s));
+    return RT_OK;
+}
+
+int mark_event(rt_feedback *fb, const int64_t *ids, uint64_t n, int alloc, int kind, double t, cudaStream_t s) {
+    if (n) {
+        long long blocks = ((long long)n + 255) / 256;
+        int grid = (int)(blocks < 1184 ? blocks : 1184);
+        rt::feedback_mark_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const long long *>(ids), (long long)n,
+                                                     fb->geo, fb->st, alloc);
+        FB_CUDA(cudaGetLastError());
+    }
+    rt::feedback_stamp_kernel<<<1, 256, 0, s>>>(fb->geo, fb->st, kind, t);
+    FB_CUDA(cudaGetLastError());
+    return RT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int rt_feedback_create(rt_plan *plan, rt_feedback **out) {
+    if (!plan || !out) return RT_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    rt_feedback *fb = new (std::nothrow) rt_feedback();
+    if (!fb) return RT_ERR_OUT_OF_MEMORY;
+    fb->plan = plan;
+    rt::plan_view(plan, &fb->view);
+    if (fb->view.layout.n_groups != 1) { delete fb; return RT_ERR_INVALID_ARGUMENT; }
+    const uint64_t cap = fb->view.layout.capacity_slots;
+    const uint32_t nb = fb->view.n_blocks;
+    fb->geo = {cap, fb->view.block_tokens, fb->view.shift, fb->view.magic, fb->view.magic_shift, nb};
+    FbDevice guard(fb->view.device);
+    // one allocation, carved into the state arrays (all of it starts at zero)
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t at = off; off += align_up(bytes); return at; };
+    size_t o_gen = take(4 * (cap + 1)), o_ver = take(4 * nb), o_rs = take(8 * nb), o_ws = take(8 * nb),
+           o_cv = take(4 * nb), o_ct = take(8 * nb), o_fh = take(8 * rt::kFreeHeadMax), o_fc = take(4),
+           o_eb = take(4 * rt::kWords), o_sm = take(4 * ((cap + 32) / 32 + 1)), o_bad = take(16),
+           o_sets = take(4 * 2 * rt::kWords), o_cnt = take(16);
+    fb->block_bytes = off;
+    cudaError_t e = cudaMalloc(&fb->block, off);
+    if (e != cudaSuccess) { delete fb; return fb_fail(e); }
+    char *base = static_cast<char *>(fb->block);
+    fb->st.generations = reinterpret_cast<int32_t *>(base + o_gen);
+    fb->st.versions = reinterpret_cast<int32_t *>(base + o_ver);
+    fb->st.read_seen = reinterpret_cast<double *>(base + o_rs);
+    fb->st.write_seen = reinterpret_cast<double *>(base + o_ws);
+    fb->st.commit_version = reinterpret_cast<int32_t *>(base + o_cv);
+    fb->st.commit_time = reinterpret_cast<double *>(base + o_ct);
+    fb->st.free_head = reinterpret_cast<long long *>(base + o_fh);
+    fb->st.free_count = reinterpret_cast<int32_t *>(base + o_fc);
+    fb->st.event_blocks = reinterpret_cast<uint32_t *>(base + o_eb);
+    fb->st.slot_marks = reinterpret_cast<uint32_t *>(base + o_sm);
+    fb->st.bad = reinterpret_cast<unsigned long long *>(base + o_bad);
+    fb->d_sets = reinterpret_cast<uint32_t *>(base + o_sets);
+    fb->d_counts = reinterpret_cast<uint32_t *>(base + o_cnt);
+    int st = clear_state(fb, fb->view.stream);
+    if (st == RT_OK && cudaStreamSynchronize(fb->view.stream) != cudaSuccess) st = RT_ERR_CUDA;
+    if (st != RT_OK) { cudaFree(fb->block); delete fb; return st; }
+    fb->epoch = 1;                      // reset() on the first allocator event, slot_feedback.py:25-33
+    *out = fb;
+    return RT_OK;
+}
+
+int rt_feedback_destroy(rt_feedback *fb) {
+    if (!fb) return RT_OK;
+    FbDevice guard(fb->view.device);
+    cudaStreamSynchronize(fb->view.stream);
+    cudaFree(fb->block);
+    delete fb;
+    return RT_OK;
+}
+
+int rt_feedback_reset(rt_feedback *fb, void *stream) {
+    if (!fb) return RT_ERR_INVALID_ARGUMENT;
+    FbDevice guard(fb->view.device);
+    int st = clear_state(fb, stream ? (cudaStream_t)stream : fb->view.stream);
+    if (st == RT_OK) ++fb->epoch;
+    return st;
+}
+
+int rt_feedback_alloc(rt_feedback *fb, const int64_t *d_slots, uint64_t n, const int64_t *d_free_head,
+                      uint32_t n_free, double t, void *stream) {
+    if (!fb || (!d_slots && n) || (!d_free_head && n_free)) return RT_ERR_INVALID_ARGUMENT;
+    FbDevice guard(fb->view.device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : fb->view.stream;
+    int st = mark_event(fb, d_slots, n, 1, 2, t, s);
+    if (st != RT_OK) return st;
+    rt::feedback_free_head_kernel<<<1, 1024, 0, s>>>(fb->st, reinterpret_cast<const long long *>(d_free_head),
+                                                    (int)n_free, d_free_head != nullptr, fb->geo.capacity);
+    FB_CUDA(cudaGetLastError());
+    if (n) {
+        long long blocks = ((long long)n + 255) / 256;
+        rt::feedback_unmark_kernel<<<(int)(blocks < 1184 ? blocks : 1184), 256, 0, s>>>(
+            reinterpret_cast<const long long *>(d_slots), (long long)n, fb->geo.capacity, fb->st);
+        FB_CUDA(cudaGetLastError());
+    }
+    return RT_OK;
+}
+
+int rt_feedback_attention(rt_feedback *fb, const int64_t *d_read, uint64_t n_read, const int64_t *d_write,
+                          uint64_t n_write, double t, void *stream) {
+    if (!fb || (!d_read && n_read) || (!d_write && n_write)) return RT_ERR_INVALID_ARGUMENT;
+    FbDevice guard(fb->view.device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : fb->view.stream;
+    int st = mark_event(fb, d_read, n_read, 0, 0, t, s);
+    if (st != RT_OK) return st;
+    return mark_event(fb, d_write, n_write, 0, 1, t, s);
+}
+
+int rt_feedback_snapshot(rt_feedback *fb, int32_t *versions, double *read_seen, double *write_seen,
+                         int64_t *free_head, uint32_t *n_free, uint64_t *epoch, uint64_t *invalid_slots) {
+    if (!fb) return RT_ERR_INVALID_ARGUMENT;
+    FbDevice guard(fb->view.device);
+    cudaStream_t s = fb->view.stream;
+    const uint32_t nb = fb->geo.n_blocks;
+    int32_t count = 0;
+    unsigned long long bad[2] = {0, 0};
+    if (versions) FB_CUDA(cudaMemcpyAsync(versions, fb->st.versions, 4 * nb, cudaMemcpyDeviceToHost, s));
+    if (read_seen) FB_CUDA(cudaMemcpyAsync(read_seen, fb->st.read_seen, 8 * nb, cudaMemcpyDeviceToHost, s));
+    if (write_seen) FB_CUDA(cudaMemcpyAsync(write_seen, fb->st.write_seen, 8 * nb, cudaMemcpyDeviceToHost, s));
+    if (free_head)
+        FB_CUDA(cudaMemcpyAsync(free_head, fb->st.free_head, 8 * rt::kFreeHeadMax, cudaMemcpyDeviceToHost, s));
+    FB_CUDA(cudaMemcpyAsync(&count, fb->st.free_count, 4, cudaMemcpyDeviceToHost, s));
+    FB_CUDA(cudaMemcpyAsync(bad, fb->st.bad, 16, cudaMemcpyDeviceToHost, s));
+    FB_CUDA(cudaStreamSynchronize(s));
+    if (n_free) *n_free = (uint32_t)count;
+    if (epoch) *epoch = fb->epoch;
+    if (invalid_slots) *invalid_slots = bad[0];
+    return RT_OK;
+}
+
+int rt_feedback_plan(rt_feedback *fb, const rt_feedback_policy *policy, double at, double now, rt_range *out,
+                     uint32_t cap, rt_plan_result *result, void *stream) {
+    if (!fb || !policy || !result || (!out && cap) || !(policy->active_seconds > 0) ||
+        !(policy->refresh_seconds > 0))
+        return RT_ERR_INVALID_ARGUMENT;
+    FbDevice guard(fb->view.device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : fb->view.stream;
+    rt::RankPolicy pol;
+    pol.budget = policy->budget;
+    pol.max_blocks = policy->max_blocks_per_update;
+    pol.flags = policy->flags;
+    pol.at = at;
+    pol.now = now;
+    pol.commit = now;
+    pol.active_seconds = policy->active_seconds;
+    pol.refresh_seconds = policy->refresh_seconds;
+    FB_CUDA(cudaMemsetAsync(fb->d_counts, 0, 16, s));
+    rt::feedback_rank_kernel<<<1, rt::kRankThreads, 0, s>>>(fb->geo, fb->st, pol, fb->view.d_resident,
+                                                          fb->d_sets, fb->d_counts);
+    FB_CUDA(cudaGetLastError());
+    rt::PlanArgs p;
+    rt::plan_fill_args(fb->plan, p, RT_MAX_BLOCKS, policy->flags | RT_PLAN_DRY_RUN, out, cap, result);
+    p.explicit_sets = 1;
+    FB_CUDA(rt::launch_plan_tail(fb->d_sets, p, s));
+    return RT_OK;
+}
+
+}  // extern "C"

@@ -9,6 +9,7 @@
 
 #include "plan_device.cuh"
 #include "rt_internal.h"
+#include "plan_internal.h"
 
 namespace rt {
 void division_magic(uint32_t d, uint32_t *magic, uint32_t *shift);
@@ -90,6 +91,7 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
     p.flags = flags;
     p.dst_device = pl->layout.dst_device;
     p.scan_only = 0;
+    p.explicit_sets = 0;
     p.alloc_bytes = pl->layout.alloc_bytes;
     p.block_bytes = pl->layout.block_bytes;
 }
@@ -170,6 +172,22 @@ void division_magic(uint32_t d, uint32_t *magic, uint32_t *shift) {
     if (twice >= d) m += 1;
     *magic = (uint32_t)(m + 1);
     *shift = k;
+}
+// What other translation units (the feedback state) need to know about a plan.
+void plan_view(const rt_plan *pl, PlanView *v) {
+    v->layout = pl->layout;
+    v->device = pl->device;
+    v->stream = pl->stream;
+    v->d_resident = pl->d_resident;
+    v->n_blocks = pl->n_blocks;
+    v->block_tokens = pl->block_tokens;
+    v->shift = pl->shift;
+    v->magic = pl->magic;
+    v->magic_shift = pl->magic_shift;
+}
+void plan_fill_args(const rt_plan *pl, PlanArgs &p, uint32_t budget, uint32_t flags, rt_range *out,
+                    uint32_t cap, rt_plan_result *result) {
+    fill_plan_args(pl, p, budget, flags, out, cap, result);
 }
 int last_cuda_error_get() { return g_last_cuda_error; }
 void last_cuda_error_set(int e) { g_last_cuda_error = e; }

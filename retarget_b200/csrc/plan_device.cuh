@@ -60,6 +60,7 @@ struct PlanArgs {
     uint32_t flags;
     int32_t dst_device;
     int scan_only;
+    int explicit_sets;                        // `want` holds [evict | add] words per bitmap
     uint32_t n_units;                         // work units of this launch (scan kernels)
     unsigned long long alloc_bytes;
     unsigned long long block_bytes;

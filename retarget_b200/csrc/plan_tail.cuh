@@ -126,7 +126,7 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
 
     // ---- pass A: one warp per bitmap, one 32-bit word per lane ----
     for (uint32_t g = warp; g < G; g += kTailWarps) {
-        uint32_t raw_w = __ldcg(&want[g * kWords + lane]);
+        uint32_t raw_w = p.explicit_sets ? 0u : __ldcg(&want[g * kWords + lane]);
         uint32_t res = p.scan_only ? 0u : __ldcg(&p.resident[g * kWords + lane]);
         if (consume) want[g * kWords + lane] = 0;
         // bits at or above n_blocks cannot come from valid ids; drop them anyway
@@ -138,6 +138,12 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
         uint32_t evict = 0, add = 0, desired = 0;
         if (p.scan_only) {
             if (p.bitmaps_out) p.bitmaps_out[g * kWords + lane] = raw_w;
+        } else if (p.explicit_sets) {
+            // the caller (the recency ranking) already chose what moves and has
+            // updated the resident words: `want` holds [evict | add] per bitmap
+            evict = __ldcg(&want[(g * 2 + 0) * kWords + lane]);
+            add = __ldcg(&want[(g * 2 + 1) * kWords + lane]);
+            desired = res;
         } else {
             // budget cut: lowest block ids first (one event: every stamp ties, and
             // ties rank by ascending block id)

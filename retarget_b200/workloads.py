@@ -206,6 +206,7 @@ class TraceStep:
     write_slots: np.ndarray    # the slot each live request writes this step
     completed_tokens: int      # cumulative prompt + generated tokens after the step
     live: int
+    free_head: np.ndarray | None = None   # first 4096 free slots, sampled on even steps
 
 
 def decode_trace(seed=0, *, steps=256, pool_slots=65536, arrival_rate=0.5, median=1024,
@@ -250,7 +251,9 @@ def decode_trace(seed=0, *, steps=256, pool_slots=65536, arrival_rate=0.5, media
             alloc_slots=page_slots(new_pages, len(new_pages) * PAGE_SLOTS),
             read_slots=np.concatenate(reads) if reads else np.zeros(0, np.int64),
             write_slots=np.array(writes, dtype=np.int64),
-            completed_tokens=completed, live=len(live)))
+            completed_tokens=completed, live=len(live),
+            free_head=(page_slots(list(pool.free)[:4096 // PAGE_SLOTS], 4096)[:len(pool.free) * PAGE_SLOTS]
+                       if step % 2 == 0 else None)))
         done = [r for r in live if r["left"] <= 0]
         live = [r for r in live if r["left"] > 0]
         for r in done:

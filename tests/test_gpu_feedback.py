@@ -1,0 +1,124 @@
+"""GPU parity for the device-resident slot-feedback state and its recency-ranked
+plan, against the CPU restatement of the reference's event-driven chain
+(SlotFeedback.consume/publish -> target_blocks -> choose -> blocksv) on the
+incremental decode trace: arrivals, one token per live request per step,
+finished requests returning pages to the free list.  Exact equality."""
+import numpy as np
+import pytest
+
+from oracle import compose
+from oracle import ref_policy as rp
+from oracle import uvm_expand as ux
+from retarget_b200 import capi, workloads
+from retarget_b200.feedback import DeviceFeedback
+from retarget_b200.planner import (DevicePlanner, ranges_from_tensor, ranges_to_tuples,
+                                   result_from_tensor)
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def canonical(snapshot):
+    s = dict(snapshot)
+    for key in ("recent_reads", "recent_writes"):
+        s[key] = sorted((-t, b) for b, t in s[key])
+    for key in ("pid", "published_monotonic_s", "sequence"):   # host-side bookkeeping
+        s.pop(key, None)
+    return s
+
+
+def run_trace(layout, trace, *, budget, max_blocks, active, refresh, evict, dt=0.03, clear_at=None):
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    planner = DevicePlanner(layout, 0)
+    fb = DeviceFeedback(planner, pid=0)
+    spec = rp.SlotSpec(block_tokens=layout.block_tokens, max_blocks_per_update=max_blocks,
+                       active_seconds=active, refresh_seconds=refresh)
+    oracle = compose.FeedbackSession(layout, spec, budget, evict=evict)
+    d_out = torch.zeros((1 << 14) * 24, dtype=torch.uint8, device=dev)
+    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
+    flags = capi.RT_PLAN_EVICT if evict else 0
+    h = stream.cuda_stream
+    moved = 0
+    for step, ev in enumerate(trace):
+        t = 100.0 + step * dt
+        if clear_at is not None and step == clear_at:
+            fb.clear(t - 0.004, h)
+            oracle.clear(t - 0.004)
+        if len(ev.alloc_slots):
+            head = None if ev.free_head is None else torch.from_numpy(ev.free_head).to(dev)
+            fb.alloc(torch.from_numpy(ev.alloc_slots).to(dev), t - 0.002, head, h)
+            oracle.alloc(ev.alloc_slots, ev.free_head, t - 0.002)
+        fb.attention(torch.from_numpy(ev.read_slots).to(dev), torch.from_numpy(ev.write_slots).to(dev), t, h)
+        oracle.attention(ev.read_slots, ev.write_slots, t)
+        now = t + 0.001
+        fb.plan(now, budget=budget, max_blocks_per_update=max_blocks, active_seconds=active,
+                refresh_seconds=refresh, flags=flags, d_out=d_out, d_result=d_res, stream=h)
+        want, info = oracle.plan(now)
+        torch.cuda.synchronize()
+        res = result_from_tensor(d_res)
+        got = ranges_to_tuples(ranges_from_tensor(d_out, res["n_ranges"]))
+        assert got == want, f"step {step}: {info}"
+        assert res["blocks_added"] == len(info["selected"]) and res["blocks_evicted"] == len(info["evicted"])
+        assert planner.get_resident()[0] == info["committed"], f"step {step}"
+        moved += len(want)
+        if step % 16 == 0 or step == len(trace) - 1:
+            assert canonical(fb.snapshot()) == canonical(oracle.snapshot()), f"step {step}"
+    assert fb.arrays()[5] == 0
+    fb.close()
+    planner.close()
+    return moved
+
+
+def test_incremental_trace_config():
+    """40 layers, 65,536-slot pool, Poisson arrivals, 25 % budget, every step planned."""
+    layout = workloads.Layout(40, 2048, 65536)
+    trace = workloads.decode_trace(0, steps=256, initial_requests=12)
+    moved = run_trace(layout, trace, budget=16, max_blocks=16, active=2.0, refresh=10.0, evict=True)
+    assert moved > 0
+
+
+def test_reference_update_limits_refresh_and_allocator_clear():
+    """The reference's own policy values (4 new blocks per update), a short
+    refresh period so that due-for-refresh blocks are re-sent, no eviction, and an
+    allocator clear in the middle."""
+    layout = workloads.Layout(4, 2048, 32768)
+    trace = workloads.decode_trace(3, steps=120, pool_slots=32768, arrival_rate=1.0, median=256,
+                                   mean_output=24, initial_requests=6)
+    moved = run_trace(layout, trace, budget=8, max_blocks=4, active=2.0, refresh=0.5, evict=False,
+                      clear_at=70)
+    assert moved > 0
+
+
+def test_small_blocks_wide_bitmap():
+    """1000 blocks of 6 slots: the multiply-shift division and a bitmap that
+    fills every lane of the ranking kernel."""
+    layout = workloads.Layout(2, 2048, 6001, 12288)
+    trace = workloads.decode_trace(5, steps=60, pool_slots=5984, arrival_rate=0.7, median=200,
+                                   mean_output=30, initial_requests=3)
+    moved = run_trace(layout, trace, budget=300, max_blocks=300, active=0.2, refresh=5.0, evict=True)
+    assert moved > 0
+
+
+def test_snapshot_feeds_the_python_controller():
+    """SlotPlacementController driven by DeviceFeedback.snapshot picks the blocks
+    the on-device plan picks."""
+    from retarget_b200.cache_window import CacheWindowSpec
+    from retarget_b200.slot_placement import SlotPlacementController, SlotPlacementSpec
+    dev = torch.device("cuda:0")
+    layout = workloads.Layout(2, 2048, 16384)
+    planner = DevicePlanner(layout, 0)
+    fb = DeviceFeedback(planner, pid=4242)
+    slots = torch.tensor([5, 6, 7, 3000, 3001, 9000, 16000], dtype=torch.int64, device=dev)
+    fb.alloc(slots, 10.0, torch.tensor([2048, 2049, 40], dtype=torch.int64, device=dev))
+    fb.attention(slots[:5], slots[5:6], 10.5)
+    ctl = SlotPlacementController(
+        CacheWindowSpec(layout.alloc_bytes, layout.n_buffers, 2048, 4096, 1024, 1024),
+        SlotPlacementSpec(block_tokens=1024, max_blocks_per_update=4), 4242, snapshot_source=fb.snapshot)
+    snap = ctl.snapshot(10.6)
+    assert snap["free_head_blocks"] == [2, 0] and snap["block_versions"][0] == 1
+    desired, selected = ctl.choose(snap, 10.6)
+    assert desired == [0, 2, 8, 15] and selected == [0, 2, 8, 15]
+    fb.close()
+    planner.close()
