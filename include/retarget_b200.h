@@ -348,6 +348,22 @@ int rt_feedback_plan(rt_feedback *fb, const rt_feedback_policy *policy, double a
                      rt_range *out, uint32_t cap, rt_plan_result *result, void *stream);
 
 /* ------------------------------------------------------------------ */
+/* Synthetic paged KV reader                                            */
+/* ------------------------------------------------------------------ */
+
+/* Reads, for every valid slot id in d_slots, the bytes_per_slot-byte row of
+ * that slot in each of the n_buffers KV buffers (d_buffers: DEVICE array of
+ * n_buffers base pointers) and writes one checksum per buffer (sum of the rows'
+ * 16-bit words) to d_sums.  No reference counterpart: it plays the serving
+ * engine's paged decode attention in the prefetch experiments, so that the same
+ * reads can be timed with the pages on the CPU, on the GPU, or moved there by a
+ * plan.  Runs on the current device, asynchronously on `stream` (NULL: legacy
+ * default stream). */
+int rt_paged_read(const void *const *d_buffers, uint32_t n_buffers, uint32_t bytes_per_slot,
+                  const int64_t *d_slots, uint64_t n_slots, uint64_t capacity_slots,
+                  uint64_t *d_sums, void *stream);
+
+/* ------------------------------------------------------------------ */
 /* UVM control server + prefetch executor (process-wide singleton)      */
 /* ------------------------------------------------------------------ */
 
