@@ -12,7 +12,8 @@ range list each accepted plan produces.  The registry is a list of dicts
 The handler is a ``static`` function of a library that only acts inside a live
 CUDA process, so it cannot be called directly; ``oracle/Makefile`` builds the
 reference library and ``oracle/drive_ref.py`` drives it through its real socket
-under a stub driver to pin this file (see tests/test_oracle_golden.py).
+under a stub driver.  The recorded replies and prefetch calls pin this file
+(tests/test_reference_socket_golden.py).
 """
 from __future__ import annotations
 

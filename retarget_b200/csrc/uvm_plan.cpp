@@ -88,11 +88,13 @@ const char *blocks_plan(const rt_alloc_info *reg, size_t n, uint64_t generation,
     if (matched != count) return "cache_allocation_count_mismatch";
     for (size_t i = 0; i < n; ++i) {
         if (reg[i].bytes != alloc_bytes) continue;
+        // the mask has at most 1024 bits; an allocation may have more blocks than that
+        const uint64_t scan_end = n_blocks < RT_MAX_BLOCKS ? n_blocks : RT_MAX_BLOCKS;
         uint64_t b = 0;
-        while (b < n_blocks) {
+        while (b < scan_end) {
             if (!bits[b]) { ++b; continue; }
             uint64_t e = b;
-            while (e < n_blocks && bits[e]) ++e;
+            while (e < scan_end && bits[e]) ++e;
             // a run that reaches the partial last block ends at the allocation end
             uint64_t end_byte = e > whole ? alloc_bytes : e * block_bytes;
             emit(reg[i], b * block_bytes, end_byte - b * block_bytes, reg[i].device);
