@@ -137,13 +137,7 @@ int grid_for(const rt_plan *pl, int units, bool tma) {
         return s ? atoi(s) : 0;
     }();
     if (cap > 0 && cap < per_sm) per_sm = cap;
-    // RT_GRID_WAVES launches that many waves of CTAs instead of one (tuning aid)
-    static const int waves = [] {
-        const char *s = getenv("RT_GRID_WAVES");
-        int w = s ? atoi(s) : 0;
-        return w > 0 ? w : 1;
-    }();
-    long long slots = (long long)pl->sm_count * per_sm * (tma ? 1 : waves);
+    long long slots = (long long)pl->sm_count * per_sm;
     return (int)(units < slots ? units : slots);
 }
 
