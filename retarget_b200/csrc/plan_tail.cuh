@@ -122,13 +122,27 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
         ignored = __ldcg(&p.global->ignored_slots);
         eflags = __ldcg(&p.global->error_flags);
     }
+    // Stage every bitmap's wanted and resident words in shared memory with ONE
+    // round trip (all loads in flight together); a load per loop iteration of
+    // pass A would cost a dependent L2 round trip per bitmap.
+    for (uint32_t i = tid; i < G * kWords; i += kScanThreads) {
+        const uint32_t g = i / kWords, l = i % kWords;
+        if (p.explicit_sets) {
+            sh.masks[(g * 2 + 0) * kWords + l] = __ldcg(&want[(g * 2 + 0) * kWords + l]);
+            sh.masks[(g * 2 + 1) * kWords + l] = __ldcg(&want[(g * 2 + 1) * kWords + l]);
+        } else {
+            sh.masks[(g * 2 + 0) * kWords + l] = __ldcg(&want[i]);
+            sh.masks[(g * 2 + 1) * kWords + l] = p.scan_only ? 0u : __ldcg(&p.resident[i]);
+            if (consume) want[i] = 0;
+        }
+    }
     cta_sync<kBar, kScanThreads>();
 
     // ---- pass A: one warp per bitmap, one 32-bit word per lane ----
     for (uint32_t g = warp; g < G; g += kTailWarps) {
-        uint32_t raw_w = p.explicit_sets ? 0u : __ldcg(&want[g * kWords + lane]);
-        uint32_t res = p.scan_only ? 0u : __ldcg(&p.resident[g * kWords + lane]);
-        if (consume) want[g * kWords + lane] = 0;
+        uint32_t raw_w = p.explicit_sets ? 0u : sh.masks[(g * 2 + 0) * kWords + lane];
+        uint32_t res = p.explicit_sets ? __ldcg(&p.resident[g * kWords + lane])
+                                       : sh.masks[(g * 2 + 1) * kWords + lane];
         // bits at or above n_blocks cannot come from valid ids; drop them anyway
         const uint32_t lo_bit = lane * 32;
         const uint32_t valid = p.n_blocks >= lo_bit + 32 ? 0xffffffffu
@@ -141,8 +155,8 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
         } else if (p.explicit_sets) {
             // the caller (the recency ranking) already chose what moves and has
             // updated the resident words: `want` holds [evict | add] per bitmap
-            evict = __ldcg(&want[(g * 2 + 0) * kWords + lane]);
-            add = __ldcg(&want[(g * 2 + 1) * kWords + lane]);
+            evict = sh.masks[(g * 2 + 0) * kWords + lane];
+            add = sh.masks[(g * 2 + 1) * kWords + lane];
             desired = res;
         } else {
             // budget cut: lowest block ids first (one event: every stamp ties, and
