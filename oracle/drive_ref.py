@@ -171,7 +171,7 @@ def scenarios():
 
 
 def main():
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    reference = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["RETARGET_REFERENCE"])
     subprocess.run(["make", "-C", str(HERE), "ref", f"REFERENCE={reference}"], check=True, capture_output=True)
     doc = dict(generated_by="oracle/drive_ref.py: unmodified select.cpp driven through its own socket under "
                             "a stub CUDA driver", scenarios=[])

@@ -358,7 +358,7 @@ def placement_controller_vectors(cw, sp, sf, ctl):
 
 
 def main():
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["RETARGET_REFERENCE"])
     cw, sp, sf, ctl, probe = load_reference(root)
     doc = dict(
         generated_by="tests/golden/make_golden.py (unmodified reference modules)",
