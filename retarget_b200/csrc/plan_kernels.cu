@@ -15,6 +15,8 @@
 // it and no tensor-core work.
 #include <cuda_runtime.h>
 
+#include <cstdio>
+
 #include "plan_device.cuh"
 #include "plan_tail.cuh"
 
@@ -24,6 +26,16 @@
 #endif
 
 namespace rt {
+
+#ifdef RT_TRACE
+// Experimental builds only: nanosecond stamps of the phases of one launch.
+__device__ unsigned long long g_trace[4] = {~0ull, 0, 0, 0};
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#endif
 
 // --------------------------------------------------------------------------
 // scan: mark slot ids in the CTA's shared block map
@@ -235,7 +247,13 @@ __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, Ha
     cta_sync<kBar, kScanThreads>();
     if (!hs.last) return;
     __threadfence();
+#ifdef RT_TRACE
+    if (threadIdx.x == 0) g_trace[2] = now_ns();
+#endif
     plan_tail<kBar>(p, &p.groups[0].want[0], true, tail_mem);
+#ifdef RT_TRACE
+    if (threadIdx.x == 0) g_trace[3] = now_ns();
+#endif
 }
 
 // --------------------------------------------------------------------------
@@ -255,6 +273,9 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
     const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
     if (q_begin >= q_end) return;
     ScanCounters c = {0, 0};
+#ifdef RT_TRACE
+    if (threadIdx.x == 0) atomicMin(&g_trace[0], now_ns());
+#endif
     clear_map(s_map);
     __syncthreads();
     for (uint32_t g = first_group(a, q_begin);; ++g) {
@@ -309,6 +330,9 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
         leave_group<0>(p, g, s_map, c);
         if (sp.q_hi >= q_end) break;
     }
+#ifdef RT_TRACE
+    if (threadIdx.x == 0) atomicMax(&g_trace[1], now_ns());
+#endif
     finish_cta<0>(p, (uint32_t)(q_end - q_begin), hs, tail_mem);
 }
 
@@ -560,6 +584,19 @@ cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, i
     } else {
         if (pow2) scan_plan_kernel<true><<<grid, kScanThreads, smem, stream>>>(a, p);
         else scan_plan_kernel<false><<<grid, kScanThreads, smem, stream>>>(a, p);
+#ifdef RT_TRACE
+        {
+            cudaStreamSynchronize(stream);
+            unsigned long long t[4], reset[4] = {~0ull, 0, 0, 0};
+            cudaMemcpyFromSymbol(t, g_trace, sizeof(t));
+            cudaMemcpyToSymbol(g_trace, reset, sizeof(reset));
+            unsigned long long tt[8];
+            cudaMemcpyFromSymbol(tt, g_tail_trace, sizeof(tt));
+            printf("TRACE stream_us=%.2f handover_us=%.2f tail_us=%.2f | stage %.2f passA %.2f prefix %.2f passB %.2f end %.2f\n",
+                   (t[1] - t[0]) / 1e3, (t[2] - t[1]) / 1e3, (t[3] - t[2]) / 1e3, (tt[1] - tt[0]) / 1e3,
+                   (tt[2] - tt[1]) / 1e3, (tt[3] - tt[2]) / 1e3, (tt[4] - tt[3]) / 1e3, (tt[5] - tt[4]) / 1e3);
+        }
+#endif
     }
     return cudaGetLastError();
 }
