@@ -323,7 +323,8 @@ def run_ours(args):
                 "staging": "cp.async.bulk (TMA) -> shared" if args.tma else "ld.global 128-bit, two register sets",
                 "evict": True}),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": PROFILED_TRAFFIC_BYTES,
+                         "frac": achieved / peak,
+                         "traffic": PROFILED_TRAFFIC_BYTES.get((args.workload, bool(args.tma))),
                          "peak_source": peak_src, "algorithmic_bytes_per_launch": bytes_step,
                          "launch_ms": launch_ms, "kernel": "scan_plan_tma_kernel" if args.tma else "scan_plan_kernel"},
             "e2e": {"value": e2e_ms * 1e3, "unit": UNIT,
@@ -343,9 +344,13 @@ def run_ours(args):
     ranks.stop()
 
 
-# DRAM bytes per launch of the scan kernel from the ncu capture summarised under
-# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until captured.
-PROFILED_TRAFFIC_BYTES = 182_585_000   # 178.33 MB read + 4.26 MB written (mean of 3 launches)
+# DRAM bytes per launch of the scan kernel from the ncu captures summarised under
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, mean of 3 launches), keyed by
+# (workload, tma); a configuration that was not captured reports null.
+PROFILED_TRAFFIC_BYTES = {
+    ("target", False): 182_067_000,   # 178.34 MB read + 3.73 MB written
+    ("target", True): 183_275_000,    # 178.34 MB read + 4.94 MB written
+}
 
 
 def main():
