@@ -7,8 +7,12 @@ One step = one placement plan for one decode step of the headline workload:
 40 layers (80 KV buffers of 512 MiB), 256 requests, a 262,144-slot pool, and per
 (layer, request) touched sets of the newest 128 slots plus 2048 Zipf(1.1)
 history draws -- 22.3 M int64 slot ids (178 MB) per step.  Two different
-batches alternate, so every step re-reads more than the L2 holds and every
-plan has real evictions and additions.
+batches alternate, so every step re-reads more than the L2 holds; one lives in
+the lower half of every buffer and one in the upper half, so every plan evicts
+one run and adds one run per buffer (160 ranges per step, the shape of the
+reference's incremental window update).  `variants` reports the same step when
+nothing moves (0 ranges), when the whole budget is replaced in single-block
+runs (6080 ranges) and when the ids are int32.
 
 `value`  device time per step, slot ids already in HBM (CUDA events on the
          launching stream, max over ranks)
@@ -41,10 +45,18 @@ UNIT = "us/step"
 FALLBACK_HBM_GBS = 6650.0
 
 
-def make_workload(name: str, seed: int):
+def make_batches(name: str):
+    """The two batches that alternate in the timed region."""
     from retarget_b200 import workloads
     if name == "target":
-        return workloads.target_step(seed)
+        return list(workloads.target_pair("moving"))
+    if name in ("steady", "fragmented"):
+        return list(workloads.target_pair(name))
+    return [make_workload(name, 0), make_workload(name, 1)]
+
+
+def make_workload(name: str, seed: int):
+    from retarget_b200 import workloads
     if name == "sparse":
         return workloads.sparse_feedback(seed)
     if name == "full_refresh":
@@ -63,7 +75,12 @@ def algorithmic_bytes(batch, n_ranges: int) -> int:
 
 def workload_config(batch, extra=None) -> dict:
     lay = batch.layout
-    cfg = {"workload": batch.name, "layers": lay.layers, "kv_buffers": lay.n_buffers,
+    name = batch.name
+    for tag, text in ((", lower half", ", steps alternate between the lower and upper half of every buffer"),
+                      (", even blocks", ", steps alternate between even and odd blocks")):
+        if name.endswith(tag):
+            name = name[:-len(tag)] + text
+    cfg = {"workload": name, "layers": lay.layers, "kv_buffers": lay.n_buffers,
            "alloc_bytes": lay.alloc_bytes, "pool_slots": lay.pool_slots,
            "bytes_per_slot": lay.bytes_per_slot, "uvm_block_bytes": lay.block_bytes,
            "bitmaps": lay.n_groups, "blocks_per_bitmap": lay.n_blocks,
@@ -186,7 +203,7 @@ def run_reference(args):
     """The reference arm: CPU only, rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    batches = [make_workload(args.workload, 0), make_workload(args.workload, 1)]
+    batches = make_batches(args.workload)
     cores = os.cpu_count() or 1
     L = batches[0].layout.n_groups
     sample = min(L, max(1, cores))
@@ -204,7 +221,7 @@ def run_reference(args):
                              "sample": sample_text},
             "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # --------------------------------------------------------------------------
@@ -219,7 +236,7 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    batches = [make_workload(args.workload, 0), make_workload(args.workload, 1)]
+    batches = make_batches(args.workload)
     lay = batches[0].layout
     # CPU baseline first: its worker processes are forked before CUDA is initialised
     cpu_lines = {}
@@ -282,6 +299,44 @@ def run_ours(args):
     if last["flags"]:
         raise SystemExit(f"bench.py: planner reported flags {last['flags']}")
 
+    # the same step under other conditions (headline workload, one GPU only)
+    variants = {}
+    if args.workload == "target" and world == 1 and not args.no_variants:
+        def timed(slot_tensors, pair, n=50):
+            def one(i):
+                planner.step_device(slot_tensors[i % 2], pair[i % 2].group_off,
+                                    pair[i % 2].budget_blocks, flags, d_out, d_res, stream.cuda_stream)
+            for i in range(4):
+                one(i)
+            torch.cuda.synchronize()
+            t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            t[0].record(stream)
+            for i in range(n):
+                one(i)
+            t[1].record(stream)
+            torch.cuda.synchronize()
+            r = result_from_tensor(d_res)
+            if r["flags"]:
+                raise SystemExit(f"bench.py: planner reported flags {r['flags']}")
+            return t[0].elapsed_time(t[1]) * 1e3 / n, r["n_ranges"], n
+
+        from retarget_b200 import workloads
+        for kind in ("steady", "fragmented"):
+            pair = workloads.target_pair(kind)
+            tensors = [torch.from_numpy(b.slots).to(dev) for b in pair]
+            us, nr, n = timed(tensors, pair)
+            variants[kind] = {"us_per_step": us, "ranges_per_step": nr, "steps": n,
+                              "gbs": algorithmic_bytes(pair[0], nr) / us / 1e3}
+            del tensors
+        tensors = [torch.from_numpy(b.slots.astype(np.int32)).to(dev) for b in batches]
+        us, nr, n = timed(tensors, batches)
+        variants["int32_ids"] = {"us_per_step": us, "ranges_per_step": nr, "steps": n,
+                                 "gbs": (algorithmic_bytes(batches[0], nr) - 4 * batches[0].n_idx) / us / 1e3}
+        del tensors
+        for i in range(2):      # leave the resident state as the main workload left it
+            device_step(W + K + i)
+        torch.cuda.synchronize()
+
     # end to end through the host-buffer call: pinned ids -> device -> plan -> ranges on the host
     out_host = np.empty(1 << 16, dtype=capi.RANGE_DTYPE)
     e2e_ranges = 0
@@ -337,9 +392,11 @@ def run_ours(args):
             "ranges_per_step": n_ranges,
             "plans_agree_across_ranks": plans_agree,
         }
+        if variants:
+            line["variants"] = variants
         if cpu_lines:
             line.update(cpu_lines)
-        print(json.dumps(line), flush=True)
+        emit(line)
     planner.close()
     ranks.stop()
 
@@ -353,6 +410,28 @@ PROFILED_TRAFFIC_BYTES = {
 }
 
 
+# Libraries under us (NCCL's version banner, for one) write to stdout.  The
+# result line must be the only thing there: everything else goes to stderr.
+_RESULT_FD = None
+
+
+def quiet_stdout():
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict):
+    text = json.dumps(line) + "\n"
+    if _RESULT_FD is None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_RESULT_FD, text.encode())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -360,11 +439,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="target",
-                    choices=["target", "sparse", "full_refresh", "tp_shard"])
+                    choices=["target", "steady", "fragmented", "sparse", "full_refresh", "tp_shard"])
     ap.add_argument("--tma", action="store_true", help="stage ids with bulk async copies (TMA)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-variants", action="store_true", help="skip the secondary measurements")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    quiet_stdout()
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -253,6 +253,27 @@ int rt_plan_step_table(rt_plan *plan, const int64_t *d_table, const int32_t *d_l
 int rt_scan_slots(rt_plan *plan, const int64_t *d_slots, const int64_t *group_off,
                   uint32_t *d_bitmaps, rt_plan_result *result, void *stream);
 
+/* The same four calls for 32-bit slot ids, the width the serving engine itself
+ * keeps them in (its kv_indices and req_to_token tensors are int32; the probe
+ * copies whatever dtype it is handed, kv_audit_probe.py:66-71, and widens the
+ * ids to Python ints with tolist() at :92).  Reading the engine's tensors in
+ * place halves the bytes per id.  Results are identical to the int64 calls on
+ * the same ids.  A negative id is ignored like any id below 1
+ * (slot_feedback.py:39); capacity_slots must not exceed 2^31 - 1
+ * (RT_ERR_INVALID_ARGUMENT).  RT_PLAN_TMA has no effect here: the bulk-copy
+ * kernel reads int64 ids only.  Pointers are 16-byte aligned as above. */
+int rt_plan_step_device_i32(rt_plan *plan, const int32_t *d_slots, const int64_t *group_off,
+                            uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                            rt_plan_result *result, void *stream);
+int rt_plan_step_i32(rt_plan *plan, const int32_t *h_slots, const int64_t *group_off,
+                     uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                     rt_plan_result *result);
+int rt_plan_step_table_i32(rt_plan *plan, const int32_t *d_table, const int32_t *d_lens,
+                           uint32_t n_rows, uint64_t stride, uint32_t budget, uint32_t flags,
+                           rt_range *out, uint32_t cap, rt_plan_result *result, void *stream);
+int rt_scan_slots_i32(rt_plan *plan, const int32_t *d_slots, const int64_t *group_off,
+                      uint32_t *d_bitmaps, rt_plan_result *result, void *stream);
+
 /* Diff + budget + coalesce only, from wanted bitmaps already on the device.
  * With the resident set holding the old window and d_want the new one this
  * yields the windowv symmetric difference (select.cpp:24231-24240) for

@@ -33,8 +33,10 @@ RT_RESULT_SLOT_RANGE = 2
 RT_RESULT_TIMEOUT = 4
 
 RT_OK = 0
+RT_ERR_INVALID_ARGUMENT = -1
 RT_ERR_NO_DEVICE = -2
 RT_ERR_CAPACITY = -5
+RT_ERR_ALIGNMENT = -6
 RT_ERR_SLOT_RANGE = -7
 RT_ERR_PLAN = -11
 RT_ERR_SPEC_POSITIVE = -20
@@ -133,6 +135,15 @@ def _load():
                                          C.c_void_p]),
         "rt_scan_slots": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_void_p]),
+        "rt_plan_step_device_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
+                                              C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]),
+        "rt_plan_step_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
+                                       C.c_void_p, C.c_uint32, C.c_void_p]),
+        "rt_plan_step_table_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64,
+                                             C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p,
+                                             C.c_void_p]),
+        "rt_scan_slots_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_void_p]),
         "rt_plan_from_bitmaps": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p,
                                            C.c_uint32, C.c_void_p, C.c_void_p]),
         "rt_plan_sync": (C.c_int, [C.c_void_p]),

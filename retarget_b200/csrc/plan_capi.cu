@@ -13,7 +13,7 @@
 
 namespace rt {
 void division_magic(uint32_t d, uint32_t *magic, uint32_t *shift);
-cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, int grid,
+cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, bool ids32, int grid,
                              cudaStream_t stream);
 cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid, cudaStream_t stream);
 cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream_t stream);
@@ -35,7 +35,7 @@ struct rt_plan {
     rt::GroupScratch *d_groups = nullptr;
     rt::GlobalScratch *d_global = nullptr;
     uint32_t *d_resident = nullptr;
-    uint8_t buffer_group[RT_MAX_BUFFERS] = {0};
+    uint8_t *d_buffer_group = nullptr;  // bitmap of every buffer, registry order
     long long *d_stage = nullptr;      // host-buffer call: slot ids land here
     uint64_t max_indices = 0;
     rt_range *h_out = nullptr;         // pinned + mapped: the kernel writes ranges here
@@ -78,7 +78,7 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
     p.groups = pl->d_groups;
     p.global = pl->d_global;
     p.resident = pl->d_resident;
-    memcpy(p.buffer_group, pl->buffer_group, sizeof(p.buffer_group));
+    p.buffer_group = pl->d_buffer_group;
     p.n_units = 0;
     p.bitmaps_out = nullptr;
     p.out = out;
@@ -98,9 +98,16 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
 
 // CSR work-unit table.  Every group gets at least one unit so that its tail
 // runs even when it has no ids this step.
-int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const int64_t *d_slots,
-                       const int64_t *group_off) {
+// ids of one 16-byte load and of one 16 KiB work unit, by id width
+inline long long ids_per_vec(bool ids32) { return ids32 ? 4 : 2; }
+inline long long ids_per_unit(bool ids32) { return ids32 ? 2 * rt::kChunkElems : rt::kChunkElems; }
+
+int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const void *d_slots,
+                       const int64_t *group_off, bool ids32) {
     const uint32_t G = pl->layout.n_groups;
+    // int32 ids: a negative id must never look like a valid large one
+    if (ids32 && pl->layout.capacity_slots > 0x7fffffffull) return RT_ERR_INVALID_ARGUMENT;
+    const long long per_vec = ids_per_vec(ids32), per_unit = ids_per_unit(ids32);
     a.slots = reinterpret_cast<const long long *>(d_slots);
     a.lens = nullptr;
     a.stride = 0;
@@ -117,8 +124,8 @@ int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const int64_t *d_slot
         if (lo < 0 || hi < lo) return RT_ERR_INVALID_ARGUMENT;
         a.group_off[g] = lo;
         a.unit_first[g] = (int)units;
-        long long span = hi - (lo & ~1LL);
-        long long n = (span + rt::kChunkElems - 1) / rt::kChunkElems;
+        long long span = hi - (lo & ~(per_vec - 1));
+        long long n = (span + per_unit - 1) / per_unit;
         units += n > 0 ? n : 1;
         if (units > 0x7fffffffLL) return RT_ERR_CAPACITY;
     }
@@ -248,8 +255,13 @@ int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, ui
         size_t rbytes = sizeof(uint32_t) * rt::kWords * L.n_groups;
         if ((e = cudaMalloc(&pl->d_resident, rbytes))) { fail(e); break; }
         if ((e = cudaMemset(pl->d_resident, 0, rbytes))) { fail(e); break; }
-        if (L.buffer_group)
-            for (uint32_t j = 0; j < L.n_buffers; ++j) pl->buffer_group[j] = (uint8_t)L.buffer_group[j];
+        {
+            uint8_t table[RT_MAX_BUFFERS] = {0};
+            if (L.buffer_group)
+                for (uint32_t j = 0; j < L.n_buffers; ++j) table[j] = (uint8_t)L.buffer_group[j];
+            if ((e = cudaMalloc(&pl->d_buffer_group, L.n_buffers))) { fail(e); break; }
+            if ((e = cudaMemcpy(pl->d_buffer_group, table, L.n_buffers, cudaMemcpyHostToDevice))) { fail(e); break; }
+        }
         if (max_indices) {
             // +2 ids of slack so a 16-byte load at the very end stays in bounds
             if ((e = cudaMalloc(&pl->d_stage, sizeof(long long) * (max_indices + 2)))) { fail(e); break; }
@@ -277,6 +289,7 @@ int rt_plan_destroy(rt_plan *pl) {
     cudaFree(pl->d_groups);
     cudaFree(pl->d_global);
     cudaFree(pl->d_resident);
+    cudaFree(pl->d_buffer_group);
     cudaFree(pl->d_stage);
     if (pl->h_out) cudaFreeHost(pl->h_out);
     if (pl->h_result) cudaFreeHost(pl->h_result);
@@ -302,38 +315,44 @@ int rt_plan_get_resident(rt_plan *pl, uint32_t *words) {
     return RT_OK;
 }
 
-int rt_plan_step_device(rt_plan *pl, const int64_t *d_slots, const int64_t *group_off,
-                        uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
-                        rt_plan_result *result, void *stream) {
+}  // extern "C"
+
+namespace {
+
+int step_device_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t *group_off,
+                     uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                     rt_plan_result *result, void *stream) {
     if (!pl || !group_off || !result || (!out && cap)) return RT_ERR_INVALID_ARGUMENT;
     if (!d_slots && group_off[pl->layout.n_groups] > 0) return RT_ERR_INVALID_ARGUMENT;
     DeviceGuard guard(pl->device);
     rt::ScanArgs a;
-    int st = fill_scan_args_csr(pl, a, d_slots, group_off);
+    int st = fill_scan_args_csr(pl, a, d_slots, group_off, ids32);
     if (st != RT_OK) return st;
     rt::PlanArgs p;
     fill_plan_args(pl, p, budget, flags, out, cap, result);
     p.n_units = (uint32_t)a.n_units;
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
-    bool tma = want_tma(flags);
+    bool tma = !ids32 && want_tma(flags);      // the bulk-copy kernel reads int64 ids only
     int grid = grid_for(pl, a.n_units, tma);
-    RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s) : rt::launch_scan_plan(a, p, false, grid, s));
+    RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s)
+                : rt::launch_scan_plan(a, p, false, ids32, grid, s));
     return RT_OK;
 }
 
-int rt_plan_step(rt_plan *pl, const int64_t *h_slots, const int64_t *group_off, uint32_t budget,
-                 uint32_t flags, rt_range *out, uint32_t cap, rt_plan_result *result) {
+int step_host_impl(rt_plan *pl, const void *h_slots, bool ids32, const int64_t *group_off,
+                   uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                   rt_plan_result *result) {
     if (!pl || !group_off || !result || (!out && cap)) return RT_ERR_INVALID_ARGUMENT;
     const uint32_t G = pl->layout.n_groups;
     int64_t n = group_off[G];
     if (n < 0 || (uint64_t)n > pl->max_indices || group_off[0] < 0) return RT_ERR_CAPACITY;
     if (n && !h_slots) return RT_ERR_INVALID_ARGUMENT;
     DeviceGuard guard(pl->device);
-    if (n) RT_CUDA(cudaMemcpyAsync(pl->d_stage, h_slots, sizeof(long long) * (size_t)n,
+    if (n) RT_CUDA(cudaMemcpyAsync(pl->d_stage, h_slots, (ids32 ? 4 : 8) * (size_t)n,
                                    cudaMemcpyHostToDevice, pl->stream));
     uint32_t dev_cap = cap < pl->max_ranges ? cap : pl->max_ranges;
-    int st = rt_plan_step_device(pl, reinterpret_cast<const int64_t *>(pl->d_stage), group_off, budget,
-                                 flags, pl->h_out, dev_cap, pl->h_result, pl->stream);
+    int st = step_device_impl(pl, pl->d_stage, ids32, group_off, budget, flags, pl->h_out, dev_cap,
+                              pl->h_result, pl->stream);
     if (st != RT_OK) return st;
     RT_CUDA(cudaStreamSynchronize(pl->stream));
     *result = *pl->h_result;
@@ -344,11 +363,12 @@ int rt_plan_step(rt_plan *pl, const int64_t *h_slots, const int64_t *group_off, 
     return RT_OK;
 }
 
-int rt_plan_step_table(rt_plan *pl, const int64_t *d_table, const int32_t *d_lens, uint32_t n_rows,
-                       uint64_t stride, uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
-                       rt_plan_result *result, void *stream) {
+int step_table_impl(rt_plan *pl, const void *d_table, bool ids32, const int32_t *d_lens,
+                    uint32_t n_rows, uint64_t stride, uint32_t budget, uint32_t flags, rt_range *out,
+                    uint32_t cap, rt_plan_result *result, void *stream) {
     if (!pl || !result || (!out && cap) || pl->layout.n_groups != 1) return RT_ERR_INVALID_ARGUMENT;
     if (!n_rows || !stride || !d_table || !d_lens) return RT_ERR_INVALID_ARGUMENT;
+    if (ids32 && pl->layout.capacity_slots > 0x7fffffffull) return RT_ERR_INVALID_ARGUMENT;
     if (reinterpret_cast<uintptr_t>(d_table) & 15u) return RT_ERR_ALIGNMENT;
     DeviceGuard guard(pl->device);
     rt::ScanArgs a;
@@ -356,8 +376,10 @@ int rt_plan_step_table(rt_plan *pl, const int64_t *d_table, const int32_t *d_len
     a.slots = reinterpret_cast<const long long *>(d_table);
     a.lens = d_lens;
     a.stride = (long long)stride;
-    // a row may start on an odd index: one more unit covers the shifted tail
-    long long per_row = ((long long)stride + 1 + rt::kChunkElems - 1) / rt::kChunkElems;
+    // a row may start off a 16-byte boundary: the units of a row cover the ids
+    // from the boundary below its start
+    const long long per_unit = ids_per_unit(ids32);
+    long long per_row = ((long long)stride + (ids_per_vec(ids32) - 1) + per_unit - 1) / per_unit;
     long long units = per_row * n_rows;
     if (units > 0x7fffffffLL) return RT_ERR_CAPACITY;
     a.units_per_row = (int)per_row;
@@ -372,16 +394,17 @@ int rt_plan_step_table(rt_plan *pl, const int64_t *d_table, const int32_t *d_len
     fill_plan_args(pl, p, budget, flags, out, cap, result);
     p.n_units = (uint32_t)a.n_units;
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
-    RT_CUDA(rt::launch_scan_plan(a, p, true, grid_for(pl, a.n_units, false), s));
+    RT_CUDA(rt::launch_scan_plan(a, p, true, ids32, grid_for(pl, a.n_units, false), s));
     return RT_OK;
 }
 
-int rt_scan_slots(rt_plan *pl, const int64_t *d_slots, const int64_t *group_off, uint32_t *d_bitmaps,
-                  rt_plan_result *result, void *stream) {
+int scan_slots_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t *group_off,
+                    uint32_t *d_bitmaps, rt_plan_result *result, void *stream) {
     if (!pl || !group_off || !result || !d_bitmaps) return RT_ERR_INVALID_ARGUMENT;
+    if (!d_slots && group_off[pl->layout.n_groups] > 0) return RT_ERR_INVALID_ARGUMENT;
     DeviceGuard guard(pl->device);
     rt::ScanArgs a;
-    int st = fill_scan_args_csr(pl, a, d_slots, group_off);
+    int st = fill_scan_args_csr(pl, a, d_slots, group_off, ids32);
     if (st != RT_OK) return st;
     rt::PlanArgs p;
     fill_plan_args(pl, p, 0, 0, nullptr, 0, result);
@@ -389,10 +412,61 @@ int rt_scan_slots(rt_plan *pl, const int64_t *d_slots, const int64_t *group_off,
     p.scan_only = 1;
     p.bitmaps_out = d_bitmaps;
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
-    bool tma = want_tma(0);
+    bool tma = !ids32 && want_tma(0);
     int grid = grid_for(pl, a.n_units, tma);
-    RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s) : rt::launch_scan_plan(a, p, false, grid, s));
+    RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s)
+                : rt::launch_scan_plan(a, p, false, ids32, grid, s));
     return RT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int rt_plan_step_device(rt_plan *pl, const int64_t *d_slots, const int64_t *group_off,
+                        uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                        rt_plan_result *result, void *stream) {
+    return step_device_impl(pl, d_slots, false, group_off, budget, flags, out, cap, result, stream);
+}
+
+int rt_plan_step_device_i32(rt_plan *pl, const int32_t *d_slots, const int64_t *group_off,
+                            uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                            rt_plan_result *result, void *stream) {
+    return step_device_impl(pl, d_slots, true, group_off, budget, flags, out, cap, result, stream);
+}
+
+int rt_plan_step(rt_plan *pl, const int64_t *h_slots, const int64_t *group_off, uint32_t budget,
+                 uint32_t flags, rt_range *out, uint32_t cap, rt_plan_result *result) {
+    return step_host_impl(pl, h_slots, false, group_off, budget, flags, out, cap, result);
+}
+
+int rt_plan_step_i32(rt_plan *pl, const int32_t *h_slots, const int64_t *group_off, uint32_t budget,
+                     uint32_t flags, rt_range *out, uint32_t cap, rt_plan_result *result) {
+    return step_host_impl(pl, h_slots, true, group_off, budget, flags, out, cap, result);
+}
+
+int rt_plan_step_table(rt_plan *pl, const int64_t *d_table, const int32_t *d_lens, uint32_t n_rows,
+                       uint64_t stride, uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
+                       rt_plan_result *result, void *stream) {
+    return step_table_impl(pl, d_table, false, d_lens, n_rows, stride, budget, flags, out, cap, result,
+                           stream);
+}
+
+int rt_plan_step_table_i32(rt_plan *pl, const int32_t *d_table, const int32_t *d_lens, uint32_t n_rows,
+                           uint64_t stride, uint32_t budget, uint32_t flags, rt_range *out,
+                           uint32_t cap, rt_plan_result *result, void *stream) {
+    return step_table_impl(pl, d_table, true, d_lens, n_rows, stride, budget, flags, out, cap, result,
+                           stream);
+}
+
+int rt_scan_slots(rt_plan *pl, const int64_t *d_slots, const int64_t *group_off, uint32_t *d_bitmaps,
+                  rt_plan_result *result, void *stream) {
+    return scan_slots_impl(pl, d_slots, false, group_off, d_bitmaps, result, stream);
+}
+
+int rt_scan_slots_i32(rt_plan *pl, const int32_t *d_slots, const int64_t *group_off,
+                      uint32_t *d_bitmaps, rt_plan_result *result, void *stream) {
+    return scan_slots_impl(pl, d_slots, true, group_off, d_bitmaps, result, stream);
 }
 
 int rt_plan_from_bitmaps(rt_plan *pl, const uint32_t *d_want, uint32_t budget, uint32_t flags,

@@ -7,7 +7,7 @@
 namespace rt {
 
 constexpr int kWords = RT_BITMAP_WORDS;      // 32 x 32 bits = RT_MAX_BLOCKS
-constexpr int kMaxRuns = RT_MAX_BLOCKS / 2;  // alternating bits give the most runs
+
 constexpr int kScanThreads = 256;
 #ifndef RT_UNROLL
 #define RT_UNROLL 4
@@ -28,7 +28,7 @@ struct GlobalScratch {
     uint32_t error_flags;
 };
 
-// Kernel arguments, passed by value (about 1.7 KiB + 1.1 KiB): no per-step upload.
+// Kernel arguments, passed by value (about 1.7 KiB + 0.1 KiB): no per-step upload.
 struct ScanArgs {
     const long long *slots;
     const int *lens;                          // table mode: valid ids per row
@@ -64,7 +64,7 @@ struct PlanArgs {
     uint32_t n_units;                         // work units of this launch (scan kernels)
     unsigned long long alloc_bytes;
     unsigned long long block_bytes;
-    uint8_t buffer_group[RT_MAX_BUFFERS];     // bitmap of every buffer, registry order
+    const uint8_t *buffer_group;              // device: bitmap of every buffer, registry order
 };
 
 }  // namespace rt

@@ -71,87 +71,128 @@ __device__ __forceinline__ void mark_slot(long long s, const ScanArgs &a, uint8_
     else ++c.invalid;
 }
 
-constexpr uint32_t kAllIds = (1u << (2 * kUnroll)) - 1u;
+// Slot ids arrive as int64 (the CSR tables the planner was first written for)
+// or as int32 (the serving engine's own kv_indices / req_to_token tensors).  A
+// thread always loads 16 bytes at a time: two or four ids.
+template <typename Id> struct IdTraits;
+template <> struct IdTraits<long long> {
+    using Vec = longlong2;
+    static constexpr int kPer = 2;
+};
+template <> struct IdTraits<int> {
+    using Vec = int4;
+    static constexpr int kPer = 4;
+};
+// ids of one work unit (16 KiB): 2048 int64 or 4096 int32
+template <typename Id>
+constexpr int kChunkIds = kScanThreads * IdTraits<Id>::kPer * kUnroll;
+static_assert(kChunkIds<long long> == kChunkElems, "unit size mismatch");
+template <typename Id>
+constexpr uint32_t kAllIdsOf = (1u << (IdTraits<Id>::kPer * kUnroll)) - 1u;
+constexpr uint32_t kAllIds = kAllIdsOf<long long>;
 
-// 2*kUnroll ids held as kUnroll 16-byte pairs, all of them real ids.
-template <bool kPow2>
-__device__ __forceinline__ void mark_full(const longlong2 (&v)[kUnroll], const ScanArgs &a,
+__device__ __forceinline__ long long vec_get(const longlong2 &v, int k) { return k ? v.y : v.x; }
+__device__ __forceinline__ int vec_get(const int4 &v, int k) {
+    return k == 0 ? v.x : k == 1 ? v.y : k == 2 ? v.z : v.w;
+}
+__device__ __forceinline__ void vec_set(longlong2 &v, int k, long long x) { (k ? v.y : v.x) = x; }
+__device__ __forceinline__ void vec_set(int4 &v, int k, int x) {
+    (k == 0 ? v.x : k == 1 ? v.y : k == 2 ? v.z : v.w) = x;
+}
+template <typename Vec> struct VecIds;
+template <> struct VecIds<longlong2> { static constexpr int kPer = 2; };
+template <> struct VecIds<int4> { static constexpr int kPer = 4; };
+
+// Folds one 16-byte vector into the batch test: OR of the high words (int64
+// only) and the largest (id - 1) as an unsigned 32-bit number -- an id of 0, and
+// every negative int32, wraps to a value no capacity reaches.
+__device__ __forceinline__ void batch_test(const longlong2 &v, uint32_t &hi_or, uint32_t &worst) {
+    hi_or |= (uint32_t)((unsigned long long)v.x >> 32) | (uint32_t)((unsigned long long)v.y >> 32);
+    worst = max(worst, max((uint32_t)v.x - 1u, (uint32_t)v.y - 1u));
+}
+__device__ __forceinline__ void batch_test(const int4 &v, uint32_t &hi_or, uint32_t &worst) {
+    worst = max(max(worst, max((uint32_t)v.x - 1u, (uint32_t)v.y - 1u)),
+                max((uint32_t)v.z - 1u, (uint32_t)v.w - 1u));
+}
+
+// kUnroll 16-byte vectors, all of them real ids.
+template <bool kPow2, typename Vec>
+__device__ __forceinline__ void mark_full(const Vec (&v)[kUnroll], const ScanArgs &a,
                                           uint8_t *s_map, ScanCounters &c) {
+    constexpr int kPer = VecIds<Vec>::kPer;
     // Fast path: one test for the whole batch.  Every id must be 1..capacity
-    // (< 2^32): the high words are OR-ed, and the largest (id - 1) -- an id of 0
-    // wraps to 2^32 - 1 -- is compared with the capacity once.  Then the stores
-    // run unconditionally.
+    // (< 2^32); then the stores run unconditionally.
     uint32_t hi_or = 0, worst = 0;
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-        hi_or |= (uint32_t)((unsigned long long)v[u].x >> 32) | (uint32_t)((unsigned long long)v[u].y >> 32);
-        worst = max(worst, max((uint32_t)v[u].x - 1u, (uint32_t)v[u].y - 1u));
-    }
+    for (int u = 0; u < kUnroll; ++u) batch_test(v[u], hi_or, worst);
     if (hi_or == 0 && worst < (uint32_t)a.capacity) {
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            s_map[block_of<kPow2>((uint32_t)v[u].x, a)] = 1;
-            s_map[block_of<kPow2>((uint32_t)v[u].y, a)] = 1;
-        }
+        for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+            for (int k = 0; k < kPer; ++k) s_map[block_of<kPow2>((uint32_t)vec_get(v[u], k), a)] = 1;
         return;
     }
     // some id is 0, negative or above capacity: classify each one exactly
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-        mark_slot<kPow2>(v[u].x, a, s_map, c);
-        mark_slot<kPow2>(v[u].y, a, s_map, c);
-    }
-}
-
-// Same with a validity mask: bit 2u / 2u+1 says whether v[u].x / v[u].y is real.
-template <bool kPow2>
-__device__ __forceinline__ void mark_masked(const longlong2 (&v)[kUnroll], uint32_t mask,
-                                            const ScanArgs &a, uint8_t *s_map, ScanCounters &c) {
+    for (int u = 0; u < kUnroll; ++u)
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-        if (mask & (1u << (2 * u))) mark_slot<kPow2>(v[u].x, a, s_map, c);
-        if (mask & (2u << (2 * u))) mark_slot<kPow2>(v[u].y, a, s_map, c);
-    }
+        for (int k = 0; k < kPer; ++k) mark_slot<kPow2>((long long)vec_get(v[u], k), a, s_map, c);
 }
 
-// One work unit as registers: kChunkElems ids starting at the even index e0, of
-// which [begin, end) belong to the unit's group.
+// Same with a validity mask: bit kPer*u + k says whether id k of v[u] is real.
+template <bool kPow2, typename Vec>
+__device__ __forceinline__ void mark_masked(const Vec (&v)[kUnroll], uint32_t mask,
+                                            const ScanArgs &a, uint8_t *s_map, ScanCounters &c) {
+    constexpr int kPer = VecIds<Vec>::kPer;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+        for (int k = 0; k < kPer; ++k)
+            if (mask & (1u << (kPer * u + k))) mark_slot<kPow2>((long long)vec_get(v[u], k), a, s_map, c);
+}
+
+// One work unit as registers: kChunkIds ids starting at the 16-byte aligned
+// index e0, of which [begin, end) belong to the unit's group.
+template <typename Id>
 struct Chunk {
-    longlong2 v[kUnroll];
+    typename IdTraits<Id>::Vec v[kUnroll];
     uint32_t mask;
 };
 
-// `mine` points at this thread's first pair of the unit (slots + e0 + 2*tid).
-__device__ __forceinline__ void load_chunk(const long long *mine, long long e0, long long begin,
-                                           long long end, Chunk &ch) {
-    if (e0 >= begin && e0 + kChunkElems <= end) {
+// `mine` points at this thread's first vector of the unit (slots + e0 + kPer*tid).
+template <typename Id>
+__device__ __forceinline__ void load_chunk(const Id *mine, long long e0, long long begin,
+                                           long long end, Chunk<Id> &ch) {
+    using Vec = typename IdTraits<Id>::Vec;
+    constexpr int kPer = IdTraits<Id>::kPer;
+    if (e0 >= begin && e0 + kChunkIds<Id> <= end) {
         // interior: kUnroll independent, fully coalesced 128-bit loads per thread
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
-            ch.v[u] = RT_LOAD(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
-        ch.mask = kAllIds;
+            ch.v[u] = RT_LOAD(reinterpret_cast<const Vec *>(mine + kPer * u * kScanThreads));
+        ch.mask = kAllIdsOf<Id>;
     } else {
         ch.mask = 0;
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            long long i = e0 + 2 * (u * kScanThreads + (int)threadIdx.x);
-            ch.v[u].x = ch.v[u].y = 0;
-            if (i >= begin && i < end) {
-                ch.v[u].x = RT_LOAD(mine + 2 * u * kScanThreads);
-                ch.mask |= 1u << (2 * u);
-            }
-            if (i + 1 >= begin && i + 1 < end) {
-                ch.v[u].y = RT_LOAD(mine + 2 * u * kScanThreads + 1);
-                ch.mask |= 2u << (2 * u);
+            const long long i = e0 + kPer * (u * kScanThreads + (int)threadIdx.x);
+#pragma unroll
+            for (int k = 0; k < kPer; ++k) {
+                Id x = 0;
+                if (i + k >= begin && i + k < end) {
+                    x = RT_LOAD(mine + kPer * u * kScanThreads + k);
+                    ch.mask |= 1u << (kPer * u + k);
+                }
+                vec_set(ch.v[u], k, x);
             }
         }
     }
 }
 
-template <bool kPow2>
-__device__ __forceinline__ void mark_chunk(const Chunk &ch, const ScanArgs &a, uint8_t *s_map,
+template <bool kPow2, typename Id>
+__device__ __forceinline__ void mark_chunk(const Chunk<Id> &ch, const ScanArgs &a, uint8_t *s_map,
                                            ScanCounters &c) {
-    if (ch.mask == kAllIds) mark_full<kPow2>(ch.v, a, s_map, c);
+    if (ch.mask == kAllIdsOf<Id>) mark_full<kPow2>(ch.v, a, s_map, c);
     else mark_masked<kPow2>(ch.v, ch.mask, a, s_map, c);
 }
 
@@ -163,6 +204,7 @@ struct GroupSpan {
     long long e0;            // even start index of unit q_lo
 };
 
+template <typename Id = long long>
 __device__ __forceinline__ GroupSpan group_span(const ScanArgs &a, uint32_t g, int q_begin, int q_end) {
     GroupSpan s;
     const int uf = a.unit_first[g], ul = a.unit_first[g + 1];
@@ -171,7 +213,7 @@ __device__ __forceinline__ GroupSpan group_span(const ScanArgs &a, uint32_t g, i
     s.units_in_group = ul - uf;
     s.lo = a.group_off[g];
     s.hi = a.group_off[g + 1];
-    s.e0 = (s.lo & ~1LL) + (long long)(s.q_lo - uf) * kChunkElems;
+    s.e0 = (s.lo & ~(long long)(IdTraits<Id>::kPer - 1)) + (long long)(s.q_lo - uf) * kChunkIds<Id>;
     return s;
 }
 
@@ -263,15 +305,19 @@ __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, Ha
 // keeps its shared block map across the units of a bitmap and hands over once
 // per (CTA, bitmap).  Inside a bitmap the next unit's loads are issued before
 // the current unit is marked.
-template <bool kPow2>
+template <bool kPow2, typename Id>
 __global__ void __launch_bounds__(kScanThreads)
 scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
+    using Vec = typename IdTraits<Id>::Vec;
+    constexpr int kPer = IdTraits<Id>::kPer;
+    constexpr int kChunk = kChunkIds<Id>;
     extern __shared__ __align__(16) unsigned char tail_mem[];
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
     const int q_begin = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
     const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
     if (q_begin >= q_end) return;
+    const Id *slots = reinterpret_cast<const Id *>(a.slots);
     ScanCounters c = {0, 0};
 #ifdef RT_TRACE
     if (threadIdx.x == 0) atomicMin(&g_trace[0], now_ns());
@@ -279,53 +325,53 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
     clear_map(s_map);
     __syncthreads();
     for (uint32_t g = first_group(a, q_begin);; ++g) {
-        const GroupSpan sp = group_span(a, g, q_begin, q_end);
+        const GroupSpan sp = group_span<Id>(a, g, q_begin, q_end);
         int q = sp.q_lo;
         long long e0 = sp.e0;
-        const long long *mine = a.slots + e0 + 2 * (int)threadIdx.x;
-        // ragged first unit of the bitmap (odd start index)
+        const Id *mine = slots + e0 + kPer * (int)threadIdx.x;
+        // ragged first unit of the bitmap (start index not on a 16-byte boundary)
         if (q < sp.q_hi && e0 < sp.lo) {
-            Chunk ch;
-            load_chunk(mine, e0, sp.lo, sp.hi, ch);
-            mark_chunk<kPow2>(ch, a, s_map, c);
-            ++q; e0 += kChunkElems; mine += kChunkElems;
+            Chunk<Id> ch;
+            load_chunk<Id>(mine, e0, sp.lo, sp.hi, ch);
+            mark_chunk<kPow2, Id>(ch, a, s_map, c);
+            ++q; e0 += kChunk; mine += kChunk;
         }
         // whole units: two register sets alternate, so the loads of one unit are
         // in flight while the other is marked, with no copies between them
-        int n_whole = (int)((sp.hi - e0) / kChunkElems);
+        int n_whole = (int)((sp.hi - e0) / kChunk);
         if (n_whole > sp.q_hi - q) n_whole = sp.q_hi - q;
         if (n_whole > 0) {
-            longlong2 va[kUnroll], vb[kUnroll];
+            Vec va[kUnroll], vb[kUnroll];
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u)
-                va[u] = RT_LOAD(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
+                va[u] = RT_LOAD(reinterpret_cast<const Vec *>(mine + kPer * u * kScanThreads));
             int left = n_whole;
             while (left >= 2) {
 #pragma unroll
                 for (int u = 0; u < kUnroll; ++u)
-                    vb[u] = RT_LOAD(reinterpret_cast<const longlong2 *>(mine + kChunkElems + 2 * u * kScanThreads));
+                    vb[u] = RT_LOAD(reinterpret_cast<const Vec *>(mine + kChunk + kPer * u * kScanThreads));
                 mark_full<kPow2>(va, a, s_map, c);
-                mine += 2 * kChunkElems;
+                mine += 2 * kChunk;
                 left -= 2;
                 if (left > 0) {
 #pragma unroll
                     for (int u = 0; u < kUnroll; ++u)
-                        va[u] = RT_LOAD(reinterpret_cast<const longlong2 *>(mine + 2 * u * kScanThreads));
+                        va[u] = RT_LOAD(reinterpret_cast<const Vec *>(mine + kPer * u * kScanThreads));
                 }
                 mark_full<kPow2>(vb, a, s_map, c);
             }
             if (left == 1) {
                 mark_full<kPow2>(va, a, s_map, c);
-                mine += kChunkElems;
+                mine += kChunk;
             }
             q += n_whole;
-            e0 += (long long)n_whole * kChunkElems;
+            e0 += (long long)n_whole * kChunk;
         }
         // ragged last unit
         if (q < sp.q_hi) {
-            Chunk ch;
-            load_chunk(mine, e0, sp.lo, sp.hi, ch);
-            mark_chunk<kPow2>(ch, a, s_map, c);
+            Chunk<Id> ch;
+            load_chunk<Id>(mine, e0, sp.lo, sp.hi, ch);
+            mark_chunk<kPow2, Id>(ch, a, s_map, c);
         }
         leave_group<0>(p, g, s_map, c);
         if (sp.q_hi >= q_end) break;
@@ -341,13 +387,15 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
 // --------------------------------------------------------------------------
 // Rows are ragged, so work units are dealt round-robin; all ids belong to
 // bitmap 0 and the CTA hands over once.
-template <bool kPow2>
+template <bool kPow2, typename Id>
 __global__ void __launch_bounds__(kScanThreads)
 scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
+    constexpr int kPer = IdTraits<Id>::kPer;
     extern __shared__ __align__(16) unsigned char tail_mem[];
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
     if ((int)blockIdx.x >= a.n_units) return;
+    const Id *slots = reinterpret_cast<const Id *>(a.slots);
     ScanCounters c = {0, 0};
     clear_map(s_map);
     __syncthreads();
@@ -358,12 +406,12 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
         if (len < 0) len = 0;
         if (len > a.stride) len = a.stride;
         const long long lo = (long long)row * a.stride, hi = lo + len;
-        const long long e0 = (lo & ~1LL) + (long long)k * kChunkElems;
+        const long long e0 = (lo & ~(long long)(kPer - 1)) + (long long)k * kChunkIds<Id>;
         ++units;
         if (e0 >= hi) continue;                                  // past the row's valid ids
-        Chunk ch;
-        load_chunk(a.slots + e0 + 2 * (int)threadIdx.x, e0, lo, hi, ch);
-        mark_chunk<kPow2>(ch, a, s_map, c);
+        Chunk<Id> ch;
+        load_chunk<Id>(slots + e0 + kPer * (int)threadIdx.x, e0, lo, hi, ch);
+        mark_chunk<kPow2, Id>(ch, a, s_map, c);
     }
     leave_group<0>(p, 0, s_map, c);
     finish_cta<0>(p, units, hs, tail_mem);
@@ -574,16 +622,24 @@ plan_tail_kernel(uint32_t *want, const __grid_constant__ PlanArgs p) {
 // --------------------------------------------------------------------------
 // host-side launchers (called from the C ABI)
 // --------------------------------------------------------------------------
-cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, int grid,
+cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, bool ids32, int grid,
                              cudaStream_t stream) {
     const bool pow2 = a.shift >= 0;
     const size_t smem = tail_smem_bytes(p.n_groups, p.n_buffers);
     if (table) {
-        if (pow2) scan_table_kernel<true><<<grid, kScanThreads, smem, stream>>>(a, p);
-        else scan_table_kernel<false><<<grid, kScanThreads, smem, stream>>>(a, p);
+        if (ids32) {
+            if (pow2) scan_table_kernel<true, int><<<grid, kScanThreads, smem, stream>>>(a, p);
+            else scan_table_kernel<false, int><<<grid, kScanThreads, smem, stream>>>(a, p);
+        } else {
+            if (pow2) scan_table_kernel<true, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
+            else scan_table_kernel<false, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
+        }
+    } else if (ids32) {
+        if (pow2) scan_plan_kernel<true, int><<<grid, kScanThreads, smem, stream>>>(a, p);
+        else scan_plan_kernel<false, int><<<grid, kScanThreads, smem, stream>>>(a, p);
     } else {
-        if (pow2) scan_plan_kernel<true><<<grid, kScanThreads, smem, stream>>>(a, p);
-        else scan_plan_kernel<false><<<grid, kScanThreads, smem, stream>>>(a, p);
+        if (pow2) scan_plan_kernel<true, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
+        else scan_plan_kernel<false, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
 #ifdef RT_TRACE
         {
             cudaStreamSynchronize(stream);
@@ -592,9 +648,11 @@ cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, i
             cudaMemcpyToSymbol(g_trace, reset, sizeof(reset));
             unsigned long long tt[8];
             cudaMemcpyFromSymbol(tt, g_tail_trace, sizeof(tt));
-            printf("TRACE stream_us=%.2f handover_us=%.2f tail_us=%.2f | stage %.2f passA %.2f prefix %.2f passB %.2f end %.2f\n",
-                   (t[1] - t[0]) / 1e3, (t[2] - t[1]) / 1e3, (t[3] - t[2]) / 1e3, (tt[1] - tt[0]) / 1e3,
-                   (tt[2] - tt[1]) / 1e3, (tt[3] - tt[2]) / 1e3, (tt[4] - tt[3]) / 1e3, (tt[5] - tt[4]) / 1e3);
+            printf("TRACE stream_us=%.2f handover_us=%.2f tail_us=%.2f | table %.2f loads %.2f passA %.2f sync %.2f "
+                   "prefix %.2f passB %.2f end %.2f\n",
+                   (t[1] - t[0]) / 1e3, (t[2] - t[1]) / 1e3, (t[3] - t[2]) / 1e3, (tt[6] - tt[0]) / 1e3,
+                   (tt[7] - tt[6]) / 1e3, (tt[1] - tt[7]) / 1e3, (tt[2] - tt[1]) / 1e3, (tt[3] - tt[2]) / 1e3,
+                   (tt[4] - tt[3]) / 1e3, (tt[5] - tt[4]) / 1e3);
         }
 #endif
     }
@@ -628,13 +686,17 @@ cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plai
         return e;
     RT_SET_SMEM(scan_plan_tma_kernel<true>, tma)
     RT_SET_SMEM(scan_plan_tma_kernel<false>, tma)
-    RT_SET_SMEM(scan_plan_kernel<true>, tail)
-    RT_SET_SMEM(scan_plan_kernel<false>, tail)
-    RT_SET_SMEM(scan_table_kernel<true>, tail)
-    RT_SET_SMEM(scan_table_kernel<false>, tail)
+    RT_SET_SMEM((scan_plan_kernel<true, long long>), tail)
+    RT_SET_SMEM((scan_plan_kernel<false, long long>), tail)
+    RT_SET_SMEM((scan_plan_kernel<true, int>), tail)
+    RT_SET_SMEM((scan_plan_kernel<false, int>), tail)
+    RT_SET_SMEM((scan_table_kernel<true, long long>), tail)
+    RT_SET_SMEM((scan_table_kernel<false, long long>), tail)
+    RT_SET_SMEM((scan_table_kernel<true, int>), tail)
+    RT_SET_SMEM((scan_table_kernel<false, int>), tail)
     RT_SET_SMEM(plan_tail_kernel, tail)
 #undef RT_SET_SMEM
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(plain_blocks_per_sm, scan_plan_kernel<true>,
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(plain_blocks_per_sm, scan_plan_kernel<true, long long>,
                                                       kScanThreads, tail);
     if (e != cudaSuccess) return e;
     return cudaOccupancyMaxActiveBlocksPerMultiprocessor(tma_blocks_per_sm, scan_plan_tma_kernel<true>,

@@ -1,9 +1,11 @@
 // Plan tail: wanted bitmaps -> budget cut -> diff against the resident set ->
 // coalesced byte ranges in queue order.  Runs in ONE CTA (the one that retired
-// the last scan unit, or the single CTA of the bitmap-only kernel) and is laid
-// out to keep dependent global round trips off the critical path: one parallel
-// load of every bitmap's wanted + resident words, everything else in shared
-// memory, then the range stores.
+// the last scan unit, or the single CTA of the bitmap-only kernel).  One CTA is
+// latency bound -- about eleven cycles per instruction per warp in measurement,
+// whatever the instruction -- so the design goal is the shortest dependent
+// instruction chain: one global round trip for every bitmap's words, one thread
+// per mask word with warp shuffles for everything that crosses words, then one
+// thread per (phase, buffer) for the range stores.
 #pragma once
 #include "plan_device.cuh"
 
@@ -15,7 +17,7 @@ static __device__ unsigned long long g_tail_trace[8];
     do {                                                                         \
         if (threadIdx.x == 0) {                                                  \
             unsigned long long t__;                                              \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));             \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__)::"memory");   \
             g_tail_trace[k] = t__;                                               \
         }                                                                        \
     } while (0)
@@ -39,17 +41,23 @@ __device__ __forceinline__ uint32_t warp_sum(uint32_t v) {
     return __reduce_add_sync(0xffffffffu, v);
 }
 
-// Lowest `k` set bits of x: binary search for the shortest low mask that holds
-// k set bits (six steps of popc; __fns is emulated in software and much slower).
+__device__ __forceinline__ unsigned long long warp_sum64(unsigned long long v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+
+// Lowest `k` set bits of x.  The answer keeps the low `pos` bits of x, pos the
+// largest width whose low bits hold at most k set bits: five unrolled steps of
+// popc (a loop costs compares and branches on the tail's critical path; __fns
+// is emulated in software and much slower).
 __device__ __forceinline__ uint32_t lowest_bits(uint32_t x, uint32_t k) {
     if (k >= (uint32_t)__popc(x)) return x;
-    uint32_t lo = 0, hi = 32;                        // mask width
-    while (lo < hi) {
-        uint32_t mid = (lo + hi) >> 1;
-        uint32_t have = __popc(x & (mid >= 32 ? 0xffffffffu : ((1u << mid) - 1u)));
-        if (have >= k) hi = mid; else lo = mid + 1;
-    }
-    return x & (lo >= 32 ? 0xffffffffu : ((1u << lo) - 1u));
+    uint32_t pos = 0;
+#pragma unroll
+    for (uint32_t s = 16; s >= 1; s >>= 1)
+        if ((uint32_t)__popc(x & ((1u << (pos + s)) - 1u)) <= k) pos += s;
+    return x & ((1u << pos) - 1u);
 }
 
 // --------------------------------------------------------------------------
@@ -81,47 +89,49 @@ __device__ __forceinline__ bool cta_or(bool pred) {
 // shared-memory layout of the tail (carved from a raw, 16-byte aligned buffer)
 // --------------------------------------------------------------------------
 constexpr int kTailWarps = kScanThreads / 32;
-// Words per bitmap in the tail's shared staging: [evict|want][add|resident] plus
-// one word of padding, so that thread-per-bitmap accesses fall in different banks.
-constexpr uint32_t kMaskStride = 2 * kWords + 1;
+// Words per bitmap in the tail's shared staging:
+//   [0, kWords)          evict words
+//   [kWords, 2*kWords)   add words
+//   [2*kWords, 3*kWords) per word, the number of runs that start in lower words:
+//                        low half = evict runs, high half = add runs
+// plus one word of padding, so that threads working on different bitmaps and
+// the same word index fall in different banks.
+constexpr uint32_t kMaskStride = 3 * kWords + 1;
 
 struct TailShared {
-    unsigned long long *bytes;   // [2]   CPU-bound / GPU-bound byte totals
-    uint32_t *stats;             // [8]   touched, desired, added, evicted, [4] = some bitmap has runs
-    uint32_t *warp_tot;          // [kTailWarps]
-    uint32_t *counts;            // [n_groups][2]        runs per (bitmap, phase)
-    uint32_t *off;               // [2*n_buffers + 1]    first range of every (phase, buffer)
-    uint32_t *masks;             // [n_groups][kMaskStride] evict / add words
-    uint16_t *stage;             // [kTailWarps][2][kMaxRuns] run begin / end per warp
+    unsigned long long *warp_bytes;  // [kTailWarps][2]  CPU-bound / GPU-bound bytes per warp
+    uint32_t *warp_stats;            // [kTailWarps][4]  touched, desired, added, evicted per warp
+    uint32_t *counts;                // [n_groups][2]        runs per (bitmap, phase)
+    uint32_t *off;                   // [2*n_buffers + 1]    first range of every (phase, buffer)
+    uint32_t *masks;                 // [n_groups][kMaskStride]
+    uint8_t *group_of;               // [n_buffers]          bitmap of every buffer
 };
 
 __host__ __device__ constexpr size_t tail_smem_bytes(uint32_t n_groups, uint32_t n_buffers) {
-    return ((4 + 8 + kTailWarps + 2 * (size_t)n_groups + (2 * (size_t)n_buffers + 1) +
-             (size_t)kMaskStride * n_groups) * 4 +
-            (size_t)kTailWarps * 2 * kMaxRuns * 2 + 15) & ~(size_t)15;
+    return ((4 * kTailWarps + 4 * kTailWarps + 2 * (size_t)n_groups +
+             (2 * (size_t)n_buffers + 1) + (size_t)kMaskStride * n_groups) * 4 +
+            (size_t)n_buffers + 15) & ~(size_t)15;
 }
 
 __device__ __forceinline__ TailShared carve_tail(unsigned char *raw, uint32_t n_groups, uint32_t n_buffers) {
     TailShared s;
     uint32_t *w = reinterpret_cast<uint32_t *>(raw);
-    s.bytes = reinterpret_cast<unsigned long long *>(w);  w += 4;
-    s.stats = w;                                           w += 8;
-    s.warp_tot = w;                                        w += kTailWarps;
-    s.counts = w;                                          w += 2 * n_groups;
-    s.off = w;                                             w += 2 * n_buffers + 1;
-    s.masks = w;                                           w += kMaskStride * n_groups;
-    s.stage = reinterpret_cast<uint16_t *>(w);
+    s.warp_bytes = reinterpret_cast<unsigned long long *>(w);  w += 4 * kTailWarps;
+    s.warp_stats = w;                                          w += 4 * kTailWarps;
+    s.counts = w;                                              w += 2 * n_groups;
+    s.off = w;                                                 w += 2 * n_buffers + 1;
+    s.masks = w;                                               w += kMaskStride * n_groups;
+    s.group_of = reinterpret_cast<uint8_t *>(w);
     return s;
 }
 
-// First and last bits of every run of set bits; lane = word index.
-__device__ __forceinline__ void run_edges(uint32_t m, uint32_t lane, uint32_t &starts, uint32_t &lasts) {
-    uint32_t prev_top = __shfl_up_sync(0xffffffffu, m, 1) >> 31;
-    uint32_t next_low = __shfl_down_sync(0xffffffffu, m, 1) & 1u;
-    if (lane == 0) prev_top = 0;
-    if (lane == 31) next_low = 0;
-    starts = m & ~((m << 1) | prev_top);
-    lasts = m & ~((m >> 1) | (next_low << 31));
+// Inclusive sum over segments of `seg` consecutive lanes (seg a power of two).
+__device__ __forceinline__ uint32_t segment_inclusive_sum(uint32_t v, uint32_t w, uint32_t seg) {
+    for (uint32_t d = 1; d < seg; d <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, v, d);
+        if (w >= d) v += t;
+    }
+    return v;
 }
 
 // --------------------------------------------------------------------------
@@ -132,12 +142,15 @@ __device__ __forceinline__ void run_edges(uint32_t m, uint32_t lane, uint32_t &s
 template <int kBar>
 __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsigned char *raw) {
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // Scalars of `p` are copied to locals first: `p` lives in parameter space and
+    // every global store below would otherwise force them to be re-read.
     const uint32_t G = p.n_groups, n = p.n_buffers;
+    const uint32_t n_blocks = p.n_blocks, budget = p.budget, flags = p.flags;
+    const bool explicit_sets = p.explicit_sets != 0, scan_only = p.scan_only != 0;
+    uint32_t *const resident = p.resident, *const bitmaps_out = p.bitmaps_out;
+    const uint32_t n_words = (n_blocks + 31) / 32;
     const TailShared sh = carve_tail(raw, G, n);
     RT_TAIL_MARK(0);
-    if (tid < 8) sh.stats[tid] = 0;
-    if (tid < 2) sh.bytes[tid] = 0;
-    cta_sync<kBar, kScanThreads>();
     // counters written by other CTAs: fetched now, used at the very end
     unsigned long long invalid = 0, ignored = 0;
     uint32_t eflags = 0;
@@ -146,225 +159,232 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
         ignored = __ldcg(&p.global->ignored_slots);
         eflags = __ldcg(&p.global->error_flags);
     }
-    // Stage every bitmap's wanted and resident words in shared memory with ONE
-    // round trip (all loads in flight together); a load per loop iteration of
-    // pass A would cost a dependent L2 round trip per bitmap.
-    // Loads first (kBatch pairs per thread in flight at once), stores second: a
-    // plain load-store loop would serialise one L2 round trip per iteration.
-    constexpr uint32_t kBatch = 8;
-    uint32_t resident_bits = 0;
-    for (uint32_t base = 0; base < G * kWords; base += kBatch * kScanThreads) {
-        uint32_t a_w[kBatch], b_w[kBatch];
+    // the buffer -> bitmap table goes to shared memory; its load is in flight
+    // together with the first mask words below
+    const uint8_t *const table = p.buffer_group;
+    const uint32_t table_first = tid < n ? __ldcg(&table[tid]) : 0u;
+    RT_TAIL_MARK(6);
+
+    // ---- pass A: one THREAD per (bitmap, word) ----
+    // A warp holds 32/seg bitmaps, seg = the power of two that covers the words
+    // in use; sums and neighbour bits cross words by shuffles inside a segment.
+    // The words of two rounds are loaded before the first is processed, so the
+    // one global round trip of the tail is paid once.
+    uint32_t seg = 1;
+    while (seg < n_words) seg <<= 1;
+    const uint32_t per_warp = 32 / seg, sub = lane / seg, w = lane & (seg - 1);
+    const uint32_t round_stride = kTailWarps * per_warp;
+    const uint32_t left = w < n_words ? n_blocks - w * 32 : 0;
+    const uint32_t valid = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
+    uint32_t n_touched = 0, n_des = 0, n_add = 0, n_ev = 0, some_runs = 0;
+    constexpr int kRounds = 2;
+    for (uint32_t g0 = warp * per_warp; g0 < G; g0 += kRounds * round_stride) {
+        uint32_t a_w[kRounds], b_w[kRounds], r_w[kRounds];
 #pragma unroll
-        for (uint32_t k = 0; k < kBatch; ++k) {
-            const uint32_t i = base + k * kScanThreads + tid;
-            a_w[k] = b_w[k] = 0;
-            if (i < G * kWords) {
-                const uint32_t g = i / kWords, l = i % kWords;
-                if (p.explicit_sets) {
-                    a_w[k] = __ldcg(&want[(g * 2 + 0) * kWords + l]);
-                    b_w[k] = __ldcg(&want[(g * 2 + 1) * kWords + l]);
-                    resident_bits += __popc(__ldcg(&p.resident[i]));   // already the new set
+        for (int k = 0; k < kRounds; ++k) {
+            const uint32_t g = g0 + k * round_stride + sub;
+            a_w[k] = b_w[k] = r_w[k] = 0;
+            if (g < G && w < n_words) {
+                if (explicit_sets) {
+                    // the caller (the recency ranking) already chose what moves and
+                    // has updated the resident words: `want` holds [evict | add]
+                    a_w[k] = __ldcg(&want[(g * 2 + 0) * kWords + w]);
+                    b_w[k] = __ldcg(&want[(g * 2 + 1) * kWords + w]);
+                    r_w[k] = __ldcg(&resident[g * kWords + w]);
                 } else {
-                    a_w[k] = __ldcg(&want[i]);
-                    if (!p.scan_only) b_w[k] = __ldcg(&p.resident[i]);
+                    a_w[k] = __ldcg(&want[g * kWords + w]);
+                    if (!scan_only) r_w[k] = __ldcg(&resident[g * kWords + w]);
                 }
             }
         }
+#ifdef RT_TRACE
+        if (tid == 0 && (a_w[0] | r_w[0]) == 0x12345u) g_tail_trace[7] = 1;   // forces the loads to land
+        else RT_TAIL_MARK(7);
+#endif
+        // no early exit for a round past the last bitmap: its lanes hold zeros,
+        // and straight-line code lets the rounds' dependent chains interleave
 #pragma unroll
-        for (uint32_t k = 0; k < kBatch; ++k) {
-            const uint32_t i = base + k * kScanThreads + tid;
-            if (i < G * kWords) {
-                const uint32_t g = i / kWords, l = i % kWords;
-                sh.masks[g * kMaskStride + l] = a_w[k];
-                sh.masks[g * kMaskStride + kWords + l] = b_w[k];
-                if (consume && !p.explicit_sets) want[i] = 0;
-            }
-        }
-    }
-    if (p.explicit_sets && resident_bits) atomicAdd(&sh.stats[1], resident_bits);
-    cta_sync<kBar, kScanThreads>();
-    RT_TAIL_MARK(1);
-
-    // ---- pass A: one THREAD per bitmap, walking its words in order ----
-    // A running count replaces the cross-lane prefix sums, the carry bit of the
-    // previous word replaces the neighbour shuffles, and all bitmaps advance in
-    // parallel (a warp per bitmap left 8 warps to do 40 bitmaps in 5 dependent
-    // rounds and took 3.2 us; this takes a fraction of that).
-    // Scalars of `p` are copied to locals first: `p` lives in parameter space and
-    // every global store in the loop would otherwise force them to be re-read.
-    const uint32_t n_blocks = p.n_blocks, budget = p.budget, flags = p.flags;
-    const bool explicit_sets = p.explicit_sets != 0, scan_only = p.scan_only != 0;
-    uint32_t *const resident = p.resident, *const bitmaps_out = p.bitmaps_out;
-    const uint32_t n_words = (n_blocks + 31) / 32;
-    uint32_t n_touched = 0, n_des = 0, n_add = 0, n_ev = 0, some_runs = 0;
-    for (uint32_t g = tid; g < G; g += kScanThreads) {
-        uint32_t *m = sh.masks + g * kMaskStride;
-        uint32_t kept = 0, c_ev = 0, c_add = 0, carry_ev = 0, carry_add = 0;
-        for (uint32_t w = 0; w < n_words; ++w) {
-            const uint32_t left = n_blocks - w * 32;
-            const uint32_t valid = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
+        for (int k = 0; k < kRounds; ++k) {
+            const uint32_t g = g0 + k * round_stride + sub;
+            const bool live = g < G && w < n_words;
             uint32_t evict, add, desired;
             if (explicit_sets) {
-                // the caller (the recency ranking) already chose what moves and
-                // has updated the resident words: staging holds [evict | add]
-                evict = m[w];
-                add = m[kWords + w];
-                desired = 0;            // counted from the resident words while staging
+                evict = a_w[k];
+                add = b_w[k];
+                desired = r_w[k];                                   // already the new set
             } else {
-                const uint32_t raw_w = m[w] & valid, res = m[kWords + w];
+                const uint32_t raw_w = a_w[k] & valid;
+                if (live && consume) want[g * kWords + w] = 0;
                 n_touched += __popc(raw_w);
                 if (scan_only) {
-                    if (bitmaps_out) bitmaps_out[g * kWords + w] = raw_w;
+                    if (live && bitmaps_out) bitmaps_out[g * kWords + w] = raw_w;
                     evict = add = desired = 0;
                 } else {
                     // budget cut: lowest block ids first (one event: every stamp
                     // ties, and ties rank by ascending block id)
-                    const uint32_t room = budget > kept ? budget - kept : 0;
-                    desired = room ? lowest_bits(raw_w, room) : 0u;
-                    kept += __popc(desired);
-                    add = desired & ~res;
-                    evict = (flags & RT_PLAN_EVICT) ? (res & ~desired) : 0u;
-                    if (!(flags & RT_PLAN_DRY_RUN)) resident[g * kWords + w] = desired;
+                    const uint32_t cnt = __popc(raw_w);
+                    const uint32_t before = segment_inclusive_sum(cnt, w, seg) - cnt;
+                    const uint32_t room = budget > before ? budget - before : 0;
+                    desired = room >= cnt ? raw_w : lowest_bits(raw_w, room);
+                    add = desired & ~r_w[k];
+                    evict = (flags & RT_PLAN_EVICT) ? (r_w[k] & ~desired) : 0u;
+                    if (live && !(flags & RT_PLAN_DRY_RUN)) resident[g * kWords + w] = desired;
                 }
             }
-            m[w] = evict;
-            m[kWords + w] = add;
             n_des += __popc(desired);
             n_add += __popc(add);
             n_ev += __popc(evict);
             // a run starts at every set bit whose lower neighbour is clear
-            c_ev += __popc(evict & ~((evict << 1) | carry_ev));
-            c_add += __popc(add & ~((add << 1) | carry_add));
-            carry_ev = evict >> 31;
-            carry_add = add >> 31;
+            const uint32_t below_ev = __shfl_up_sync(0xffffffffu, evict, 1);
+            const uint32_t below_add = __shfl_up_sync(0xffffffffu, add, 1);
+            const uint32_t c = __popc(evict & ~((evict << 1) | (w ? below_ev >> 31 : 0u))) |
+                               (__popc(add & ~((add << 1) | (w ? below_add >> 31 : 0u))) << 16);
+            const uint32_t upto = segment_inclusive_sum(c, w, seg);   // both halves at once: each <= 512
+            if (live) {
+                uint32_t *m = sh.masks + g * kMaskStride;
+                m[w] = evict;
+                m[kWords + w] = add;
+                m[2 * kWords + w] = upto - c;                         // runs that start below this word
+                if (w == n_words - 1) {
+                    sh.counts[g * 2 + 0] = upto & 0xffffu;
+                    sh.counts[g * 2 + 1] = upto >> 16;
+                    some_runs |= upto;
+                }
+            }
         }
-        if (scan_only && bitmaps_out)
-            for (uint32_t w = n_words; w < kWords; ++w) bitmaps_out[g * kWords + w] = 0;
-        for (uint32_t w = n_words; w < kWords; ++w) { m[w] = 0; m[kWords + w] = 0; }
-        sh.counts[g * 2 + 0] = c_ev;
-        sh.counts[g * 2 + 1] = c_add;
-        some_runs |= c_ev | c_add;
     }
-    // totals: one reduction per warp, then at most one shared atomic per warp and counter
+    if (tid < n) sh.group_of[tid] = (uint8_t)table_first;
+    for (uint32_t j = tid + kScanThreads; j < n; j += kScanThreads) sh.group_of[j] = __ldcg(&table[j]);
+    RT_TAIL_MARK(1);
+    if (scan_only && bitmaps_out)                                    // words past the ones in use
+        for (uint32_t i = tid; i < G * kWords; i += kScanThreads)
+            if ((i & (kWords - 1)) >= n_words) bitmaps_out[i] = 0;
     n_touched = warp_sum(n_touched);
     n_des = warp_sum(n_des);
     n_add = warp_sum(n_add);
     n_ev = warp_sum(n_ev);
-    some_runs = __any_sync(0xffffffffu, some_runs != 0);
     if (lane == 0) {
-        if (n_touched) atomicAdd(&sh.stats[0], n_touched);
-        if (n_des) atomicAdd(&sh.stats[1], n_des);
-        if (n_add) atomicAdd(&sh.stats[2], n_add);
-        if (n_ev) atomicAdd(&sh.stats[3], n_ev);
-        if (some_runs) sh.stats[4] = 1;
+        uint32_t *ws = sh.warp_stats + warp * 4;
+        ws[0] = n_touched; ws[1] = n_des; ws[2] = n_add; ws[3] = n_ev;
     }
-    cta_sync<kBar, kScanThreads>();
-    RT_TAIL_MARK(2);
     // steady state: nothing moves, so there is nothing to lay out
-    const bool any_runs = sh.stats[4] != 0;
+    const bool any_runs = cta_or<kBar, kScanThreads>(some_runs != 0);
+    RT_TAIL_MARK(2);
 
-    // ---- exclusive prefix sum of run counts over (phase, buffer) ----
-    const uint32_t items = (p.scan_only || !any_runs) ? 0 : 2 * n;
-    const uint32_t per = (items + kScanThreads - 1) / kScanThreads;
-    const uint32_t first = tid * per;
-    uint32_t local = 0;
-    for (uint32_t k = 0; k < per; ++k) {
-        uint32_t i = first + k;
-        if (i < items) {
-            uint32_t phase = i >= n, j = i - phase * n;
-            local += sh.counts[p.buffer_group[j] * 2 + phase];
+    // ---- exclusive prefix sum of run counts over (phase, buffer): warp 0 ----
+    // One warp, consecutive items per lane, one shuffle scan: a CTA-wide scan
+    // costs a second barrier and a pass through shared memory, which is more
+    // than 2*n_buffers/32 additions per lane.
+    const uint32_t items = (scan_only || !any_runs) ? 0 : 2 * n;
+    uint32_t total = 0;
+    if (warp == 0 && items) {
+        const uint32_t per = (items + 31) / 32, first = lane * per;
+        uint32_t local = 0;
+        for (uint32_t k = 0; k < per; ++k) {
+            const uint32_t i = first + k;
+            if (i < items) {
+                const uint32_t phase = i >= n, j = i - phase * n;
+                local += sh.counts[sh.group_of[j] * 2 + phase];
+            }
         }
-    }
-    const uint32_t incl = warp_inclusive_sum(local, lane);
-    if (lane == 31) sh.warp_tot[warp] = incl;
-    cta_sync<kBar, kScanThreads>();
-    uint32_t base = 0, total = 0;
-    for (uint32_t w = 0; w < (uint32_t)kTailWarps; ++w) {
-        if (w < warp) base += sh.warp_tot[w];
-        total += sh.warp_tot[w];
-    }
-    uint32_t run = base + incl - local;
-    for (uint32_t k = 0; k < per; ++k) {
-        uint32_t i = first + k;
-        if (i < items) {
-            sh.off[i] = run;
-            uint32_t phase = i >= n, j = i - phase * n;
-            run += sh.counts[p.buffer_group[j] * 2 + phase];
+        const uint32_t incl = warp_inclusive_sum(local, lane);
+        uint32_t run = incl - local;
+        for (uint32_t k = 0; k < per; ++k) {
+            const uint32_t i = first + k;
+            if (i < items) {
+                sh.off[i] = run;
+                const uint32_t phase = i >= n, j = i - phase * n;
+                run += sh.counts[sh.group_of[j] * 2 + phase];
+            }
         }
+        if (lane == 31) sh.off[items] = incl;
     }
-    if (tid == 0) sh.off[items] = total;
     cta_sync<kBar, kScanThreads>();
+    if (items) total = sh.off[items];
     const uint32_t n_cpu = items ? sh.off[n] : 0;
     RT_TAIL_MARK(3);
 
-    // ---- pass B: one warp per (bitmap, phase): stage its run list in shared
-    //      memory, then write it once for every buffer of the bitmap ----
-    uint16_t *sb = sh.stage + (size_t)warp * 2 * kMaxRuns, *se = sb + kMaxRuns;
-    unsigned long long my_bytes[2] = {0, 0};
-    for (uint32_t t = warp; t < 2 * G && items; t += kTailWarps) {
-        const uint32_t count = sh.counts[t];
-        if (!count) continue;                                   // uniform over the warp
-        const uint32_t g = t >> 1, phase = t & 1;
-        uint32_t starts, lasts;
-        run_edges(sh.masks[g * kMaskStride + phase * kWords + lane], lane, starts, lasts);
-        uint32_t bpos = warp_inclusive_sum(__popc(starts), lane) - __popc(starts);
-        uint32_t epos = warp_inclusive_sum(__popc(lasts), lane) - __popc(lasts);
-        while (starts) {
-            uint32_t b = __ffs(starts) - 1;
-            starts &= starts - 1;
-            sb[bpos++] = (uint16_t)(lane * 32 + b);
-        }
-        while (lasts) {
-            uint32_t b = __ffs(lasts) - 1;
-            lasts &= lasts - 1;
-            se[epos++] = (uint16_t)(lane * 32 + b + 1);
-        }
-        __syncwarp();
-        const int32_t dst = phase ? p.dst_device : RT_DST_CPU;
-        for (uint32_t j0 = 0; j0 < n; j0 += 32) {
-            const uint32_t j = j0 + lane;
-            uint32_t mine = __ballot_sync(0xffffffffu, j < n && p.buffer_group[j] == g);
-            while (mine) {
-                const uint32_t jj = j0 + (uint32_t)__ffs(mine) - 1;
-                mine &= mine - 1;
-                const uint32_t at = sh.off[phase * n + jj];
-                for (uint32_t k = lane; k < count; k += 32) {
-                    unsigned long long b = (unsigned long long)sb[k] * p.block_bytes;
-                    unsigned long long e = (unsigned long long)se[k] * p.block_bytes;
-                    if (e > p.alloc_bytes) e = p.alloc_bytes;   // final partial block, select.cpp:24188
-                    my_bytes[phase] += e - b;
-                    if (at + k < p.cap) {
-                        rt_range r;
-                        r.buffer = jj;
-                        r.dst = dst;
-                        r.offset = b;
-                        r.bytes = e - b;
-                        p.out[at + k] = r;
-                    }
+    // ---- pass B: one thread per (phase, buffer) ----
+    // The thread walks the words of its bitmap's evict or add mask and writes
+    // the runs; where they go is the prefix sum above.  (A warp per (bitmap,
+    // phase) handing its run list to every buffer in turn took ten dependent
+    // rounds for 40 bitmaps: 17 us for 160 ranges.)
+    const unsigned long long block_bytes = p.block_bytes, alloc_bytes = p.alloc_bytes;
+    const uint32_t cap = p.cap;
+    const int32_t dst_gpu = p.dst_device;
+    rt_range *const out = p.out;
+    unsigned long long cpu_bytes = 0, gpu_bytes = 0;
+    for (uint32_t i = tid; i < items; i += kScanThreads) {
+        const uint32_t phase = i >= n, j = i - phase * n, g = sh.group_of[j];
+        if (!sh.counts[g * 2 + phase]) continue;
+        const uint32_t *m = sh.masks + g * kMaskStride + phase * kWords;
+        uint32_t at = sh.off[i], below_top = 0;
+        unsigned long long moved = 0;
+        for (uint32_t k = 0; k < n_words; ++k) {
+            const uint32_t word = m[k];
+            uint32_t starts = word & ~((word << 1) | below_top);
+            below_top = word >> 31;
+            while (starts) {
+                const uint32_t b = __ffs(starts) - 1;
+                starts &= starts - 1;
+                // first clear bit above b, in this word or the following ones
+                const uint32_t clear = ~(word >> b);        // zero only for b == 0 and a full word
+                uint32_t e = clear ? b + (uint32_t)__ffs(clear) - 1 : 32u;
+                if (e == 32) {
+                    uint32_t k2 = k + 1;
+                    while (k2 < n_words && m[k2] == 0xffffffffu) ++k2;
+                    e = (k2 - k) * 32 + (k2 < n_words ? (uint32_t)__ffs(~m[k2]) - 1 : 0u);
                 }
+                const unsigned long long lo = (unsigned long long)(k * 32 + b) * block_bytes;
+                unsigned long long hi = (unsigned long long)(k * 32 + e) * block_bytes;
+                if (hi > alloc_bytes) hi = alloc_bytes;             // final partial block, select.cpp:24188
+                moved += hi - lo;
+                if (at < cap) {
+                    rt_range rg;
+                    rg.buffer = j;
+                    rg.dst = phase ? dst_gpu : RT_DST_CPU;
+                    rg.offset = lo;
+                    rg.bytes = hi - lo;
+                    out[at] = rg;
+                }
+                ++at;
             }
         }
-        __syncwarp();
+        if (phase) gpu_bytes += moved; else cpu_bytes += moved;
     }
     RT_TAIL_MARK(4);
-    if (my_bytes[0]) atomicAdd(&sh.bytes[0], my_bytes[0]);
-    if (my_bytes[1]) atomicAdd(&sh.bytes[1], my_bytes[1]);
+    if (items) {
+        cpu_bytes = warp_sum64(cpu_bytes);
+        gpu_bytes = warp_sum64(gpu_bytes);
+    }
+    if (lane == 0) {
+        sh.warp_bytes[warp * 2 + 0] = cpu_bytes;
+        sh.warp_bytes[warp * 2 + 1] = gpu_bytes;
+    }
     cta_sync<kBar, kScanThreads>();
     if (tid == 0) {
         rt_plan_result res;
+        uint32_t st[4] = {0, 0, 0, 0};
+        unsigned long long by[2] = {0, 0};
+#pragma unroll
+        for (int k = 0; k < kTailWarps; ++k) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) st[q] += sh.warp_stats[k * 4 + q];
+            by[0] += sh.warp_bytes[k * 2 + 0];
+            by[1] += sh.warp_bytes[k * 2 + 1];
+        }
         res.n_ranges = total;
         res.n_cpu_ranges = n_cpu;
-        res.flags = (total > p.cap ? RT_RESULT_OVERFLOW : 0u) | (invalid ? RT_RESULT_SLOT_RANGE : 0u) | eflags;
-        res.blocks_touched = sh.stats[0];
-        res.blocks_desired = sh.stats[1];
-        res.blocks_added = sh.stats[2];
-        res.blocks_evicted = sh.stats[3];
+        res.flags = (total > cap ? RT_RESULT_OVERFLOW : 0u) | (invalid ? RT_RESULT_SLOT_RANGE : 0u) | eflags;
+        res.blocks_touched = st[0];
+        res.blocks_desired = st[1];
+        res.blocks_added = st[2];
+        res.blocks_evicted = st[3];
         res.reserved = 0;
         res.invalid_slots = invalid;
         res.ignored_slots = ignored;
-        res.cpu_bytes = sh.bytes[0];
-        res.gpu_bytes = sh.bytes[1];
+        res.cpu_bytes = by[0];
+        res.gpu_bytes = by[1];
         *p.result = res;
         // leave the scratch clean for the next launch
         GlobalScratch &gl = *p.global;

@@ -13,6 +13,16 @@ from . import capi
 from .workloads import Layout
 
 
+def _is_i32(x) -> bool:
+    """True for int32 ids, False for int64; anything else is refused."""
+    name = str(x.dtype)
+    if name in ("int32", "torch.int32"):
+        return True
+    if name in ("int64", "torch.int64"):
+        return False
+    raise TypeError(f"slot ids must be int32 or int64, not {name}")
+
+
 def _ptr(x):
     """Raw address of a torch tensor, numpy array or None."""
     if x is None:
@@ -63,11 +73,12 @@ class DevicePlanner:
     def step_host(self, slots: np.ndarray, group_off: np.ndarray, budget: int, flags: int = 0,
                   *, out: np.ndarray | None = None, raise_on_slot_range: bool = True):
         """Host buffers in, host ranges out (copies inside). Returns (ranges, result)."""
-        assert slots.dtype == np.int64 and group_off.dtype == np.int64
+        assert group_off.dtype == np.int64
         if out is None:
             out = np.empty(self.max_ranges, dtype=capi.RANGE_DTYPE)
         res = capi.PlanResult()
-        st = capi.lib.rt_plan_step(self._h, _ptr(slots), _ptr(group_off), budget, flags,
+        fn = capi.lib.rt_plan_step_i32 if _is_i32(slots) else capi.lib.rt_plan_step
+        st = fn(self._h, _ptr(slots), _ptr(group_off), budget, flags,
                                    _ptr(out), len(out), C.byref(res))
         if st == capi.RT_ERR_SLOT_RANGE and not raise_on_slot_range:
             st = 0
@@ -76,21 +87,25 @@ class DevicePlanner:
 
     def step_device(self, d_slots, group_off: np.ndarray, budget: int, flags: int, d_out, d_result,
                     stream=None):
-        """Everything already on the device (torch tensors); asynchronous."""
+        """Everything already on the device (torch tensors); asynchronous.
+        ``d_slots`` may be int64 or int32."""
         cap = d_out.numel() * d_out.element_size() // capi.RANGE_DTYPE.itemsize
-        capi.check(capi.lib.rt_plan_step_device(
+        fn = capi.lib.rt_plan_step_device_i32 if _is_i32(d_slots) else capi.lib.rt_plan_step_device
+        capi.check(fn(
             self._h, _ptr(d_slots), _ptr(group_off), budget, flags, _ptr(d_out), cap,
             _ptr(d_result), C.c_void_p(stream) if stream else None), "rt_plan_step_device")
 
     def step_table(self, d_table, d_lens, budget: int, flags: int, d_out, d_result, stream=None):
         rows, stride = d_table.shape
         cap = d_out.numel() * d_out.element_size() // capi.RANGE_DTYPE.itemsize
-        capi.check(capi.lib.rt_plan_step_table(
+        fn = capi.lib.rt_plan_step_table_i32 if _is_i32(d_table) else capi.lib.rt_plan_step_table
+        capi.check(fn(
             self._h, _ptr(d_table), _ptr(d_lens), rows, stride, budget, flags, _ptr(d_out), cap,
             _ptr(d_result), C.c_void_p(stream) if stream else None), "rt_plan_step_table")
 
     def scan(self, d_slots, group_off: np.ndarray, d_bitmaps, d_result, stream=None):
-        capi.check(capi.lib.rt_scan_slots(
+        fn = capi.lib.rt_scan_slots_i32 if _is_i32(d_slots) else capi.lib.rt_scan_slots
+        capi.check(fn(
             self._h, _ptr(d_slots), _ptr(group_off), _ptr(d_bitmaps), _ptr(d_result),
             C.c_void_p(stream) if stream else None), "rt_scan_slots")
 

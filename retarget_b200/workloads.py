@@ -195,6 +195,47 @@ def target_step(seed=0) -> SlotBatch:
     return b
 
 
+def confine(batch: SlotBatch, blocks, tag: str) -> SlotBatch:
+    """Move a batch onto a subset of the pool's blocks: block b of the original
+    goes to ``blocks[b % len(blocks)]`` and every id keeps its offset inside
+    the block.  Sizes, request structure and the repeat pattern of the ids are
+    unchanged; only the set of touched blocks is."""
+    lay = batch.layout
+    T = lay.block_tokens
+    table = np.asarray(list(blocks), dtype=np.int64)
+    assert len(table) and table.max() < lay.n_blocks and batch.slots.min() >= 1
+    s = batch.slots
+    moved = np.maximum(table[(s // T) % len(table)] * T + s % T, 1)   # id 0 is the padding slot
+    assert moved.max() <= lay.capacity
+    return dataclasses.replace(batch, slots=moved, name=f"{batch.name}, {tag}")
+
+
+def target_pair(kind: str = "moving"):
+    """Two headline-sized steps that alternate in the benchmark.
+
+    ``moving``      step A lives in the lower half of every buffer, step B in the
+                    upper half: each plan evicts one run and adds one run per
+                    buffer (160 ranges), the shape of the reference's incremental
+                    window update
+    ``steady``      both steps want the same blocks: after the first plan nothing
+                    moves (0 ranges), the common case of consecutive decode steps
+    ``fragmented``  step A touches only even blocks, step B only odd ones: every
+                    plan replaces the whole budget in single-block runs
+                    (2 x 38 x 80 = 6080 ranges), the most the tail can be asked for
+    """
+    a, b = target_step(0), target_step(1)
+    nb = a.layout.n_blocks
+    if kind == "steady":
+        return a, b
+    if kind == "moving":
+        return (confine(a, range(0, nb // 2), "lower half"),
+                confine(b, range(nb // 2, nb), "upper half"))
+    if kind == "fragmented":
+        return (confine(a, range(0, nb, 2), "even blocks"),
+                confine(b, range(1, nb, 2), "odd blocks"))
+    raise ValueError(kind)
+
+
 # --------------------------------------------------------------------------
 # incremental decode trace
 # --------------------------------------------------------------------------

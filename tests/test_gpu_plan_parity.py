@@ -16,7 +16,10 @@ pytestmark = pytest.mark.gpu
 
 torch = pytest.importorskip("torch")
 
-MODES = [pytest.param(0, id="ld128"), pytest.param(capi.RT_PLAN_TMA, id="tma")]
+# (flags, id dtype): the register-staged kernel, the bulk-copy kernel, and the
+# register-staged kernel reading 32-bit ids
+MODES = [pytest.param((0, np.int64), id="ld128"), pytest.param((capi.RT_PLAN_TMA, np.int64), id="tma"),
+         pytest.param((0, np.int32), id="i32")]
 
 
 def random_batch(rng, *, layers, pool_slots, bytes_per_slot, shared, n_req, max_len, budget,
@@ -51,11 +54,14 @@ def random_batch(rng, *, layers, pool_slots, bytes_per_slot, shared, n_req, max_
 def run_steps(batches, *, evict, flags, literal=True):
     """Feeds the same sequence of batches to the device planner (host-buffer
     entry point) and to the oracle; compares every step."""
+    flags, dtype = flags if isinstance(flags, tuple) else (flags, np.int64)
     lay = batches[0].layout
     planner = DevicePlanner(lay, 0, max_indices=max(b.n_idx for b in batches) + 8, max_ranges=1 << 16)
     resident = [set() for _ in range(lay.n_groups)]
     f = flags | (capi.RT_PLAN_EVICT if evict else 0)
     for step, b in enumerate(batches):
+        # oracle and planner both see the ids in the dtype under test
+        b = dataclasses.replace(b, slots=b.slots.astype(dtype))
         want, info = compose.plan_step(b, resident, evict=evict, literal=literal)
         got, res = planner.step_host(b.slots, b.group_off, b.budget_blocks, f)
         assert ranges_to_tuples(got) == want, f"step {step}"
@@ -141,10 +147,12 @@ def test_sparse_feedback_config_full(flags):
     run_steps([b, b], evict=True, flags=flags, literal=False)
 
 
-def test_device_resident_entry_points_agree():
+@pytest.mark.parametrize("dtype", [np.int64, np.int32], ids=["i64", "i32"])
+def test_device_resident_entry_points_agree(dtype):
     """step_device (ids already in HBM), the padded-table entry point and the
     scan-only + from-bitmaps pair all give the host-buffer call's answer."""
     b = workloads.full_refresh(2)
+    b = dataclasses.replace(b, slots=b.slots.astype(dtype))
     lay = b.layout
     dev = torch.device("cuda:0")
     resident0 = [set(range(3, 9))]
@@ -171,7 +179,7 @@ def test_device_resident_entry_points_agree():
     # padded [requests, stride] table with an odd stride
     lens = np.diff(b.req_off).astype(np.int32)
     stride = int(lens.max()) + 3
-    table = np.full((len(lens), stride), -7, dtype=np.int64)
+    table = np.full((len(lens), stride), -7, dtype=dtype)
     for r, n in enumerate(lens):
         table[r, :n] = b.slots[b.req_off[r]:b.req_off[r + 1]]
     p = fresh()
@@ -240,6 +248,55 @@ def test_slot_above_capacity_is_reported():
     got, res = p.step_host(slots[:2], np.array([0, 2], np.int64), 4)
     assert res.invalid_slots == 0 and res.flags == 0
     p.close()
+
+
+@pytest.mark.parametrize("kind", ["moving", "fragmented"])
+def test_benchmark_pairs_match_oracle(kind):
+    """The alternating batches the benchmark times: every step evicts and adds
+    (160 ranges when the halves alternate, 6080 single-block ranges when even
+    and odd blocks do)."""
+    a, b = workloads.target_pair(kind)
+    run_steps([a, b, a], evict=True, flags=(0, np.int64), literal=False)
+    want = {"moving": 160, "fragmented": 6080}[kind]
+    resident = [set() for _ in range(a.layout.n_groups)]
+    compose.plan_step(a, resident, literal=False)
+    ranges, _ = compose.plan_step(b, resident, literal=False)
+    assert len(ranges) == want
+
+
+def test_int32_ids_negative_and_above_capacity():
+    """32-bit ids: negatives are ignored like any id below 1, ids above the
+    capacity are counted, and an odd start offset inside a 16-byte vector works."""
+    lay = workloads.Layout(2, 2048, 8192)
+    slots = np.array([99, 5, -3, 8191, 8192, 2**31 - 1, 9, -2**31, 0, 4000, 4001], dtype=np.int32)
+    p = DevicePlanner(lay, 0, max_indices=64)
+    # ids [1, 11): starts at index 1 of the first 4-id vector
+    got, res = p.step_host(slots, np.array([1, 11], np.int64), 8, raise_on_slot_range=False)
+    assert res.invalid_slots == 2 and res.ignored_slots == 3
+    assert res.flags & capi.RT_RESULT_SLOT_RANGE
+    assert p.get_resident() == [[0, 3, 7]]
+    p.close()
+    # a pool too large for 32-bit ids is refused up front
+    big = workloads.Layout(1, 1, (1 << 31) + 2, block_bytes=1 << 22)
+    pb = DevicePlanner(big, 0, max_indices=16)
+    with pytest.raises(capi.RtError) as e:
+        pb.step_host(np.array([1], np.int32), np.array([0, 1], np.int64), 1)
+    assert e.value.status == capi.RT_ERR_INVALID_ARGUMENT
+    pb.close()
+
+
+def test_int32_matches_int64_at_headline_size():
+    """The benchmark's 22.3 M ids as int32 and as int64 give the same plan."""
+    b = workloads.target_step(0)
+    p64 = DevicePlanner(b.layout, 0, max_indices=b.n_idx + 8)
+    p32 = DevicePlanner(b.layout, 0, max_indices=b.n_idx + 8)
+    a, ra = p64.step_host(b.slots, b.group_off, b.budget_blocks, capi.RT_PLAN_EVICT)
+    c, rc = p32.step_host(b.slots.astype(np.int32), b.group_off, b.budget_blocks, capi.RT_PLAN_EVICT)
+    assert ranges_to_tuples(a) == ranges_to_tuples(c) and len(a) > 0
+    assert ra.as_dict() == rc.as_dict()
+    assert p64.get_resident() == p32.get_resident()
+    p64.close()
+    p32.close()
 
 
 def test_range_capacity_overflow_is_reported():
