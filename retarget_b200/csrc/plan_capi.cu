@@ -36,6 +36,7 @@ struct rt_plan {
     rt::GlobalScratch *d_global = nullptr;
     uint32_t *d_resident = nullptr;
     uint8_t *d_buffer_group = nullptr;  // bitmap of every buffer, registry order
+    uint16_t *d_group_size = nullptr;   // buffers per bitmap
     long long *d_stage = nullptr;      // host-buffer call: slot ids land here
     uint64_t max_indices = 0;
     rt_range *h_out = nullptr;         // pinned + mapped: the kernel writes ranges here
@@ -79,6 +80,7 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
     p.global = pl->d_global;
     p.resident = pl->d_resident;
     p.buffer_group = pl->d_buffer_group;
+    p.group_size = pl->d_group_size;
     p.n_units = 0;
     p.bitmaps_out = nullptr;
     p.out = out;
@@ -259,8 +261,12 @@ int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, ui
             uint8_t table[RT_MAX_BUFFERS] = {0};
             if (L.buffer_group)
                 for (uint32_t j = 0; j < L.n_buffers; ++j) table[j] = (uint8_t)L.buffer_group[j];
+            uint16_t sizes[RT_MAX_GROUPS] = {0};
+            for (uint32_t j = 0; j < L.n_buffers; ++j) ++sizes[table[j]];
             if ((e = cudaMalloc(&pl->d_buffer_group, L.n_buffers))) { fail(e); break; }
             if ((e = cudaMemcpy(pl->d_buffer_group, table, L.n_buffers, cudaMemcpyHostToDevice))) { fail(e); break; }
+            if ((e = cudaMalloc(&pl->d_group_size, sizeof(uint16_t) * L.n_groups))) { fail(e); break; }
+            if ((e = cudaMemcpy(pl->d_group_size, sizes, sizeof(uint16_t) * L.n_groups, cudaMemcpyHostToDevice))) { fail(e); break; }
         }
         if (max_indices) {
             // +2 ids of slack so a 16-byte load at the very end stays in bounds
@@ -290,6 +296,7 @@ int rt_plan_destroy(rt_plan *pl) {
     cudaFree(pl->d_global);
     cudaFree(pl->d_resident);
     cudaFree(pl->d_buffer_group);
+    cudaFree(pl->d_group_size);
     cudaFree(pl->d_stage);
     if (pl->h_out) cudaFreeHost(pl->h_out);
     if (pl->h_result) cudaFreeHost(pl->h_result);

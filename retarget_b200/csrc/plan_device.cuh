@@ -65,6 +65,7 @@ struct PlanArgs {
     unsigned long long alloc_bytes;
     unsigned long long block_bytes;
     const uint8_t *buffer_group;              // device: bitmap of every buffer, registry order
+    const uint16_t *group_size;               // device: buffers per bitmap
 };
 
 }  // namespace rt

@@ -47,17 +47,18 @@ __device__ __forceinline__ unsigned long long warp_sum64(unsigned long long v) {
     return v;
 }
 
-// Lowest `k` set bits of x.  The answer keeps the low `pos` bits of x, pos the
-// largest width whose low bits hold at most k set bits: five unrolled steps of
-// popc (a loop costs compares and branches on the tail's critical path; __fns
-// is emulated in software and much slower).
+// Lowest `k` set bits of x, without a branch.  The answer keeps the low `pos`
+// bits of x, pos the largest width below 32 whose low bits hold at most k set
+// bits: five unrolled steps of popc.  (A search loop costs compares and
+// branches on the tail's critical path and keeps the compiler from overlapping
+// independent bitmaps; __fns is emulated in software and much slower.)
 __device__ __forceinline__ uint32_t lowest_bits(uint32_t x, uint32_t k) {
-    if (k >= (uint32_t)__popc(x)) return x;
     uint32_t pos = 0;
 #pragma unroll
     for (uint32_t s = 16; s >= 1; s >>= 1)
-        if ((uint32_t)__popc(x & ((1u << (pos + s)) - 1u)) <= k) pos += s;
-    return x & ((1u << pos) - 1u);
+        pos += ((uint32_t)__popc(x & ((1u << (pos + s)) - 1u)) <= k) ? s : 0u;
+    const uint32_t cut = x & ((1u << pos) - 1u);
+    return k >= (uint32_t)__popc(x) ? x : cut;
 }
 
 // --------------------------------------------------------------------------
@@ -92,46 +93,98 @@ constexpr int kTailWarps = kScanThreads / 32;
 // Words per bitmap in the tail's shared staging:
 //   [0, kWords)          evict words
 //   [kWords, 2*kWords)   add words
-//   [2*kWords, 3*kWords) per word, the number of runs that start in lower words:
-//                        low half = evict runs, high half = add runs
 // plus one word of padding, so that threads working on different bitmaps and
 // the same word index fall in different banks.
-constexpr uint32_t kMaskStride = 3 * kWords + 1;
+constexpr uint32_t kMaskStride = 2 * kWords + 1;
+// Run lists of at most kFew runs per (bitmap, phase) are written out by pass A
+// as (begin, end) block pairs, so the common plans -- a window that moves, a
+// few blocks that change -- need no second look at the mask words.
+constexpr uint32_t kFew = 2;
+constexpr int kWarpStats = 8;   // touched, desired, added, evicted, buffer-blocks to CPU / GPU, partial last blocks to CPU / GPU
 
 struct TailShared {
-    unsigned long long *warp_bytes;  // [kTailWarps][2]  CPU-bound / GPU-bound bytes per warp
-    uint32_t *warp_stats;            // [kTailWarps][4]  touched, desired, added, evicted per warp
+    uint32_t *warp_stats;            // [kTailWarps][kWarpStats]
+    uint32_t *warp_tot;              // [kTailWarps]
     uint32_t *counts;                // [n_groups][2]        runs per (bitmap, phase)
     uint32_t *off;                   // [2*n_buffers + 1]    first range of every (phase, buffer)
     uint32_t *masks;                 // [n_groups][kMaskStride]
+    uint16_t *few;                   // [n_groups][2][kFew][2]  begin, end of the first runs
     uint8_t *group_of;               // [n_buffers]          bitmap of every buffer
 };
 
 __host__ __device__ constexpr size_t tail_smem_bytes(uint32_t n_groups, uint32_t n_buffers) {
-    return ((4 * kTailWarps + 4 * kTailWarps + 2 * (size_t)n_groups +
-             (2 * (size_t)n_buffers + 1) + (size_t)kMaskStride * n_groups) * 4 +
+    return ((kWarpStats * kTailWarps + kTailWarps + 2 * (size_t)n_groups + (2 * (size_t)n_buffers + 1) +
+             (size_t)kMaskStride * n_groups + 2 * kFew * (size_t)n_groups) * 4 +
             (size_t)n_buffers + 15) & ~(size_t)15;
 }
 
 __device__ __forceinline__ TailShared carve_tail(unsigned char *raw, uint32_t n_groups, uint32_t n_buffers) {
     TailShared s;
     uint32_t *w = reinterpret_cast<uint32_t *>(raw);
-    s.warp_bytes = reinterpret_cast<unsigned long long *>(w);  w += 4 * kTailWarps;
-    s.warp_stats = w;                                          w += 4 * kTailWarps;
+    s.warp_stats = w;                                          w += kWarpStats * kTailWarps;
+    s.warp_tot = w;                                            w += kTailWarps;
     s.counts = w;                                              w += 2 * n_groups;
     s.off = w;                                                 w += 2 * n_buffers + 1;
     s.masks = w;                                               w += kMaskStride * n_groups;
+    s.few = reinterpret_cast<uint16_t *>(w);                   w += 2 * kFew * n_groups;
     s.group_of = reinterpret_cast<uint8_t *>(w);
     return s;
 }
 
-// Inclusive sum over segments of `seg` consecutive lanes (seg a power of two).
-__device__ __forceinline__ uint32_t segment_inclusive_sum(uint32_t v, uint32_t w, uint32_t seg) {
-    for (uint32_t d = 1; d < seg; d <<= 1) {
+// Inclusive sum over segments of consecutive lanes; `w` is the lane's index in
+// its segment.  Always five steps: a lane only adds what lies inside its own
+// segment (w >= d), and a fixed count keeps the code free of branches.
+__device__ __forceinline__ uint32_t segment_inclusive_sum(uint32_t v, uint32_t w) {
+#pragma unroll
+    for (uint32_t d = 1; d < 32; d <<= 1) {
         const uint32_t t = __shfl_up_sync(0xffffffffu, v, d);
-        if (w >= d) v += t;
+        v += w >= d ? t : 0u;
     }
     return v;
+}
+
+// Pass A helper for one phase's mask word: number of runs that start in it and,
+// for the first kFew runs of the bitmap, their begin / end blocks.
+//   below_top  bit 31 of the word below (0 for word 0)
+//   above_low  bit 0 of the word above (0 for the last word)
+__device__ __forceinline__ uint32_t run_starts(uint32_t x, uint32_t below_top) {
+    return x & ~((x << 1) | below_top);
+}
+__device__ __forceinline__ void note_few(uint16_t *few, uint32_t x, uint32_t w, uint32_t below_top,
+                                         uint32_t above_low, uint32_t starts_below) {
+    uint32_t starts = run_starts(x, below_top);
+    uint32_t lasts = x & ~((x >> 1) | (above_low << 31));
+    uint32_t si = starts_below;
+    // a run that crosses in from the word below has started but not ended there
+    uint32_t ei = starts_below - (below_top & x & 1u);
+#pragma unroll
+    for (uint32_t q = 0; q < kFew; ++q) {
+        if (starts && si < kFew) {
+            few[2 * si] = (uint16_t)(w * 32 + __ffs(starts) - 1);
+            starts &= starts - 1;
+            ++si;
+        }
+        if (lasts && ei < kFew) {
+            few[2 * ei + 1] = (uint16_t)(w * 32 + __ffs(lasts));
+            lasts &= lasts - 1;
+            ++ei;
+        }
+    }
+}
+
+__device__ __forceinline__ void store_range(rt_range *out, uint32_t at, uint32_t cap, uint32_t buffer,
+                                            int32_t dst, uint32_t begin, uint32_t end,
+                                            unsigned long long block_bytes, unsigned long long alloc_bytes) {
+    if (at >= cap) return;
+    const unsigned long long lo = (unsigned long long)begin * block_bytes;
+    unsigned long long hi = (unsigned long long)end * block_bytes;
+    if (hi > alloc_bytes) hi = alloc_bytes;                     // final partial block, select.cpp:24188
+    rt_range rg;
+    rg.buffer = buffer;
+    rg.dst = dst;
+    rg.offset = lo;
+    rg.bytes = hi - lo;
+    out[at] = rg;
 }
 
 // --------------------------------------------------------------------------
@@ -162,6 +215,7 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
     // the buffer -> bitmap table goes to shared memory; its load is in flight
     // together with the first mask words below
     const uint8_t *const table = p.buffer_group;
+    const uint16_t *const group_size = p.group_size;
     const uint32_t table_first = tid < n ? __ldcg(&table[tid]) : 0u;
     RT_TAIL_MARK(6);
 
@@ -169,22 +223,26 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
     // A warp holds 32/seg bitmaps, seg = the power of two that covers the words
     // in use; sums and neighbour bits cross words by shuffles inside a segment.
     // The words of two rounds are loaded before the first is processed, so the
-    // one global round trip of the tail is paid once.
+    // one global round trip of the tail is paid once, and the body is
+    // straight-line code, so the two rounds' dependent chains overlap.
     uint32_t seg = 1;
     while (seg < n_words) seg <<= 1;
     const uint32_t per_warp = 32 / seg, sub = lane / seg, w = lane & (seg - 1);
     const uint32_t round_stride = kTailWarps * per_warp;
     const uint32_t left = w < n_words ? n_blocks - w * 32 : 0;
     const uint32_t valid = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
-    uint32_t n_touched = 0, n_des = 0, n_add = 0, n_ev = 0, some_runs = 0;
+    const uint32_t last_bit = (w == n_words - 1) ? 1u << ((n_blocks - 1) & 31) : 0u;
+    uint32_t st[kWarpStats] = {0, 0, 0, 0, 0, 0, 0, 0};
+    uint32_t some_runs = 0;
     constexpr int kRounds = 2;
     for (uint32_t g0 = warp * per_warp; g0 < G; g0 += kRounds * round_stride) {
-        uint32_t a_w[kRounds], b_w[kRounds], r_w[kRounds];
+        uint32_t a_w[kRounds], b_w[kRounds], r_w[kRounds], size_g[kRounds];
 #pragma unroll
         for (int k = 0; k < kRounds; ++k) {
             const uint32_t g = g0 + k * round_stride + sub;
-            a_w[k] = b_w[k] = r_w[k] = 0;
+            a_w[k] = b_w[k] = r_w[k] = size_g[k] = 0;
             if (g < G && w < n_words) {
+                size_g[k] = __ldcg(&group_size[g]);
                 if (explicit_sets) {
                     // the caller (the recency ranking) already chose what moves and
                     // has updated the resident words: `want` holds [evict | add]
@@ -201,10 +259,9 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
         if (tid == 0 && (a_w[0] | r_w[0]) == 0x12345u) g_tail_trace[7] = 1;   // forces the loads to land
         else RT_TAIL_MARK(7);
 #endif
-        // no early exit for a round past the last bitmap: its lanes hold zeros,
-        // and straight-line code lets the rounds' dependent chains interleave
 #pragma unroll
         for (int k = 0; k < kRounds; ++k) {
+            // a round past the last bitmap is not skipped: its lanes hold zeros
             const uint32_t g = g0 + k * round_stride + sub;
             const bool live = g < G && w < n_words;
             uint32_t evict, add, desired;
@@ -215,7 +272,7 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
             } else {
                 const uint32_t raw_w = a_w[k] & valid;
                 if (live && consume) want[g * kWords + w] = 0;
-                n_touched += __popc(raw_w);
+                st[0] += __popc(raw_w);
                 if (scan_only) {
                     if (live && bitmaps_out) bitmaps_out[g * kWords + w] = raw_w;
                     evict = add = desired = 0;
@@ -223,28 +280,39 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
                     // budget cut: lowest block ids first (one event: every stamp
                     // ties, and ties rank by ascending block id)
                     const uint32_t cnt = __popc(raw_w);
-                    const uint32_t before = segment_inclusive_sum(cnt, w, seg) - cnt;
-                    const uint32_t room = budget > before ? budget - before : 0;
-                    desired = room >= cnt ? raw_w : lowest_bits(raw_w, room);
+                    const uint32_t before = segment_inclusive_sum(cnt, w) - cnt;
+                    desired = lowest_bits(raw_w, budget > before ? budget - before : 0u);
                     add = desired & ~r_w[k];
                     evict = (flags & RT_PLAN_EVICT) ? (r_w[k] & ~desired) : 0u;
                     if (live && !(flags & RT_PLAN_DRY_RUN)) resident[g * kWords + w] = desired;
                 }
             }
-            n_des += __popc(desired);
-            n_add += __popc(add);
-            n_ev += __popc(evict);
+            st[1] += __popc(desired);
+            st[2] += __popc(add);
+            st[3] += __popc(evict);
+            // bytes moved are counted in blocks x buffers of the bitmap here; the
+            // last block of a buffer may be partial and is counted separately
+            st[4] += __popc(evict) * size_g[k];
+            st[5] += __popc(add) * size_g[k];
+            st[6] += (evict & last_bit) ? size_g[k] : 0u;
+            st[7] += (add & last_bit) ? size_g[k] : 0u;
+            // neighbour bits across the word boundaries of the bitmap
+            const uint32_t dn_ev = __shfl_up_sync(0xffffffffu, evict, 1);
+            const uint32_t dn_add = __shfl_up_sync(0xffffffffu, add, 1);
+            const uint32_t up_ev = __shfl_down_sync(0xffffffffu, evict, 1);
+            const uint32_t up_add = __shfl_down_sync(0xffffffffu, add, 1);
+            const uint32_t below_ev = w ? dn_ev >> 31 : 0u, below_add = w ? dn_add >> 31 : 0u;
+            const uint32_t above_ev = w + 1 < seg ? up_ev & 1u : 0u, above_add = w + 1 < seg ? up_add & 1u : 0u;
             // a run starts at every set bit whose lower neighbour is clear
-            const uint32_t below_ev = __shfl_up_sync(0xffffffffu, evict, 1);
-            const uint32_t below_add = __shfl_up_sync(0xffffffffu, add, 1);
-            const uint32_t c = __popc(evict & ~((evict << 1) | (w ? below_ev >> 31 : 0u))) |
-                               (__popc(add & ~((add << 1) | (w ? below_add >> 31 : 0u))) << 16);
-            const uint32_t upto = segment_inclusive_sum(c, w, seg);   // both halves at once: each <= 512
+            const uint32_t c = __popc(run_starts(evict, below_ev)) | (__popc(run_starts(add, below_add)) << 16);
+            const uint32_t upto = segment_inclusive_sum(c, w);        // both halves at once: each <= 512
             if (live) {
                 uint32_t *m = sh.masks + g * kMaskStride;
                 m[w] = evict;
                 m[kWords + w] = add;
-                m[2 * kWords + w] = upto - c;                         // runs that start below this word
+                uint16_t *few = sh.few + g * 4 * kFew;
+                note_few(few, evict, w, below_ev, above_ev, (upto - c) & 0xffffu);
+                note_few(few + 2 * kFew, add, w, below_add, above_add, (upto - c) >> 16);
                 if (w == n_words - 1) {
                     sh.counts[g * 2 + 0] = upto & 0xffffu;
                     sh.counts[g * 2 + 1] = upto >> 16;
@@ -259,26 +327,26 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
     if (scan_only && bitmaps_out)                                    // words past the ones in use
         for (uint32_t i = tid; i < G * kWords; i += kScanThreads)
             if ((i & (kWords - 1)) >= n_words) bitmaps_out[i] = 0;
-    n_touched = warp_sum(n_touched);
-    n_des = warp_sum(n_des);
-    n_add = warp_sum(n_add);
-    n_ev = warp_sum(n_ev);
+#pragma unroll
+    for (int q = 0; q < kWarpStats; ++q) st[q] = warp_sum(st[q]);
     if (lane == 0) {
-        uint32_t *ws = sh.warp_stats + warp * 4;
-        ws[0] = n_touched; ws[1] = n_des; ws[2] = n_add; ws[3] = n_ev;
+#pragma unroll
+        for (int q = 0; q < kWarpStats; ++q) sh.warp_stats[warp * kWarpStats + q] = st[q];
     }
     // steady state: nothing moves, so there is nothing to lay out
     const bool any_runs = cta_or<kBar, kScanThreads>(some_runs != 0);
     RT_TAIL_MARK(2);
 
-    // ---- exclusive prefix sum of run counts over (phase, buffer): warp 0 ----
-    // One warp, consecutive items per lane, one shuffle scan: a CTA-wide scan
-    // costs a second barrier and a pass through shared memory, which is more
-    // than 2*n_buffers/32 additions per lane.
+    // ---- exclusive prefix sum of run counts over (phase, buffer) ----
+    // With at most one item per thread (2*n_buffers <= 256, the usual case) the
+    // thread that computed an item's offset is the one that writes its ranges,
+    // so the offsets stay in registers and one barrier is saved.
     const uint32_t items = (scan_only || !any_runs) ? 0 : 2 * n;
-    uint32_t total = 0;
-    if (warp == 0 && items) {
-        const uint32_t per = (items + 31) / 32, first = lane * per;
+    const bool one_each = items <= (uint32_t)kScanThreads;
+    uint32_t total = 0, n_cpu = 0, my_at = 0;
+    if (items) {
+        const uint32_t per = one_each ? 1u : (items + kScanThreads - 1) / kScanThreads;
+        const uint32_t first = tid * per;
         uint32_t local = 0;
         for (uint32_t k = 0; k < per; ++k) {
             const uint32_t i = first + k;
@@ -288,41 +356,59 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
             }
         }
         const uint32_t incl = warp_inclusive_sum(local, lane);
-        uint32_t run = incl - local;
-        for (uint32_t k = 0; k < per; ++k) {
-            const uint32_t i = first + k;
-            if (i < items) {
-                sh.off[i] = run;
-                const uint32_t phase = i >= n, j = i - phase * n;
-                run += sh.counts[sh.group_of[j] * 2 + phase];
-            }
+        if (lane == 31) sh.warp_tot[warp] = incl;
+        cta_sync<kBar, kScanThreads>();
+        uint32_t base = 0;
+#pragma unroll
+        for (uint32_t k = 0; k < (uint32_t)kTailWarps; ++k) {
+            const uint32_t t = sh.warp_tot[k];
+            base += k < warp ? t : 0u;
+            total += t;
         }
-        if (lane == 31) sh.off[items] = incl;
+        my_at = base + incl - local;
+        if (one_each) {
+            if (tid == n) sh.off[n] = my_at;                  // ranges of phase 0, for the result record
+        } else {
+            uint32_t run = my_at;
+            for (uint32_t k = 0; k < per; ++k) {
+                const uint32_t i = first + k;
+                if (i < items) {
+                    sh.off[i] = run;
+                    const uint32_t phase = i >= n, j = i - phase * n;
+                    run += sh.counts[sh.group_of[j] * 2 + phase];
+                }
+            }
+            cta_sync<kBar, kScanThreads>();
+        }
     }
-    cta_sync<kBar, kScanThreads>();
-    if (items) total = sh.off[items];
-    const uint32_t n_cpu = items ? sh.off[n] : 0;
     RT_TAIL_MARK(3);
 
     // ---- pass B: one thread per (phase, buffer) ----
-    // The thread walks the words of its bitmap's evict or add mask and writes
-    // the runs; where they go is the prefix sum above.  (A warp per (bitmap,
-    // phase) handing its run list to every buffer in turn took ten dependent
-    // rounds for 40 bitmaps: 17 us for 160 ranges.)
+    // Short run lists come ready-made from pass A; longer ones are read off the
+    // mask words.  Where a buffer's ranges go is the prefix sum above.  (A warp
+    // per (bitmap, phase) handing its run list to every buffer in turn took ten
+    // dependent rounds for 40 bitmaps: 17 us for 160 ranges.)
     const unsigned long long block_bytes = p.block_bytes, alloc_bytes = p.alloc_bytes;
     const uint32_t cap = p.cap;
     const int32_t dst_gpu = p.dst_device;
     rt_range *const out = p.out;
-    unsigned long long cpu_bytes = 0, gpu_bytes = 0;
     for (uint32_t i = tid; i < items; i += kScanThreads) {
         const uint32_t phase = i >= n, j = i - phase * n, g = sh.group_of[j];
-        if (!sh.counts[g * 2 + phase]) continue;
+        const uint32_t count = sh.counts[g * 2 + phase];
+        if (!count) continue;
+        const int32_t dst = phase ? dst_gpu : RT_DST_CPU;
+        uint32_t at = one_each ? my_at : sh.off[i];
+        if (count <= kFew) {
+            const uint16_t *few = sh.few + (g * 2 + phase) * 2 * kFew;
+            for (uint32_t q = 0; q < count; ++q)
+                store_range(out, at + q, cap, j, dst, few[2 * q], few[2 * q + 1], block_bytes, alloc_bytes);
+            continue;
+        }
         const uint32_t *m = sh.masks + g * kMaskStride + phase * kWords;
-        uint32_t at = sh.off[i], below_top = 0;
-        unsigned long long moved = 0;
+        uint32_t below_top = 0;
         for (uint32_t k = 0; k < n_words; ++k) {
             const uint32_t word = m[k];
-            uint32_t starts = word & ~((word << 1) | below_top);
+            uint32_t starts = run_starts(word, below_top);
             below_top = word >> 31;
             while (starts) {
                 const uint32_t b = __ffs(starts) - 1;
@@ -335,56 +421,35 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
                     while (k2 < n_words && m[k2] == 0xffffffffu) ++k2;
                     e = (k2 - k) * 32 + (k2 < n_words ? (uint32_t)__ffs(~m[k2]) - 1 : 0u);
                 }
-                const unsigned long long lo = (unsigned long long)(k * 32 + b) * block_bytes;
-                unsigned long long hi = (unsigned long long)(k * 32 + e) * block_bytes;
-                if (hi > alloc_bytes) hi = alloc_bytes;             // final partial block, select.cpp:24188
-                moved += hi - lo;
-                if (at < cap) {
-                    rt_range rg;
-                    rg.buffer = j;
-                    rg.dst = phase ? dst_gpu : RT_DST_CPU;
-                    rg.offset = lo;
-                    rg.bytes = hi - lo;
-                    out[at] = rg;
-                }
+                store_range(out, at, cap, j, dst, k * 32 + b, k * 32 + e, block_bytes, alloc_bytes);
                 ++at;
             }
         }
-        if (phase) gpu_bytes += moved; else cpu_bytes += moved;
     }
     RT_TAIL_MARK(4);
-    if (items) {
-        cpu_bytes = warp_sum64(cpu_bytes);
-        gpu_bytes = warp_sum64(gpu_bytes);
-    }
-    if (lane == 0) {
-        sh.warp_bytes[warp * 2 + 0] = cpu_bytes;
-        sh.warp_bytes[warp * 2 + 1] = gpu_bytes;
-    }
     cta_sync<kBar, kScanThreads>();
     if (tid == 0) {
+        if (items) n_cpu = sh.off[n];
         rt_plan_result res;
-        uint32_t st[4] = {0, 0, 0, 0};
-        unsigned long long by[2] = {0, 0};
+        uint32_t sum[kWarpStats] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-        for (int k = 0; k < kTailWarps; ++k) {
+        for (int k = 0; k < kTailWarps; ++k)
 #pragma unroll
-            for (int q = 0; q < 4; ++q) st[q] += sh.warp_stats[k * 4 + q];
-            by[0] += sh.warp_bytes[k * 2 + 0];
-            by[1] += sh.warp_bytes[k * 2 + 1];
-        }
+            for (int q = 0; q < kWarpStats; ++q) sum[q] += sh.warp_stats[k * kWarpStats + q];
+        // what the last block of a buffer lacks to a whole block
+        const unsigned long long short_by = (unsigned long long)n_blocks * block_bytes - alloc_bytes;
         res.n_ranges = total;
         res.n_cpu_ranges = n_cpu;
         res.flags = (total > cap ? RT_RESULT_OVERFLOW : 0u) | (invalid ? RT_RESULT_SLOT_RANGE : 0u) | eflags;
-        res.blocks_touched = st[0];
-        res.blocks_desired = st[1];
-        res.blocks_added = st[2];
-        res.blocks_evicted = st[3];
+        res.blocks_touched = sum[0];
+        res.blocks_desired = sum[1];
+        res.blocks_added = sum[2];
+        res.blocks_evicted = sum[3];
         res.reserved = 0;
         res.invalid_slots = invalid;
         res.ignored_slots = ignored;
-        res.cpu_bytes = by[0];
-        res.gpu_bytes = by[1];
+        res.cpu_bytes = scan_only ? 0 : sum[4] * block_bytes - sum[6] * short_by;
+        res.gpu_bytes = scan_only ? 0 : sum[5] * block_bytes - sum[7] * short_by;
         *p.result = res;
         // leave the scratch clean for the next launch
         GlobalScratch &gl = *p.global;
