@@ -406,8 +406,8 @@ def run_ours(args):
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, mean of 3 launches), keyed by
 # (workload, tma); a configuration that was not captured reports null.
 PROFILED_TRAFFIC_BYTES = {
-    ("target", False): 182_067_000,   # 178.34 MB read + 3.73 MB written
-    ("target", True): 183_275_000,    # 178.34 MB read + 4.94 MB written
+    ("target", False): 181_904_000,   # 178.34 MB read + 3.57 MB written
+    ("target", True): 182_592_000,    # 178.33 MB read + 4.26 MB written
 }
 
 

@@ -314,8 +314,13 @@ __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, Ha
 // keeps its shared block map across the units of a bitmap and hands over once
 // per (CTA, bitmap).  Inside a bitmap the next unit's loads are issued before
 // the current unit is marked.
+#ifdef RT_MIN_CTAS
+#define RT_SCAN_BOUNDS __launch_bounds__(kScanThreads, RT_MIN_CTAS)
+#else
+#define RT_SCAN_BOUNDS __launch_bounds__(kScanThreads)
+#endif
 template <bool kPow2, typename Id>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void RT_SCAN_BOUNDS
 scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
     using Vec = typename IdTraits<Id>::Vec;
     constexpr int kPer = IdTraits<Id>::kPer;
