@@ -292,15 +292,6 @@ __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, Ha
 #ifdef RT_TRACE
     if (threadIdx.x == 0) g_trace[2] = now_ns();
 #endif
-#ifdef RT_TRACE_WARM
-    {   // experiment: run the tail once without side effects so the timed run finds its code cached
-        PlanArgs dry = p;
-        dry.flags |= RT_PLAN_DRY_RUN;
-        plan_tail<kBar>(dry, &p.groups[0].want[0], false, tail_mem);
-        cta_sync<kBar, kScanThreads>();
-        if (threadIdx.x == 0) g_trace[2] = now_ns();
-    }
-#endif
     plan_tail<kBar>(p, &p.groups[0].want[0], true, tail_mem);
 #ifdef RT_TRACE
     if (threadIdx.x == 0) g_trace[3] = now_ns();

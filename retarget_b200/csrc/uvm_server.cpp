@@ -41,6 +41,8 @@ struct Allocation {
 };
 
 struct Server {
+    std::mutex control;                  // start / stop, held for the whole call; no thread of the
+                                         // server ever takes it, so joining under it cannot deadlock
     std::mutex life;
     std::mutex state;
     std::condition_variable wake;        // worker: a job arrived / stop
@@ -361,11 +363,20 @@ void listener_main() {
 }
 
 void unlink_owned_socket() {
+    std::string path;
+    dev_t dev;
+    ino_t ino;
+    {
+        std::lock_guard<std::mutex> lock(g.state);
+        path = g.socket_path;
+        dev = g.socket_dev;
+        ino = g.socket_ino;
+        g.socket_ino = 0;
+    }
     struct stat st;
-    if (g.socket_ino && lstat(g.socket_path.c_str(), &st) == 0 && S_ISSOCK(st.st_mode) &&
-        st.st_uid == getuid() && st.st_dev == g.socket_dev && st.st_ino == g.socket_ino)
-        unlink(g.socket_path.c_str());
-    g.socket_ino = 0;
+    if (ino && lstat(path.c_str(), &st) == 0 && S_ISSOCK(st.st_mode) && st.st_uid == getuid() &&
+        st.st_dev == dev && st.st_ino == ino)
+        unlink(path.c_str());
 }
 
 int open_socket(const char *path) {
@@ -382,16 +393,21 @@ int open_socket(const char *path) {
     if (fd < 0) return RT_ERR_IO;
     // never remove a path that already exists, even if it looks stale
     if (bind(fd, (struct sockaddr *)&address, sizeof(address)) != 0) { close(fd); return RT_ERR_IO; }
-    g.socket_path = path;
     struct stat st;
     if (lstat(path, &st) != 0) { close(fd); return RT_ERR_IO; }
-    g.socket_dev = st.st_dev;
-    g.socket_ino = st.st_ino;
+    {
+        // status readers look at these under `state`
+        std::lock_guard<std::mutex> lock(g.state);
+        g.socket_path = path;
+        g.socket_dev = st.st_dev;
+        g.socket_ino = st.st_ino;
+    }
     if (chmod(path, 0600) != 0 || listen(fd, 16) != 0) {
         close(fd);
         unlink_owned_socket();
         return RT_ERR_IO;
     }
+    std::lock_guard<std::mutex> lock(g.state);
     g.listen_fd = fd;
     return RT_OK;
 }
@@ -407,7 +423,7 @@ using rt::g;
 extern "C" {
 
 int rt_uvm_start(const rt_uvm_config *config) {
-    std::lock_guard<std::mutex> life(g.life);
+    std::lock_guard<std::mutex> control(g.control);
     {
         std::lock_guard<std::mutex> st(g.state);
         if (g.running) return RT_ERR_BUSY;
@@ -423,27 +439,39 @@ int rt_uvm_start(const rt_uvm_config *config) {
         if (s && rt::parse_u64(s, strlen(s), &mb) && mb >= 1 && mb <= 256) chunk = mb << 20;
     }
     long page = sysconf(_SC_PAGESIZE);
-    g.page = page > 0 ? (uint64_t)page : 4096;
-    g.chunk = chunk;
-    g.batch = cfg.batch_bytes ? cfg.batch_bytes : (256ull << 20);
-    if (g.batch < g.chunk) g.batch = g.chunk;
-    g.n_streams = cfg.streams ? cfg.streams : 4;
-    g.owner = getpid();
-    g.stop = false;
-    g.listen_fd = -1;
-    g.socket_path.clear();
+    {
+        // callers of the other entry points may be running while the server
+        // restarts: everything they read changes under the locks they hold
+        std::lock_guard<std::mutex> life(g.life);
+        std::lock_guard<std::mutex> st(g.state);
+        g.page = page > 0 ? (uint64_t)page : 4096;
+        g.chunk = chunk;
+        g.batch = cfg.batch_bytes ? cfg.batch_bytes : (256ull << 20);
+        if (g.batch < g.chunk) g.batch = g.chunk;
+        g.n_streams = cfg.streams ? cfg.streams : 4;
+        g.owner = getpid();
+        g.stop = false;
+        g.listen_fd = -1;
+        g.socket_path.clear();
+    }
     if (cfg.listen) {
         int st = rt::open_socket(cfg.socket_path);
         if (st != RT_OK) return st;
     }
     g.worker = std::thread(rt::worker_main);
-    if (g.listen_fd >= 0) g.listener = std::thread(rt::listener_main);
+    bool listening;
+    {
+        std::lock_guard<std::mutex> st(g.state);
+        listening = g.listen_fd >= 0;
+    }
+    if (listening) g.listener = std::thread(rt::listener_main);
     std::lock_guard<std::mutex> st(g.state);
     g.running = true;
     return RT_OK;
 }
 
 int rt_uvm_stop(void) {
+    std::lock_guard<std::mutex> control(g.control);
     {
         std::lock_guard<std::mutex> st(g.state);
         if (!g.running) return RT_ERR_NOT_RUNNING;
@@ -453,11 +481,11 @@ int rt_uvm_stop(void) {
     }
     if (g.listener.joinable()) g.listener.join();
     if (g.worker.joinable()) g.worker.join();
-    if (g.listen_fd >= 0) close(g.listen_fd);
-    g.listen_fd = -1;
     rt::unlink_owned_socket();
     std::lock_guard<std::mutex> life(g.life);
     std::lock_guard<std::mutex> st(g.state);
+    if (g.listen_fd >= 0) close(g.listen_fd);
+    g.listen_fd = -1;
     g.running = false;
     g.busy = false;
     g.job.clear();

@@ -98,6 +98,29 @@ def test_random_small_multi_step(flags, evict):
         run_steps(batches, evict=evict, flags=flags)
 
 
+@pytest.mark.parametrize("evict", [True, False])
+def test_wide_layouts(evict):
+    """Shapes that take the tail's general paths: more bitmaps than one pass of
+    the CTA holds (100 x 1024 blocks), more (phase, buffer) pairs than threads
+    (200 and 300 buffers), long run lists, a partial last block."""
+    rng = np.random.default_rng(11)
+    shapes = [
+        # 100 bitmaps of 1024 blocks, 200 buffers
+        dict(layers=100, pool_slots=8192, bytes_per_slot=512, shared=False, n_req=2, max_len=1500,
+             budget=200, block_bytes=4096),
+        # one bitmap shared by 300 buffers, 1001 blocks of 6 slots, last block partial
+        dict(layers=150, pool_slots=6001, bytes_per_slot=2048, shared=True, n_req=5, max_len=2500,
+             budget=80, block_bytes=12288),
+        # 128 bitmaps (the most a plan can hold), 256 buffers, 64 blocks
+        dict(layers=128, pool_slots=65536, bytes_per_slot=2048, shared=False, n_req=2, max_len=3000,
+             budget=9),
+    ]
+    for shape in shapes:
+        batches = [random_batch(rng, **shape) for _ in range(3)]
+        batches.append(dataclasses.replace(batches[0], budget_blocks=max(1, shape["budget"] // 3)))
+        run_steps(batches, evict=evict, flags=(0, np.int64), literal=False)
+
+
 @pytest.mark.parametrize("flags", MODES)
 def test_ragged_and_empty_inputs(flags):
     rng = np.random.default_rng(7)
