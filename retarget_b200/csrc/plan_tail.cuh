@@ -179,12 +179,18 @@ __device__ __forceinline__ void store_range(rt_range *out, uint32_t at, uint32_t
     const unsigned long long lo = (unsigned long long)begin * block_bytes;
     unsigned long long hi = (unsigned long long)end * block_bytes;
     if (hi > alloc_bytes) hi = alloc_bytes;                     // final partial block, select.cpp:24188
-    rt_range rg;
-    rg.buffer = buffer;
-    rg.dst = dst;
-    rg.offset = lo;
-    rg.bytes = hi - lo;
-    out[at] = rg;
+    // 24 bytes as one 16-byte and one 8-byte store (which half is 16-byte aligned
+    // alternates with `at`): when a plan has thousands of ranges the tail is bound
+    // by the number of store instructions one SM can retire
+    const unsigned long long head = (unsigned long long)buffer | ((unsigned long long)(uint32_t)dst << 32);
+    unsigned long long *q = reinterpret_cast<unsigned long long *>(out + at);
+    if ((reinterpret_cast<uintptr_t>(q) & 15u) == 0) {
+        *reinterpret_cast<ulonglong2 *>(q) = make_ulonglong2(head, lo);
+        q[2] = hi - lo;
+    } else {
+        q[0] = head;
+        *reinterpret_cast<ulonglong2 *>(q + 1) = make_ulonglong2(lo, hi - lo);
+    }
 }
 
 // --------------------------------------------------------------------------
