@@ -402,6 +402,117 @@ def run_ours(args):
     ranks.stop()
 
 
+# --------------------------------------------------------------------------
+# event-driven path: device-resident feedback state, one plan per decode step
+# --------------------------------------------------------------------------
+def run_feedback(args):
+    """--workload feedback: the incremental decode trace (65,536-slot pool, 40
+    layers, Poisson arrivals, one token per live request per step) through
+    rt_feedback_alloc / rt_feedback_attention / rt_feedback_plan, every index
+    tensor already in HBM; beside it the Python restatement of
+    SlotFeedback.consume -> publish -> target_blocks -> choose -> blocksv on one
+    host core.  One GPU only."""
+    import torch
+    from retarget_b200 import capi, workloads
+    from retarget_b200.feedback import DeviceFeedback
+    from retarget_b200.planner import DevicePlanner, result_from_tensor
+
+    K, W = args.steps, args.warmup
+    layout = workloads.Layout(40, 2048, 65536)
+    trace = workloads.decode_trace(0, steps=W + K, initial_requests=48)
+    budget, max_blocks, active, refresh = 16, 16, 2.0, 10.0
+    times = [100.0 + 0.03 * i for i in range(len(trace))]
+    cpu = None
+    if not args.no_cpu:
+        from oracle import compose
+        from oracle import ref_policy as rp
+        spec = rp.SlotSpec(block_tokens=layout.block_tokens, max_blocks_per_update=max_blocks,
+                           active_seconds=active, refresh_seconds=refresh)
+        session = compose.FeedbackSession(layout, spec, budget, evict=True)
+        cpu_ranges, t_cpu = 0, 0.0
+        for i, ev in enumerate(trace):
+            t0 = time.perf_counter()
+            if len(ev.alloc_slots):
+                session.alloc(ev.alloc_slots, ev.free_head, times[i] - 0.002)
+            session.attention(ev.read_slots, ev.write_slots, times[i])
+            out, _ = session.plan(times[i] + 0.001)
+            if i >= W:
+                t_cpu += time.perf_counter() - t0
+                cpu_ranges += len(out)
+        cpu = {"value": t_cpu / K * 1e6, "unit": UNIT, "cores": 1, "kind": "port",
+               "sample": f"all {K} timed steps through the Python restatement of the reference's "
+                         f"event-driven chain", "ranges": cpu_ranges}
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; retarget_b200 has no CPU path to fall back to")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    planner = DevicePlanner(layout, 0)
+    fb = DeviceFeedback(planner, pid=0)
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    d_steps = [(up(ev.alloc_slots) if len(ev.alloc_slots) else None,
+                up(ev.free_head) if ev.free_head is not None and len(ev.alloc_slots) else None,
+                up(ev.read_slots), up(ev.write_slots)) for ev in trace]
+    d_out = torch.zeros((1 << 14) * 24, dtype=torch.uint8, device=dev)
+    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
+    h = stream.cuda_stream
+    launches = 0
+
+    def step(i):
+        nonlocal launches
+        a, head, r, w = d_steps[i]
+        if a is not None:
+            fb.alloc(a, times[i] - 0.002, head, h)
+        fb.attention(r, w, times[i], h)
+        fb.plan(times[i] + 0.001, budget=budget, max_blocks_per_update=max_blocks, active_seconds=active,
+                refresh_seconds=refresh, flags=capi.RT_PLAN_EVICT, d_out=d_out, d_result=d_res, stream=h)
+
+    sampler = ClockSampler(0)
+    for i in range(W):
+        step(i)
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record(stream)
+    gpu_ranges = 0
+    for i in range(W, W + K):
+        step(i)
+    ev[1].record(stream)
+    torch.cuda.synchronize()
+    us = ev[0].elapsed_time(ev[1]) * 1e3 / K
+    # same trace again, synchronising every step, to count the ranges and to
+    # get the latency a caller sees (launch + run + read-back of the result)
+    fb.clear(99.0, h)
+    planner.set_resident([set()])
+    t_sync = 0.0
+    for i in range(W + K):
+        t0 = time.perf_counter()
+        step(i)
+        stream.synchronize()
+        n = result_from_tensor(d_res)["n_ranges"]
+        if i >= W:
+            t_sync += time.perf_counter() - t0
+            gpu_ranges += n
+    clocks = sampler.stop()
+    ids = sum(len(e.alloc_slots) + len(e.read_slots) + len(e.write_slots) for e in trace[W:]) / K
+    line = {"metric": "feedback_plan_us_per_decode_step", "value": us, "unit": UNIT, "n_gpus": 1, "steps": K,
+            "warmup": W, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+            "config": {"workload": "incremental decode trace L40 S65536, event-driven feedback state",
+                       "layers": 40, "pool_slots": 65536, "blocks_per_bitmap": layout.n_blocks,
+                       "budget_blocks": budget, "event_ids_per_step": ids,
+                       "live_requests_last_step": trace[-1].live},
+            "e2e": {"value": t_sync / K * 1e6, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 64,
+                    "note": "ids already on the device; launch + run + result read-back, one step at a time"},
+            "ranges_total": gpu_ranges, "clocks": clocks}
+    if cpu:
+        line["cpu_baseline"] = cpu
+        line["ranges_match_cpu"] = cpu["ranges"] == gpu_ranges
+    emit(line)
+    fb.close()
+    planner.close()
+
+
 # DRAM bytes per launch of the scan kernel from the ncu captures summarised under
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, mean of 3 launches), keyed by
 # (workload, tma); a configuration that was not captured reports null.
@@ -440,14 +551,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="target",
-                    choices=["target", "steady", "fragmented", "sparse", "full_refresh", "tp_shard"])
+                    choices=["target", "steady", "fragmented", "sparse", "full_refresh", "tp_shard", "feedback"])
     ap.add_argument("--tma", action="store_true", help="stage ids with bulk async copies (TMA)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-variants", action="store_true", help="skip the secondary measurements")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     quiet_stdout()
-    if args.impl == "reference":
+    if args.workload == "feedback":
+        run_feedback(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -185,45 +185,63 @@ struct RankPolicy {
     double refresh_seconds;
 };
 
-struct RankKey {
-    uint32_t cls;              // 0 active read, 1 active write, 2 free-list head, 3 history, 7 unranked
-    unsigned long long tkey;   // sortable image of -t (0 where time does not matter)
-    uint32_t aux;              // class 2: position in the free head; class 3: 0 read entry, 1 write entry
-};
-
 // Doubles -> unsigned integers with the same order.
 __device__ __forceinline__ unsigned long long ordered_bits(double x) {
     unsigned long long u = (unsigned long long)__double_as_longlong(x);
     return (u >> 63) ? ~u : (u | 0x8000000000000000ull);
 }
 
-__device__ __forceinline__ bool key_less(const RankKey &a, uint32_t ia, const RankKey &b, uint32_t ib) {
-    if (a.cls != b.cls) return a.cls < b.cls;
-    if (a.tkey != b.tkey) return a.tkey < b.tkey;
-    if (a.aux != b.aux) return a.aux < b.aux;
-    return ia < ib;
+// Rank key of a block as two 64-bit words that compare like the tuple
+// (class, -t, aux, block id):
+//   class  0 active read, 1 active write, 2 free-list head, 3 history, 7 unranked
+//   -t     sortable image of the stamp (0 where time does not matter)
+//   aux    class 2: position in the free head (< 4096); class 3: 0 read entry, 1 write entry
+//   hi = class:3 | tkey[63:3]        lo = tkey[2:0]:3 | aux:32 | block id:10
+// Block ids are distinct, so no two keys are equal.
+struct RankKey {
+    unsigned long long hi, lo;
+};
+__device__ __forceinline__ RankKey make_key(uint32_t cls, unsigned long long tkey, uint32_t aux, uint32_t id) {
+    RankKey k;
+    k.hi = ((unsigned long long)cls << 61) | (tkey >> 3);
+    k.lo = ((tkey & 7ull) << 61) | ((unsigned long long)aux << 10) | id;
+    return k;
+}
+__device__ __forceinline__ bool key_less(const RankKey &a, const RankKey &b) {
+    return a.hi < b.hi || (a.hi == b.hi && a.lo < b.lo);
 }
 
-// sets: [0..31] evict words, [32..63] add words (read by the plan tail in
-// explicit mode).  counts: [0] desired [1] added [2] evicted.
+// One compare-exchange step of the bitonic network: this thread keeps the
+// smaller or the larger of its key and its partner's.
+__device__ __forceinline__ void keep_one(RankKey &mine, const RankKey &theirs, bool keep_min) {
+    if (key_less(theirs, mine) == keep_min) mine = theirs;
+}
+
+// Working memory of the plan tail inside the ranking kernel: the sort buffers,
+// free once the order is known.
+static_assert(2 * 2 * kRankThreads * sizeof(unsigned long long) >= tail_smem_bytes(1, RT_MAX_BUFFERS),
+              "sort buffers too small to host the plan tail");
+
+// Ranking, selection and range emission in one launch.  blockDim = the power of
+// two that covers the blocks (at least kScanThreads, which the tail needs).
+//   sets: [0..31] evict words, [32..63] add words (read back by the tail part)
 __global__ void __launch_bounds__(kRankThreads)
 feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *resident, uint32_t *sets,
-                     uint32_t *counts) {
-    __shared__ RankKey s_key[kRankThreads];
-    __shared__ uint16_t s_idx[kRankThreads];
+                     const __grid_constant__ PlanArgs tail) {
+    __shared__ __align__(16) unsigned long long s_swap[2][2][kRankThreads];   // [buffer][hi|lo][thread]
     __shared__ int s_free_pos[kRankThreads];
     __shared__ uint32_t s_warp[32];
     __shared__ uint8_t s_sel[kRankThreads], s_des[kRankThreads];
-    const uint32_t b = threadIdx.x, lane = b & 31, warp = b >> 5;
+    const uint32_t b = threadIdx.x, lane = b & 31, warp = b >> 5, n_threads = blockDim.x;
     s_free_pos[b] = 0x7fffffff;
     __syncthreads();
     const int n_free = *st.free_count;
-    for (int i = b; i < n_free; i += kRankThreads) {
+    for (int i = b; i < n_free; i += n_threads) {
         long long slot = st.free_head[i];
         if (slot >= 0) {
             unsigned long long blk = geo.shift >= 0 ? ((unsigned long long)slot >> geo.shift)
                                                     : ((unsigned long long)slot / geo.block_tokens);
-            if (blk < kRankThreads) atomicMin(&s_free_pos[blk], i);
+            if (blk < n_threads) atomicMin(&s_free_pos[blk], i);
         }
     }
     __syncthreads();
@@ -232,36 +250,40 @@ feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *r
     const bool recent_r = isfinite(r) && pol.at - r <= 30.0, recent_w = isfinite(w) && pol.at - w <= 30.0;
     const bool active_r = recent_r && pol.now - r <= pol.active_seconds;
     const bool active_w = recent_w && pol.now - w <= pol.active_seconds;
-    RankKey k;
-    k.cls = 7; k.tkey = 0; k.aux = 0;
-    if (active_r) { k.cls = 0; k.tkey = ordered_bits(-r); }
-    else if (active_w) { k.cls = 1; k.tkey = ordered_bits(-w); }
-    else if (s_free_pos[b] != 0x7fffffff) { k.cls = 2; k.aux = (uint32_t)s_free_pos[b]; }
+    RankKey k = make_key(7, 0, 0, b);
+    if (active_r) k = make_key(0, ordered_bits(-r), 0, b);
+    else if (active_w) k = make_key(1, ordered_bits(-w), 0, b);
+    else if (real && s_free_pos[b] != 0x7fffffff) k = make_key(2, 0, (uint32_t)s_free_pos[b], b);
     else if (recent_r || recent_w) {
         // first of the block's entries in reads+writes sorted by -t (stable: reads first)
         const bool use_r = recent_r && (!recent_w || r >= w);
-        k.cls = 3; k.tkey = ordered_bits(-(use_r ? r : w)); k.aux = use_r ? 0u : 1u;
+        k = make_key(3, ordered_bits(-(use_r ? r : w)), use_r ? 0u : 1u, b);
     }
-    s_key[b] = k;
-    s_idx[b] = (uint16_t)b;
-    __syncthreads();
-    // bitonic sort of block ids by key
-    for (uint32_t size = 2; size <= kRankThreads; size <<= 1) {
+    // Bitonic sort, one key per thread, keys in registers: partners up to 16
+    // lanes away trade by shuffle, farther ones through shared memory (two
+    // buffers in turn, so one barrier per step is enough).
+    uint32_t turn = 0;
+    for (uint32_t size = 2; size <= n_threads; size <<= 1) {
         for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
-            uint32_t partner = b ^ stride;
-            if (partner > b) {
-                uint32_t ia = s_idx[b], ib = s_idx[partner];
-                bool up = (b & size) == 0;
-                bool swap = up ? key_less(s_key[ib], ib, s_key[ia], ia) : key_less(s_key[ia], ia, s_key[ib], ib);
-                if (swap) { s_idx[b] = (uint16_t)ib; s_idx[partner] = (uint16_t)ia; }
+            RankKey other;
+            if (stride < 32) {
+                other.hi = __shfl_xor_sync(0xffffffffu, k.hi, stride);
+                other.lo = __shfl_xor_sync(0xffffffffu, k.lo, stride);
+            } else {
+                s_swap[turn][0][b] = k.hi;
+                s_swap[turn][1][b] = k.lo;
+                __syncthreads();
+                other.hi = s_swap[turn][0][b ^ stride];
+                other.lo = s_swap[turn][1][b ^ stride];
+                turn ^= 1;
             }
-            __syncthreads();
+            // ascending runs keep the minimum at the lower index
+            keep_one(k, other, ((b & size) == 0) == ((b & stride) == 0));
         }
     }
     // position b of the sorted order holds block `blk`
-    const uint32_t blk = s_idx[b];
-    const RankKey kb = s_key[blk];
-    const bool desired = kb.cls != 7 && b < pol.budget;
+    const uint32_t blk = (uint32_t)(k.lo & 1023u);
+    const bool desired = (k.hi >> 61) != 7 && b < pol.budget;
     const bool held = (resident[blk >> 5] >> (blk & 31)) & 1u;
     bool todo = false;
     if (desired) {
@@ -292,16 +314,18 @@ feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *r
     const uint32_t add_word = __ballot_sync(0xffffffffu, sel_b);
     const uint32_t evict_word = __ballot_sync(0xffffffffu, evict_b);
     const uint32_t keep_word = __ballot_sync(0xffffffffu, (held_b && des_b) || sel_b);
-    const uint32_t des_word = __ballot_sync(0xffffffffu, des_b);
-    __syncthreads();
+    __syncthreads();                        // every thread has read `resident`
     if (lane == 0) {
         sets[warp] = evict_word;
         sets[kWords + warp] = add_word;
         if (!(pol.flags & RT_PLAN_DRY_RUN)) resident[warp] = keep_word;
-        atomicAdd(&counts[0], __popc(des_word));
-        atomicAdd(&counts[1], __popc(add_word));
-        atomicAdd(&counts[2], __popc(evict_word));
     }
+    if (b == 0)                             // words of blocks beyond this launch's threads
+        for (uint32_t wv = n_threads >> 5; wv < (uint32_t)kWords; ++wv) sets[wv] = sets[kWords + wv] = 0;
+    __syncthreads();                        // the words above are visible to the whole CTA
+    // ---- byte ranges: the plan tail, run by the first kScanThreads threads ----
+    if (b >= (uint32_t)kScanThreads) return;
+    plan_tail<1>(tail, sets, false, reinterpret_cast<unsigned char *>(&s_swap[0][0][0]));
 }
 
 }  // namespace rt
@@ -505,14 +529,15 @@ int rt_feedback_plan(rt_feedback *fb, const rt_feedback_policy *policy, double a
     pol.commit = now;
     pol.active_seconds = policy->active_seconds;
     pol.refresh_seconds = policy->refresh_seconds;
-    FB_CUDA(cudaMemsetAsync(fb->d_counts, 0, 16, s));
-    rt::feedback_rank_kernel<<<1, rt::kRankThreads, 0, s>>>(fb->geo, fb->st, pol, fb->view.d_resident,
-                                                          fb->d_sets, fb->d_counts);
-    FB_CUDA(cudaGetLastError());
     rt::PlanArgs p;
     rt::plan_fill_args(fb->plan, p, RT_MAX_BLOCKS, policy->flags | RT_PLAN_DRY_RUN, out, cap, result);
     p.explicit_sets = 1;
-    FB_CUDA(rt::launch_plan_tail(fb->d_sets, p, s));
+    // one thread per block id, a power of two for the sorting network, and at
+    // least the CTA the tail part needs
+    uint32_t threads = rt::kScanThreads;
+    while (threads < fb->geo.n_blocks) threads <<= 1;
+    rt::feedback_rank_kernel<<<1, threads, 0, s>>>(fb->geo, fb->st, pol, fb->view.d_resident, fb->d_sets, p);
+    FB_CUDA(cudaGetLastError());
     return RT_OK;
 }
 
