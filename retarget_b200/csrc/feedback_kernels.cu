@@ -32,7 +32,8 @@ struct FeedbackState {
     double *commit_time;       // [n_blocks]
     long long *free_head;      // [kFreeHeadMax] slot ids, queue order
     int32_t *free_count;       // [1]
-    uint32_t *event_blocks;    // [kWords] scratch: blocks touched by the current event
+    uint32_t *event_blocks;    // [2 * kWords] scratch: blocks touched by the current event's two lists
+    uint32_t *arrivals;        // [1] scratch: CTAs of the current event that have finished marking
     uint32_t *slot_marks;      // [(capacity + 32) / 32] scratch: slots of the current alloc event
     unsigned long long *bad;   // [2] invalid / ignored ids seen so far
 };
@@ -51,18 +52,33 @@ __device__ __forceinline__ uint32_t block_of_slot(uint32_t slot, const Geometry 
     return (((slot - q) >> 1) + q) >> g.magic_shift;
 }
 
-// ids of one event -> event_blocks words; for allocations also generations[id] += 1
-// (once per occurrence, like `generations[begin:end] += 1` over order-preserving
-// runs) and a mark per slot for the free-head filter.
-__global__ void __launch_bounds__(256)
-feedback_mark_kernel(const long long *ids, long long n, Geometry geo, FeedbackState st, int alloc) {
-    __shared__ uint8_t s_map[RT_MAX_BLOCKS];
-    reinterpret_cast<uint32_t *>(s_map)[threadIdx.x] = 0;
-    __syncthreads();
-    uint32_t invalid = 0, ignored = 0;
+// --------------------------------------------------------------------------
+// one launch per event
+// --------------------------------------------------------------------------
+// Every CTA marks the blocks its share of the ids falls in (a byte map per
+// list in shared memory, folded into the event words with one atomicOr per
+// non-zero word); for allocations it also does generations[id] += 1 -- once per
+// occurrence, like `generations[begin:end] += 1` over order-preserving runs --
+// and sets a mark per slot for the free-head filter.  The CTA that arrives last
+// then does what needs the whole event: the stamps, the free-list head, the
+// clean-up of the scratch words.  Nobody waits for anybody.
+struct EventArgs {
+    const long long *ids_a;    // attention: read ids; allocation: the allocated slots
+    long long n_a;
+    const long long *ids_b;    // attention: written ids; allocation: unused
+    long long n_b;
+    const long long *fresh;    // allocation: the new free-list head, or null
+    int n_fresh;
+    int alloc;                 // 0 attention, 1 allocation
+    double t;
+};
+
+__device__ __forceinline__ void mark_ids(const long long *ids, long long n, const Geometry &geo,
+                                         const FeedbackState &st, int alloc, uint8_t *s_map, uint32_t &invalid,
+                                         uint32_t &ignored) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (long long)gridDim.x * blockDim.x) {
-        long long s = ids[i];
+        long long s = __ldcs(ids + i);
         if ((unsigned long long)(s - 1) < geo.capacity) {
             uint32_t v = (uint32_t)s;
             s_map[block_of_slot(v, geo)] = 1;
@@ -77,74 +93,44 @@ feedback_mark_kernel(const long long *ids, long long n, Geometry geo, FeedbackSt
             ++invalid;
         }
     }
-    __syncthreads();
+}
+
+// Byte map -> the event's words (call between two CTA barriers).
+__device__ __forceinline__ void flush_event_map(const uint8_t *s_map, uint32_t *words) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         uint32_t word = warp * 4 + k;
         uint32_t bits = __ballot_sync(0xffffffffu, s_map[word * 32 + lane] != 0);
-        if (lane == 0 && bits) atomicOr(&st.event_blocks[word], bits);
-    }
-    uint32_t inv = warp_sum(invalid), ign = warp_sum(ignored);
-    if (lane == 0) {
-        if (inv) atomicAdd(&st.bad[0], (unsigned long long)inv);
-        if (ign) atomicAdd(&st.bad[1], (unsigned long long)ign);
+        if (lane == 0 && bits) atomicOr(&words[word], bits);
     }
 }
 
-// Stamps the blocks of the current event and clears the event words.
-//   kind 0: read_seen = t        (slot_feedback.py:72-73)
-//   kind 1: write_seen = t       (slot_feedback.py:74-75)
-//   kind 2: versions[b] = max(generations[b*T .. (b+1)*T)), write_seen = t   (:59-62)
-__global__ void __launch_bounds__(256)
-feedback_stamp_kernel(Geometry geo, FeedbackState st, int kind, double t) {
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (uint32_t b = warp; b < geo.n_blocks; b += blockDim.x >> 5) {
-        if (!((st.event_blocks[b >> 5] >> (b & 31)) & 1u)) continue;      // uniform over the warp
-        if (kind == 2) {
-            unsigned long long lo = (unsigned long long)b * geo.block_tokens;
-            unsigned long long hi = lo + geo.block_tokens;
-            if (hi > geo.capacity + 1) hi = geo.capacity + 1;
-            int best = 0;
-            for (unsigned long long s = lo + lane; s < hi; s += 32) best = max(best, st.generations[s]);
-            best = __reduce_max_sync(0xffffffffu, best);
-            if (lane == 0) { st.versions[b] = best; st.write_seen[b] = t; }
-        } else if (lane == 0) {
-            (kind == 0 ? st.read_seen : st.write_seen)[b] = t;
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x < kWords) st.event_blocks[threadIdx.x] = 0;
-}
-
-// Free-list head.  replace = 1: the event carried a fresh head (slot_feedback.py:63-64).
-// replace = 0: drop the slots this event allocated from the known head, keeping the
-// order (slot_feedback.py:65-70).  One CTA; the head is at most 4096 entries.
-__global__ void __launch_bounds__(1024)
-feedback_free_head_kernel(FeedbackState st, const long long *fresh, int n_fresh, int replace,
-                          unsigned long long capacity) {
-    __shared__ int s_warp[32];
-    __shared__ int s_base;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (replace) {
+// Free-list head, by one CTA.  With a fresh head the event replaces it
+// (slot_feedback.py:63-64); without, the slots this event allocated are dropped
+// from the known head, order kept (slot_feedback.py:65-70).
+__device__ void update_free_head(const FeedbackState &st, const long long *fresh, int n_fresh,
+                                 unsigned long long capacity, int *s_warp, int *s_base) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+    if (fresh) {
         int n = n_fresh < kFreeHeadMax ? n_fresh : kFreeHeadMax;
         for (int i = tid; i < n; i += blockDim.x) st.free_head[i] = fresh[i];
         if (tid == 0) *st.free_count = n;
         return;
     }
     const int n = *st.free_count;
-    if (tid == 0) s_base = 0;
+    if (tid == 0) *s_base = 0;
     __syncthreads();
     for (int start = 0; start < n; start += blockDim.x) {
         int i = start + tid;
         long long slot = i < n ? st.free_head[i] : 0;
         bool keep = i < n;
         if (keep && (unsigned long long)slot <= capacity)
-            keep = !((st.slot_marks[(uint32_t)slot >> 5] >> ((uint32_t)slot & 31)) & 1u);
+            keep = !((__ldcg(&st.slot_marks[(uint32_t)slot >> 5]) >> ((uint32_t)slot & 31)) & 1u);
         uint32_t mask = __ballot_sync(0xffffffffu, keep);
         if (lane == 0) s_warp[warp] = __popc(mask);
         __syncthreads();
-        int before = s_base;
+        int before = *s_base;
         for (int w = 0; w < warp; ++w) before += s_warp[w];
         int pos = before + __popc(mask & ((1u << lane) - 1u));
         __syncthreads();                       // everyone has read its slot before anyone writes
@@ -152,22 +138,70 @@ feedback_free_head_kernel(FeedbackState st, const long long *fresh, int n_fresh,
         __syncthreads();
         if (tid == 0) {
             int total = 0;
-            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += s_warp[w];
-            s_base += total;
+            for (int w = 0; w < n_warps; ++w) total += s_warp[w];
+            *s_base += total;
         }
         __syncthreads();
     }
-    if (tid == 0) *st.free_count = s_base;
+    if (tid == 0) *st.free_count = *s_base;
 }
 
-// Clears the per-slot marks of an alloc event (second pass over the same ids).
 __global__ void __launch_bounds__(256)
-feedback_unmark_kernel(const long long *ids, long long n, unsigned long long capacity, FeedbackState st) {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-         i += (long long)gridDim.x * blockDim.x) {
-        long long s = ids[i];
-        if ((unsigned long long)s <= capacity) st.slot_marks[(uint32_t)s >> 5] = 0;
+feedback_event_kernel(EventArgs ev, Geometry geo, FeedbackState st) {
+    __shared__ uint8_t s_map[2][RT_MAX_BLOCKS];
+    __shared__ int s_warp[8], s_base, s_last;
+    reinterpret_cast<uint32_t *>(s_map[0])[threadIdx.x] = 0;
+    reinterpret_cast<uint32_t *>(s_map[1])[threadIdx.x] = 0;
+    __syncthreads();
+    uint32_t invalid = 0, ignored = 0;
+    mark_ids(ev.ids_a, ev.n_a, geo, st, ev.alloc, s_map[0], invalid, ignored);
+    mark_ids(ev.ids_b, ev.n_b, geo, st, 0, s_map[1], invalid, ignored);
+    __syncthreads();
+    flush_event_map(s_map[0], st.event_blocks);
+    if (ev.n_b) flush_event_map(s_map[1], st.event_blocks + kWords);
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t inv = warp_sum(invalid), ign = warp_sum(ignored);
+    if (lane == 0) {
+        if (inv) atomicAdd(&st.bad[0], (unsigned long long)inv);
+        if (ign) atomicAdd(&st.bad[1], (unsigned long long)ign);
     }
+    // arrival: the last CTA finishes the event
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(st.arrivals, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (!ev.alloc) {
+        // read_seen = t (slot_feedback.py:72-73), write_seen = t (:74-75)
+        for (uint32_t b = threadIdx.x; b < geo.n_blocks; b += blockDim.x) {
+            if ((__ldcg(&st.event_blocks[b >> 5]) >> (b & 31)) & 1u) st.read_seen[b] = ev.t;
+            if ((__ldcg(&st.event_blocks[kWords + (b >> 5)]) >> (b & 31)) & 1u) st.write_seen[b] = ev.t;
+        }
+    } else {
+        // versions[b] = max(generations[b*T .. (b+1)*T)), write_seen = t (slot_feedback.py:59-62):
+        // a warp per touched block
+        for (uint32_t b = warp; b < geo.n_blocks; b += blockDim.x >> 5) {
+            if (!((__ldcg(&st.event_blocks[b >> 5]) >> (b & 31)) & 1u)) continue;      // uniform over the warp
+            unsigned long long lo = (unsigned long long)b * geo.block_tokens;
+            unsigned long long hi = lo + geo.block_tokens;
+            if (hi > geo.capacity + 1) hi = geo.capacity + 1;
+            int best = 0;
+            for (unsigned long long s = lo + lane; s < hi; s += 32) best = max(best, __ldcg(&st.generations[s]));
+            best = __reduce_max_sync(0xffffffffu, best);
+            if (lane == 0) { st.versions[b] = best; st.write_seen[b] = ev.t; }
+        }
+        update_free_head(st, ev.fresh, ev.n_fresh, geo.capacity, s_warp, &s_base);
+        __syncthreads();
+        // the slot marks served the free-head filter: clear them again
+        for (long long i = threadIdx.x; i < ev.n_a; i += blockDim.x) {
+            long long s = ev.ids_a[i];
+            if ((unsigned long long)s <= geo.capacity) st.slot_marks[(uint32_t)s >> 5] = 0;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * kWords) st.event_blocks[threadIdx.x] = 0;
+    if (threadIdx.x == 0) *st.arrivals = 0;
 }
 
 
@@ -341,7 +375,6 @@ struct rt_feedback {
     rt::Geometry geo;
     rt::FeedbackState st;
     uint32_t *d_sets = nullptr;       // [2 * kWords] evict | add
-    uint32_t *d_counts = nullptr;     // [4]
     uint64_t epoch = 0;
     void *block = nullptr;            // one allocation behind all state arrays
     size_t block_bytes = 0;
@@ -384,15 +417,10 @@ int clear_state(rt_feedback *fb, cudaStream_t s) {
     return RT_OK;
 }
 
-int mark_event(rt_feedback *fb, const int64_t *ids, uint64_t n, int alloc, int kind, double t, cudaStream_t s) {
-    if (n) {
-        long long blocks = ((long long)n + 255) / 256;
-        int grid = (int)(blocks < 1184 ? blocks : 1184);
-        rt::feedback_mark_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const long long *>(ids), (long long)n,
-                                                     fb->geo, fb->st, alloc);
-        FB_CUDA(cudaGetLastError());
-    }
-    rt::feedback_stamp_kernel<<<1, 256, 0, s>>>(fb->geo, fb->st, kind, t);
+int launch_event(rt_feedback *fb, const rt::EventArgs &ev, cudaStream_t s) {
+    long long blocks = (ev.n_a + ev.n_b + 255) / 256;
+    int grid = (int)(blocks < 1 ? 1 : blocks < 1184 ? blocks : 1184);
+    rt::feedback_event_kernel<<<grid, 256, 0, s>>>(ev, fb->geo, fb->st);
     FB_CUDA(cudaGetLastError());
     return RT_OK;
 }
@@ -418,8 +446,8 @@ int rt_feedback_create(rt_plan *plan, rt_feedback **out) {
     auto take = [&](size_t bytes) { size_t at = off; off += align_up(bytes); return at; };
     size_t o_gen = take(4 * (cap + 1)), o_ver = take(4 * nb), o_rs = take(8 * nb), o_ws = take(8 * nb),
            o_cv = take(4 * nb), o_ct = take(8 * nb), o_fh = take(8 * rt::kFreeHeadMax), o_fc = take(4),
-           o_eb = take(4 * rt::kWords), o_sm = take(4 * ((cap + 32) / 32 + 1)), o_bad = take(16),
-           o_sets = take(4 * 2 * rt::kWords), o_cnt = take(16);
+           o_eb = take(4 * 2 * rt::kWords), o_arr = take(4), o_sm = take(4 * ((cap + 32) / 32 + 1)), o_bad = take(16),
+           o_sets = take(4 * 2 * rt::kWords);
     fb->block_bytes = off;
     cudaError_t e = cudaMalloc(&fb->block, off);
     if (e != cudaSuccess) { delete fb; return fb_fail(e); }
@@ -433,10 +461,10 @@ int rt_feedback_create(rt_plan *plan, rt_feedback **out) {
     fb->st.free_head = reinterpret_cast<long long *>(base + o_fh);
     fb->st.free_count = reinterpret_cast<int32_t *>(base + o_fc);
     fb->st.event_blocks = reinterpret_cast<uint32_t *>(base + o_eb);
+    fb->st.arrivals = reinterpret_cast<uint32_t *>(base + o_arr);
     fb->st.slot_marks = reinterpret_cast<uint32_t *>(base + o_sm);
     fb->st.bad = reinterpret_cast<unsigned long long *>(base + o_bad);
     fb->d_sets = reinterpret_cast<uint32_t *>(base + o_sets);
-    fb->d_counts = reinterpret_cast<uint32_t *>(base + o_cnt);
     int st = clear_state(fb, fb->view.stream);
     if (st == RT_OK && cudaStreamSynchronize(fb->view.stream) != cudaSuccess) st = RT_ERR_CUDA;
     if (st != RT_OK) { cudaFree(fb->block); delete fb; return st; }
@@ -467,18 +495,14 @@ int rt_feedback_alloc(rt_feedback *fb, const int64_t *d_slots, uint64_t n, const
     if (!fb || (!d_slots && n) || (!d_free_head && n_free)) return RT_ERR_INVALID_ARGUMENT;
     FbDevice guard(fb->view.device);
     cudaStream_t s = stream ? (cudaStream_t)stream : fb->view.stream;
-    int st = mark_event(fb, d_slots, n, 1, 2, t, s);
-    if (st != RT_OK) return st;
-    rt::feedback_free_head_kernel<<<1, 1024, 0, s>>>(fb->st, reinterpret_cast<const long long *>(d_free_head),
-                                                    (int)n_free, d_free_head != nullptr, fb->geo.capacity);
-    FB_CUDA(cudaGetLastError());
-    if (n) {
-        long long blocks = ((long long)n + 255) / 256;
-        rt::feedback_unmark_kernel<<<(int)(blocks < 1184 ? blocks : 1184), 256, 0, s>>>(
-            reinterpret_cast<const long long *>(d_slots), (long long)n, fb->geo.capacity, fb->st);
-        FB_CUDA(cudaGetLastError());
-    }
-    return RT_OK;
+    rt::EventArgs ev = {};
+    ev.ids_a = reinterpret_cast<const long long *>(d_slots);
+    ev.n_a = (long long)n;
+    ev.fresh = reinterpret_cast<const long long *>(d_free_head);
+    ev.n_fresh = (int)n_free;
+    ev.alloc = 1;
+    ev.t = t;
+    return launch_event(fb, ev, s);
 }
 
 int rt_feedback_attention(rt_feedback *fb, const int64_t *d_read, uint64_t n_read, const int64_t *d_write,
@@ -486,9 +510,13 @@ int rt_feedback_attention(rt_feedback *fb, const int64_t *d_read, uint64_t n_rea
     if (!fb || (!d_read && n_read) || (!d_write && n_write)) return RT_ERR_INVALID_ARGUMENT;
     FbDevice guard(fb->view.device);
     cudaStream_t s = stream ? (cudaStream_t)stream : fb->view.stream;
-    int st = mark_event(fb, d_read, n_read, 0, 0, t, s);
-    if (st != RT_OK) return st;
-    return mark_event(fb, d_write, n_write, 0, 1, t, s);
+    rt::EventArgs ev = {};
+    ev.ids_a = reinterpret_cast<const long long *>(d_read);
+    ev.n_a = (long long)n_read;
+    ev.ids_b = reinterpret_cast<const long long *>(d_write);
+    ev.n_b = (long long)n_write;
+    ev.t = t;
+    return launch_event(fb, ev, s);
 }
 
 int rt_feedback_snapshot(rt_feedback *fb, int32_t *versions, double *read_seen, double *write_seen,
