@@ -340,6 +340,14 @@ int rt_feedback_alloc(rt_feedback *fb, const int64_t *d_slots, uint64_t n, const
 int rt_feedback_attention(rt_feedback *fb, const int64_t *d_read, uint64_t n_read,
                           const int64_t *d_write, uint64_t n_write, double t, void *stream);
 
+/* The two event calls for 32-bit ids (the serving engine's kv_indices are
+ * int32); all lists of one call have the same width.  Same state, same plans.
+ * capacity_slots must not exceed 2^31 - 1 (RT_ERR_INVALID_ARGUMENT). */
+int rt_feedback_alloc_i32(rt_feedback *fb, const int32_t *d_slots, uint64_t n,
+                          const int32_t *d_free_head, uint32_t n_free, double t, void *stream);
+int rt_feedback_attention_i32(rt_feedback *fb, const int32_t *d_read, uint64_t n_read,
+                              const int32_t *d_write, uint64_t n_write, double t, void *stream);
+
 /* Copies the state to the host (any pointer may be NULL): n_blocks versions and
  * stamps (-inf = never), up to 4096 free-head slot ids.  This is the content of
  * the snapshot file of slot_feedback.py:86-91 before ranking.  Synchronous. */

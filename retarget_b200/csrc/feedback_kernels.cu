@@ -62,23 +62,25 @@ __device__ __forceinline__ uint32_t block_of_slot(uint32_t slot, const Geometry 
 // and sets a mark per slot for the free-head filter.  The CTA that arrives last
 // then does what needs the whole event: the stamps, the free-list head, the
 // clean-up of the scratch words.  Nobody waits for anybody.
+// The id lists are int64 or int32 (template parameter of the kernel).
 struct EventArgs {
-    const long long *ids_a;    // attention: read ids; allocation: the allocated slots
+    const void *ids_a;         // attention: read ids; allocation: the allocated slots
     long long n_a;
-    const long long *ids_b;    // attention: written ids; allocation: unused
+    const void *ids_b;         // attention: written ids; allocation: unused
     long long n_b;
-    const long long *fresh;    // allocation: the new free-list head, or null
+    const void *fresh;         // allocation: the new free-list head, or null
     int n_fresh;
     int alloc;                 // 0 attention, 1 allocation
     double t;
 };
 
-__device__ __forceinline__ void mark_ids(const long long *ids, long long n, const Geometry &geo,
+template <typename Id>
+__device__ __forceinline__ void mark_ids(const Id *ids, long long n, const Geometry &geo,
                                          const FeedbackState &st, int alloc, uint8_t *s_map, uint32_t &invalid,
                                          uint32_t &ignored) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (long long)gridDim.x * blockDim.x) {
-        long long s = __ldcs(ids + i);
+        long long s = (long long)__ldcs(ids + i);
         if ((unsigned long long)(s - 1) < geo.capacity) {
             uint32_t v = (uint32_t)s;
             s_map[block_of_slot(v, geo)] = 1;
@@ -109,12 +111,13 @@ __device__ __forceinline__ void flush_event_map(const uint8_t *s_map, uint32_t *
 // Free-list head, by one CTA.  With a fresh head the event replaces it
 // (slot_feedback.py:63-64); without, the slots this event allocated are dropped
 // from the known head, order kept (slot_feedback.py:65-70).
-__device__ void update_free_head(const FeedbackState &st, const long long *fresh, int n_fresh,
+template <typename Id>
+__device__ void update_free_head(const FeedbackState &st, const Id *fresh, int n_fresh,
                                  unsigned long long capacity, int *s_warp, int *s_base) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
     if (fresh) {
         int n = n_fresh < kFreeHeadMax ? n_fresh : kFreeHeadMax;
-        for (int i = tid; i < n; i += blockDim.x) st.free_head[i] = fresh[i];
+        for (int i = tid; i < n; i += blockDim.x) st.free_head[i] = (long long)fresh[i];
         if (tid == 0) *st.free_count = n;
         return;
     }
@@ -146,16 +149,18 @@ __device__ void update_free_head(const FeedbackState &st, const long long *fresh
     if (tid == 0) *st.free_count = *s_base;
 }
 
+template <typename Id>
 __global__ void __launch_bounds__(256)
 feedback_event_kernel(EventArgs ev, Geometry geo, FeedbackState st) {
+    const Id *ids_a = static_cast<const Id *>(ev.ids_a), *ids_b = static_cast<const Id *>(ev.ids_b);
     __shared__ uint8_t s_map[2][RT_MAX_BLOCKS];
     __shared__ int s_warp[8], s_base, s_last;
     reinterpret_cast<uint32_t *>(s_map[0])[threadIdx.x] = 0;
     reinterpret_cast<uint32_t *>(s_map[1])[threadIdx.x] = 0;
     __syncthreads();
     uint32_t invalid = 0, ignored = 0;
-    mark_ids(ev.ids_a, ev.n_a, geo, st, ev.alloc, s_map[0], invalid, ignored);
-    mark_ids(ev.ids_b, ev.n_b, geo, st, 0, s_map[1], invalid, ignored);
+    mark_ids(ids_a, ev.n_a, geo, st, ev.alloc, s_map[0], invalid, ignored);
+    mark_ids(ids_b, ev.n_b, geo, st, 0, s_map[1], invalid, ignored);
     __syncthreads();
     flush_event_map(s_map[0], st.event_blocks);
     if (ev.n_b) flush_event_map(s_map[1], st.event_blocks + kWords);
@@ -191,11 +196,11 @@ feedback_event_kernel(EventArgs ev, Geometry geo, FeedbackState st) {
             best = __reduce_max_sync(0xffffffffu, best);
             if (lane == 0) { st.versions[b] = best; st.write_seen[b] = ev.t; }
         }
-        update_free_head(st, ev.fresh, ev.n_fresh, geo.capacity, s_warp, &s_base);
+        update_free_head(st, static_cast<const Id *>(ev.fresh), ev.n_fresh, geo.capacity, s_warp, &s_base);
         __syncthreads();
         // the slot marks served the free-head filter: clear them again
         for (long long i = threadIdx.x; i < ev.n_a; i += blockDim.x) {
-            long long s = ev.ids_a[i];
+            long long s = (long long)ids_a[i];
             if ((unsigned long long)s <= geo.capacity) st.slot_marks[(uint32_t)s >> 5] = 0;
         }
     }
@@ -417,10 +422,13 @@ int clear_state(rt_feedback *fb, cudaStream_t s) {
     return RT_OK;
 }
 
-int launch_event(rt_feedback *fb, const rt::EventArgs &ev, cudaStream_t s) {
+int launch_event(rt_feedback *fb, const rt::EventArgs &ev, bool ids32, cudaStream_t s) {
+    // 32-bit ids: a negative id must never look like a valid large one
+    if (ids32 && fb->geo.capacity > 0x7fffffffull) return RT_ERR_INVALID_ARGUMENT;
     long long blocks = (ev.n_a + ev.n_b + 255) / 256;
     int grid = (int)(blocks < 1 ? 1 : blocks < 1184 ? blocks : 1184);
-    rt::feedback_event_kernel<<<grid, 256, 0, s>>>(ev, fb->geo, fb->st);
+    if (ids32) rt::feedback_event_kernel<int><<<grid, 256, 0, s>>>(ev, fb->geo, fb->st);
+    else rt::feedback_event_kernel<long long><<<grid, 256, 0, s>>>(ev, fb->geo, fb->st);
     FB_CUDA(cudaGetLastError());
     return RT_OK;
 }
@@ -490,33 +498,53 @@ int rt_feedback_reset(rt_feedback *fb, void *stream) {
     return st;
 }
 
-int rt_feedback_alloc(rt_feedback *fb, const int64_t *d_slots, uint64_t n, const int64_t *d_free_head,
-                      uint32_t n_free, double t, void *stream) {
+static int feedback_alloc(rt_feedback *fb, const void *d_slots, uint64_t n, const void *d_free_head,
+                          uint32_t n_free, double t, void *stream, bool ids32) {
     if (!fb || (!d_slots && n) || (!d_free_head && n_free)) return RT_ERR_INVALID_ARGUMENT;
     FbDevice guard(fb->view.device);
     cudaStream_t s = stream ? (cudaStream_t)stream : fb->view.stream;
     rt::EventArgs ev = {};
-    ev.ids_a = reinterpret_cast<const long long *>(d_slots);
+    ev.ids_a = d_slots;
     ev.n_a = (long long)n;
-    ev.fresh = reinterpret_cast<const long long *>(d_free_head);
+    ev.fresh = d_free_head;
     ev.n_fresh = (int)n_free;
     ev.alloc = 1;
     ev.t = t;
-    return launch_event(fb, ev, s);
+    return launch_event(fb, ev, ids32, s);
 }
 
-int rt_feedback_attention(rt_feedback *fb, const int64_t *d_read, uint64_t n_read, const int64_t *d_write,
-                          uint64_t n_write, double t, void *stream) {
+static int feedback_attention(rt_feedback *fb, const void *d_read, uint64_t n_read, const void *d_write,
+                              uint64_t n_write, double t, void *stream, bool ids32) {
     if (!fb || (!d_read && n_read) || (!d_write && n_write)) return RT_ERR_INVALID_ARGUMENT;
     FbDevice guard(fb->view.device);
     cudaStream_t s = stream ? (cudaStream_t)stream : fb->view.stream;
     rt::EventArgs ev = {};
-    ev.ids_a = reinterpret_cast<const long long *>(d_read);
+    ev.ids_a = d_read;
     ev.n_a = (long long)n_read;
-    ev.ids_b = reinterpret_cast<const long long *>(d_write);
+    ev.ids_b = d_write;
     ev.n_b = (long long)n_write;
     ev.t = t;
-    return launch_event(fb, ev, s);
+    return launch_event(fb, ev, ids32, s);
+}
+
+int rt_feedback_alloc(rt_feedback *fb, const int64_t *d_slots, uint64_t n, const int64_t *d_free_head,
+                      uint32_t n_free, double t, void *stream) {
+    return feedback_alloc(fb, d_slots, n, d_free_head, n_free, t, stream, false);
+}
+
+int rt_feedback_alloc_i32(rt_feedback *fb, const int32_t *d_slots, uint64_t n, const int32_t *d_free_head,
+                          uint32_t n_free, double t, void *stream) {
+    return feedback_alloc(fb, d_slots, n, d_free_head, n_free, t, stream, true);
+}
+
+int rt_feedback_attention(rt_feedback *fb, const int64_t *d_read, uint64_t n_read, const int64_t *d_write,
+                          uint64_t n_write, double t, void *stream) {
+    return feedback_attention(fb, d_read, n_read, d_write, n_write, t, stream, false);
+}
+
+int rt_feedback_attention_i32(rt_feedback *fb, const int32_t *d_read, uint64_t n_read, const int32_t *d_write,
+                              uint64_t n_write, double t, void *stream) {
+    return feedback_attention(fb, d_read, n_read, d_write, n_write, t, stream, true);
 }
 
 int rt_feedback_snapshot(rt_feedback *fb, int32_t *versions, double *read_seen, double *write_seen,

@@ -17,7 +17,7 @@ import os
 import numpy as np
 
 from . import capi
-from .planner import DevicePlanner, _ptr
+from .planner import DevicePlanner, _is_i32, _ptr
 
 FREE_HEAD_MAX = 4096
 
@@ -35,6 +35,8 @@ def _bind():
     lib.rt_feedback_reset.argtypes = [vp, vp]
     lib.rt_feedback_alloc.argtypes = [vp, vp, C.c_uint64, vp, C.c_uint32, C.c_double, vp]
     lib.rt_feedback_attention.argtypes = [vp, vp, C.c_uint64, vp, C.c_uint64, C.c_double, vp]
+    lib.rt_feedback_alloc_i32.argtypes = lib.rt_feedback_alloc.argtypes
+    lib.rt_feedback_attention_i32.argtypes = lib.rt_feedback_attention.argtypes
     lib.rt_feedback_snapshot.argtypes = [vp, vp, vp, vp, vp, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64),
                                          C.POINTER(C.c_uint64)]
     lib.rt_feedback_plan.argtypes = [vp, C.POINTER(FeedbackPolicy), C.c_double, C.c_double, vp, C.c_uint32,
@@ -72,12 +74,20 @@ class DeviceFeedback:
     def alloc(self, d_slots, t, d_free_head=None, stream=None):
         self._event(t)
         n_free = 0 if d_free_head is None else min(int(d_free_head.numel()), FREE_HEAD_MAX)
-        capi.check(self.lib.rt_feedback_alloc(self._h, _ptr(d_slots), int(d_slots.numel()), _ptr(d_free_head),
+        narrow = _is_i32(d_slots)
+        if d_free_head is not None and _is_i32(d_free_head) != narrow:
+            raise TypeError("the slot list and the free head of one event must have the same dtype")
+        fn = self.lib.rt_feedback_alloc_i32 if narrow else self.lib.rt_feedback_alloc
+        capi.check(fn(self._h, _ptr(d_slots), int(d_slots.numel()), _ptr(d_free_head),
                                               n_free, float(t), stream), "rt_feedback_alloc")
 
     def attention(self, d_read, d_write, t, stream=None):
         self._event(t)
-        capi.check(self.lib.rt_feedback_attention(self._h, _ptr(d_read), int(d_read.numel()), _ptr(d_write),
+        narrow = _is_i32(d_read)
+        if _is_i32(d_write) != narrow:
+            raise TypeError("the read and write lists of one event must have the same dtype")
+        fn = self.lib.rt_feedback_attention_i32 if narrow else self.lib.rt_feedback_attention
+        capi.check(fn(self._h, _ptr(d_read), int(d_read.numel()), _ptr(d_write),
                                                   int(d_write.numel()), float(t), stream), "rt_feedback_attention")
 
     def plan(self, now, *, budget, max_blocks_per_update, active_seconds, refresh_seconds, flags,

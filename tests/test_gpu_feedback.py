@@ -27,7 +27,8 @@ def canonical(snapshot):
     return s
 
 
-def run_trace(layout, trace, *, budget, max_blocks, active, refresh, evict, dt=0.03, clear_at=None):
+def run_trace(layout, trace, *, budget, max_blocks, active, refresh, evict, dt=0.03, clear_at=None,
+              dtype=np.int64):
     dev = torch.device("cuda:0")
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
@@ -41,16 +42,20 @@ def run_trace(layout, trace, *, budget, max_blocks, active, refresh, evict, dt=0
     flags = capi.RT_PLAN_EVICT if evict else 0
     h = stream.cuda_stream
     moved = 0
+
+    def up(ids):
+        return torch.from_numpy(np.ascontiguousarray(ids).astype(dtype)).to(dev)
+
     for step, ev in enumerate(trace):
         t = 100.0 + step * dt
         if clear_at is not None and step == clear_at:
             fb.clear(t - 0.004, h)
             oracle.clear(t - 0.004)
         if len(ev.alloc_slots):
-            head = None if ev.free_head is None else torch.from_numpy(ev.free_head).to(dev)
-            fb.alloc(torch.from_numpy(ev.alloc_slots).to(dev), t - 0.002, head, h)
+            head = None if ev.free_head is None else up(ev.free_head)
+            fb.alloc(up(ev.alloc_slots), t - 0.002, head, h)
             oracle.alloc(ev.alloc_slots, ev.free_head, t - 0.002)
-        fb.attention(torch.from_numpy(ev.read_slots).to(dev), torch.from_numpy(ev.write_slots).to(dev), t, h)
+        fb.attention(up(ev.read_slots), up(ev.write_slots), t, h)
         oracle.attention(ev.read_slots, ev.write_slots, t)
         now = t + 0.001
         fb.plan(now, budget=budget, max_blocks_per_update=max_blocks, active_seconds=active,
@@ -79,15 +84,16 @@ def test_incremental_trace_config():
     assert moved > 0
 
 
-def test_reference_update_limits_refresh_and_allocator_clear():
+@pytest.mark.parametrize("dtype", [np.int64, np.int32], ids=["i64", "i32"])
+def test_reference_update_limits_refresh_and_allocator_clear(dtype):
     """The reference's own policy values (4 new blocks per update), a short
     refresh period so that due-for-refresh blocks are re-sent, no eviction, and an
-    allocator clear in the middle."""
+    allocator clear in the middle.  Once with 64-bit and once with 32-bit ids."""
     layout = workloads.Layout(4, 2048, 32768)
     trace = workloads.decode_trace(3, steps=120, pool_slots=32768, arrival_rate=1.0, median=256,
                                    mean_output=24, initial_requests=6)
     moved = run_trace(layout, trace, budget=8, max_blocks=4, active=2.0, refresh=0.5, evict=False,
-                      clear_at=70)
+                      clear_at=70, dtype=dtype)
     assert moved > 0
 
 
