@@ -36,6 +36,50 @@ class UvmConfig(C.Structure):
                 ("streams", C.c_uint32), ("listen", C.c_int32)]
 
 
+class UmCounters:
+    """GPU page-fault groups and migrated bytes from CUPTI's unified-memory
+    activity records, when libretarget_umcount.so was built and CUPTI agrees."""
+    NAMES = ("gpu_page_fault_groups", "cpu_page_faults", "bytes_host_to_device", "bytes_device_to_host",
+             "records", "records_dropped")
+
+    def __init__(self):
+        from pathlib import Path
+        self.ok, self.why, self.lib = False, "", None
+        path = Path(__file__).resolve().parent / "libretarget_umcount.so"
+        if not path.exists():
+            self.why = "libretarget_umcount.so was not built (no CUPTI in the toolkit)"
+            return
+        try:
+            self.lib = C.CDLL(str(path))
+        except OSError as e:
+            self.why = f"cannot load the CUPTI helper: {e}"
+            return
+        self.lib.rt_um_counters_error.restype = C.c_char_p
+        if self.lib.rt_um_counters_enable() != 0:
+            self.why = self.lib.rt_um_counters_error().decode()
+            return
+        self.ok = True
+        self.kinds = int(self.lib.rt_um_counters_kinds())
+
+    def read(self):
+        if not self.ok:
+            return None
+        buf = (C.c_uint64 * 6)()
+        if self.lib.rt_um_counters_read(buf) != 0:
+            self.ok, self.why = False, self.lib.rt_um_counters_error().decode()
+            return None
+        got = dict(zip(self.NAMES, (int(v) for v in buf)))
+        if self.kinds < 4:
+            got["cpu_page_faults"] = None
+        if self.kinds < 3:
+            got["gpu_page_fault_groups"] = None
+        return got
+
+    def close(self):
+        if self.ok:
+            self.lib.rt_um_counters_disable()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--buffers", type=int, default=8)
@@ -52,6 +96,9 @@ def main():
 
     lib = capi.lib
     dev = torch.device("cuda:0")
+    # the counters are switched on between driver initialisation and the first context
+    cu.cuInit(0)
+    counters = UmCounters()
     torch.cuda.set_device(0)
     torch.zeros(1, device=dev)
     out = {"gpu": torch.cuda.get_device_name(0)}
@@ -155,7 +202,9 @@ def main():
 
     read_bytes = len(slots) * bytes_per_slot * args.buffers
     run_job(f"targetv {gen} 0")
+    counters.read()                                    # drop what the set-up caused
     t_fault, sums_fault = read_once()                  # every page faults in
+    um_fault = counters.read()
     t_warm, _ = read_once()                            # now resident
     run_job(f"targetv {gen} 0")
     planner = DevicePlanner(layout, 0)
@@ -176,7 +225,9 @@ def main():
     capi.check(lib.rt_uvm_submit_ranges(ranges.ctypes.data, len(ranges), id_arr, len(ids), C.byref(job)), "submit")
     capi.check(lib.rt_uvm_wait(job.value, 600.0, C.byref(cuda_err)), "wait")
     t_prefetch = time.perf_counter() - t0
+    um_prefetch = counters.read()
     t_after, sums_after = read_once()
+    um_after = counters.read()
     out["plan_prefetch_read"] = {
         "buffers": args.buffers, "alloc_bytes": alloc, "live_slots": int(len(slots)),
         "rows_read_bytes": read_bytes, "plan_ranges": int(res["n_ranges"]),
@@ -185,7 +236,9 @@ def main():
         "prefetch_frac_of_h2d_link": res["gpu_bytes"] / t_prefetch / 1e9 / h2d,
         "read_seconds_pages_on_cpu": t_fault, "read_seconds_after_plan": t_after,
         "read_seconds_resident": t_warm, "checksums_equal": bool(np.array_equal(sums_fault, sums_after)),
-        "fault_counts": "unavailable (no CUPTI unified-memory counters in this build)"}
+        "um_counters": {"reader_pages_on_cpu": um_fault, "prefetch_of_the_plan": um_prefetch,
+                        "reader_after_plan": um_after} if counters.ok else f"unavailable ({counters.why})"}
+    counters.close()
     capi.check(lib.rt_uvm_stop(), "rt_uvm_stop")
     planner.close()
     for p in ptrs:
