@@ -86,3 +86,24 @@ def test_workload_shapes_match_the_stated_configs():
     trace = workloads.decode_trace(0, steps=40)
     assert len(trace) == 40 and trace[-1].completed_tokens > 0
     assert workloads.full_refresh(0).slots.tobytes() == b.slots.tobytes()      # seeded
+
+
+def test_benchmark_pairs_move_what_they_say():
+    """The alternating pairs the benchmark times, through the vectorised and the
+    C oracle: 160 ranges per step when the halves alternate, 6080 single-block
+    ranges when even and odd blocks do, none once the steady pair has settled."""
+    expected = {"moving": 160, "fragmented": 6080, "steady": 0}
+    for kind, ranges in expected.items():
+        a, b = workloads.target_pair(kind)
+        assert a.n_idx == b.n_idx == 22_282_240 and a.layout.n_groups == 40
+        assert a.slots.min() >= 1 and a.slots.max() <= a.layout.capacity
+        resident = [set() for _ in range(a.layout.n_groups)]
+        co = c_oracle.COracle(a.layout)
+        for step, batch in enumerate((a, b, a)):
+            want, info = compose.plan_step(batch, resident, literal=False)
+            got, invalid = co.step(batch.slots, batch.group_off, batch.budget_blocks, True, 4)
+            assert _tuples(got) == want and invalid == 0
+            if step:
+                assert len(want) == ranges, (kind, step)
+                if ranges:
+                    assert info["blocks_added"] == info["blocks_evicted"] == 40 * 38
