@@ -1,15 +1,15 @@
 // Planner kernels for sm_100a.
 //
 // One launch per decode step does all of:
-//   scan     slot ids -> per-bitmap "touched block" words (shared-memory bitmap
-//            per CTA, one global atomicOr per non-zero word per CTA and bitmap)
-//   tail     per bitmap, by the CTA that retires the bitmap's last work unit: budget
-//            cut, diff against the resident words, run coalescing (one warp,
-//            one 32-bit word per lane, ballot/popc/shuffle only)
-//   finalize by the CTA that retires the last bitmap: prefix sum over
-//            (phase, buffer) and emission of the byte ranges in queue order
-// CTAs never wait for each other: hand-over is by arrival counters ("last one
-// out does the next stage"), so nothing in here can hang.
+//   scan  slot ids -> per-bitmap "touched block" words: every CTA owns a
+//         contiguous span of 16 KiB work units, marks blocks in a shared byte map
+//         and folds it into the bitmap's global words (one atomicOr per non-zero
+//         word) whenever it leaves a bitmap
+//   tail  by the CTA that retires the launch's last work unit (plan_tail.cuh):
+//         budget cut, diff against the resident words, run coalescing, prefix sum
+//         over (phase, buffer), byte ranges in queue order, result record
+// CTAs never wait for each other: hand-over is by one arrival counter ("last one
+// out does the tail"), so nothing in here can hang.
 //
 // The path is index arithmetic bound by HBM reads; there is no contraction in
 // it and no tensor-core work.
