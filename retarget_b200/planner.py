@@ -51,7 +51,9 @@ class DevicePlanner:
 
     def close(self):
         if getattr(self, "_h", None):
-            capi.lib.rt_plan_destroy(self._h)
+            lib = getattr(capi, "lib", None)     # gone when the interpreter is shutting down
+            if lib is not None:
+                lib.rt_plan_destroy(self._h)
             self._h = None
 
     __del__ = close
