@@ -296,7 +296,8 @@ def run_ours(args):
     if args.launch == "graph" and K >= 2:
         per_replay = min(20, K - K % 2)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
+        # thread-local capture mode: the process group's watchdog thread may query events meanwhile
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
             for i in range(per_replay):
                 b = batches[(W + i) % 2]
                 planner.step_device(d_slots[(W + i) % 2], b.group_off, b.budget_blocks, flags, d_out,
