@@ -377,12 +377,31 @@ def run_ours(args):
         e2e_ranges = res.n_ranges
     torch.cuda.synchronize()
     e2e_s = (time.perf_counter() - t0) / K
+    plan = out_host[:e2e_ranges].copy()      # the last timed plan, compared across ranks below
+    if variants:
+        # the host-buffer call on int32 ids: half the bytes over the host link
+        h32 = [torch.from_numpy(b.slots.astype(np.int32)).pin_memory() for b in batches]
+        n32 = 20
+        for i in range(2):
+            planner.step_host(h32[i].numpy(), batches[i].group_off, batches[i].budget_blocks, flags,
+                              out=out_host)
+        t0 = time.perf_counter()
+        for i in range(n32):
+            b = batches[i % 2]
+            planner.step_host(h32[i % 2].numpy(), b.group_off, b.budget_blocks, flags, out=out_host)
+        torch.cuda.synchronize()
+        variants["int32_ids_host_call"] = {"us_per_step": (time.perf_counter() - t0) / n32 * 1e6,
+                                           "steps": n32, "h2d_bytes_per_step": 4 * batches[0].n_idx}
+        del h32
+        for i in range(2):      # back to the main pair's resident state
+            planner.step_host(h_slots[(W + K + i) % 2].numpy(), batches[(W + K + i) % 2].group_off,
+                              batches[(W + K + i) % 2].budget_blocks, flags, out=out_host)
     clocks = sampler.stop() if sampler else None
 
     ms_per_step, e2e_ms = ranks.max_over_ranks([total_ms / K, e2e_s * 1e3])
     launch_ms = ms_per_step           # one launch per step, nothing else on the stream
     # every rank planned from the same slot table: the plans must agree
-    plan = out_host[:e2e_ranges]          # dst names the rank's own GPU; the rest must agree
+    # (dst names the rank's own GPU; the rest must agree)
     plans_agree = ranks.same_everywhere(b"".join(plan[k].tobytes() for k in ("buffer", "offset", "bytes")))
 
     if rank == 0:
