@@ -103,6 +103,14 @@ int rt_window_accounting(const rt_window_spec *spec, uint64_t n_cache, uint64_t 
                          const uint64_t old_window[2], const uint64_t new_window[2],
                          int full, int refresh, uint64_t *gpu_bytes, uint64_t *cpu_bytes);
 
+/* aligned_uvm_target, experiments/control.py:379-400: a global residency target
+ * of `desired` bytes over the allocations in registry order, rounded down so
+ * that the one partly resident allocation is cut at a page boundary (the
+ * prefix walk of target/targetv/retarget, select.cpp:24257-24263, rejects
+ * anything else as unaligned_target).  A target beyond the total is the total. */
+int rt_aligned_target(const uint64_t *allocation_bytes, size_t n, uint64_t desired, uint64_t page,
+                      uint64_t *target);
+
 /* SlotPlacementController.__init__ budget rule, experiments/slot_placement.py:60-64. */
 int rt_slot_budget(const rt_window_spec *spec, uint64_t block_tokens, uint64_t *budget_blocks);
 

@@ -113,6 +113,8 @@ def _load():
         "rt_window_spec_check": (C.c_int, [C.POINTER(WindowSpecStruct), C.POINTER(C.c_int)]),
         "rt_window": (C.c_int, [C.POINTER(WindowSpecStruct), C.c_double, u64p]),
         "rt_interval_difference": (C.c_int, [u64p, u64p, u64p]),
+        "rt_aligned_target": (C.c_int, [C.POINTER(C.c_uint64), C.c_size_t, C.c_uint64, C.c_uint64,
+                                        C.POINTER(C.c_uint64)]),
         "rt_window_accounting": (C.c_int, [C.POINTER(WindowSpecStruct), C.c_uint64, C.c_uint64,
                                            u64p, u64p, C.c_int, C.c_int, u64p, u64p]),
         "rt_slot_budget": (C.c_int, [C.POINTER(WindowSpecStruct), C.c_uint64, u64p]),

@@ -4,6 +4,9 @@ Same wire behaviour as the reference's ``UvmController.command/status/
 _allocation_snapshot/wait_idle/_wait_job`` (experiments/control.py:403-544): one
 ASCII line per connection (shorter than 512 bytes), one JSON line back, 50 ms
 polling while a job runs, and refusal to talk to a PID that has been replaced.
+The prefix plans of the trainer side are here too: ``aligned_uvm_target``,
+``set_target`` and ``retarget`` with their result records
+(experiments/control.py:379-400,488-654).
 The shared-memory registry, the message-queue doorbell and the timeslice
 controls of that file belong to the scheduler's control path and are not part
 of this package.
@@ -54,6 +57,51 @@ class UvmStatus:
         return cls(**{k: (bool(v) if k == "busy" else int(v)) for k, v in fields.items()})
 
 
+@dataclasses.dataclass(frozen=True)
+class UvmTargetResult:
+    """What ``set_target`` did: the request, the request clamped to the managed
+    bytes, and the page-aligned target that was sent."""
+    requested_bytes: int
+    clamped_bytes: int
+    submitted_bytes: int
+    status: UvmStatus
+
+
+@dataclasses.dataclass(frozen=True)
+class UvmRetargetResult:
+    """What ``retarget`` did, with the previous target it moved away from."""
+    previous_requested_bytes: int
+    previous_submitted_bytes: int
+    requested_bytes: int
+    clamped_bytes: int
+    submitted_bytes: int
+    status: UvmStatus
+
+
+def aligned_uvm_target(allocation_sizes, desired_bytes: int, page_size: int) -> int:
+    """A global residency target rounded down to where the preload library accepts
+    it: only the offset inside the one partly resident allocation has to be a
+    page multiple (experiments/control.py:379-400).  Arithmetic: rt_aligned_target."""
+    if desired_bytes < 0 or page_size <= 0:
+        raise ValueError("invalid target or page size")
+    sizes = [int(x) for x in allocation_sizes]
+    if any(x < 0 for x in sizes):
+        raise ValueError("allocation sizes must be non-negative")
+    array = (C.c_uint64 * max(len(sizes), 1))(*sizes)
+    out = C.c_uint64()
+    capi.check(capi.lib.rt_aligned_target(array, len(sizes), desired_bytes, page_size, C.byref(out)),
+               "rt_aligned_target")
+    return out.value
+
+
+@dataclasses.dataclass(frozen=True)
+class _Placement:
+    """The registry a prefix plan was computed for and the target it asked for."""
+    signature: tuple
+    generation: int
+    target: int
+
+
 def process_start_time(pid: int) -> int:
     """Field 22 of /proc/<pid>/stat; guards against PID reuse."""
     try:
@@ -72,9 +120,21 @@ class _Protocol:
     command()."""
 
     pid: int
+    # prefix plans: the placement the process is known to be in (None: unknown, the
+    # next retarget becomes a full target) and a job submitted without waiting
+    _placed: _Placement | None = None
+    _in_flight: tuple[int, _Placement] | None = None
 
     def command(self, command: str) -> dict[str, Any]:
         raise NotImplementedError
+
+    @property
+    def _submitted_target(self):
+        return self._placed.target if self._placed else None
+
+    @property
+    def _pending_job(self):
+        return self._in_flight[0] if self._in_flight else None
 
     def status(self) -> UvmStatus:
         status = UvmStatus.from_reply(self.command("status"))
@@ -98,10 +158,26 @@ class _Protocol:
         while True:
             status = self.status()
             if not status.busy:
+                self._settle_in_flight(status)
                 return status
             if time.monotonic() >= deadline:
                 raise ControlError(f"UVM worker for PID {self.pid} remained busy")
             time.sleep(poll_seconds)
+
+    def _settle_in_flight(self, status: UvmStatus) -> None:
+        """An idle worker settles a job that was submitted without waiting
+        (experiments/control.py:488-513)."""
+        if self._in_flight is None:
+            return
+        job_id, placement = self._in_flight
+        if status.completed_job < job_id:
+            raise ControlError(f"UVM worker for PID {self.pid} became idle before job {job_id} completed")
+        self._in_flight = None
+        if status.last_error != 0:
+            self._placed = None
+            raise ControlError(f"UVM job {job_id} for PID {self.pid} failed with CUDA error "
+                               f"{status.last_error}")
+        self._placed = placement
 
     def _wait_job(self, job_id: int, timeout: float = 120.0, poll_seconds: float = 0.05) -> UvmStatus:
         deadline = time.monotonic() + timeout
@@ -115,6 +191,70 @@ class _Protocol:
             if time.monotonic() >= deadline:
                 raise ControlError(f"timed out waiting for UVM job {job_id}")
             time.sleep(poll_seconds)
+
+    def _registry(self, status: UvmStatus, *targets: int):
+        """Generation, signature and the page-aligned form of each target, clamped
+        to what is managed."""
+        generation, allocations = self._allocation_snapshot()
+        signature = tuple((a["id"], a["bytes"], a["device"]) for a in allocations)
+        sizes = [a["bytes"] for a in allocations]
+        page = os.sysconf("SC_PAGE_SIZE")
+        clamped = [min(t, status.managed_bytes) for t in targets]
+        return generation, signature, clamped, [aligned_uvm_target(sizes, c, page) for c in clamped]
+
+    def _submit_prefix_plan(self, line: str, what: str, placement: _Placement, wait: bool, timeout: float):
+        reply = self.command(line)
+        if not reply.get("ok"):
+            raise ControlError(f"UVM {what} for PID {self.pid} failed: {reply}")
+        job_id = int(reply["job_id"])
+        if not wait:
+            self._in_flight = (job_id, placement)
+            return job_id, None
+        try:
+            completed = self._wait_job(job_id, timeout=timeout)
+        except Exception:
+            self._placed = None
+            raise
+        self._placed = placement
+        return job_id, completed
+
+    def set_target(self, gpu_bytes: int, *, timeout: float = 120.0, wait: bool = True):
+        """Makes the first ``gpu_bytes`` of the managed allocations (registry
+        order) GPU resident and the rest CPU resident: ``targetv``
+        (experiments/control.py:546-592).  With ``wait=False`` returns the job id;
+        the next ``wait_idle`` settles it."""
+        if gpu_bytes < 0:
+            raise ValueError("gpu_bytes must be non-negative")
+        status = self.wait_idle(timeout=timeout)
+        generation, signature, (desired,), (target,) = self._registry(status, gpu_bytes)
+        job_id, completed = self._submit_prefix_plan(
+            f"targetv {generation} {target}", f"target {target}",
+            _Placement(signature, generation, target), wait, timeout)
+        if completed is None:
+            return job_id
+        return UvmTargetResult(requested_bytes=gpu_bytes, clamped_bytes=desired, submitted_bytes=target,
+                               status=completed)
+
+    def retarget(self, previous_gpu_bytes: int, gpu_bytes: int, *, timeout: float = 120.0, wait: bool = True):
+        """Moves only the bytes between the previous target and the new one:
+        ``retarget`` (experiments/control.py:594-654).  Falls back to ``set_target``
+        whenever the process is not known to be in the previous placement (other
+        registry, other generation, other target, or a failed job since)."""
+        if previous_gpu_bytes < 0 or gpu_bytes < 0:
+            raise ValueError("GPU targets must be non-negative")
+        status = self.wait_idle(timeout=timeout)
+        generation, signature, (_, desired), (previous_target, target) = self._registry(
+            status, previous_gpu_bytes, gpu_bytes)
+        if self._placed != _Placement(signature, generation, previous_target):
+            return self.set_target(gpu_bytes, timeout=timeout, wait=wait)
+        job_id, completed = self._submit_prefix_plan(
+            f"retarget {generation} {previous_target} {target}", f"retarget {previous_target}->{target}",
+            _Placement(signature, generation, target), wait, timeout)
+        if completed is None:
+            return job_id
+        return UvmRetargetResult(previous_requested_bytes=previous_gpu_bytes,
+                                 previous_submitted_bytes=previous_target, requested_bytes=gpu_bytes,
+                                 clamped_bytes=desired, submitted_bytes=target, status=completed)
 
     def prefetch(self, allocation_id: int, offset: int, length: int, where: str,
                  timeout: float = 120.0) -> UvmStatus:

@@ -136,6 +136,25 @@ int rt_window_accounting(const rt_window_spec *s, uint64_t n_cache, uint64_t oth
     return RT_OK;
 }
 
+int rt_aligned_target(const uint64_t *allocation_bytes, size_t n, uint64_t desired, uint64_t page,
+                      uint64_t *target) {
+    if ((!allocation_bytes && n) || !page || !target) return RT_ERR_INVALID_ARGUMENT;
+    uint64_t covered = 0;                 // bytes of the allocations that are resident in full
+    for (size_t i = 0; i < n; ++i) {
+        const uint64_t size = allocation_bytes[i];
+        if (size > UINT64_MAX - covered) return RT_ERR_INVALID_ARGUMENT;
+        if (desired - covered >= size) {  // desired >= covered holds throughout
+            covered += size;
+            continue;
+        }
+        const uint64_t inside = desired - covered;
+        *target = covered + inside / page * page;
+        return RT_OK;
+    }
+    *target = covered;
+    return RT_OK;
+}
+
 int rt_slot_budget(const rt_window_spec *s, uint64_t block_tokens, uint64_t *budget_blocks) {
     if (!s || !block_tokens || !budget_blocks) return RT_ERR_INVALID_ARGUMENT;
     uint64_t budget = s->width_tokens / block_tokens;

@@ -357,6 +357,115 @@ def placement_controller_vectors(cw, sp, sf, ctl):
     return dict(cache_spec=kw, slot_spec=sspec, allocations=allocs, generation=7, pid=4242, log=log)
 
 
+TARGET_SCRIPT = [
+    # (operation, arguments) against the scripted transport below
+    ("set_target", dict(gpu_bytes=0)),
+    ("set_target", dict(gpu_bytes=50 * (1 << 20) + 1234)),
+    ("retarget", dict(previous_gpu_bytes=50 * (1 << 20) + 1234, gpu_bytes=12 * (1 << 20))),
+    ("retarget", dict(previous_gpu_bytes=1, gpu_bytes=13 * (1 << 20) + 5)),          # stale previous
+    ("bump_generation", dict()),
+    ("retarget", dict(previous_gpu_bytes=13 * (1 << 20) + 5, gpu_bytes=70 * (1 << 20))),  # registry changed
+    ("set_target", dict(gpu_bytes=1 << 40)),                                           # clamped
+    ("set_target", dict(gpu_bytes=3 * (1 << 20), wait=False)),
+    ("wait_idle", dict()),
+    ("retarget", dict(previous_gpu_bytes=3 * (1 << 20), gpu_bytes=9 * (1 << 20) + 777, wait=False)),
+    ("wait_idle", dict()),
+    ("retarget", dict(previous_gpu_bytes=9 * (1 << 20) + 777, gpu_bytes=2 * (1 << 20))),
+    ("reject_next", dict(error="busy")),
+    ("retarget", dict(previous_gpu_bytes=2 * (1 << 20), gpu_bytes=5 * (1 << 20))),
+    ("fail_next_job", dict(code=700)),
+    ("retarget", dict(previous_gpu_bytes=2 * (1 << 20), gpu_bytes=6 * (1 << 20))),
+    ("retarget", dict(previous_gpu_bytes=6 * (1 << 20), gpu_bytes=7 * (1 << 20))),     # state was dropped
+    ("fail_next_job", dict(code=2)),
+    ("set_target", dict(gpu_bytes=8 * (1 << 20), wait=False)),
+    ("wait_idle", dict()),
+    ("retarget", dict(previous_gpu_bytes=8 * (1 << 20), gpu_bytes=1 << 20)),
+    ("set_target", dict(gpu_bytes=-1)),
+]
+TARGET_ALLOCATIONS = [dict(id=3, bytes=10 * (1 << 20) + 100, device=0), dict(id=4, bytes=64 * (1 << 20), device=0),
+                      dict(id=9, bytes=4 * (1 << 20) + 3 * 4096, device=1)]
+
+
+class ScriptedServer:
+    """Answers status / list / plan lines like the preload library's socket would,
+    completing every accepted job at once."""
+
+    def __init__(self, pid, allocations):
+        self.pid, self.allocs, self.generation = pid, [dict(a) for a in allocations], 5
+        self.job, self.last_error, self.reject, self.fail_code = 0, 0, None, 0
+        self.lines = []
+
+    def __call__(self, line):
+        self.lines.append(line)
+        if line == "status":
+            return dict(ok=True, pid=self.pid, managed_bytes=sum(a["bytes"] for a in self.allocs),
+                        allocation_count=len(self.allocs), allocation_generation=self.generation, busy=False,
+                        job_id=self.job, completed_job=self.job, last_error=self.last_error,
+                        completed_cpu_bytes=0, completed_gpu_bytes=0, job_completed_bytes=0)
+        if line == "list":
+            return dict(ok=True, allocation_generation=self.generation, allocations=[dict(a) for a in self.allocs])
+        if self.reject:
+            error, self.reject = self.reject, None
+            return dict(ok=False, error=error)
+        self.job += 1
+        self.last_error, self.fail_code = self.fail_code, 0
+        return dict(ok=True, job_id=self.job)
+
+
+def run_target_script(make_controller, ControlError, page):
+    """Shared by the generator (reference controller) and the replay test."""
+    server = ScriptedServer(os.getpid(), TARGET_ALLOCATIONS)
+    c = make_controller(server)
+    log = []
+    for op, kw in TARGET_SCRIPT:
+        before = len(server.lines)
+        entry = dict(op=op, args=kw)
+        if op == "bump_generation":
+            server.generation += 1
+            server.allocs.append(dict(id=12, bytes=8 * page, device=0))
+        elif op == "reject_next":
+            server.reject = kw["error"]
+        elif op == "fail_next_job":
+            server.fail_code = kw["code"]
+        else:
+            try:
+                res = getattr(c, op)(**kw)
+                if dataclasses.is_dataclass(res):
+                    kind = type(res).__name__
+                    res = {k: v for k, v in dataclasses.asdict(res).items() if k != "status"}
+                    res["type"] = kind
+                entry["result"] = res
+            except (ControlError, ValueError) as e:
+                entry["error"] = [type(e).__name__, str(e)]
+        entry["lines"] = server.lines[before:]
+        entry["submitted_target"] = getattr(c, "_submitted_target", None)
+        entry["pending_job"] = getattr(c, "_pending_job", None)
+        log.append(entry)
+    return log
+
+
+def target_vectors(ctl):
+    """aligned_uvm_target, and UvmController.set_target / retarget / wait_idle
+    driven through a scripted transport (control.py:379-400,488-654)."""
+    rng = np.random.default_rng(4)
+    aligned = []
+    for _ in range(200):
+        page = int(rng.choice([4096, 65536]))
+        sizes = [int(rng.integers(0, 40) * page + rng.choice([0, 0, 100, page // 2])) for _ in range(rng.integers(0, 6))]
+        total = sum(sizes)
+        desired = int(rng.integers(0, total + 3 * page + 1))
+        aligned.append([sizes, desired, page, ctl.aligned_uvm_target(sizes, desired, page)])
+    page = os.sysconf("SC_PAGE_SIZE")
+
+    def make(server):
+        c = ctl.UvmController(os.getpid())
+        c.command = server
+        return c
+    return dict(aligned=aligned, page=page, pid=os.getpid(),
+                script=run_target_script(make, ctl.ControlError, page))
+
+
+
 def main():
     root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["RETARGET_REFERENCE"])
     cw, sp, sf, ctl, probe = load_reference(root)
@@ -368,6 +477,7 @@ def main():
         feedback=feedback_vectors(sf, sp, probe),
         window_controller=controller_vectors(cw, sp, sf, ctl),
         placement_controller=placement_controller_vectors(cw, sp, sf, ctl),
+        targets=target_vectors(ctl),
     )
     path = HERE / "reference_policy.json"
     path.write_text(json.dumps(doc, separators=(",", ":"), allow_nan=True))

@@ -132,3 +132,53 @@ def test_budget_rules():
     with pytest.raises(ValueError, match="slot blocks must be page aligned"):
         sp.SlotPlacementController(cw.CacheWindowSpec(16 * 2097152, 4, 4, 4096, 1024, 1024),
                                    sp.SlotPlacementSpec(block_tokens=512), 1, snapshot_source=lambda n: None)
+
+
+def _golden_tools():
+    import importlib.util
+    from pathlib import Path
+    path = Path(__file__).resolve().parent / "golden" / "make_golden.py"
+    spec = importlib.util.spec_from_file_location("make_golden", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+def test_aligned_target_matches_reference(golden):
+    from retarget_b200.control import aligned_uvm_target
+    for sizes, desired, page, want in golden["targets"]["aligned"]:
+        assert aligned_uvm_target(sizes, desired, page) == want
+    with pytest.raises(ValueError):
+        aligned_uvm_target([4096], -1, 4096)
+    with pytest.raises(ValueError):
+        aligned_uvm_target([4096, -2], 0, 4096)
+    with pytest.raises(ValueError):
+        aligned_uvm_target([4096], 0, 0)
+
+
+def test_prefix_plans_replay(golden):
+    """set_target / retarget / wait_idle against the scripted transport the
+    reference client was recorded with: same lines on the wire, same results,
+    same errors, same remembered placement after every call."""
+    import os
+    from retarget_b200.control import UvmController
+    tools = _golden_tools()
+    block = golden["targets"]
+    assert block["page"] == os.sysconf("SC_PAGE_SIZE")
+
+    def make(server):
+        c = UvmController(os.getpid())
+        c.command = server
+        return c
+
+    got = tools.run_target_script(make, ControlError, block["page"])
+    theirs, ours = str(block["pid"]), str(os.getpid())
+    assert len(got) == len(block["script"])
+    for mine, want in zip(got, block["script"]):
+        want = json.loads(json.dumps(want))
+        if "error" in want:                       # the messages name the controlled PID
+            want["error"][1] = want["error"][1].replace(f"PID {theirs}", f"PID {ours}")
+        if isinstance(want.get("result"), dict) and "pid" in want["result"]:
+            want["result"]["pid"] = int(ours)
+        mine = json.loads(json.dumps(mine))
+        assert mine == want, want["op"]

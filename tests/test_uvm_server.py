@@ -257,6 +257,50 @@ def test_generation_moves_with_the_registry(server):
     assert reply["ok"] and len(calls) == 4
 
 
+@pytest.mark.parametrize("via", ["local", "socket"])
+def test_prefix_plans_through_the_client(server, via):
+    """set_target / retarget of the client against the running server: the
+    prefetch calls are the oracle's expansion of targetv / retarget for the
+    page-aligned targets, and an incremental retarget moves only the difference."""
+    from retarget_b200.control import UvmRetargetResult, UvmTargetResult, aligned_uvm_target
+    env = server
+    client = env.local if via == "local" else env.remote
+    client._placed = None
+    sizes = [a["bytes"] for a in env.registry]
+    page = os.sysconf("SC_PAGE_SIZE")
+
+    def calls_of(action):
+        env.fake.fake_cuda_reset()
+        result = action()
+        calls = [tuple(l.split()[1:4]) for l in env.log() if l.startswith("prefetch")]
+        return result, [(int(p, 16), int(b), int(d)) for p, b, d in calls]
+
+    gen = env.local.status().allocation_generation
+    first = 200 * MIB + 1234
+    res, calls = calls_of(lambda: client.set_target(first))
+    t1 = aligned_uvm_target(sizes, first, page)
+    assert isinstance(res, UvmTargetResult) and res.submitted_bytes == t1 and res.clamped_bytes == first
+    assert calls == expected_calls(env, ux.expand_target(env.registry, gen, nbytes=t1, gen=gen))
+    second = 330 * MIB + 4099
+    res, calls = calls_of(lambda: client.retarget(first, second))
+    t2 = aligned_uvm_target(sizes, second, page)
+    assert isinstance(res, UvmRetargetResult) and (res.previous_submitted_bytes, res.submitted_bytes) == (t1, t2)
+    assert calls == expected_calls(env, ux.expand_retarget(env.registry, gen, gen=gen, old=t1, new=t2))
+    assert sum(c[1] for c in calls) == t2 - t1
+    # a previous target the client did not submit: full plan instead
+    res, calls = calls_of(lambda: client.retarget(17 * MIB, 64 * MIB))
+    assert isinstance(res, UvmTargetResult)
+    assert calls == expected_calls(env, ux.expand_target(env.registry, gen, nbytes=64 * MIB, gen=gen))
+    # submitted without waiting, settled by wait_idle, then shrunk incrementally
+    job = client.set_target(10 ** 12, wait=False)
+    assert isinstance(job, int) and client._pending_job == job
+    st = client.wait_idle(timeout=20)
+    assert client._pending_job is None and client._submitted_target == st.managed_bytes
+    res, calls = calls_of(lambda: client.retarget(10 ** 12, 0))
+    assert isinstance(res, UvmRetargetResult) and sum(c[1] for c in calls) == st.managed_bytes
+    assert all(c[2] == ux.CPU for c in calls)
+
+
 def test_device_planner_ranges_can_be_submitted_directly(server):
     """rt_uvm_submit_ranges: planner output -> job, without the text round trip."""
     import numpy as np
