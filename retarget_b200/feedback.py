@@ -12,7 +12,10 @@ serves both ways of planning:
 from __future__ import annotations
 
 import ctypes as C
+import json
 import os
+import pathlib
+import time
 
 import numpy as np
 
@@ -107,6 +110,21 @@ class DeviceFeedback:
                                                  C.byref(n_free), C.byref(epoch), C.byref(bad)),
                    "rt_feedback_snapshot")
         return versions, reads, writes, free[:n_free.value], epoch.value, bad.value
+
+    def publish(self, directory, at=None):
+        """Writes the snapshot where the reference's controller looks for it:
+        ``<directory>/<pid>.json``, through ``.<pid>.tmp`` and a rename
+        (experiments/slot_feedback.py:86-96)."""
+        directory = pathlib.Path(directory)
+        directory.mkdir(parents=True, exist_ok=True)
+        row = self.snapshot()
+        if at is not None:
+            row["observed_monotonic_s"] = at
+        row["published_monotonic_s"] = time.monotonic()
+        tmp = directory / f".{self.pid}.tmp"
+        tmp.write_text(json.dumps(row, separators=(",", ":")))
+        tmp.replace(directory / f"{self.pid}.json")
+        return row
 
     def snapshot(self, now=None):
         """The reference's snapshot document (experiments/slot_feedback.py:86-91);

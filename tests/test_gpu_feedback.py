@@ -128,3 +128,33 @@ def test_snapshot_feeds_the_python_controller():
     assert desired == [0, 2, 8, 15] and selected == [0, 2, 8, 15]
     fb.close()
     planner.close()
+
+
+def test_published_file_feeds_the_controller(tmp_path, monkeypatch):
+    """DeviceFeedback.publish writes <dir>/<pid>.json the way the reference's
+    SlotFeedback does; a controller that reads the directory sees the same state."""
+    import json
+    import time
+    from retarget_b200.cache_window import CacheWindowSpec
+    from retarget_b200.slot_placement import SlotPlacementController, SlotPlacementSpec
+    dev = torch.device("cuda:0")
+    layout = workloads.Layout(2, 2048, 16384)
+    planner = DevicePlanner(layout, 0)
+    fb = DeviceFeedback(planner, pid=4242)
+    now = time.monotonic()
+    slots = torch.tensor([5, 6, 7, 3000, 3001, 9000, 16000], dtype=torch.int32, device=dev)
+    fb.alloc(slots, now - 0.3, torch.tensor([2048, 2049, 40], dtype=torch.int32, device=dev))
+    fb.attention(slots[:5], slots[5:6], now - 0.1)
+    row = fb.publish(tmp_path)
+    on_disk = json.loads((tmp_path / "4242.json").read_text())
+    assert on_disk == row and not (tmp_path / ".4242.tmp").exists()
+    assert on_disk["version"] == 1 and on_disk["block_tokens"] == 1024 and on_disk["epoch"] == 1
+    monkeypatch.setenv("RETARGET_SLOT_FEEDBACK_DIR", str(tmp_path))
+    ctl = SlotPlacementController(
+        CacheWindowSpec(layout.alloc_bytes, layout.n_buffers, 2048, 4096, 1024, 1024),
+        SlotPlacementSpec(block_tokens=1024, max_blocks_per_update=4), 4242)
+    snap = ctl.snapshot(now)
+    assert snap is not None and snap["free_head_blocks"] == [2, 0]
+    assert ctl.choose(snap, now)[0] == [0, 2, 8, 15]
+    fb.close()
+    planner.close()
