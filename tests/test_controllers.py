@@ -182,3 +182,29 @@ def test_prefix_plans_replay(golden):
             want["result"]["pid"] = int(ours)
         mine = json.loads(json.dumps(mine))
         assert mine == want, want["op"]
+
+
+# The policy blocks of the reference's case files (configs/qwen_*.json, configs/llama_incremental.json),
+# as the scheduler passes them on: CacheWindowSpec(**block), SlotPlacementSpec(**block).
+QWEN_WINDOW = dict(allocation_bytes=448790528, allocation_count=80, bytes_per_token=2048, width_tokens=32768,
+                   lookahead_tokens=16384, quantum_tokens=8192, min_update_seconds=1.0, idle_only=True)
+LLAMA_WINDOW = dict(allocation_bytes=297795584, allocation_count=120, bytes_per_token=2048, width_tokens=21840,
+                    lookahead_tokens=10920, quantum_tokens=5460, min_update_seconds=1.0, idle_only=True)
+QWEN_SLOTS = dict(block_tokens=256, lookahead_tokens=4096, min_update_seconds=0.25, max_blocks_per_update=4,
+                  active_seconds=2.0, refresh_seconds=10.0, max_feedback_lag_seconds=1.0)
+
+
+def test_case_file_blocks_are_accepted(tmp_path, monkeypatch):
+    for block in (QWEN_WINDOW, dict(QWEN_WINDOW, update_mode="full_cache"),
+                  dict(QWEN_WINDOW, update_mode="initial_only"), LLAMA_WINDOW):
+        spec = cw.CacheWindowSpec(**block)
+        lo, hi = spec.window(0)
+        assert (lo, hi) == (0, block["width_tokens"] * block["bytes_per_token"])
+    # known answers at the two geometries (recorded from the reference)
+    assert cw.CacheWindowSpec(**QWEN_WINDOW).window(16385) == (16777216, 83886080)
+    assert cw.CacheWindowSpec(**QWEN_WINDOW).window(1e9) == (369098752, 436207616)
+    assert cw.CacheWindowSpec(**LLAMA_WINDOW).window(10921) == (11182080, 55910400)
+    assert cw.CacheWindowSpec(**LLAMA_WINDOW).window(145404) == (246005760, 290734080)
+    monkeypatch.setenv("RETARGET_SLOT_FEEDBACK_DIR", str(tmp_path))
+    ctl = sp.SlotPlacementController(cw.CacheWindowSpec(**QWEN_WINDOW), sp.SlotPlacementSpec(**QWEN_SLOTS), 4242)
+    assert ctl.budget == 32768 // 256

@@ -273,6 +273,48 @@ def test_slot_above_capacity_is_reported():
     p.close()
 
 
+@pytest.mark.parametrize("shared", [True, False])
+def test_partial_last_block_is_clamped(shared):
+    """Plans that include the final, partial block of every buffer: its range
+    ends at the allocation size (select.cpp:24188) and the byte totals count it
+    short, when it is added and when it is evicted again."""
+    lay = workloads.Layout(3, 2048, 6001, 12288, shared)          # 1001 blocks of 6 slots, 1 slot in the last
+    assert lay.n_blocks == 1001 and lay.alloc_bytes % lay.block_bytes == 2048
+    G = lay.n_groups
+    tail_ids = np.array([5990, 5995, 6000, 5999, 17], dtype=np.int64)     # blocks 998, 999, 1000, 2
+    head_ids = np.array([1, 7, 13], dtype=np.int64)
+    def batch(ids, budget):
+        slots = np.tile(ids, G)
+        off = np.arange(G + 1, dtype=np.int64) * len(ids)
+        return workloads.SlotBatch(lay, slots, off, off, budget)
+    steps = [batch(tail_ids, 10), batch(head_ids, 10), batch(tail_ids, 3), batch(tail_ids, 10)]
+    run_steps(steps, evict=True, flags=(0, np.int64))
+    # the figure itself, once: 4 blocks per buffer, the last one 2048 bytes long
+    p = DevicePlanner(lay, 0, max_indices=64)
+    got, res = p.step_host(steps[0].slots, steps[0].group_off, 10, capi.RT_PLAN_EVICT)
+    assert res.gpu_bytes == lay.n_buffers * (3 * 12288 + 2048)
+    assert int(got["offset"].max() + got["bytes"][got["offset"].argmax()]) == lay.alloc_bytes
+    p.close()
+
+
+@pytest.mark.parametrize("flags", MODES)
+def test_reference_qwen_geometry(flags):
+    """The reference's own deployment: 80 KV allocations of 448,790,528 bytes
+    (219,136 slots of 2048 bytes; the last 512 KiB block is partial), 256-token
+    blocks (856 of them), one mask for all allocations, a 32,768-token budget
+    (128 blocks).  Literal chain on the first two steps, vectorised after."""
+    rng = np.random.default_rng(23)
+    shape = dict(layers=40, pool_slots=219136, bytes_per_slot=2048, shared=True, n_req=24, max_len=4096,
+                 budget=32768 // 256, block_bytes=256 * 2048)
+    batches = [random_batch(rng, **shape) for _ in range(4)]
+    lay = batches[0].layout
+    assert lay.alloc_bytes == 448790528 and lay.n_buffers == 80 and lay.n_blocks == 856
+    assert lay.alloc_bytes % lay.block_bytes != 0
+    run_steps(batches[:2], evict=True, flags=flags, literal=True)
+    run_steps(batches, evict=True, flags=flags, literal=False)
+    run_steps(batches, evict=False, flags=flags, literal=False)
+
+
 @pytest.mark.parametrize("kind", ["moving", "fragmented"])
 def test_benchmark_pairs_match_oracle(kind):
     """The alternating batches the benchmark times: every step evicts and adds
