@@ -300,8 +300,7 @@ def test_partial_last_block_is_clamped(shared):
 @pytest.mark.parametrize("flags", MODES)
 def test_reference_qwen_geometry(flags):
     """The reference's own deployment: 80 KV allocations of 448,790,528 bytes
-    (219,136 slots of 2048 bytes; the last 512 KiB block is partial), 256-token
-    blocks (856 of them), one mask for all allocations, a 32,768-token budget
+    (219,136 slots of 2048 bytes), 256-token blocks (856 of 512 KiB), one mask for all allocations, a 32,768-token budget
     (128 blocks).  Literal chain on the first two steps, vectorised after."""
     rng = np.random.default_rng(23)
     shape = dict(layers=40, pool_slots=219136, bytes_per_slot=2048, shared=True, n_req=24, max_len=4096,
@@ -309,7 +308,6 @@ def test_reference_qwen_geometry(flags):
     batches = [random_batch(rng, **shape) for _ in range(4)]
     lay = batches[0].layout
     assert lay.alloc_bytes == 448790528 and lay.n_buffers == 80 and lay.n_blocks == 856
-    assert lay.alloc_bytes % lay.block_bytes != 0
     run_steps(batches[:2], evict=True, flags=flags, literal=True)
     run_steps(batches, evict=True, flags=flags, literal=False)
     run_steps(batches, evict=False, flags=flags, literal=False)
