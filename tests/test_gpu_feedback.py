@@ -158,3 +158,72 @@ def test_published_file_feeds_the_controller(tmp_path, monkeypatch):
     assert ctl.choose(snap, now)[0] == [0, 2, 8, 15]
     fb.close()
     planner.close()
+
+
+def test_device_writer_publishes_what_the_reference_probe_would(tmp_path):
+    """DeviceWriter.submit fed with the decode trace as the probe's hooks would
+    feed it (int32 kv indices, int64 written slots, free-head samples, a
+    geometry event, frees, an allocator clear), against the restated
+    SlotFeedback consuming the same rows as run lists: every file the writer
+    drops equals the snapshot the reference would have published."""
+    import json
+    from retarget_b200.probe import DeviceWriter
+    dev = torch.device("cuda:0")
+    trace = workloads.decode_trace(7, steps=90, pool_slots=32768, arrival_rate=1.0, median=256,
+                                   mean_output=24, initial_requests=6)
+    capacity = 32767
+    clock = {"t": 50.0}
+    writer = DeviceWriter(tmp_path, pid=77, block_tokens=256, publish_seconds=.05, buffers=8, slot_bytes=2048,
+                          clock=lambda: clock["t"])
+    oracle = rp.FeedbackState(block_tokens=256, publish_seconds=.05, pid=77)
+    sequence = 0
+    published = 0
+
+    def both(kind, tensors=None, **fields):
+        nonlocal sequence, published
+        if kind == "attention":
+            sampled_out = clock["t"] - both.last_attention < .05
+            if not sampled_out:
+                both.last_attention = clock["t"]
+        else:
+            sampled_out = False
+        writer.submit(kind, {k: (None if v is None else torch.from_numpy(v).to(dev)) for k, v in (tensors or {}).items()},
+                      **fields)
+        if sampled_out:
+            return
+        row = dict(event=kind, monotonic_s=clock["t"], sequence=sequence, **fields)
+        sequence += 1
+        for key, value in (tensors or {}).items():
+            if value is not None:
+                row[key + "_runs"] = rp.encode_runs(value.tolist())
+        before = oracle.last_publish
+        oracle.consume(row)
+        if oracle.last_publish != before:
+            published += 1
+            on_disk = json.loads((tmp_path / "77.json").read_text())
+            assert canonical(on_disk) == canonical(oracle.last_snapshot), (kind, sequence)
+            assert on_disk["sequence"] == oracle.last_snapshot["sequence"]
+            assert on_disk["observed_monotonic_s"] == oracle.last_snapshot["observed_monotonic_s"]
+    both.last_attention = -float("inf")
+
+    for step, ev in enumerate(trace):
+        if step == 3:
+            both("geometry", allocations=[dict(slot_bytes=2048)] * 8, allocator_size=capacity)
+        if step == 60:
+            both("allocator_clear", allocator_size=capacity, need_sort=False)
+        if len(ev.alloc_slots):
+            tensors = {"slot": ev.alloc_slots.astype(np.int64)}
+            if ev.free_head is not None:
+                tensors["free_head"] = ev.free_head.astype(np.int64)
+            both("alloc", tensors, allocator_size=capacity, need_sort=False)
+        clock["t"] += 0.011
+        both("attention", {"read": ev.read_slots.astype(np.int32), "write": ev.write_slots.astype(np.int64)},
+             path="eager", mode="DECODE", batch_size=ev.live, reads="all_cached_kv")
+        clock["t"] += 0.011
+        if step % 7 == 0 and len(ev.write_slots):
+            both("free", {"slot": ev.write_slots[:1].astype(np.int64)}, grouped=False)
+        clock["t"] += 0.011
+    assert published > 20 and oracle.epoch == 2
+    with pytest.raises(AssertionError):
+        writer.submit("geometry", allocations=[dict(slot_bytes=4096)] * 8, allocator_size=capacity)
+    writer.close()
