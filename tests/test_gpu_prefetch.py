@@ -115,3 +115,69 @@ def test_executor_moves_managed_ranges(managed):
         for p in ptrs:
             lib.rt_uvm_unregister_ptr(p)
         lib.rt_uvm_stop()
+
+
+def test_probe_to_prefetch_chain(managed, tmp_path, monkeypatch):
+    """The whole event-driven path on real managed memory: probe events on the
+    device -> published snapshot -> the scheduler-side controller -> blocksv on
+    the control protocol -> the executor's cuMemPrefetchAsync calls.  The blocks
+    the policy picks end up with the GPU as their last prefetch location in
+    every buffer; nothing else was touched."""
+    import time
+    cudart, ctx, ptrs, size = managed
+    from retarget_b200 import capi
+    from retarget_b200.cache_window import CacheWindowSpec
+    from retarget_b200.control import LocalUvm
+    from retarget_b200.probe import DeviceWriter
+    from retarget_b200.slot_placement import SlotPlacementController, SlotPlacementSpec
+    lib = capi.lib
+    lib.rt_uvm_register.argtypes = [C.c_uint64, C.c_uint64, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_uint64)]
+    lib.rt_uvm_unregister_ptr.argtypes = [C.c_uint64]
+    slot_bytes, block_tokens = 2048, 256
+    capacity = size // slot_bytes - 1                       # 4095 slots, 16 blocks of 512 KiB
+    block_bytes = slot_bytes * block_tokens
+    monkeypatch.setenv("RETARGET_SLOT_FEEDBACK_DIR", str(tmp_path))
+    dev = torch.device("cuda:0")
+    cfg = UvmConfig(None, 2 * MIB, 6 * MIB, 2, 0)
+    capi.check(lib.rt_uvm_start(C.byref(cfg)), "start")
+    writer = None
+    try:
+        for p in ptrs:
+            capi.check(lib.rt_uvm_register(p, size, C.c_void_p(ctx), 0, 1, None), "register")
+        uvm = LocalUvm()
+        gen, _ = uvm._allocation_snapshot()
+        # everything to the CPU first, so that a GPU location afterwards is the plan's doing
+        reply = uvm.command(f"targetv {gen} 0")
+        uvm._wait_job(reply["job_id"], timeout=60, poll_seconds=0.002)
+        writer = DeviceWriter(pid=os.getpid(), block_tokens=block_tokens, buffers=len(ptrs), slot_bytes=slot_bytes)
+        held = torch.arange(1, 700, dtype=torch.int64, device=dev)                 # blocks 0..2
+        writer.submit("alloc", {"slot": held, "free_head": torch.arange(3000, 3100, dtype=torch.int64, device=dev)},
+                      allocator_size=capacity, need_sort=False)
+        reads = torch.cat([torch.arange(1, 300, device=dev), torch.arange(2600, 2700, device=dev)]).to(torch.int32)
+        writer.submit("attention", {"read": reads, "write": torch.tensor([699], dtype=torch.int64, device=dev)},
+                      path="eager", mode="DECODE", batch_size=2, reads="all_cached_kv")
+        writer.publish(writer.feedback.at)
+        spec = CacheWindowSpec(size, len(ptrs), slot_bytes, 4 * block_tokens, block_tokens, block_tokens)
+        ctl = SlotPlacementController(spec, SlotPlacementSpec(block_tokens=block_tokens, max_blocks_per_update=4),
+                                      os.getpid())
+        assert ctl.budget == 4
+        now = time.monotonic()
+        snap = ctl.snapshot(now)
+        desired, selected = ctl.choose(snap, now)
+        # reads: blocks 0, 1 and 10; writes: block 2 (the write stamp of the attention event); then the free head
+        assert desired == [0, 1, 10, 2] and selected == desired
+        result = ctl.update(uvm, {}, now)
+        assert result is not None and uvm.status().last_error == 0
+        assert uvm.status().job_completed_bytes == len(ptrs) * 4 * block_bytes
+        for p in ptrs:
+            for b in range(16):
+                where = last_location(cudart, p + b * block_bytes, block_bytes)
+                assert where == (0 if b in desired else -1), (b, where)
+        # a second update with nothing new to move sends nothing
+        assert ctl.update(uvm, {}, time.monotonic()) is None
+    finally:
+        if writer is not None:
+            writer.close()
+        for p in ptrs:
+            lib.rt_uvm_unregister_ptr(p)
+        lib.rt_uvm_stop()
