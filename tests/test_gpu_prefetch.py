@@ -181,3 +181,58 @@ def test_probe_to_prefetch_chain(managed, tmp_path, monkeypatch):
         for p in ptrs:
             lib.rt_uvm_unregister_ptr(p)
         lib.rt_uvm_stop()
+
+
+def test_window_controller_moves_the_window(managed):
+    """The counter-driven path on real managed memory: Prometheus counters ->
+    CacheWindowController.update -> windowv on the control protocol -> executor.
+    After every accepted update the window's bytes were last sent to the GPU and
+    everything outside it to the CPU, in every buffer."""
+    cudart, ctx, ptrs, size = managed
+    from retarget_b200 import capi
+    from retarget_b200.cache_window import CacheWindowController, CacheWindowSpec
+    from retarget_b200.control import LocalUvm
+    lib = capi.lib
+    lib.rt_uvm_register.argtypes = [C.c_uint64, C.c_uint64, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_uint64)]
+    lib.rt_uvm_unregister_ptr.argtypes = [C.c_uint64]
+    spec = CacheWindowSpec(size, len(ptrs), 2048, 1024, 512, 512, min_update_seconds=1.0, idle_only=True)
+    ctl = CacheWindowController(spec)
+    cfg = UvmConfig(None, 1 * MIB, 4 * MIB, 2, 0)
+    capi.check(lib.rt_uvm_start(C.byref(cfg)), "start")
+
+    def metrics(prompt, generated, running=0, queued=0):
+        return {"sglang:prompt_tokens_total": float(prompt), "sglang:generation_tokens_total": float(generated),
+                "sglang:num_running_reqs": float(running), "sglang:num_queue_reqs": float(queued)}
+
+    def check(window):
+        lo, hi = window
+        for p in ptrs:
+            if lo:
+                assert last_location(cudart, p, lo) == -1
+            assert last_location(cudart, p + lo, hi - lo) == 0
+            if hi < size:
+                assert last_location(cudart, p + hi, size - hi) == -1
+
+    try:
+        for p in ptrs:
+            capi.check(lib.rt_uvm_register(p, size, C.c_void_p(ctx), 0, 1, None), "register")
+        uvm = LocalUvm()
+        first = ctl.update(uvm, metrics(100, 0), 10.0, initial=True)
+        assert first["initial"] and first["new_window"] == [0, 2 * MIB]
+        assert first["requested_gpu_bytes"] == len(ptrs) * 2 * MIB
+        assert first["requested_cpu_bytes"] == len(ptrs) * (size - 2 * MIB)
+        check(first["new_window"])
+        assert ctl.update(uvm, metrics(700, 200, running=2), 12.0) is None          # not idle
+        moved = ctl.update(uvm, metrics(700, 200), 12.5)
+        assert moved["old_window"] == [0, 2 * MIB] and moved["new_window"] == [1 * MIB, 3 * MIB]
+        assert moved["requested_gpu_bytes"] == moved["requested_cpu_bytes"] == len(ptrs) * MIB
+        check(moved["new_window"])
+        assert ctl.update(uvm, metrics(3000, 500), 12.9) is None                    # too soon
+        far = ctl.update(uvm, metrics(3000, 500), 14.0)
+        assert far["new_window"] == [6 * MIB, 8 * MIB]
+        check(far["new_window"])
+        assert uvm.status().last_error == 0
+    finally:
+        for p in ptrs:
+            lib.rt_uvm_unregister_ptr(p)
+        lib.rt_uvm_stop()
