@@ -23,6 +23,7 @@ from __future__ import annotations
 import argparse
 import ctypes as C
 import json
+import os
 import time
 
 import numpy as np
@@ -241,6 +242,24 @@ def main():
     counters.close()
     capi.check(lib.rt_uvm_stop(), "rt_uvm_stop")
     planner.close()
+    # ---- incremental window moves: every step evicts one stride and grows one stride per buffer ----
+    # (the reference's incremental update, select.cpp:24231-24240; CPU-bound ranges are waited for
+    # before the GPU-bound ones.  Letting the two directions overlap was tried and gained nothing:
+    # the driver runs the migrations of one process one after the other.)
+    cfg = UvmConfig(None, 16 * MIB, 256 * MIB, 4, 0)
+    capi.check(lib.rt_uvm_start(C.byref(cfg)), "rt_uvm_start")
+    gen = uvm.status().allocation_generation
+    width, stride, big = alloc // 4, alloc // 8, (1 << 64) - 1
+    run_job(f"windowv {gen} {alloc} {args.buffers} {big} {big} 0 {width}")
+    lo, times = 0, []
+    for _ in range(5):
+        times.append(run_job(f"windowv {gen} {alloc} {args.buffers} {lo} {lo + width} "
+                             f"{lo + stride} {lo + stride + width}"))
+        lo += stride
+    out["window_moves"] = {"bytes_each_way_per_step": stride * args.buffers, "seconds_per_step_best": min(times),
+                           "seconds_per_step_median": sorted(times)[2],
+                           "gbs_both_directions": 2 * stride * args.buffers / min(times) / 1e9}
+    capi.check(lib.rt_uvm_stop(), "rt_uvm_stop")
     for p in ptrs:
         cudart.cudaFree(p)
     print(json.dumps(out))
