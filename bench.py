@@ -26,6 +26,7 @@ Prints one JSON line (rank 0).
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import multiprocessing as mp
 import os
@@ -358,6 +359,31 @@ def run_ours(args):
         variants["int32_ids"] = {"us_per_step": us, "ranges_per_step": nr, "steps": n,
                                  "gbs": (algorithmic_bytes(batches[0], nr) - 4 * batches[0].n_idx) / us / 1e3}
         del tensors
+        # the padded-table entry point (the serving engine's req_to_token layout) on the same ids as
+        # int32: one row per (layer, request), one bitmap for all buffers
+        rows = batches[0].n_idx // 2176
+        if rows * 2176 == batches[0].n_idx:
+            shared = dataclasses.replace(lay, shared_bitmap=True)
+            table_planner = DevicePlanner(shared, local)
+            tables = [torch.from_numpy(b.slots.astype(np.int32).reshape(rows, 2176)).to(dev) for b in batches]
+            lens = torch.full((rows,), 2176, dtype=torch.int32, device=dev)
+            for i in range(4):
+                table_planner.step_table(tables[i % 2], lens, batches[0].budget_blocks, flags, d_out, d_res,
+                                         stream.cuda_stream)
+            torch.cuda.synchronize()
+            t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            t[0].record(stream)
+            for i in range(50):
+                table_planner.step_table(tables[i % 2], lens, batches[0].budget_blocks, flags, d_out, d_res,
+                                         stream.cuda_stream)
+            t[1].record(stream)
+            torch.cuda.synchronize()
+            us = t[0].elapsed_time(t[1]) * 1e3 / 50
+            variants["table_int32_one_bitmap"] = {"us_per_step": us, "rows": rows, "stride": 2176, "steps": 50,
+                                                  "ranges_per_step": result_from_tensor(d_res)["n_ranges"],
+                                                  "gbs": 4 * batches[0].n_idx / us / 1e3}
+            table_planner.close()
+            del tables
         for i in range(2):      # leave the resident state as the main workload left it
             device_step(W + K + i)
         torch.cuda.synchronize()

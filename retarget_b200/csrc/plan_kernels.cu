@@ -684,6 +684,11 @@ cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plai
                                 int *tma_blocks_per_sm) {
     const int tail = (int)tail_smem_bytes(n_groups, n_buffers);
     const int tma = kStages * kStageBytes;
+    // The attribute belongs to the kernel, not to a plan: it is set to what the
+    // largest plan needs, so that plans of different geometry can live in one
+    // process (set per plan, a smaller plan created later made the launches of a
+    // larger one fail with "invalid value").
+    const int tail_max = (int)tail_smem_bytes(RT_MAX_GROUPS, RT_MAX_BUFFERS);
     cudaError_t e;
 #define RT_SET_SMEM(kernel, bytes)                                                           \
     if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes)) != \
@@ -691,15 +696,15 @@ cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plai
         return e;
     RT_SET_SMEM(scan_plan_tma_kernel<true>, tma)
     RT_SET_SMEM(scan_plan_tma_kernel<false>, tma)
-    RT_SET_SMEM((scan_plan_kernel<true, long long>), tail)
-    RT_SET_SMEM((scan_plan_kernel<false, long long>), tail)
-    RT_SET_SMEM((scan_plan_kernel<true, int>), tail)
-    RT_SET_SMEM((scan_plan_kernel<false, int>), tail)
-    RT_SET_SMEM((scan_table_kernel<true, long long>), tail)
-    RT_SET_SMEM((scan_table_kernel<false, long long>), tail)
-    RT_SET_SMEM((scan_table_kernel<true, int>), tail)
-    RT_SET_SMEM((scan_table_kernel<false, int>), tail)
-    RT_SET_SMEM(plan_tail_kernel, tail)
+    RT_SET_SMEM((scan_plan_kernel<true, long long>), tail_max)
+    RT_SET_SMEM((scan_plan_kernel<false, long long>), tail_max)
+    RT_SET_SMEM((scan_plan_kernel<true, int>), tail_max)
+    RT_SET_SMEM((scan_plan_kernel<false, int>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<true, long long>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<false, long long>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<true, int>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<false, int>), tail_max)
+    RT_SET_SMEM(plan_tail_kernel, tail_max)
 #undef RT_SET_SMEM
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(plain_blocks_per_sm, scan_plan_kernel<true, long long>,
                                                       kScanThreads, tail);

@@ -68,7 +68,8 @@ bool socket_command(const std::string &line, std::string *reply) {
         return false;                       // server between stop and start
     }
     std::string out = line + "\n";
-    bool ok = write(fd, out.data(), out.size()) == (ssize_t)out.size();
+    // the server may stop between connect and write: no SIGPIPE, just a failed command
+    bool ok = send(fd, out.data(), out.size(), MSG_NOSIGNAL) == (ssize_t)out.size();
     reply->clear();
     char buf[4096];
     while (ok) {
