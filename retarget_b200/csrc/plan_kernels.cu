@@ -140,15 +140,29 @@ __device__ __forceinline__ void mark_full(const Vec (&v)[kUnroll], const ScanArg
 }
 
 // Same with a validity mask: bit kPer*u + k says whether id k of v[u] is real.
+// A vector whose ids are all real still gets the one-test fast path; only the
+// vectors that straddle the ends of the id list are classified id by id.
 template <bool kPow2, typename Vec>
 __device__ __forceinline__ void mark_masked(const Vec (&v)[kUnroll], uint32_t mask,
                                             const ScanArgs &a, uint8_t *s_map, ScanCounters &c) {
     constexpr int kPer = VecIds<Vec>::kPer;
+    constexpr uint32_t kWhole = (1u << kPer) - 1u;
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
+    for (int u = 0; u < kUnroll; ++u) {
+        const uint32_t bits = (mask >> (kPer * u)) & kWhole;
+        if (bits == kWhole) {
+            uint32_t hi_or = 0, worst = 0;
+            batch_test(v[u], hi_or, worst);
+            if (hi_or == 0 && worst < (uint32_t)a.capacity) {
+#pragma unroll
+                for (int k = 0; k < kPer; ++k) s_map[block_of<kPow2>((uint32_t)vec_get(v[u], k), a)] = 1;
+                continue;
+            }
+        }
 #pragma unroll
         for (int k = 0; k < kPer; ++k)
-            if (mask & (1u << (kPer * u + k))) mark_slot<kPow2>((long long)vec_get(v[u], k), a, s_map, c);
+            if (bits & (1u << k)) mark_slot<kPow2>((long long)vec_get(v[u], k), a, s_map, c);
+    }
 }
 
 // One work unit as registers: kChunkIds ids starting at the 16-byte aligned
@@ -176,6 +190,11 @@ __device__ __forceinline__ void load_chunk(const Id *mine, long long e0, long lo
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const long long i = e0 + kPer * (u * kScanThreads + (int)threadIdx.x);
+            if (i >= begin && i + kPer <= end) {         // whole vector inside: one 128-bit load
+                ch.v[u] = RT_LOAD(reinterpret_cast<const Vec *>(mine + kPer * u * kScanThreads));
+                ch.mask |= ((1u << kPer) - 1u) << (kPer * u);
+                continue;
+            }
 #pragma unroll
             for (int k = 0; k < kPer; ++k) {
                 Id x = 0;
@@ -405,18 +424,31 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
     clear_map(s_map);
     __syncthreads();
     uint32_t units = 0;
-    for (int q = blockIdx.x; q < a.n_units; q += gridDim.x) {
+    // loads of unit q: the row's length first, then its ids (an empty chunk when
+    // the unit lies past the row's valid ids)
+    auto fetch = [&](int q, Chunk<Id> &ch) {
         const int row = q / a.units_per_row, k = q - row * a.units_per_row;
-        long long len = a.lens[row];
+        long long len = __ldg(a.lens + row);
         if (len < 0) len = 0;
         if (len > a.stride) len = a.stride;
         const long long lo = (long long)row * a.stride, hi = lo + len;
         const long long e0 = (lo & ~(long long)(kPer - 1)) + (long long)k * kChunkIds<Id>;
-        ++units;
-        if (e0 >= hi) continue;                                  // past the row's valid ids
-        Chunk<Id> ch;
+        if (e0 >= hi) {
+            ch.mask = 0;
+            return;
+        }
         load_chunk<Id>(slots + e0 + kPer * (int)threadIdx.x, e0, lo, hi, ch);
-        mark_chunk<kPow2, Id>(ch, a, s_map, c);
+    };
+    // the next unit's loads are in flight while this one is marked
+    Chunk<Id> cur, nxt;
+    fetch(blockIdx.x, cur);
+    for (int q = blockIdx.x; q < a.n_units; q += gridDim.x) {
+        const int qn = q + (int)gridDim.x;
+        if (qn < a.n_units) fetch(qn, nxt);
+        else nxt.mask = 0;
+        if (cur.mask) mark_chunk<kPow2, Id>(cur, a, s_map, c);
+        ++units;
+        cur = nxt;
     }
     leave_group<0>(p, 0, s_map, c);
     finish_cta<0>(p, units, hs, tail_mem);
