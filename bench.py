@@ -589,7 +589,7 @@ def run_feedback(args):
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, mean of 3 launches), keyed by
 # (workload, tma); a configuration that was not captured reports null.
 PROFILED_TRAFFIC_BYTES = {
-    ("target", False): 182_568_000,   # 178.33 MB read + 4.23 MB written
+    ("target", False): 181_694_000,   # 178.35 MB read + 3.35 MB written
     ("target", True): 182_592_000,    # 178.33 MB read + 4.26 MB written
 }
 
