@@ -590,7 +590,7 @@ def run_feedback(args):
 # (workload, tma); a configuration that was not captured reports null.
 PROFILED_TRAFFIC_BYTES = {
     ("target", False): 181_694_000,   # 178.35 MB read + 3.35 MB written
-    ("target", True): 182_592_000,    # 178.33 MB read + 4.26 MB written
+    ("target", True): 182_228_000,    # 178.34 MB read + 3.89 MB written
 }
 
 
