@@ -2,6 +2,7 @@
 """Placement-plan benchmark.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+                    [--launch graph|stream] [--tma] [--no-cpu] [--no-variants]
 
 One step = one placement plan for one decode step of the headline workload:
 40 layers (80 KV buffers of 512 MiB), 256 requests, a 262,144-slot pool, and per
@@ -14,8 +15,11 @@ reference's incremental window update).  `variants` reports the same step when
 nothing moves (0 ranges), when the whole budget is replaced in single-block
 runs (6080 ranges) and when the ids are int32.
 
-`value`  device time per step, slot ids already in HBM (CUDA events on the
-         launching stream, max over ranks)
+`value`  device time per step, slot ids already in HBM (two CUDA events on the
+         launching stream around the K steps, max over ranks); the steps are
+         issued as CUDA-graph replays (--launch graph, default) or one by one
+--workload feedback  the event-driven path (device-resident feedback state)
+         on an incremental decode trace, beside the Python chain on one core
 `e2e`    the same plan through the host-buffer C-ABI call: pinned host ids are
          copied to the device, planned, and the range list is copied back
 --impl reference  times the CPU restatement of the reference's Python path on
