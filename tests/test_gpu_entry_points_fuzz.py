@@ -1,9 +1,11 @@
 """GPU parity of the device-resident entry points over seeded random geometries:
 ids already in HBM (one flat list with per-bitmap offsets), the padded request
 table with a random stride, and the scan-only call followed by the plan from
-bitmaps.  All three must give the CPU oracle's range list from the same random
-resident set, for 64- and 32-bit ids; the scan's bitmaps must equal the set of
-blocks the oracle finds, bit for bit."""
+bitmaps (plus, for 64-bit ids, the allocation-free scan).  All three must give
+the CPU oracle's range list from the same random resident set, for 64- and
+32-bit ids; the scans' bitmaps must equal the set of blocks the oracle finds,
+bit for bit."""
+import ctypes as C
 import dataclasses
 
 import numpy as np
@@ -73,6 +75,19 @@ def test_device_entry_points(seed, dtype):
     assert result_from_tensor(d_res)["blocks_touched"] == touched
     p.from_bitmaps(d_bits, b.budget_blocks, flags, d_out, d_res, stream)
     check(p, "scan, then plan from bitmaps")
+
+    if dtype is np.int64:      # the allocation-free scan takes 64-bit ids
+        d_static = torch.full((G * capi.RT_BITMAP_WORDS,), -1, dtype=torch.int32, device=dev)
+        fn = capi.lib.rt_scan_slots_static
+        fn.restype = C.c_int
+        fn.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32,
+                       C.c_void_p, C.c_void_p, C.c_void_p]
+        status = fn(d_slots.data_ptr() if d_slots.numel() else None, b.group_off.ctypes.data, G, lay.capacity,
+                    lay.block_tokens, lay.n_blocks, d_static.data_ptr(), d_res.data_ptr(), stream)
+        assert status == 0, capi.strerror(status)
+        torch.cuda.synchronize()
+        assert np.array_equal(d_static.cpu().numpy().view(np.uint32).reshape(G, -1), bits)
+        assert result_from_tensor(d_res)["blocks_touched"] == touched
 
     if G == 1:      # the request table feeds one bitmap
         lens = np.diff(b.req_off).astype(np.int32)
