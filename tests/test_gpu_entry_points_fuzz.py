@@ -7,6 +7,7 @@ the CPU oracle's range list from the same random resident set, for 64- and
 bit for bit."""
 import ctypes as C
 import dataclasses
+import os
 
 import numpy as np
 import pytest
@@ -19,11 +20,14 @@ from test_gpu_plan_fuzz import random_shape
 from test_gpu_plan_parity import random_batch
 
 pytestmark = pytest.mark.gpu
+
+# RETARGET_FUZZ_SEEDS=N runs a longer sweep of the same generator
+SEEDS = int(os.environ.get("RETARGET_FUZZ_SEEDS", 16))
 torch = pytest.importorskip("torch")
 
 
 @pytest.mark.parametrize("dtype", [np.int64, np.int32], ids=["i64", "i32"])
-@pytest.mark.parametrize("seed", range(16))
+@pytest.mark.parametrize("seed", range(SEEDS))
 def test_device_entry_points(seed, dtype):
     rng = np.random.default_rng(5200 + seed)
     shape = random_shape(rng)

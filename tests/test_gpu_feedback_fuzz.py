@@ -5,6 +5,8 @@ and refresh periods shorter and longer than the trace, with and without
 eviction, 64- and 32-bit ids, an allocator clear somewhere in the middle.  Every
 step's range list, counters and resident set, and the snapshot every 16 steps,
 must equal the CPU restatement of the reference's chain exactly."""
+import os
+
 import numpy as np
 import pytest
 
@@ -12,6 +14,9 @@ from retarget_b200 import workloads
 from test_gpu_feedback import run_trace
 
 pytestmark = pytest.mark.gpu
+
+# RETARGET_FUZZ_SEEDS=N runs a longer sweep of the same generator
+SEEDS = int(os.environ.get("RETARGET_FUZZ_SEEDS", 16))
 
 
 def random_case(rng):
@@ -34,7 +39,7 @@ def random_case(rng):
         dtype=np.int32 if rng.random() < .5 else np.int64)
 
 
-@pytest.mark.parametrize("seed", range(16))
+@pytest.mark.parametrize("seed", range(SEEDS))
 def test_random_policy_and_geometry(seed):
     rng = np.random.default_rng(7100 + seed)
     case = random_case(rng)

@@ -4,6 +4,7 @@ shared and per-layer bitmaps, budgets from one block to the whole buffer, ids
 out of range mixed in.  Each case runs a few consecutive steps through the C ABI
 and compares ranges, counters and the resident set with the CPU oracle, exactly."""
 import dataclasses
+import os
 import math
 
 import numpy as np
@@ -12,6 +13,9 @@ import pytest
 from test_gpu_plan_parity import MODES, random_batch, run_steps
 
 pytestmark = pytest.mark.gpu
+
+# RETARGET_FUZZ_SEEDS=N runs a longer sweep of the same generator
+SEEDS = int(os.environ.get("RETARGET_FUZZ_SEEDS", 24))
 
 # bitmap widths worth hitting on purpose: around 32-bit words, around the widths
 # the tail's segmented scans switch at, and the protocol's limit of 1024 blocks
@@ -38,7 +42,7 @@ def random_shape(rng):
 
 
 @pytest.mark.parametrize("flags", MODES)
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(SEEDS))
 def test_random_geometry(seed, flags):
     rng = np.random.default_rng(9000 + seed)
     shape = random_shape(rng)
