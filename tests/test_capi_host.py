@@ -198,3 +198,96 @@ def test_expand_command_fuzz():
 def test_expand_command_odd_lines(line):
     reg = [dict(id=1, bytes=4096, device=0, concurrent=1)]
     _both(reg, 0, line)
+
+
+# --------------------------------------------------------------------------
+# host policy arithmetic on random inputs: C ABI vs the oracle (itself pinned
+# to the reference's vectors above)
+# --------------------------------------------------------------------------
+def _random_window_spec(rng):
+    """A spec that may or may not be valid: every rule of the reference's
+    validation is broken some of the time."""
+    bytes_per_token = rng.choice([256, 512, 1024, 2048, 4096, 3, 1536])
+    quantum = rng.choice([16, 256, 1024, 8192, 24, 1000])
+    width = quantum * rng.randint(1, 12) + (rng.choice([0, 0, 0, 1, quantum // 2]))
+    lookahead = quantum * rng.randint(0, 12)
+    allocation = width * bytes_per_token + rng.choice([-4096, 0, 0, 4096, 12345, 7 * quantum * bytes_per_token + 5])
+    return dict(allocation_bytes=allocation, allocation_count=rng.randint(0, 80), bytes_per_token=bytes_per_token,
+                width_tokens=width, lookahead_tokens=lookahead, quantum_tokens=quantum,
+                min_update_seconds=rng.choice([0.0, 1.0, -1.0]))
+
+
+def test_window_arithmetic_random_against_oracle():
+    rng = random.Random(31)
+    out = (C.c_uint64 * 2)()
+    valid = 0
+    for _ in range(3000):
+        kw = _random_window_spec(rng)
+        if any(kw[k] < 0 for k in ("allocation_bytes", "lookahead_tokens")):
+            continue                                  # unsigned in the C structure
+        spec = rp.WindowSpec(**kw)
+        s = capi.window_spec_struct(**kw)
+        st = capi.lib.rt_window_spec_check(C.byref(s), None)
+        try:
+            rp.check_window_spec(spec)
+        except ValueError as e:
+            message = str(e)
+            if st == capi.RT_ERR_SPEC_POSITIVE:
+                assert message.endswith("must be a positive integer"), kw
+            else:
+                assert capi.strerror(st) == message, kw
+            continue
+        assert st == 0, (kw, capi.strerror(st))
+        valid += 1
+        for _ in range(8):
+            completed = rng.choice([0.0, rng.random() * 10, float(rng.randint(0, 1 << 22)),
+                                    rng.random() * (1 << 22), float(1 << 53), 1e18, 3.5e300])
+            assert capi.lib.rt_window(C.byref(s), completed, out) == 0
+            assert (out[0], out[1]) == rp.window(spec, completed), (kw, completed)
+    assert valid > 300
+
+
+def test_interval_difference_random_against_oracle():
+    rng = random.Random(32)
+    out = (C.c_uint64 * 4)()
+    for _ in range(5000):
+        a = sorted(rng.randint(0, 40) for _ in range(2))
+        b = sorted(rng.randint(0, 40) for _ in range(2))
+        n = capi.lib.rt_interval_difference((C.c_uint64 * 2)(*a), (C.c_uint64 * 2)(*b), out)
+        assert [(out[2 * i], out[2 * i + 1]) for i in range(n)] == rp.interval_difference(a, b), (a, b)
+
+
+def test_runs_masks_and_budget_random_against_oracle():
+    rng = random.Random(33)
+    buf = C.create_string_buffer(300)
+    for _ in range(500):
+        blocks = [rng.randint(0, 1023) for _ in range(rng.randint(0, 60))]
+        arr = (C.c_uint32 * max(1, len(blocks)))(*blocks)
+        n = capi.lib.rt_encode_mask(arr, len(blocks), buf, 300)
+        want = rp.encode_mask(blocks)
+        assert n == len(want) and buf.value.decode() == want
+        # consecutive stretches, repeats, steps back, negative ids
+        values, v = [], rng.randint(-5, 50)
+        for _ in range(rng.randint(0, 200)):
+            v += rng.choice([1, 1, 1, 1, 0, 2, -1, rng.randint(-40, 40)])
+            values.append(v)
+        vals = np.asarray(values, dtype=np.int64)
+        runs = np.zeros((max(1, len(values)), 2), dtype=np.int64)
+        count = C.c_size_t()
+        st = capi.lib.rt_encode_runs(vals.ctypes.data_as(C.POINTER(C.c_int64)), len(vals),
+                                     runs.ctypes.data_as(C.POINTER(C.c_int64)), len(runs), C.byref(count))
+        assert st == 0 and runs[:count.value].tolist() == rp.encode_runs(values)
+    b = C.c_uint64()
+    for _ in range(2000):
+        width = rng.choice([256, 1024, 4096, 32768, 3000])
+        bytes_per_token = rng.choice([3, 256, 2048, 4096, 1536])
+        block_tokens = rng.choice([1, 2, 6, 16, 256, 1024, 3000, 65536])
+        w = rp.WindowSpec(1 << 40, 4, bytes_per_token, width, 1, 1)
+        s = capi.window_spec_struct(1 << 40, 4, bytes_per_token, width, 1, 1)
+        st = capi.lib.rt_slot_budget(C.byref(s), block_tokens, C.byref(b))
+        try:
+            want = rp.slot_plan_budget(w, rp.SlotSpec(block_tokens=block_tokens))
+        except ValueError as e:
+            assert capi.strerror(st) == str(e), (width, bytes_per_token, block_tokens)
+        else:
+            assert st == 0 and b.value == want
