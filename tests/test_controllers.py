@@ -208,3 +208,38 @@ def test_case_file_blocks_are_accepted(tmp_path, monkeypatch):
     monkeypatch.setenv("RETARGET_SLOT_FEEDBACK_DIR", str(tmp_path))
     ctl = sp.SlotPlacementController(cw.CacheWindowSpec(**QWEN_WINDOW), sp.SlotPlacementSpec(**QWEN_SLOTS), 4242)
     assert ctl.budget == 32768 // 256
+
+
+def test_choose_random_snapshots_against_oracle():
+    """The controller's ranking and selection on random snapshots -- ties in the
+    stamps, blocks that are in both lists, stale and fresh commitments, changed
+    versions -- against the oracle's restatement (itself pinned to the reference's
+    logs in test_oracle_golden.py)."""
+    import random
+
+    from oracle import ref_policy as rp
+    rng = random.Random(77)
+    for _ in range(400):
+        n_blocks = rng.choice([4, 16, 64])
+        block_tokens = rng.choice([16, 256])
+        budget = rng.randint(1, n_blocks)
+        kw = dict(block_tokens=block_tokens, max_blocks_per_update=rng.randint(1, budget),
+                  active_seconds=rng.choice([.5, 2.0]), refresh_seconds=rng.choice([1.0, 10.0]))
+        ctl = sp.SlotPlacementController(
+            cw.CacheWindowSpec(n_blocks * block_tokens * 2048, 2, 2048, budget * block_tokens, block_tokens // 2,
+                               block_tokens // 2),
+            sp.SlotPlacementSpec(**kw), 1, snapshot_source=lambda now: None)
+        assert ctl.budget == budget
+        now = 100.0
+        stamp = lambda: now - rng.choice([0.0, .25, .5, 1.0, 2.0, 2.5, 30.0])
+        snapshot = dict(
+            recent_reads=[[b, stamp()] for b in rng.sample(range(n_blocks), rng.randint(0, n_blocks))],
+            recent_writes=[[b, stamp()] for b in rng.sample(range(n_blocks), rng.randint(0, n_blocks // 2))],
+            free_head_blocks=rng.sample(range(n_blocks), rng.randint(0, 3)),
+            block_versions=[rng.randint(0, 2) for _ in range(n_blocks)])
+        committed = {b: (rng.randint(0, 2), now - rng.choice([.1, 1.0, 5.0, 50.0]))
+                     for b in rng.sample(range(n_blocks), rng.randint(0, n_blocks))}
+        ctl.committed = dict(committed)
+        want = rp.choose(snapshot, rp.SlotSpec(**kw), budget, committed, now)
+        assert ctl.choose(snapshot, now) == want
+        assert sp.target_blocks(snapshot, ctl.slot_spec, budget, now) == want[0]
