@@ -48,6 +48,7 @@ typedef enum rt_status {
     RT_ERR_NOT_RUNNING = -9,
     RT_ERR_IO = -10,
     RT_ERR_PLAN = -11,              /* plan command rejected; text from rt_uvm_command reply  */
+    RT_ERR_TIMEOUT = -12,           /* a bounded device-side wait gave up; nothing was planned */
     /* experiments/cache_window.py:31-50, one code per message, in check order */
     RT_ERR_SPEC_POSITIVE = -20,
     RT_ERR_SPEC_TRAILING = -21,
@@ -189,9 +190,17 @@ typedef struct rt_layout {
                              /* (default: register-staged 128-bit loads, which measured    */
                              /* faster at the sizes a decode step produces)                */
 
-#define RT_RESULT_OVERFLOW   1u   /* more ranges than `cap`; the first cap were written */
-#define RT_RESULT_SLOT_RANGE 2u   /* some slot id was above capacity                    */
-#define RT_RESULT_TIMEOUT    4u   /* a bounded device-side wait gave up                 */
+/* A step whose result carries any of these flags has NOT changed the resident
+ * bitmaps: a plan that cannot be delivered in full is not committed (the
+ * reference drops its record on any failure, experiments/slot_placement.py:140-147,
+ * and checks the slot range before it stamps anything, experiments/slot_feedback.py:42).
+ * The host-buffer calls turn them into RT_ERR_CAPACITY, RT_ERR_SLOT_RANGE and
+ * RT_ERR_TIMEOUT; callers of the device-side calls read them from the result. */
+#define RT_RESULT_OVERFLOW   1u   /* more ranges than `cap`: n_ranges says how many the   */
+                                  /* plan needs, the first cap were written               */
+#define RT_RESULT_SLOT_RANGE 2u   /* some slot id was above capacity; no range reported   */
+#define RT_RESULT_TIMEOUT    4u   /* a bounded device-side wait gave up (bulk-copy        */
+                                  /* staging only); no range reported                     */
 
 typedef struct rt_plan_result {
     uint32_t n_ranges;        /* total emitted (may exceed cap, see flags)  */

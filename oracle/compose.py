@@ -19,7 +19,9 @@ parity test run the same recipe:
   that are no longer desired are expanded the same way with destination CPU
   and are listed before every GPU range, mirroring the CPU-before-GPU phase
   order of the window commands;
-* afterwards the committed set equals the desired set.
+* afterwards the committed set of a group equals its desired set -- unless
+  nothing of the group moved, in which case its record is left as it was, as
+  the reference's controller returns early when nothing was selected.
 """
 from __future__ import annotations
 
@@ -53,6 +55,14 @@ def group_blocks_literal(slots, req_off, layout):
     fb.consume(dict(event="attention", monotonic_s=T_NOW, sequence=0,
                     read_runs=runs, write_runs=[]))
     return fb
+
+
+def touched_blocks(slots, layout):
+    """Ascending block ids touched by ``slots`` (all within 1..capacity or below
+    1), through the restated reference functions: encode_runs -> blocks."""
+    fb = rp.FeedbackState(block_tokens=layout.block_tokens)
+    fb.reset(layout.capacity)
+    return sorted(fb.blocks(rp.encode_runs(np.asarray(slots).tolist())))
 
 
 def group_blocks_fast(slots, layout):
@@ -106,9 +116,14 @@ def plan_step(batch, resident, *, evict=True, literal=True, device=0):
                         free_head_blocks=[], block_versions=[0] * (lay.capacity // lay.block_tokens + 1))
         committed = {b: (0, T_NOW) for b in resident[g]}
         desired, selected = rp.choose(snap, spec, batch.budget_blocks, committed, T_NOW)
+        gone = set(resident[g]) - set(desired) if evict else set()
         add_sets.append(set(selected))
-        evict_sets.append(set(resident[g]) - set(desired) if evict else set())
-        resident[g] = set(desired)
+        evict_sets.append(gone)
+        if selected or gone:
+            # retained = committed & desired, plus what was sent (experiments/slot_placement.py:150-153)
+            resident[g] = set(desired)
+        # else: nothing moves and the controller returns before it touches
+        # `committed` (experiments/slot_placement.py:131-132)
     out = []
     for phase, sets, dst in ((0, evict_sets, ux.CPU), (1, add_sets, device)):
         for j in range(lay.n_buffers):
@@ -177,6 +192,11 @@ class FeedbackSession:
             row["free_head_runs"] = rp.encode_runs(np.asarray(free_head).tolist())
         self.fb.consume(row)
 
+    def free(self, slots, t):
+        """A `free` row: ignored by the state (experiments/slot_feedback.py:76-77),
+        but it moves the time of the last observation."""
+        self.fb.consume(self._row("free", t, slot_runs=rp.encode_runs(np.asarray(slots).tolist())))
+
     def attention(self, read, write, t):
         self.fb.consume(self._row("attention", t, read_runs=rp.encode_runs(np.asarray(read).tolist()),
                                   write_runs=rp.encode_runs(np.asarray(write).tolist())))
@@ -189,6 +209,11 @@ class FeedbackSession:
         snap = self.snapshot()
         desired, selected = rp.choose(snap, self.spec, self.budget, self.committed, now)
         evicted = (set(self.committed) - set(desired)) if self.evict else set()
+        if not selected and not evicted:
+            # the controller returns before it touches `committed`
+            # (experiments/slot_placement.py:131-132): a committed block that is
+            # not desired right now stays on record
+            return [], dict(desired=desired, selected=[], evicted=[], committed=sorted(self.committed))
         self.committed = rp.retain_committed(self.committed, desired, selected, snap["block_versions"], now)
         out = []
         for chosen, dst in ((evicted, ux.CPU), (set(selected), self.device)):

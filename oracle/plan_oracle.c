@@ -130,14 +130,19 @@ int64_t orc_plan_step(const int64_t *slots, const int64_t *group_off, int n_grou
     for (int g = 0; g < n_groups; ++g) {
         uint8_t *want = add + (size_t)g * ORC_MAX_BLOCKS, *res = resident + (size_t)g * ORC_MAX_BLOCKS;
         uint8_t *out_ev = ev + (size_t)g * ORC_MAX_BLOCKS;
-        uint32_t kept = 0;
+        uint8_t desired[ORC_MAX_BLOCKS];
+        uint32_t kept = 0, moved = 0;
         for (uint32_t b = 0; b < ORC_MAX_BLOCKS; ++b) {
-            uint8_t desired = 0;
-            if (b < n_blocks && want[b] && kept < budget) { desired = 1; ++kept; }
-            out_ev[b] = (uint8_t)(evict && res[b] && !desired);
-            want[b] = (uint8_t)(desired && !res[b]);
-            res[b] = desired;
+            desired[b] = 0;
+            if (b < n_blocks && want[b] && kept < budget) { desired[b] = 1; ++kept; }
+            out_ev[b] = (uint8_t)(evict && res[b] && !desired[b]);
+            want[b] = (uint8_t)(desired[b] && !res[b]);
+            moved += out_ev[b] + want[b];
         }
+        /* nothing selected: the controller returns before it touches `committed`
+         * (experiments/slot_placement.py:131-132); otherwise committed = the part
+         * of it that is still desired + what was sent (:150-153) */
+        if (moved) memcpy(res, desired, ORC_MAX_BLOCKS);
     }
     int64_t pos = 0;
     for (int j = 0; j < n_buffers; ++j)

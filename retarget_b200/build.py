@@ -28,7 +28,7 @@ CXX_FLAGS = ["-O2", "-g", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-pthread",
 
 CORE_CU = ["plan_kernels.cu", "plan_capi.cu"]
 CORE_CPP = ["host_policy.cpp", "uvm_plan.cpp"]
-OPTIONAL_CORE_CPP = ["uvm_server.cpp", "prefetch_exec.cpp", "driver_api.cpp"]
+OPTIONAL_CORE_CPP = ["uvm_server.cpp", "driver_api.cpp"]
 OPTIONAL_CORE_CU = ["feedback_kernels.cu", "paged_reader.cu", "noalloc_scan.cu"]
 PRELOAD_CPP = ["preload_hooks.cpp"]
 
@@ -117,6 +117,28 @@ def build(force: bool = False, verbose: bool = False) -> dict:
     if verbose:
         print("".join(log))
     return out
+
+
+def build_stall_variant(force: bool = False) -> Path:
+    """Test build of the core library in which the bulk-copy kernel's producer
+    skips one copy and the bounded waits last 0.2 ms: the only way to reach the
+    wait-ran-out path without breaking anything.  Used by tests/test_gpu_timeout.py;
+    the product library never contains the injection."""
+    build()
+    out_dir = ROOT / "tests" / "_build"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
+    src, obj = CSRC / "plan_kernels.cu", OBJ / "plan_kernels.stall.o"
+    if force or _stale(obj, [src, *headers]):
+        _run([nvcc(), *NVCC_FLAGS, "-DRT_TEST_STALL", "-DRT_WAIT_NS=200000ull", "-c", str(src), "-o", str(obj)])
+    names = CORE_CU + [f for f in OPTIONAL_CORE_CU if (CSRC / f).exists()] + \
+        CORE_CPP + [f for f in OPTIONAL_CORE_CPP if (CSRC / f).exists()]
+    objs = [obj if n == "plan_kernels.cu" else OBJ / (n + ".o") for n in names]
+    lib = out_dir / "libretarget_b200_stall.so"
+    if force or _stale(lib, objs):
+        _run([nvcc(), "-shared", "-o", str(lib), *map(str, objs),
+              "-cudart", "static", "-Xlinker", "--no-undefined", "-lpthread", "-ldl", "-lrt"])
+    return lib
 
 
 if __name__ == "__main__":

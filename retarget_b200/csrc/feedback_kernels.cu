@@ -263,7 +263,14 @@ static_assert(2 * 2 * kRankThreads * sizeof(unsigned long long) >= tail_smem_byt
 
 // Ranking, selection and range emission in one launch.  blockDim = the power of
 // two that covers the blocks (at least kScanThreads, which the tail needs).
-//   sets: [0..31] evict words, [32..63] add words (read back by the tail part)
+//   sets: [0..31] evict words, [32..63] add words, [64..95] the resident words
+//   after this plan (read back by the tail part)
+// Nothing is committed before the tail has said that the plan is deliverable,
+// and nothing at all when no block moves: the reference's controller returns
+// before it touches `committed` when nothing was selected
+// (experiments/slot_placement.py:131-132), so a committed block that drops out
+// of the desired set for a while is not sent again when it comes back with its
+// version unchanged.
 __global__ void __launch_bounds__(kRankThreads)
 feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *resident, uint32_t *sets,
                      const __grid_constant__ PlanArgs tail) {
@@ -271,6 +278,7 @@ feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *r
     __shared__ int s_free_pos[kRankThreads];
     __shared__ uint32_t s_warp[32];
     __shared__ uint8_t s_sel[kRankThreads], s_des[kRankThreads];
+    __shared__ int s_delivered;
     const uint32_t b = threadIdx.x, lane = b & 31, warp = b >> 5, n_threads = blockDim.x;
     s_free_pos[b] = 0x7fffffff;
     __syncthreads();
@@ -341,10 +349,7 @@ feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *r
     const bool selected = todo && before < pol.max_blocks;
     s_sel[blk] = selected;
     s_des[blk] = desired;
-    if (selected && !(pol.flags & RT_PLAN_DRY_RUN)) {
-        st.commit_version[blk] = st.versions[blk];
-        st.commit_time[blk] = pol.commit;
-    }
+    const int32_t version_now = selected ? st.versions[blk] : 0;
     __syncthreads();
     // back to block-id order: thread b speaks for block b, warp = bitmap word
     const bool sel_b = s_sel[b], des_b = s_des[b];
@@ -353,18 +358,32 @@ feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *r
     const uint32_t add_word = __ballot_sync(0xffffffffu, sel_b);
     const uint32_t evict_word = __ballot_sync(0xffffffffu, evict_b);
     const uint32_t keep_word = __ballot_sync(0xffffffffu, (held_b && des_b) || sel_b);
-    __syncthreads();                        // every thread has read `resident`
+    const uint32_t held_word = __ballot_sync(0xffffffffu, held_b);
+    // does anything move?  (also the barrier after which every thread has read `resident`)
+    const bool moves = __syncthreads_or(sel_b || evict_b);
+    const uint32_t new_word = moves ? keep_word : held_word;
     if (lane == 0) {
         sets[warp] = evict_word;
         sets[kWords + warp] = add_word;
-        if (!(pol.flags & RT_PLAN_DRY_RUN)) resident[warp] = keep_word;
+        sets[2 * kWords + warp] = new_word;
     }
     if (b == 0)                             // words of blocks beyond this launch's threads
-        for (uint32_t wv = n_threads >> 5; wv < (uint32_t)kWords; ++wv) sets[wv] = sets[kWords + wv] = 0;
+        for (uint32_t wv = n_threads >> 5; wv < (uint32_t)kWords; ++wv)
+            sets[wv] = sets[kWords + wv] = sets[2 * kWords + wv] = 0;
     __syncthreads();                        // the words above are visible to the whole CTA
     // ---- byte ranges: the plan tail, run by the first kScanThreads threads ----
-    if (b >= (uint32_t)kScanThreads) return;
-    plan_tail<1>(tail, sets, false, reinterpret_cast<unsigned char *>(&s_swap[0][0][0]));
+    if (b < (uint32_t)kScanThreads) {
+        const bool ok = plan_tail<1>(tail, sets, false, reinterpret_cast<unsigned char *>(&s_swap[0][0][0]));
+        if (b == 0) s_delivered = ok;
+    }
+    __syncthreads();
+    // ---- commit, now that the plan is known to fit the caller's range buffer ----
+    if (!s_delivered || !moves || (pol.flags & RT_PLAN_DRY_RUN)) return;
+    if (selected) {
+        st.commit_version[blk] = version_now;
+        st.commit_time[blk] = pol.commit;
+    }
+    if (lane == 0) resident[warp] = new_word;
 }
 
 }  // namespace rt
@@ -379,7 +398,7 @@ struct rt_feedback {
     rt::PlanView view;
     rt::Geometry geo;
     rt::FeedbackState st;
-    uint32_t *d_sets = nullptr;       // [2 * kWords] evict | add
+    uint32_t *d_sets = nullptr;       // [3 * kWords] evict | add | resident after the plan
     uint64_t epoch = 0;
     void *block = nullptr;            // one allocation behind all state arrays
     size_t block_bytes = 0;
@@ -455,7 +474,7 @@ int rt_feedback_create(rt_plan *plan, rt_feedback **out) {
     size_t o_gen = take(4 * (cap + 1)), o_ver = take(4 * nb), o_rs = take(8 * nb), o_ws = take(8 * nb),
            o_cv = take(4 * nb), o_ct = take(8 * nb), o_fh = take(8 * rt::kFreeHeadMax), o_fc = take(4),
            o_eb = take(4 * 2 * rt::kWords), o_arr = take(4), o_sm = take(4 * ((cap + 32) / 32 + 1)), o_bad = take(16),
-           o_sets = take(4 * 2 * rt::kWords);
+           o_sets = take(4 * 3 * rt::kWords);
     fb->block_bytes = off;
     cudaError_t e = cudaMalloc(&fb->block, off);
     if (e != cudaSuccess) { delete fb; return fb_fail(e); }

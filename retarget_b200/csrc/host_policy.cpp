@@ -39,6 +39,7 @@ const char *rt_strerror(int status) {
         case RT_ERR_NOT_RUNNING: return "UVM server not running";
         case RT_ERR_IO: return "I/O error";
         case RT_ERR_PLAN: return "plan command rejected";
+        case RT_ERR_TIMEOUT: return "a bounded device-side wait gave up; nothing was planned";
         // messages of experiments/cache_window.py:31-54
         case RT_ERR_SPEC_POSITIVE: return "cache_window field must be a positive integer";
         case RT_ERR_SPEC_TRAILING: return "cache window must retain a trailing region";

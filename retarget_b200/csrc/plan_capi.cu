@@ -138,25 +138,14 @@ int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const void *d_slots,
     return RT_OK;
 }
 
+// One wave: every CTA is resident from the start and owns one contiguous span.
 int grid_for(const rt_plan *pl, int units, bool tma) {
-    int per_sm = tma ? pl->tma_blocks_per_sm : pl->plain_blocks_per_sm;
-    // RT_CTAS_PER_SM caps the resident CTAs per SM (tuning aid)
-    static const int cap = [] {
-        const char *s = getenv("RT_CTAS_PER_SM");
-        return s ? atoi(s) : 0;
-    }();
-    if (cap > 0 && cap < per_sm) per_sm = cap;
+    const int per_sm = tma ? pl->tma_blocks_per_sm : pl->plain_blocks_per_sm;
     long long slots = (long long)pl->sm_count * per_sm;
     return (int)(units < slots ? units : slots);
 }
 
-bool want_tma(uint32_t flags) {
-    static const bool env_on = [] {
-        const char *s = getenv("RT_USE_TMA");
-        return s && *s == '1';
-    }();
-    return (flags & RT_PLAN_TMA) || env_on;
-}
+bool want_tma(uint32_t flags) { return (flags & RT_PLAN_TMA) != 0; }
 
 }  // namespace
 
@@ -365,6 +354,8 @@ int step_host_impl(rt_plan *pl, const void *h_slots, bool ids32, const int64_t *
     *result = *pl->h_result;
     uint32_t n_copy = result->n_ranges < dev_cap ? result->n_ranges : dev_cap;
     if (n_copy) memcpy(out, pl->h_out, sizeof(rt_range) * n_copy);
+    // none of these plans was committed: the resident bitmaps are what they were
+    if (result->flags & RT_RESULT_TIMEOUT) return RT_ERR_TIMEOUT;
     if (result->flags & RT_RESULT_SLOT_RANGE) return RT_ERR_SLOT_RANGE;
     if (result->flags & RT_RESULT_OVERFLOW) return RT_ERR_CAPACITY;
     return RT_OK;
@@ -419,10 +410,7 @@ int scan_slots_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t 
     p.scan_only = 1;
     p.bitmaps_out = d_bitmaps;
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
-    bool tma = !ids32 && want_tma(0);
-    int grid = grid_for(pl, a.n_units, tma);
-    RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s)
-                : rt::launch_scan_plan(a, p, false, ids32, grid, s));
+    RT_CUDA(rt::launch_scan_plan(a, p, false, ids32, grid_for(pl, a.n_units, false), s));
     return RT_OK;
 }
 

@@ -15,8 +15,6 @@
 // it and no tensor-core work.
 #include <cuda_runtime.h>
 
-#include <cstdio>
-
 #include "plan_device.cuh"
 #include "plan_tail.cuh"
 
@@ -27,15 +25,6 @@
 
 namespace rt {
 
-#ifdef RT_TRACE
-// Experimental builds only: nanosecond stamps of the phases of one launch.
-__device__ unsigned long long g_trace[4] = {~0ull, 0, 0, 0};
-__device__ __forceinline__ unsigned long long now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#endif
 
 // --------------------------------------------------------------------------
 // scan: mark slot ids in the CTA's shared block map
@@ -296,9 +285,12 @@ __device__ __forceinline__ void leave_group(const PlanArgs &p, uint32_t g, uint8
 
 // The CTA is done with its `count` work units.  Whoever brings the launch-wide
 // counter to the total runs the tail; nobody waits for anybody.
+// `tail_mem_unsafe`: this CTA gave up waiting for a bulk copy into the memory
+// the tail would work in.  A copy that lands late could overwrite the tail's
+// working set, so the CTA then only cleans up (tail_abort) and plans nothing.
 template <int kBar>
 __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, HandoverShared &hs,
-                                           unsigned char *tail_mem) {
+                                           unsigned char *tail_mem, bool tail_mem_unsafe = false) {
     __threadfence();                      // this CTA's atomicOr / atomicAdd before the arrival
     cta_sync<kBar, kScanThreads>();
     if (threadIdx.x == 0) {
@@ -308,13 +300,8 @@ __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, Ha
     cta_sync<kBar, kScanThreads>();
     if (!hs.last) return;
     __threadfence();
-#ifdef RT_TRACE
-    if (threadIdx.x == 0) g_trace[2] = now_ns();
-#endif
-    plan_tail<kBar>(p, &p.groups[0].want[0], true, tail_mem);
-#ifdef RT_TRACE
-    if (threadIdx.x == 0) g_trace[3] = now_ns();
-#endif
+    if (tail_mem_unsafe) tail_abort(p);
+    else plan_tail<kBar>(p, &p.groups[0].want[0], true, tail_mem);
 }
 
 // --------------------------------------------------------------------------
@@ -343,9 +330,6 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
     if (q_begin >= q_end) return;
     const Id *slots = reinterpret_cast<const Id *>(a.slots);
     ScanCounters c = {0, 0};
-#ifdef RT_TRACE
-    if (threadIdx.x == 0) atomicMin(&g_trace[0], now_ns());
-#endif
     clear_map(s_map);
     __syncthreads();
     for (uint32_t g = first_group(a, q_begin);; ++g) {
@@ -400,9 +384,6 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
         leave_group<0>(p, g, s_map, c);
         if (sp.q_hi >= q_end) break;
     }
-#ifdef RT_TRACE
-    if (threadIdx.x == 0) atomicMax(&g_trace[1], now_ns());
-#endif
     finish_cta<0>(p, (uint32_t)(q_end - q_begin), hs, tail_mem);
 }
 
@@ -465,9 +446,11 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
 // data: the bytes in flight per SM are set by shared memory (kStages x 16 KiB
 // per CTA), not by occupancy.
 //
-// Every wait on an mbarrier is bounded; when the bound is hit the CTA records
-// RT_RESULT_TIMEOUT, skips the unit and still retires it, so the grid always
-// drains.
+// Every wait on an mbarrier is bounded in time.  The first wait of a CTA that
+// runs out records RT_RESULT_TIMEOUT; from then on the CTA waits for nothing
+// any more, it only retires its remaining units, so the grid always drains and
+// a failed launch costs a few waits, not one per unit.  A plan made from an
+// incomplete scan is never committed (see plan_tail).
 #ifndef RT_STAGES
 #define RT_STAGES 4
 #endif
@@ -476,7 +459,12 @@ constexpr int kStageBytes = kChunkElems * 8;
 // the staging ring is reused as the tail's working memory once streaming is over
 static_assert((size_t)kStages * kStageBytes >= tail_smem_bytes(RT_MAX_GROUPS, RT_MAX_BUFFERS),
               "staging ring too small to host the plan tail");
-constexpr uint32_t kWaitLimit = 1u << 20;
+// Longest time one wait on an mbarrier may take.  A 16 KiB copy lands in a few
+// microseconds; a wait that lasts milliseconds means the copy is not coming.
+#ifndef RT_WAIT_NS
+#define RT_WAIT_NS 4000000ull
+#endif
+constexpr unsigned long long kWaitNs = RT_WAIT_NS;
 
 __device__ __forceinline__ uint32_t smem_addr(const void *ptr) {
     return (uint32_t)__cvta_generic_to_shared(ptr);
@@ -504,10 +492,19 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits at most kWaitNs of wall-clock time (the device's nanosecond timer), so
+// the bound does not depend on how long the hardware suspends a try_wait.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
-    for (uint32_t it = 0; it < kWaitLimit; ++it)
-        if (mbar_test(bar, parity)) return true;
-    return false;
+    if (mbar_test(bar, parity)) return true;
+    const unsigned long long until = global_ns() + kWaitNs;
+    while (!mbar_test(bar, parity))
+        if (global_ns() > until) return false;
+    return true;
 }
 __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile(
@@ -569,6 +566,11 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
                         break;
                     }
                     const long long n = copy_end_of(e0, sp.hi, copy_limit) - e0;
+#ifdef RT_TEST_STALL
+                    // test build only: CTA 0 "loses" its first copy, so that the
+                    // consumers' bounded wait runs out (nothing faults, nothing hangs)
+                    if (blockIdx.x == 0 && i == 0) continue;
+#endif
                     if (n > 0) {
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         mbar_expect_tx(&full_bar[stage], (uint32_t)(n * 8));
@@ -596,7 +598,7 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
             const uint32_t parity = (uint32_t)(i / kStages) & 1u;
             const longlong2 *src =
                 reinterpret_cast<const longlong2 *>(stage_mem + stage * kStageBytes) + tid;
-            const bool landed = mbar_wait_bounded(&full_bar[stage], parity);
+            const bool landed = !gave_up && mbar_wait_bounded(&full_bar[stage], parity);
             longlong2 v[kUnroll];
             uint32_t mask = 0;
             if (landed) {
@@ -634,17 +636,21 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
         leave_group<kConsumerBar>(p, g, s_map, c);
         if (sp.q_hi >= q_end) break;
     }
+    // (one thread's wait running out means the whole CTA stops trusting its ring)
+    gave_up = cta_or<kConsumerBar, kScanThreads>(gave_up);
     if (gave_up) {
-        if ((tid & 31) == 0) atomicOr(&p.global->error_flags, RT_RESULT_TIMEOUT);
+        if (tid == 0) atomicOr(&p.global->error_flags, RT_RESULT_TIMEOUT);
         // copies that never signalled may still be in flight: give them one more
         // bounded chance to land before the CTA's shared memory is released
-        for (int s = 0; s < kStages; ++s) {
-            int uses = (q_end - q_begin - s + kStages - 1) / kStages;
-            if (uses > 0) mbar_wait_bounded(&full_bar[s], (uint32_t)(uses - 1) & 1u);
-        }
+        if (tid == 0)
+            for (int s = 0; s < kStages; ++s) {
+                int uses = (q_end - q_begin - s + kStages - 1) / kStages;
+                if (uses > 0) mbar_wait_bounded(&full_bar[s], (uint32_t)(uses - 1) & 1u);
+            }
     }
     // every stage has been consumed: the staging memory now serves the tail
-    finish_cta<kConsumerBar>(p, (uint32_t)(q_end - q_begin), hs, stage_mem);
+    // (unless this CTA gave up on a copy, which might still land there)
+    finish_cta<kConsumerBar>(p, (uint32_t)(q_end - q_begin), hs, stage_mem, gave_up);
 }
 
 // --------------------------------------------------------------------------
@@ -677,21 +683,6 @@ cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, b
     } else {
         if (pow2) scan_plan_kernel<true, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
         else scan_plan_kernel<false, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
-#ifdef RT_TRACE
-        {
-            cudaStreamSynchronize(stream);
-            unsigned long long t[4], reset[4] = {~0ull, 0, 0, 0};
-            cudaMemcpyFromSymbol(t, g_trace, sizeof(t));
-            cudaMemcpyToSymbol(g_trace, reset, sizeof(reset));
-            unsigned long long tt[8];
-            cudaMemcpyFromSymbol(tt, g_tail_trace, sizeof(tt));
-            printf("TRACE stream_us=%.2f handover_us=%.2f tail_us=%.2f | table %.2f loads %.2f passA %.2f sync %.2f "
-                   "prefix %.2f passB %.2f end %.2f\n",
-                   (t[1] - t[0]) / 1e3, (t[2] - t[1]) / 1e3, (t[3] - t[2]) / 1e3, (tt[6] - tt[0]) / 1e3,
-                   (tt[7] - tt[6]) / 1e3, (tt[1] - tt[7]) / 1e3, (tt[2] - tt[1]) / 1e3, (tt[3] - tt[2]) / 1e3,
-                   (tt[4] - tt[3]) / 1e3, (tt[5] - tt[4]) / 1e3);
-        }
-#endif
     }
     return cudaGetLastError();
 }

@@ -11,20 +11,6 @@
 
 namespace rt {
 
-#ifdef RT_TRACE
-static __device__ unsigned long long g_tail_trace[8];
-#define RT_TAIL_MARK(k)                                                          \
-    do {                                                                         \
-        if (threadIdx.x == 0) {                                                  \
-            unsigned long long t__;                                              \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__)::"memory");   \
-            g_tail_trace[k] = t__;                                               \
-        }                                                                        \
-    } while (0)
-#else
-#define RT_TAIL_MARK(k)
-#endif
-
 // --------------------------------------------------------------------------
 // small warp helpers
 // --------------------------------------------------------------------------
@@ -91,7 +77,8 @@ __device__ __forceinline__ bool cta_or(bool pred) {
 // --------------------------------------------------------------------------
 constexpr int kTailWarps = kScanThreads / 32;
 // Words per bitmap in the tail's shared staging:
-//   [0, kWords)          evict words
+//   [0, kWords)          words that leave the resident set (announced as CPU-bound
+//                        ranges only under RT_PLAN_EVICT)
 //   [kWords, 2*kWords)   add words
 // plus one word of padding, so that threads working on different bitmaps and
 // the same word index fall in different banks.
@@ -109,12 +96,13 @@ struct TailShared {
     uint32_t *off;                   // [2*n_buffers + 1]    first range of every (phase, buffer)
     uint32_t *masks;                 // [n_groups][kMaskStride]
     uint16_t *few;                   // [n_groups][2][kFew][2]  begin, end of the first runs
+    uint32_t *verdict;               // [1]  the scan saw ids above capacity or gave up a wait
     uint8_t *group_of;               // [n_buffers]          bitmap of every buffer
 };
 
 __host__ __device__ constexpr size_t tail_smem_bytes(uint32_t n_groups, uint32_t n_buffers) {
     return ((kWarpStats * kTailWarps + kTailWarps + 2 * (size_t)n_groups + (2 * (size_t)n_buffers + 1) +
-             (size_t)kMaskStride * n_groups + 2 * kFew * (size_t)n_groups) * 4 +
+             (size_t)kMaskStride * n_groups + 2 * kFew * (size_t)n_groups + 1) * 4 +
             (size_t)n_buffers + 15) & ~(size_t)15;
 }
 
@@ -127,6 +115,7 @@ __device__ __forceinline__ TailShared carve_tail(unsigned char *raw, uint32_t n_
     s.off = w;                                                 w += 2 * n_buffers + 1;
     s.masks = w;                                               w += kMaskStride * n_groups;
     s.few = reinterpret_cast<uint16_t *>(w);                   w += 2 * kFew * n_groups;
+    s.verdict = w;                                             w += 1;
     s.group_of = reinterpret_cast<uint8_t *>(w);
     return s;
 }
@@ -221,6 +210,7 @@ __device__ __forceinline__ void pass_a(const PassA &in, const TailShared &sh, ui
     while (seg < n_words) seg <<= 1;
     const uint32_t per_warp = 32 / seg, sub = lane / seg, w = lane & (seg - 1);
     const uint32_t round_stride = kTailWarps * per_warp;
+    const uint32_t seg_lanes = (seg >= 32 ? 0xffffffffu : ((1u << seg) - 1u)) << (sub * seg);   // lanes of this thread's bitmap
     const uint32_t left = w < n_words ? in.n_blocks - w * 32 : 0;
     const uint32_t valid = left >= 32 ? 0xffffffffu : ((1u << left) - 1u);
     const uint32_t last_bit = (w == n_words - 1) ? 1u << ((in.n_blocks - 1) & 31) : 0u;
@@ -236,28 +226,25 @@ __device__ __forceinline__ void pass_a(const PassA &in, const TailShared &sh, ui
                 size_g[k] = __ldcg(&in.group_size[g]);
                 if (kMode == kTailExplicit) {
                     // the caller (the recency ranking) already chose what moves and
-                    // has updated the resident words: `want` holds [evict | add]
-                    a_w[k] = __ldcg(&in.want[(g * 2 + 0) * kWords + w]);
-                    b_w[k] = __ldcg(&in.want[(g * 2 + 1) * kWords + w]);
-                    r_w[k] = __ldcg(&in.resident[g * kWords + w]);
+                    // commits it itself: `want` holds [evict | add | new resident]
+                    a_w[k] = __ldcg(&in.want[(g * 3 + 0) * kWords + w]);
+                    b_w[k] = __ldcg(&in.want[(g * 3 + 1) * kWords + w]);
+                    r_w[k] = __ldcg(&in.want[(g * 3 + 2) * kWords + w]);
                 } else {
                     a_w[k] = __ldcg(&in.want[g * kWords + w]);
                     if (kMode == kTailPlan) r_w[k] = __ldcg(&in.resident[g * kWords + w]);
                 }
             }
         }
-#ifdef RT_TRACE
-        if (tid == 0 && (a_w[0] | r_w[0]) == 0x12345u) g_tail_trace[7] = 1;   // forces the loads to land
-        else RT_TAIL_MARK(7);
-#endif
         // arithmetic of both rounds (a round past the last bitmap is not skipped:
         // its lanes hold zeros)
-        uint32_t raw[kRounds], evict[kRounds], add[kRounds], desired[kRounds];
+        uint32_t raw[kRounds], evict[kRounds], add[kRounds], desired[kRounds], gone[kRounds];
         uint32_t below_ev[kRounds], below_add[kRounds], above_ev[kRounds], above_add[kRounds];
         uint32_t c[kRounds], upto[kRounds];
 #pragma unroll
         for (int k = 0; k < kRounds; ++k) {
             raw[k] = 0;
+            gone[k] = 0;
             if (kMode == kTailExplicit) {
                 evict[k] = a_w[k];
                 add[k] = b_w[k];
@@ -274,7 +261,15 @@ __device__ __forceinline__ void pass_a(const PassA &in, const TailShared &sh, ui
                     const uint32_t before = segment_inclusive_sum(cnt, w) - cnt;
                     desired[k] = lowest_bits(raw[k], in.budget > before ? in.budget - before : 0u);
                     add[k] = desired[k] & ~r_w[k];
-                    evict[k] = evicting ? (r_w[k] & ~desired[k]) : 0u;
+                    // what leaves the resident set; only announced when evicting
+                    gone[k] = r_w[k] & ~desired[k];
+                    evict[k] = evicting ? gone[k] : 0u;
+                    // A bitmap whose plan moves nothing keeps its record as it is:
+                    // the reference's controller returns before it touches
+                    // `committed` when nothing was selected
+                    // (experiments/slot_placement.py:131-132).  Only without
+                    // eviction can that differ from the desired set.
+                    if (!evicting && (__ballot_sync(0xffffffffu, add[k] != 0) & seg_lanes) == 0) gone[k] = 0;
                 }
             }
             st[1] += __popc(desired[k]);
@@ -306,9 +301,13 @@ __device__ __forceinline__ void pass_a(const PassA &in, const TailShared &sh, ui
             if (!(g < G && w < n_words)) continue;
             if (kMode != kTailExplicit && in.consume) in.want[g * kWords + w] = 0;
             if (kMode == kTailScanOnly && in.bitmaps_out) in.bitmaps_out[g * kWords + w] = raw[k];
-            if (kMode == kTailPlan && !dry) in.resident[g * kWords + w] = desired[k];
+            // new resident word = (old | add) & ~gone: the desired set, or the old
+            // record when the bitmap's plan moved nothing
+            if (kMode == kTailPlan && !dry) in.resident[g * kWords + w] = (r_w[k] | add[k]) & ~gone[k];
+            // (the old resident word is (new & ~add) | gone: the tail puts it back
+            // when the plan turns out not to be deliverable)
             uint32_t *m = sh.masks + g * kMaskStride;
-            m[w] = evict[k];
+            m[w] = kMode == kTailPlan ? gone[k] : evict[k];
             m[kWords + w] = add[k];
             uint16_t *few = sh.few + g * 4 * kFew;
             note_few(few, evict[k], w, below_ev[k], above_ev[k], (upto[k] - c[k]) & 0xffffu);
@@ -323,12 +322,42 @@ __device__ __forceinline__ void pass_a(const PassA &in, const TailShared &sh, ui
 }
 
 // --------------------------------------------------------------------------
+// tail of a launch whose scan failed in the CTA that would plan: no plan, the
+// resident words stay as they are, the scratch is cleaned for the next launch
+// --------------------------------------------------------------------------
+__device__ __forceinline__ void tail_abort(const PlanArgs &p) {
+    uint32_t *want = &p.groups[0].want[0];
+    for (uint32_t i = threadIdx.x; i < p.n_groups * kWords; i += kScanThreads) want[i] = 0;
+    if (threadIdx.x == 0) {
+        GlobalScratch &gl = *p.global;
+        rt_plan_result res = {};
+        res.flags = __ldcg(&gl.error_flags) | RT_RESULT_TIMEOUT |
+                    (__ldcg(&gl.invalid_slots) ? RT_RESULT_SLOT_RANGE : 0u);
+        res.invalid_slots = __ldcg(&gl.invalid_slots);
+        res.ignored_slots = __ldcg(&gl.ignored_slots);
+        *p.result = res;
+        gl.invalid_slots = 0;
+        gl.ignored_slots = 0;
+        gl.units_done = 0;
+        gl.error_flags = 0;
+    }
+}
+
+// --------------------------------------------------------------------------
 // the tail itself: kScanThreads threads of one CTA
 // --------------------------------------------------------------------------
 // `want` holds n_groups x kWords words; `consume` zeroes them after reading
 // (they are the scan's accumulation words).
+//
+// Returns whether the plan is deliverable (the same answer in every thread).  It
+// is not when the scan saw an id above the capacity, when a bounded wait of the
+// scan gave up, or when there are more ranges than `cap`: the resident words
+// are then put back to what they were before the call -- a plan that cannot be
+// executed must not count as resident on the next step (the reference drops
+// its record on any failure, experiments/slot_placement.py:140-147, and checks
+// the slot range before it stamps anything, experiments/slot_feedback.py:42).
 template <int kBar>
-__device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsigned char *raw) {
+__device__ bool plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsigned char *raw) {
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // Scalars of `p` are copied to locals first: `p` lives in parameter space and
     // every global store below would otherwise force them to be re-read.
@@ -338,7 +367,6 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
     uint32_t *const resident = p.resident, *const bitmaps_out = p.bitmaps_out;
     const uint32_t n_words = (n_blocks + 31) / 32;
     const TailShared sh = carve_tail(raw, G, n);
-    RT_TAIL_MARK(0);
     // counters written by other CTAs: fetched now, used at the very end
     unsigned long long invalid = 0, ignored = 0;
     uint32_t eflags = 0;
@@ -346,12 +374,12 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
         invalid = __ldcg(&p.global->invalid_slots);
         ignored = __ldcg(&p.global->ignored_slots);
         eflags = __ldcg(&p.global->error_flags);
+        sh.verdict[0] = (invalid != 0) | ((eflags & RT_RESULT_TIMEOUT) != 0);   // read after the barrier below
     }
     // the buffer -> bitmap table goes to shared memory; its load is in flight
     // together with the first mask words below
     const uint8_t *const table = p.buffer_group;
     const uint32_t table_first = tid < n ? __ldcg(&table[tid]) : 0u;
-    RT_TAIL_MARK(6);
 
     // ---- pass A: one THREAD per (bitmap, word) ----
     PassA pa;
@@ -365,7 +393,6 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
     else pass_a<kTailPlan>(pa, sh, st, some_runs);
     if (tid < n) sh.group_of[tid] = (uint8_t)table_first;
     for (uint32_t j = tid + kScanThreads; j < n; j += kScanThreads) sh.group_of[j] = __ldcg(&table[j]);
-    RT_TAIL_MARK(1);
     if (scan_only && bitmaps_out)                                    // words past the ones in use
         for (uint32_t i = tid; i < G * kWords; i += kScanThreads)
             if ((i & (kWords - 1)) >= n_words) bitmaps_out[i] = 0;
@@ -377,7 +404,6 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
     }
     // steady state: nothing moves, so there is nothing to lay out
     const bool any_runs = cta_or<kBar, kScanThreads>(some_runs != 0);
-    RT_TAIL_MARK(2);
 
     // ---- exclusive prefix sum of run counts over (phase, buffer) ----
     // With at most one item per thread (2*n_buffers <= 256, the usual case) the
@@ -423,7 +449,6 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
             cta_sync<kBar, kScanThreads>();
         }
     }
-    RT_TAIL_MARK(3);
 
     // ---- pass B: one thread per (phase, buffer) ----
     // Short run lists come ready-made from pass A; longer ones are read off the
@@ -468,8 +493,18 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
             }
         }
     }
-    RT_TAIL_MARK(4);
     cta_sync<kBar, kScanThreads>();
+    // ---- deliverable? ----
+    const bool scan_failed = sh.verdict[0] != 0;
+    const bool delivered = !scan_failed && total <= cap;
+    if (!delivered && !explicit_sets && !scan_only && !(flags & RT_PLAN_DRY_RUN)) {
+        // pass A has stored the new resident words: put the old ones back
+        for (uint32_t i = tid; i < G * n_words; i += kScanThreads) {
+            const uint32_t g = i / n_words, w = i - g * n_words;
+            const uint32_t *m = sh.masks + g * kMaskStride;
+            resident[g * kWords + w] = (resident[g * kWords + w] & ~m[kWords + w]) | m[w];
+        }
+    }
     if (tid == 0) {
         if (items) n_cpu = sh.off[n];
         rt_plan_result res;
@@ -480,8 +515,9 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
             for (int q = 0; q < kWarpStats; ++q) sum[q] += sh.warp_stats[k * kWarpStats + q];
         // what the last block of a buffer lacks to a whole block
         const unsigned long long short_by = (unsigned long long)n_blocks * block_bytes - alloc_bytes;
-        res.n_ranges = total;
-        res.n_cpu_ranges = n_cpu;
+        // after a failed scan the ranges come from incomplete bitmaps: none is reported
+        res.n_ranges = scan_failed ? 0u : total;
+        res.n_cpu_ranges = scan_failed ? 0u : n_cpu;
         res.flags = (total > cap ? RT_RESULT_OVERFLOW : 0u) | (invalid ? RT_RESULT_SLOT_RANGE : 0u) | eflags;
         res.blocks_touched = sum[0];
         res.blocks_desired = sum[1];
@@ -490,8 +526,8 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
         res.reserved = 0;
         res.invalid_slots = invalid;
         res.ignored_slots = ignored;
-        res.cpu_bytes = scan_only ? 0 : sum[4] * block_bytes - sum[6] * short_by;
-        res.gpu_bytes = scan_only ? 0 : sum[5] * block_bytes - sum[7] * short_by;
+        res.cpu_bytes = (scan_only || scan_failed) ? 0 : sum[4] * block_bytes - sum[6] * short_by;
+        res.gpu_bytes = (scan_only || scan_failed) ? 0 : sum[5] * block_bytes - sum[7] * short_by;
         *p.result = res;
         // leave the scratch clean for the next launch
         GlobalScratch &gl = *p.global;
@@ -500,7 +536,7 @@ __device__ void plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
         gl.units_done = 0;
         gl.error_flags = 0;
     }
-    RT_TAIL_MARK(5);
+    return delivered;
 }
 
 }  // namespace rt

@@ -74,6 +74,11 @@ class DeviceFeedback:
         self._event(t)
         capi.check(self.lib.rt_feedback_reset(self._h, stream), "rt_feedback_reset")
 
+    def free(self, t):
+        """A `free` row: the state ignores it (experiments/slot_feedback.py:76-77),
+        only the time of the last observation moves."""
+        self._event(t)
+
     def alloc(self, d_slots, t, d_free_head=None, stream=None):
         self._event(t)
         n_free = 0 if d_free_head is None else min(int(d_free_head.numel()), FREE_HEAD_MAX)

@@ -357,6 +357,103 @@ def placement_controller_vectors(cw, sp, sf, ctl):
     return dict(cache_spec=kw, slot_spec=sspec, allocations=allocs, generation=7, pid=4242, log=log)
 
 
+def placement_chain_vectors(cw, sp, sf, ctl, probe):
+    """The whole event-driven chain of the reference, unmodified: event rows ->
+    SlotFeedback.consume/publish (snapshot file) -> SlotPlacementController.update,
+    over a scripted 45 s during which committed blocks drop out of the desired set
+    while nothing is selected (their stamps age past the 30 s horizon; the sampled
+    free-list head moves away) and later come back with their versions unchanged.
+    The controller must not send them again: it returns before it touches
+    ``committed`` when nothing was selected.  Stamps are tie-free."""
+    kw = dict(allocation_bytes=16 * 2097152, allocation_count=4, bytes_per_token=2048,
+              width_tokens=4096, lookahead_tokens=1024, quantum_tokens=1024)
+    allocs = [dict(id=i + 1, bytes=16 * 2097152, device=0) for i in range(4)]
+    sspec = dict(block_tokens=1024, lookahead_tokens=4096, min_update_seconds=.25,
+                 max_blocks_per_update=2, active_seconds=2.0, refresh_seconds=1000.0,
+                 max_feedback_lag_seconds=1.0)
+    cap = 16383
+    # (time, kind, fields); "update" rows call the controller at that time
+    script = [
+        (100.00, "alloc", dict(slots=list(range(1, 200)), free_head=list(range(5000, 5010)))),
+        (100.05, "alloc", dict(slots=list(range(1100, 1300)))),
+        (100.10, "attention", dict(read=list(range(10, 20)), write=[])),
+        (100.20, "attention", dict(read=list(range(1100, 1200)), write=[])),
+        (100.30, "update", {}),          # desired [1, 0, 4]: the first two are sent
+        (100.60, "update", {}),          # block 4 follows
+        (100.90, "update", {}),          # nothing to do
+        # the sampled free head moves into block 0: block 4 is no longer desired, nothing is selected
+        (101.00, "alloc", dict(slots=[], free_head=list(range(100, 110)))),
+        (101.30, "update", {}),
+        # ... and comes back: block 4 is desired again, still committed, version unchanged
+        (101.50, "alloc", dict(slots=[], free_head=list(range(5000, 5010)))),
+        (101.80, "update", {}),
+        # 30 s later every stamp has aged out: only the free head is desired
+        (131.00, "free", dict(slots=[7000])),
+        (131.30, "update", {}),
+        # block 0 is read again: desired, still committed, version unchanged
+        (132.00, "attention", dict(read=list(range(30, 40)), write=[])),
+        (132.30, "update", {}),
+        # a re-allocation bumps block 1's version: this one is sent again
+        (133.00, "alloc", dict(slots=list(range(1100, 1110)))),
+        (133.30, "update", {}),
+        # a new block becomes active: sent, and what is no longer desired is dropped
+        (140.00, "attention", dict(read=list(range(9300, 9310)), write=list(range(12300, 12301)))),
+        (140.30, "update", {}),
+        (140.60, "update", {}),
+        (145.00, "attention", dict(read=list(range(5005, 5006)), write=[])),
+        (145.30, "update", {}),
+    ]
+    log = []
+    clock = {"now": 0.0}
+
+    class ScriptedTime:
+        @staticmethod
+        def monotonic():
+            return clock["now"]
+    real_sp, real_sf = sp.time, sf.time
+    sp.time = sf.time = ScriptedTime
+    try:
+        with tempfile.TemporaryDirectory() as tmp:
+            os.environ["RETARGET_SLOT_FEEDBACK_DIR"] = tmp
+            fb = sf.SlotFeedback(tmp, pid=4242, block_tokens=1024, publish_seconds=0.0)
+            c = sp.SlotPlacementController(cw.CacheWindowSpec(**kw), sp.SlotPlacementSpec(**sspec), 4242)
+            c.signature = tuple((a["id"], a["bytes"], a["device"]) for a in allocs)
+            c.epoch = 1
+            uvm = RecordingUvm(ctl, allocs)
+            seq = 0
+            for t, kind, f in script:
+                clock["now"] = t
+                if kind == "update":
+                    m = {"sglang:prompt_tokens_total": 0.0, "sglang:generation_tokens_total": 0.0}
+                    before = len(uvm.commands)
+                    res = c.update(uvm, m, t)
+                    if res is not None:
+                        res = {k: res[k] for k in ("desired_blocks", "gpu_blocks", "committed_blocks",
+                                                   "requested_gpu_bytes")}
+                    log.append(dict(t=t, kind=kind, commands=uvm.commands[before:], result=res,
+                                    committed=sorted(c.committed),
+                                    committed_versions={str(k): v[0] for k, v in c.committed.items()}))
+                    continue
+                row = dict(event=kind, monotonic_s=t, sequence=seq)
+                seq += 1
+                if kind == "alloc":
+                    row["slot_runs"] = probe.encode_runs(f["slots"])
+                    row["allocator_size"] = cap
+                    if "free_head" in f:
+                        row["free_head_runs"] = probe.encode_runs(f["free_head"])
+                elif kind == "attention":
+                    row["read_runs"] = probe.encode_runs(f["read"])
+                    row["write_runs"] = probe.encode_runs(f["write"])
+                else:
+                    row["slot_runs"] = probe.encode_runs(f["slots"])
+                fb.consume(row)
+                log.append(dict(t=t, kind=kind, fields=f))
+    finally:
+        sp.time, sf.time = real_sp, real_sf
+    return dict(cache_spec=kw, slot_spec=sspec, capacity=cap, allocations=allocs, generation=7, pid=4242,
+                log=log)
+
+
 TARGET_SCRIPT = [
     # (operation, arguments) against the scripted transport below
     ("set_target", dict(gpu_bytes=0)),
@@ -477,6 +574,7 @@ def main():
         feedback=feedback_vectors(sf, sp, probe),
         window_controller=controller_vectors(cw, sp, sf, ctl),
         placement_controller=placement_controller_vectors(cw, sp, sf, ctl),
+        placement_chain=placement_chain_vectors(cw, sp, sf, ctl, probe),
         targets=target_vectors(ctl),
     )
     path = HERE / "reference_policy.json"

@@ -73,7 +73,7 @@ def test_device_entry_points(seed, dtype):
     bits = d_bits.cpu().numpy().view(np.uint32).reshape(G, capi.RT_BITMAP_WORDS)
     touched = 0
     for g in range(G):
-        blocks = compose.group_blocks_fast(b.slots[b.group_off[g]:b.group_off[g + 1]], lay)
+        blocks = compose.touched_blocks(b.slots[b.group_off[g]:b.group_off[g + 1]], lay)
         assert np.array_equal(bits[g], blocks_to_bitmap(blocks)), g
         touched += len(blocks)
     assert result_from_tensor(d_res)["blocks_touched"] == touched

@@ -227,3 +227,44 @@ def test_device_writer_publishes_what_the_reference_probe_would(tmp_path):
     with pytest.raises(AssertionError):
         writer.submit("geometry", allocations=[dict(slot_bytes=4096)] * 8, allocator_size=capacity)
     writer.close()
+
+
+def test_chain_over_the_recency_horizon():
+    """The script recorded from the reference's whole chain (SlotFeedback ->
+    snapshot file -> SlotPlacementController.update, 45 s): committed blocks that
+    leave the desired set while nothing is selected stay on record and are not
+    sent again when they return unchanged.  Device, oracle and the reference's
+    recorded commands agree at every update."""
+    import json
+    from pathlib import Path
+    from chain_replay import chain_session, replay_chain
+    block = json.loads((Path(__file__).parent / "golden" / "reference_policy.json").read_text())["placement_chain"]
+    session, layout = chain_session(block)
+    dev = torch.device("cuda:0")
+    planner = DevicePlanner(layout, 0)
+    fb = DeviceFeedback(planner, pid=block["pid"])
+    d_out = torch.zeros(4096 * 24, dtype=torch.uint8, device=dev)
+    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
+    up = lambda ids: torch.from_numpy(np.asarray(ids, dtype=np.int64)).to(dev)
+    spec = session.spec
+
+    def on_event(kind, f, t):
+        if kind == "alloc":
+            fb.alloc(up(f["slots"]), t, up(f["free_head"]) if "free_head" in f else None)
+        elif kind == "attention":
+            fb.attention(up(f["read"]), up(f["write"]), t)
+        else:
+            fb.free(t)
+
+    def on_plan(t, want, info):
+        fb.plan(t, budget=session.budget, max_blocks_per_update=spec.max_blocks_per_update,
+                active_seconds=spec.active_seconds, refresh_seconds=spec.refresh_seconds, flags=0,
+                d_out=d_out, d_result=d_res)
+        torch.cuda.synchronize()
+        res = result_from_tensor(d_res)
+        assert ranges_to_tuples(ranges_from_tensor(d_out, res["n_ranges"])) == want, t
+        assert planner.get_resident()[0] == info["committed"], t
+
+    replay_chain(block, session, on_event=on_event, on_plan=on_plan)
+    fb.close()
+    planner.close()

@@ -51,18 +51,43 @@ def random_batch(rng, *, layers, pool_slots, bytes_per_slot, shared, n_req, max_
     return workloads.SlotBatch(lay, slots.astype(np.int64), group_off, req_off, budget, "random")
 
 
+class CChain:
+    """The literal chain in C (oracle/plan_oracle.c: encode_runs -> blocks ->
+    one-event ranking -> choose -> blocksv run walk), for inputs on which the
+    Python restatement would take minutes."""
+
+    def __init__(self, layout):
+        from oracle import c_oracle
+        self.c = c_oracle.COracle(layout)
+
+    def step(self, b, evict):
+        before = self.c.resident_sets()
+        out, invalid = self.c.step(np.ascontiguousarray(b.slots, dtype=np.int64), b.group_off, b.budget_blocks, evict)
+        assert invalid == 0
+        after = self.c.resident_sets()
+        info = dict(blocks_added=sum(len(x - y) for x, y in zip(after, before)),
+                    blocks_evicted=sum(len(y - x) for x, y in zip(after, before)) if evict else 0)
+        return ranges_to_tuples(out), info, after
+
+
 def run_steps(batches, *, evict, flags, literal=True):
     """Feeds the same sequence of batches to the device planner (host-buffer
-    entry point) and to the oracle; compares every step."""
+    entry point) and to the oracle; compares every step.  ``literal=True``: the
+    Python restatement of the reference chain; ``literal=False``: the same chain
+    in C (sizes the Python loops cannot finish in seconds)."""
     flags, dtype = flags if isinstance(flags, tuple) else (flags, np.int64)
     lay = batches[0].layout
     planner = DevicePlanner(lay, 0, max_indices=max(b.n_idx for b in batches) + 8, max_ranges=1 << 16)
     resident = [set() for _ in range(lay.n_groups)]
+    chain = None if literal else CChain(lay)
     f = flags | (capi.RT_PLAN_EVICT if evict else 0)
     for step, b in enumerate(batches):
         # oracle and planner both see the ids in the dtype under test
         b = dataclasses.replace(b, slots=b.slots.astype(dtype))
-        want, info = compose.plan_step(b, resident, evict=evict, literal=literal)
+        if literal:
+            want, info = compose.plan_step(b, resident, evict=evict, literal=True)
+        else:
+            want, info, resident = chain.step(b, evict)
         got, res = planner.step_host(b.slots, b.group_off, b.budget_blocks, f)
         assert ranges_to_tuples(got) == want, f"step {step}"
         assert res.n_ranges == len(want)
@@ -219,7 +244,7 @@ def test_device_resident_entry_points_agree(dtype):
     d_bits = torch.zeros(32, dtype=torch.int32, device=dev)
     p.scan(d_slots, b.group_off, d_bits, d_res, stream)
     torch.cuda.synchronize()
-    touched = compose.group_blocks_fast(b.slots, lay)
+    touched = compose.touched_blocks(b.slots, lay)
     assert np.array_equal(d_bits.cpu().numpy().view(np.uint32), blocks_to_bitmap(touched))
     assert result_from_tensor(d_res)["blocks_touched"] == len(touched)
     p.from_bitmaps(d_bits, b.budget_blocks, capi.RT_PLAN_EVICT, d_out, d_res, stream)
@@ -301,7 +326,7 @@ def test_partial_last_block_is_clamped(shared):
 def test_reference_qwen_geometry(flags):
     """The reference's own deployment: 80 KV allocations of 448,790,528 bytes
     (219,136 slots of 2048 bytes), 256-token blocks (856 of 512 KiB), one mask for all allocations, a 32,768-token budget
-    (128 blocks).  Literal chain on the first two steps, vectorised after."""
+    (128 blocks).  Python chain on the first two steps, the same chain in C after."""
     rng = np.random.default_rng(23)
     shape = dict(layers=40, pool_slots=219136, bytes_per_slot=2048, shared=True, n_req=24, max_len=4096,
                  budget=32768 // 256, block_bytes=256 * 2048)
@@ -321,9 +346,9 @@ def test_benchmark_pairs_match_oracle(kind):
     a, b = workloads.target_pair(kind)
     run_steps([a, b, a], evict=True, flags=(0, np.int64), literal=False)
     want = {"moving": 160, "fragmented": 6080}[kind]
-    resident = [set() for _ in range(a.layout.n_groups)]
-    compose.plan_step(a, resident, literal=False)
-    ranges, _ = compose.plan_step(b, resident, literal=False)
+    chain = CChain(a.layout)
+    chain.step(a, True)
+    ranges, _, _ = chain.step(b, True)
     assert len(ranges) == want
 
 
@@ -337,6 +362,11 @@ def test_int32_ids_negative_and_above_capacity():
     got, res = p.step_host(slots, np.array([1, 11], np.int64), 8, raise_on_slot_range=False)
     assert res.invalid_slots == 2 and res.ignored_slots == 3
     assert res.flags & capi.RT_RESULT_SLOT_RANGE
+    assert p.get_resident() == [[]]              # a step that failed commits nothing
+    # the same ids without the two that are out of range
+    ok = slots[(slots <= lay.capacity)].copy()
+    got, res = p.step_host(ok, np.array([1, len(ok)], np.int64), 8)
+    assert res.invalid_slots == 0 and res.ignored_slots == 3 and res.flags == 0
     assert p.get_resident() == [[0, 3, 7]]
     p.close()
     # a pool too large for 32-bit ids is refused up front
@@ -375,13 +405,13 @@ def test_range_capacity_overflow_is_reported():
 
 def test_headline_step_properties():
     """At the benchmark's full size (40 layers x 256 requests, 262,144 slots)
-    the answer is checked through the vectorised oracle and size-independent
-    properties: idempotence, sorted non-overlapping ranges, byte accounting."""
+    the answer is checked against the literal chain in C and through
+    size-independent properties: idempotence, sorted non-overlapping ranges,
+    byte accounting."""
     b = workloads.target_step(0)
     lay = b.layout
     p = DevicePlanner(lay, 0, max_indices=b.n_idx + 8)
-    resident = [set() for _ in range(lay.n_groups)]
-    want, _ = compose.plan_step(b, resident, literal=False)
+    want, _, _ = CChain(lay).step(b, True)
     got, res = p.step_host(b.slots, b.group_off, b.budget_blocks, capi.RT_PLAN_EVICT)
     assert ranges_to_tuples(got) == want
     assert res.gpu_bytes == int(got["bytes"].sum()) and res.cpu_bytes == 0

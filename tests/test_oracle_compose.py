@@ -48,6 +48,27 @@ def test_literal_fast_and_c_oracles_agree(evict):
             assert co.resident_sets() == r_lit == r_fast
 
 
+def test_three_oracle_forms_agree_at_a_million_ids():
+    """8 layers x 64 requests x 2176 ids = 1.1 M ids, two steps that move blocks:
+    the Python chain (one loop iteration per id, as the reference has it), the
+    vectorised shortcut and the C chain give the same ranges and records.  The
+    C chain is what the full-size GPU tests compare with."""
+    nb = workloads.sparse_feedback(0, layers=8, requests=64).layout.n_blocks
+    seq = [workloads.confine(workloads.sparse_feedback(0, layers=8, requests=64), range(0, nb, 2), "even"),
+           workloads.confine(workloads.sparse_feedback(1, layers=8, requests=64), range(1, nb, 2), "odd")]
+    assert seq[0].n_idx == 8 * 64 * 2176 > 1_000_000
+    lay = seq[0].layout
+    r_lit, r_fast = ([set() for _ in range(lay.n_groups)] for _ in range(2))
+    co = c_oracle.COracle(lay)
+    for b in seq:
+        want = compose.plan_step(b, r_lit, evict=True, literal=True)
+        assert compose.plan_step(b, r_fast, evict=True, literal=False) == want
+        got, invalid = co.step(b.slots, b.group_off, b.budget_blocks, True)
+        assert _tuples(got) == want[0] and invalid == 0 and len(got) > 0
+        assert co.resident_sets() == r_lit == r_fast
+    assert want[1]["blocks_evicted"] > 0
+
+
 def test_slot_zero_and_negative_ids_are_dropped():
     lay = workloads.Layout(1, 2048, 4096)
     slots = np.array([0, -1, 0, 1, 2, 3, -9], dtype=np.int64)

@@ -139,3 +139,15 @@ def test_placement_controller_selection(golden):
         committed = rp.retain_committed(committed, desired, selected, snap["block_versions"], now)
         assert sorted(committed) == res["committed_blocks"]
         assert {str(k): v[0] for k, v in committed.items()} == step["committed_versions"]
+
+
+def test_placement_chain_over_the_recency_horizon(golden):
+    """Committed blocks that leave the desired set while nothing is selected stay
+    on record, and are not sent again when they return with the same version."""
+    from chain_replay import chain_session, replay_chain
+    block = golden["placement_chain"]
+    session, _ = chain_session(block)
+    sent = []
+    replay_chain(block, session, on_plan=lambda t, out, info: sent.append(info["selected"]))
+    # the script does contain the situation: updates with nothing to send after the first three
+    assert sent[:2] == [[1, 0], [4]] and sent[2:7] == [[]] * 5 and sent[7] == [1]

@@ -8,7 +8,8 @@ entirely by the serving engine's pool.  For them the scan keeps its working
 memory in a static device array.  This test calls that entry point through the
 C ABI twice in a row -- the second call finds the array as the first one left
 it -- and requires the same bitmaps and counters as the plan-based
-``rt_scan_slots`` (integer work: exact equality).
+``rt_scan_slots`` and as the CPU oracle's restatement of the reference's
+encode_runs -> blocks chain (integer work: exact equality).
 
 Collected last on purpose: a run that stops at the first failure has then
 already run every other test.
@@ -18,8 +19,9 @@ import ctypes as C
 import numpy as np
 import pytest
 
+from oracle import compose
 from retarget_b200 import capi, workloads
-from retarget_b200.planner import DevicePlanner, result_from_tensor
+from retarget_b200.planner import DevicePlanner, blocks_to_bitmap, result_from_tensor
 
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
@@ -65,6 +67,17 @@ def test_static_scan_matches_plan_scan_twice_in_a_row():
         for key in ("blocks_touched", "invalid_slots", "ignored_slots", "flags"):
             assert got[key] == want[key], key
         assert got["n_ranges"] == 0
+        # ... and against the oracle itself, bitmap by bitmap
+        lay, bits = batch.layout, got_bits.view(np.uint32).reshape(batch.layout.n_groups, 32)
+        touched = 0
+        for g in range(lay.n_groups):
+            ids = batch.slots[batch.group_off[g]:batch.group_off[g + 1]]
+            blocks = compose.touched_blocks(ids[ids <= lay.capacity], lay)
+            assert np.array_equal(bits[g], blocks_to_bitmap(blocks)), g
+            touched += len(blocks)
+        assert got["blocks_touched"] == touched
+        assert got["invalid_slots"] == int((batch.slots > lay.capacity).sum())
+        assert got["ignored_slots"] == int((batch.slots < 1).sum())
     assert want["invalid_slots"] == 0 and want["blocks_touched"] > 0
 
 
