@@ -263,6 +263,9 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     ranks = Ranks("nccl").start(dev)
     flags = capi.RT_PLAN_EVICT | (capi.RT_PLAN_TMA if args.tma else 0)
+    # back-to-back steps of one plan: each may scan under the tail of the one before
+    if not args.unchained:
+        flags |= capi.RT_PLAN_CHAINED
     planner = DevicePlanner(lay, local, max_indices=max(b.n_idx for b in batches) + 8,
                             max_ranges=1 << 16)
     d_slots = [torch.from_numpy(b.slots).to(dev) for b in batches]
@@ -451,7 +454,9 @@ def run_ours(args):
                 "l2": "178 MB of ids per step (> 126 MB L2); two batches alternate",
                 "staging": "cp.async.bulk (TMA) -> shared" if args.tma else "ld.global 128-bit, two register sets",
                 "launch": (f"CUDA graph of {per_replay} steps, replayed" if graph is not None
-                           else "one launch per step on the stream"),
+                           else "one launch per step on the stream") +
+                          ("" if args.unchained else "; steps chained (programmatic dependent launch): "
+                           "the scan of step i+1 runs over the tail of step i"),
                 "evict": True}),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
@@ -631,6 +636,8 @@ def main():
     ap.add_argument("--tma", action="store_true", help="stage ids with bulk async copies (TMA)")
     ap.add_argument("--launch", default="graph", choices=["graph", "stream"],
                     help="how the timed launches are issued: CUDA graph replays or one by one")
+    ap.add_argument("--unchained", action="store_true",
+                    help="launch every step fully serialised after the one before it (no RT_PLAN_CHAINED)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-variants", action="store_true", help="skip the secondary measurements")
     args = ap.parse_args()

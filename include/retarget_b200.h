@@ -189,6 +189,18 @@ typedef struct rt_layout {
 #define RT_PLAN_TMA     4u   /* stage ids through shared memory with bulk async copies     */
                              /* (default: register-staged 128-bit loads, which measured    */
                              /* faster at the sizes a decode step produces)                */
+#define RT_PLAN_CHAINED 8u   /* device-side step calls only: this step may start scanning  */
+                             /* while the kernel before it in `stream` is still finishing. */
+                             /* Meant for steps of one plan issued back to back (or        */
+                             /* captured into one CUDA graph): the slot scan of step i+1   */
+                             /* then runs over the range-emitting tail of step i; results  */
+                             /* are identical.  The caller promises that the slot ids and  */
+                             /* offsets of this step are complete before the PREVIOUS      */
+                             /* operation in `stream` starts -- true when that operation   */
+                             /* is another step, false when it is the kernel that writes   */
+                             /* this step's ids and that kernel itself releases its        */
+                             /* dependents early (programmatic dependent launch).  After   */
+                             /* any other kind of operation the flag changes nothing.      */
 
 /* A step whose result carries any of these flags has NOT changed the resident
  * bitmaps: a plan that cannot be delivered in full is not committed (the

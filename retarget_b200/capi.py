@@ -27,6 +27,7 @@ RT_INITIAL = (1 << 64) - 1
 RT_PLAN_EVICT = 1
 RT_PLAN_DRY_RUN = 2
 RT_PLAN_TMA = 4
+RT_PLAN_CHAINED = 8
 
 RT_RESULT_OVERFLOW = 1
 RT_RESULT_SLOT_RANGE = 2

@@ -14,8 +14,9 @@
 namespace rt {
 void division_magic(uint32_t d, uint32_t *magic, uint32_t *shift);
 cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, bool ids32, int grid,
-                             cudaStream_t stream);
-cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid, cudaStream_t stream);
+                             cudaStream_t stream, bool chained);
+cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid, cudaStream_t stream,
+                                 bool chained);
 cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream_t stream);
 cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plain_blocks_per_sm,
                                 int *tma_blocks_per_sm);
@@ -32,8 +33,9 @@ struct rt_plan {
     int shift = -1;
     uint32_t magic = 0, magic_shift = 0;
     cudaStream_t stream = nullptr;
-    rt::GroupScratch *d_groups = nullptr;
-    rt::GlobalScratch *d_global = nullptr;
+    rt::GroupScratch *d_groups = nullptr;    // two sets of n_groups, used by the scan launches in turn
+    rt::GlobalScratch *d_global = nullptr;   // two sets
+    uint32_t scans = 0;                      // scan launches issued so far
     uint32_t *d_resident = nullptr;
     uint8_t *d_buffer_group = nullptr;  // bitmap of every buffer, registry order
     uint16_t *d_group_size = nullptr;   // buffers per bitmap
@@ -76,7 +78,7 @@ struct DeviceGuard {
 
 void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_t flags,
                     rt_range *out, uint32_t cap, rt_plan_result *result) {
-    p.groups = pl->d_groups;
+    p.groups = pl->d_groups;                 // set 0; scan launches choose theirs with next_scratch()
     p.global = pl->d_global;
     p.resident = pl->d_resident;
     p.buffer_group = pl->d_buffer_group;
@@ -98,6 +100,13 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
     p.block_bytes = pl->layout.block_bytes;
 }
 
+// Scan launches alternate between the plan's two scratch sets (plan_device.cuh).
+void next_scratch(rt_plan *pl, rt::PlanArgs &p) {
+    const uint32_t set = pl->scans++ & 1u;
+    p.groups = pl->d_groups + (size_t)set * pl->layout.n_groups;
+    p.global = pl->d_global + set;
+}
+
 // CSR work-unit table.  Every group gets at least one unit so that its tail
 // runs even when it has no ids this step.
 // ids of one 16-byte load and of one 16 KiB work unit, by id width
@@ -113,7 +122,9 @@ int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const void *d_slots,
     a.slots = reinterpret_cast<const long long *>(d_slots);
     a.lens = nullptr;
     a.stride = 0;
-    a.units_per_row = 0;
+    a.seg_ids = 0;
+    a.n_rows = 0;
+    a.segs_per_row = 0;
     a.n_groups = (int)G;
     a.capacity = pl->layout.capacity_slots;
     a.block_tokens = pl->block_tokens;
@@ -238,11 +249,11 @@ int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, ui
         if (pl->plain_blocks_per_sm < 1) pl->plain_blocks_per_sm = 1;
         if (pl->tma_blocks_per_sm < 1) pl->tma_blocks_per_sm = 1;
         if ((e = cudaStreamCreateWithFlags(&pl->stream, cudaStreamNonBlocking))) { fail(e); break; }
-        size_t gbytes = sizeof(rt::GroupScratch) * L.n_groups;
+        size_t gbytes = 2 * sizeof(rt::GroupScratch) * L.n_groups;
         if ((e = cudaMalloc(&pl->d_groups, gbytes))) { fail(e); break; }
         if ((e = cudaMemset(pl->d_groups, 0, gbytes))) { fail(e); break; }
-        if ((e = cudaMalloc(&pl->d_global, sizeof(rt::GlobalScratch)))) { fail(e); break; }
-        if ((e = cudaMemset(pl->d_global, 0, sizeof(rt::GlobalScratch)))) { fail(e); break; }
+        if ((e = cudaMalloc(&pl->d_global, 2 * sizeof(rt::GlobalScratch)))) { fail(e); break; }
+        if ((e = cudaMemset(pl->d_global, 0, 2 * sizeof(rt::GlobalScratch)))) { fail(e); break; }
         size_t rbytes = sizeof(uint32_t) * rt::kWords * L.n_groups;
         if ((e = cudaMalloc(&pl->d_resident, rbytes))) { fail(e); break; }
         if ((e = cudaMemset(pl->d_resident, 0, rbytes))) { fail(e); break; }
@@ -327,11 +338,13 @@ int step_device_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t
     rt::PlanArgs p;
     fill_plan_args(pl, p, budget, flags, out, cap, result);
     p.n_units = (uint32_t)a.n_units;
+    next_scratch(pl, p);
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
+    const bool chained = (flags & RT_PLAN_CHAINED) != 0;
     bool tma = !ids32 && want_tma(flags);      // the bulk-copy kernel reads int64 ids only
     int grid = grid_for(pl, a.n_units, tma);
-    RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s)
-                : rt::launch_scan_plan(a, p, false, ids32, grid, s));
+    RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s, chained)
+                : rt::launch_scan_plan(a, p, false, ids32, grid, s, chained));
     return RT_OK;
 }
 
@@ -347,8 +360,9 @@ int step_host_impl(rt_plan *pl, const void *h_slots, bool ids32, const int64_t *
     if (n) RT_CUDA(cudaMemcpyAsync(pl->d_stage, h_slots, (ids32 ? 4 : 8) * (size_t)n,
                                    cudaMemcpyHostToDevice, pl->stream));
     uint32_t dev_cap = cap < pl->max_ranges ? cap : pl->max_ranges;
-    int st = step_device_impl(pl, pl->d_stage, ids32, group_off, budget, flags, pl->h_out, dev_cap,
-                              pl->h_result, pl->stream);
+    // (the copy precedes the kernel in the stream: nothing to chain to)
+    int st = step_device_impl(pl, pl->d_stage, ids32, group_off, budget, flags & ~RT_PLAN_CHAINED,
+                              pl->h_out, dev_cap, pl->h_result, pl->stream);
     if (st != RT_OK) return st;
     RT_CUDA(cudaStreamSynchronize(pl->stream));
     *result = *pl->h_result;
@@ -374,14 +388,29 @@ int step_table_impl(rt_plan *pl, const void *d_table, bool ids32, const int32_t 
     a.slots = reinterpret_cast<const long long *>(d_table);
     a.lens = d_lens;
     a.stride = (long long)stride;
-    // a row may start off a 16-byte boundary: the units of a row cover the ids
-    // from the boundary below its start
-    const long long per_unit = ids_per_unit(ids32);
-    long long per_row = ((long long)stride + (ids_per_vec(ids32) - 1) + per_unit - 1) / per_unit;
-    long long units = per_row * n_rows;
-    if (units > 0x7fffffffLL) return RT_ERR_CAPACITY;
-    a.units_per_row = (int)per_row;
-    a.n_units = (int)units;
+    if (stride > (1ull << 40)) return RT_ERR_INVALID_ARGUMENT;
+    // Work is dealt by row segment.  One segment per row is best when there are
+    // several rows for every CTA; a table of few, long rows is cut into segments
+    // of at least 4096 ids so that every CTA still gets a share.
+    const int per_sm = pl->plain_blocks_per_sm;
+    const unsigned long long ctas = (unsigned long long)pl->sm_count * per_sm;
+    unsigned long long segs = 1;
+    if (n_rows < 4 * ctas) {
+        segs = (4 * ctas + n_rows - 1) / n_rows;
+        const unsigned long long most = (stride + 4095) / 4096;
+        if (segs > most) segs = most;
+    }
+    unsigned long long seg_ids = (stride + segs - 1) / segs;
+    seg_ids = (seg_ids + 3) & ~3ull;                              // segments start on the row's own 16-byte grid
+    if (seg_ids > (1ull << 20)) seg_ids = 1ull << 20;             // keeps a pass's vector count in 32 bits
+    segs = (stride + seg_ids - 1) / seg_ids;
+    if (segs > 0xffffffffull) return RT_ERR_CAPACITY;
+    a.seg_ids = (long long)seg_ids;
+    a.n_rows = n_rows;
+    a.segs_per_row = (uint32_t)segs;
+    const unsigned long long n_virtual = (unsigned long long)n_rows * segs;
+    const int grid = (int)(n_virtual < ctas ? n_virtual : ctas);
+    a.n_units = grid;                                             // every CTA arrives once
     a.n_groups = 1;
     a.capacity = pl->layout.capacity_slots;
     a.block_tokens = pl->block_tokens;
@@ -391,8 +420,9 @@ int step_table_impl(rt_plan *pl, const void *d_table, bool ids32, const int32_t 
     rt::PlanArgs p;
     fill_plan_args(pl, p, budget, flags, out, cap, result);
     p.n_units = (uint32_t)a.n_units;
+    next_scratch(pl, p);
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
-    RT_CUDA(rt::launch_scan_plan(a, p, true, ids32, grid_for(pl, a.n_units, false), s));
+    RT_CUDA(rt::launch_scan_plan(a, p, true, ids32, grid, s, (flags & RT_PLAN_CHAINED) != 0));
     return RT_OK;
 }
 
@@ -409,8 +439,9 @@ int scan_slots_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t 
     p.n_units = (uint32_t)a.n_units;
     p.scan_only = 1;
     p.bitmaps_out = d_bitmaps;
+    next_scratch(pl, p);
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
-    RT_CUDA(rt::launch_scan_plan(a, p, false, ids32, grid_for(pl, a.n_units, false), s));
+    RT_CUDA(rt::launch_scan_plan(a, p, false, ids32, grid_for(pl, a.n_units, false), s, false));
     return RT_OK;
 }
 

@@ -17,6 +17,13 @@ constexpr int kChunkElems = kScanThreads * 2 * kUnroll;   // 2048 slot ids = 16 
 
 // Per-bitmap accumulation words, filled with atomicOr by the scan.  The tail
 // zeroes them after reading, so back-to-back launches need no memset.
+//
+// A plan owns TWO sets of scratch (words + counters) and its launches use them
+// in turn.  A chained launch (RT_PLAN_CHAINED) may start scanning while the
+// tail of the launch before it is still reading and clearing its set; it can
+// never meet the launch two before it, because the CTA that runs a tail first
+// waits for the previous launch to complete and only then lets the next launch
+// start (finish_cta in plan_kernels.cu).
 struct GroupScratch {
     uint32_t want[kWords];
 };
@@ -34,9 +41,11 @@ struct ScanArgs {
     const int *lens;                          // table mode: valid ids per row
     long long group_off[RT_MAX_GROUPS + 1];   // CSR mode
     int unit_first[RT_MAX_GROUPS + 1];        // CSR mode: first work unit of each group
-    long long stride;                         // table mode
-    int units_per_row;                        // table mode
-    int n_units;                              // work units of kChunkElems ids each
+    long long stride;                         // table mode: ids from one row to the next
+    long long seg_ids;                        // table mode: ids per row segment (a multiple of 4)
+    uint32_t n_rows;                          // table mode
+    uint32_t segs_per_row;                    // table mode: ceil(stride / seg_ids)
+    int n_units;                              // CSR mode: work units of kChunkElems ids each
     int n_groups;
     unsigned long long capacity;              // largest valid slot id
     uint32_t block_tokens;

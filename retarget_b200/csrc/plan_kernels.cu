@@ -11,6 +11,14 @@
 // CTAs never wait for each other: hand-over is by one arrival counter ("last one
 // out does the tail"), so nothing in here can hang.
 //
+// Chained launches (RT_PLAN_CHAINED): the kernel is launched with programmatic
+// stream serialization.  Its scanning CTAs need nothing from the launch before
+// it, so they start as soon as that launch has finished SCANNING; only the CTA
+// that ends up running the tail executes griddepcontrol.wait (the previous
+// launch has completed: its resident words, ranges and result are final) and
+// then griddepcontrol.launch_dependents (the next launch may start).  The tail
+// of step i thus runs under the scan of step i+1.
+//
 // The path is index arithmetic bound by HBM reads; there is no contraction in
 // it and no tensor-core work.
 #include <cuda_runtime.h>
@@ -242,6 +250,15 @@ struct HandoverShared {
     int last;      // this CTA retired the last work unit of the launch
 };
 
+// Programmatic dependent launch.  Both are no-ops in a kernel that was launched
+// without the attribute.
+__device__ __forceinline__ void griddep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 template <int kBar>
 __device__ __forceinline__ void flush_counters(const PlanArgs &p, ScanCounters &c) {
     // rare path: any thread of the CTA saw an id outside 1..capacity
@@ -298,8 +315,15 @@ __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, Ha
         hs.last = prev + count == p.n_units;
     }
     cta_sync<kBar, kScanThreads>();
-    if (!hs.last) return;
+    if (!hs.last) return;                 // (a CTA that exits counts as having let the next launch go)
     __threadfence();
+    // Order matters.  First: the launch before this one has completed, so what its
+    // tail wrote (resident words, its scratch set cleaned) is final.  Then: the
+    // next launch may start scanning.  It uses the other scratch set, and the one
+    // after it cannot start before that one's tail CTA has come through here,
+    // i.e. before THIS launch has completed -- so two launches never share a set.
+    griddep_wait();
+    griddep_launch_dependents();
     if (tail_mem_unsafe) tail_abort(p);
     else plan_tail<kBar>(p, &p.groups[0].want[0], true, tail_mem);
 }
@@ -390,8 +414,64 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
 // --------------------------------------------------------------------------
 // kernel: padded [rows, stride] table (the serving engine's req_to_token)
 // --------------------------------------------------------------------------
-// Rows are ragged, so work units are dealt round-robin; all ids belong to
-// bitmap 0 and the CTA hands over once.
+// Row r holds lens[r] valid ids at table[r * stride ..]; the rest of the row is
+// padding that is never read.  Work is dealt by ROW SEGMENT (seg_ids ids of one
+// row; one segment per row unless the table has few, long rows), round-robin
+// over the CTAs.  A CTA first turns its segments into a list of 16-byte vectors:
+// per segment the first vector and the number of vectors that hold valid ids,
+// with an exclusive prefix sum over the list in shared memory.  It then streams
+// the flattened vector list exactly like the CSR kernel streams a span -- 256
+// threads x kUnroll independent 128-bit loads, the next batch in flight while
+// this one is marked -- so short rows (2176 ids = 8.5 KiB) cost no idle lanes
+// and no dependent load per row.  All ids feed bitmap 0.
+constexpr int kSegsPerPass = 1024;
+
+struct TableSeg {
+    long long lo, hi;        // valid ids of the segment: flat indices [lo, hi)
+};
+
+struct TableShared {
+    TableSeg seg[kSegsPerPass];
+    unsigned int vec_before[kSegsPerPass + 1];   // exclusive prefix of the segments' vector counts
+    unsigned int warp_sum[kScanThreads / 32];
+};
+
+// Batch `b` of the flattened list: kUnroll vectors per thread.  `cur` is the
+// thread's cursor into the segment list; it only moves forward.
+template <typename Id>
+__device__ __forceinline__ void fetch_table_batch(const Id *slots, const TableShared &sh, int n_segs,
+                                                  unsigned int total, unsigned int base, int &cur,
+                                                  Chunk<Id> &ch) {
+    using Vec = typename IdTraits<Id>::Vec;
+    constexpr int kPer = IdTraits<Id>::kPer;
+    constexpr uint32_t kWhole = (1u << kPer) - 1u;
+    ch.mask = 0;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        const unsigned int vi = base + (unsigned int)(u * kScanThreads) + threadIdx.x;
+        if (vi >= total) continue;
+        while (cur + 1 < n_segs && vi >= sh.vec_before[cur + 1]) ++cur;
+        const long long lo = sh.seg[cur].lo, hi = sh.seg[cur].hi;
+        // the segment's first vector starts at the 16-byte boundary at or below `lo`
+        const long long i0 = (lo & ~(long long)(kPer - 1)) + (long long)(vi - sh.vec_before[cur]) * kPer;
+        if (i0 >= lo && i0 + kPer <= hi) {
+            ch.v[u] = RT_LOAD(reinterpret_cast<const Vec *>(slots + i0));
+            ch.mask |= kWhole << (kPer * u);
+        } else {
+            // first or last vector of a segment: only the ids inside it are read
+#pragma unroll
+            for (int k = 0; k < kPer; ++k) {
+                Id x = 0;
+                if (i0 + k >= lo && i0 + k < hi) {
+                    x = RT_LOAD(slots + i0 + k);
+                    ch.mask |= 1u << (kPer * u + k);
+                }
+                vec_set(ch.v[u], k, x);
+            }
+        }
+    }
+}
+
 template <bool kPow2, typename Id>
 __global__ void __launch_bounds__(kScanThreads)
 scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
@@ -399,40 +479,70 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
     extern __shared__ __align__(16) unsigned char tail_mem[];
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
-    if ((int)blockIdx.x >= a.n_units) return;
+    __shared__ TableShared sh;
     const Id *slots = reinterpret_cast<const Id *>(a.slots);
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     ScanCounters c = {0, 0};
     clear_map(s_map);
-    __syncthreads();
-    uint32_t units = 0;
-    // loads of unit q: the row's length first, then its ids (an empty chunk when
-    // the unit lies past the row's valid ids)
-    auto fetch = [&](int q, Chunk<Id> &ch) {
-        const int row = q / a.units_per_row, k = q - row * a.units_per_row;
-        long long len = __ldg(a.lens + row);
-        if (len < 0) len = 0;
-        if (len > a.stride) len = a.stride;
-        const long long lo = (long long)row * a.stride, hi = lo + len;
-        const long long e0 = (lo & ~(long long)(kPer - 1)) + (long long)k * kChunkIds<Id>;
-        if (e0 >= hi) {
-            ch.mask = 0;
-            return;
+    // this CTA's segments: blockIdx.x, blockIdx.x + gridDim.x, ...
+    const unsigned long long n_virtual = (unsigned long long)a.n_rows * a.segs_per_row;
+    const unsigned long long mine =
+        n_virtual > blockIdx.x ? (n_virtual - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    for (unsigned long long pass = 0; pass < mine; pass += kSegsPerPass) {
+        const int n_segs = (int)(mine - pass < (unsigned long long)kSegsPerPass ? mine - pass : kSegsPerPass);
+        __syncthreads();                         // the previous pass is done with the lists
+        // ---- the segment list: 4 consecutive entries per thread ----
+        unsigned int cnt[4], local = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = (int)tid * 4 + e;
+            cnt[e] = 0;
+            if (k < n_segs) {
+                const unsigned long long v = blockIdx.x + (pass + k) * gridDim.x;
+                const uint32_t row = (uint32_t)(v / a.segs_per_row), seg = (uint32_t)(v - (unsigned long long)row * a.segs_per_row);
+                long long len = __ldg(a.lens + row);
+                if (len < 0) len = 0;
+                if (len > a.stride) len = a.stride;
+                const long long row_lo = (long long)row * a.stride;
+                long long lo = row_lo + (long long)seg * a.seg_ids, hi = lo + a.seg_ids;
+                if (hi > row_lo + len) hi = row_lo + len;
+                if (hi < lo) hi = lo;
+                const long long v0 = lo / kPer, v1 = (hi + kPer - 1) / kPer;
+                sh.seg[k].lo = lo;
+                sh.seg[k].hi = hi;
+                cnt[e] = hi > lo ? (unsigned int)(v1 - v0) : 0u;
+            }
+            local += cnt[e];
         }
-        load_chunk<Id>(slots + e0 + kPer * (int)threadIdx.x, e0, lo, hi, ch);
-    };
-    // the next unit's loads are in flight while this one is marked
-    Chunk<Id> cur, nxt;
-    fetch(blockIdx.x, cur);
-    for (int q = blockIdx.x; q < a.n_units; q += gridDim.x) {
-        const int qn = q + (int)gridDim.x;
-        if (qn < a.n_units) fetch(qn, nxt);
-        else nxt.mask = 0;
-        if (cur.mask) mark_chunk<kPow2, Id>(cur, a, s_map, c);
-        ++units;
-        cur = nxt;
+        const unsigned int incl = warp_inclusive_sum(local, lane);
+        if (lane == 31) sh.warp_sum[warp] = incl;
+        __syncthreads();
+        unsigned int before = incl - local;
+#pragma unroll
+        for (int w = 0; w < kScanThreads / 32; ++w) before += (uint32_t)w < warp ? sh.warp_sum[w] : 0u;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = (int)tid * 4 + e;
+            if (k < n_segs) sh.vec_before[k] = before;
+            before += cnt[e];
+        }
+        if (tid == kScanThreads - 1) sh.vec_before[n_segs] = before;     // the last thread's running sum is the total
+        __syncthreads();
+        const unsigned int total = sh.vec_before[n_segs];
+        // ---- stream the flattened vector list ----
+        constexpr unsigned int kBatch = kScanThreads * kUnroll;
+        int cur = 0;                              // batches are fetched in order: one cursor serves them all
+        Chunk<Id> now, nxt;
+        fetch_table_batch<Id>(slots, sh, n_segs, total, 0, cur, now);
+        for (unsigned int base = 0; base < total; base += kBatch) {
+            if (base + kBatch < total) fetch_table_batch<Id>(slots, sh, n_segs, total, base + kBatch, cur, nxt);
+            else nxt.mask = 0;
+            if (now.mask) mark_chunk<kPow2, Id>(now, a, s_map, c);
+            now = nxt;
+        }
     }
     leave_group<0>(p, 0, s_map, c);
-    finish_cta<0>(p, units, hs, tail_mem);
+    finish_cta<0>(p, 1u, hs, tail_mem);
 }
 
 // --------------------------------------------------------------------------
@@ -665,26 +775,40 @@ plan_tail_kernel(uint32_t *want, const __grid_constant__ PlanArgs p) {
 // --------------------------------------------------------------------------
 // host-side launchers (called from the C ABI)
 // --------------------------------------------------------------------------
+// `chained`: launch with programmatic stream serialization, so that the scan may
+// start while the kernel before it in the stream is still in its tail.
+template <typename Kernel>
+static cudaError_t launch_scan(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t stream,
+                               bool chained, const ScanArgs &a, const PlanArgs &p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = chained ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, a, p);
+}
+
 cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, bool ids32, int grid,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, bool chained) {
     const bool pow2 = a.shift >= 0;
     const size_t smem = tail_smem_bytes(p.n_groups, p.n_buffers);
     if (table) {
-        if (ids32) {
-            if (pow2) scan_table_kernel<true, int><<<grid, kScanThreads, smem, stream>>>(a, p);
-            else scan_table_kernel<false, int><<<grid, kScanThreads, smem, stream>>>(a, p);
-        } else {
-            if (pow2) scan_table_kernel<true, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
-            else scan_table_kernel<false, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
-        }
-    } else if (ids32) {
-        if (pow2) scan_plan_kernel<true, int><<<grid, kScanThreads, smem, stream>>>(a, p);
-        else scan_plan_kernel<false, int><<<grid, kScanThreads, smem, stream>>>(a, p);
-    } else {
-        if (pow2) scan_plan_kernel<true, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
-        else scan_plan_kernel<false, long long><<<grid, kScanThreads, smem, stream>>>(a, p);
+        if (ids32)
+            return pow2 ? launch_scan(scan_table_kernel<true, int>, grid, kScanThreads, smem, stream, chained, a, p)
+                        : launch_scan(scan_table_kernel<false, int>, grid, kScanThreads, smem, stream, chained, a, p);
+        return pow2 ? launch_scan(scan_table_kernel<true, long long>, grid, kScanThreads, smem, stream, chained, a, p)
+                    : launch_scan(scan_table_kernel<false, long long>, grid, kScanThreads, smem, stream, chained, a, p);
     }
-    return cudaGetLastError();
+    if (ids32)
+        return pow2 ? launch_scan(scan_plan_kernel<true, int>, grid, kScanThreads, smem, stream, chained, a, p)
+                    : launch_scan(scan_plan_kernel<false, int>, grid, kScanThreads, smem, stream, chained, a, p);
+    return pow2 ? launch_scan(scan_plan_kernel<true, long long>, grid, kScanThreads, smem, stream, chained, a, p)
+                : launch_scan(scan_plan_kernel<false, long long>, grid, kScanThreads, smem, stream, chained, a, p);
 }
 
 cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream_t stream) {
@@ -693,12 +817,11 @@ cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream
     return cudaGetLastError();
 }
 
-cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid, cudaStream_t stream) {
-    if (a.shift >= 0)
-        scan_plan_tma_kernel<true><<<grid, kTmaThreads, kStages * kStageBytes, stream>>>(a, p);
-    else
-        scan_plan_tma_kernel<false><<<grid, kTmaThreads, kStages * kStageBytes, stream>>>(a, p);
-    return cudaGetLastError();
+cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid, cudaStream_t stream,
+                                 bool chained) {
+    const size_t smem = kStages * kStageBytes;
+    return a.shift >= 0 ? launch_scan(scan_plan_tma_kernel<true>, grid, kTmaThreads, smem, stream, chained, a, p)
+                        : launch_scan(scan_plan_tma_kernel<false>, grid, kTmaThreads, smem, stream, chained, a, p);
 }
 
 // Opt in to the dynamic shared memory the kernels need and report how many CTAs

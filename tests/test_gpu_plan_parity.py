@@ -424,3 +424,109 @@ def test_headline_step_properties():
     again, res2 = p.step_host(b.slots, b.group_off, b.budget_blocks, capi.RT_PLAN_EVICT)
     assert len(again) == 0 and res2.blocks_added == 0 and res2.blocks_evicted == 0
     p.close()
+
+
+def _table_case(rng, rows, stride, dtype, lay, fill):
+    """A padded request table and the CSR batch holding the same valid ids."""
+    if fill == "full":
+        lens = np.full(rows, stride, np.int32)
+    elif fill == "ragged":
+        lens = rng.integers(0, stride + 1, rows).astype(np.int32)
+        lens[rng.integers(0, rows, max(1, rows // 7))] = 0
+    else:                                   # mostly padding, as in a request pool with few live rows
+        lens = np.zeros(rows, np.int32)
+        live = rng.choice(rows, max(1, rows // 20), replace=False)
+        lens[live] = rng.integers(1, stride + 1, len(live))
+    table = rng.integers(lay.capacity + 5, lay.capacity + 900, (rows, stride)).astype(dtype)   # padding: never read
+    flat = []
+    for r in range(rows):
+        n = int(lens[r])
+        if n:
+            start = int(rng.integers(1, lay.capacity - n)) if n < lay.capacity - 2 and rng.random() < 0.5 else None
+            ids = np.arange(start, start + n) if start else rng.integers(0, lay.capacity + 1, n)
+            table[r, :n] = ids
+            flat.append(ids.astype(np.int64))
+    slots = np.concatenate(flat) if flat else np.zeros(0, np.int64)
+    off = np.array([0, len(slots)], np.int64)
+    return table, lens, workloads.SlotBatch(lay, slots, off, off, 12)
+
+
+@pytest.mark.parametrize("dtype", [np.int64, np.int32], ids=["i64", "i32"])
+def test_request_table_shapes(dtype):
+    """The padded-table entry point over the shapes its work split distinguishes:
+    many short rows (one segment each), few long rows (cut into segments), odd
+    strides (rows off the 16-byte grid), empty rows, a table that is mostly
+    padding, and more rows than one pass of a CTA lists."""
+    rng = np.random.default_rng(5)
+    lay = workloads.Layout(3, 2048, 65536, shared_bitmap=True)
+    dev = torch.device("cuda:0")
+    d_out = torch.zeros(4096 * 24, dtype=torch.uint8, device=dev)
+    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
+    shapes = [(10240, 96, "full"), (3000, 217, "ragged"), (7, 40001, "ragged"), (64, 20000, "full"),
+              (1, 5, "full"), (5000, 33, "sparse"), (3, 1 << 21, "sparse"), (700_000, 6, "ragged")]
+    for rows, stride, fill in shapes:
+        table, lens, batch = _table_case(rng, rows, stride, dtype, lay, fill)
+        chain = CChain(lay)
+        p = DevicePlanner(lay, 0)
+        for step in range(2):               # the second step plans against what the first left
+            if step:
+                table, lens, batch = _table_case(rng, rows, stride, dtype, lay, fill)
+            want, info, resident = chain.step(batch, True)
+            p.step_table(torch.from_numpy(table).to(dev), torch.from_numpy(lens).to(dev), batch.budget_blocks,
+                         capi.RT_PLAN_EVICT, d_out, d_res)
+            p.sync()
+            res = result_from_tensor(d_res)
+            assert res["flags"] == 0 and res["invalid_slots"] == 0, (rows, stride, fill)
+            assert res["ignored_slots"] == int((batch.slots < 1).sum())
+            assert ranges_to_tuples(ranges_from_tensor(d_out, res["n_ranges"])) == want, (rows, stride, fill, step)
+            assert p.get_resident() == [sorted(s) for s in resident]
+        p.close()
+
+
+@pytest.mark.parametrize("flags", MODES)
+@pytest.mark.parametrize("launch", ["stream", "graph"])
+def test_chained_steps_match_the_oracle(flags, launch):
+    """RT_PLAN_CHAINED: steps issued back to back, each allowed to start scanning
+    while the one before it is still in its tail.  Every step writes to buffers
+    of its own, so all plans can be compared afterwards; small steps (tail longer
+    than the scan, so tails queue up), medium ones and empty ones are mixed."""
+    flag, dtype = flags
+    rng = np.random.default_rng(77)
+    shape = dict(layers=6, pool_slots=65536, bytes_per_slot=2048, shared=False, n_req=4, budget=9)
+    sizes = [40, 30000, 0, 60, 25000, 50, 0, 20, 70000, 35, 10, 45000]
+    batches = [random_batch(rng, max_len=n, **shape) for n in sizes]
+    lay = batches[0].layout
+    dev = torch.device("cuda:0")
+    f = flag | capi.RT_PLAN_EVICT | capi.RT_PLAN_CHAINED
+    d_slots = [torch.from_numpy(np.ascontiguousarray(b.slots.astype(dtype))).to(dev) for b in batches]
+    d_out = [torch.zeros(1024 * 24, dtype=torch.uint8, device=dev) for _ in batches]
+    d_res = [torch.zeros(64, dtype=torch.uint8, device=dev) for _ in batches]
+    stream = torch.cuda.Stream(device=dev)
+    p = DevicePlanner(lay, 0)
+    torch.cuda.synchronize()
+
+    def issue(handle):
+        for k, b in enumerate(batches):
+            p.step_device(d_slots[k], b.group_off, b.budget_blocks, f, d_out[k], d_res[k], handle)
+
+    rounds = 1
+    if launch == "stream":
+        issue(stream.cuda_stream)
+    else:
+        rounds = 3                           # captured once, replayed: the state carries over between replays
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            issue(torch.cuda.current_stream().cuda_stream)   # capture only records: nothing runs yet
+    resident = [set() for _ in range(lay.n_groups)]
+    for r in range(rounds):
+        if launch == "graph":
+            graph.replay()
+        torch.cuda.synchronize()
+        for k, b in enumerate(batches):
+            want, info = compose.plan_step(b, resident, evict=True, literal=True)
+            res = result_from_tensor(d_res[k])
+            assert res["flags"] == 0
+            assert ranges_to_tuples(ranges_from_tensor(d_out[k], res["n_ranges"])) == want, (r, k)
+            assert res["blocks_added"] == info["blocks_added"] and res["blocks_evicted"] == info["blocks_evicted"]
+        assert p.get_resident() == [sorted(s) for s in resident]
+    p.close()

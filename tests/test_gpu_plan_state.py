@@ -35,11 +35,11 @@ def test_state_after_capacity_and_slot_range_errors(flags, dtype):
     lay = workloads.Layout(3, 2048, 65536, shared_bitmap=False)          # 3 bitmaps x 64 blocks, 6 buffers
     T = lay.block_tokens
     before = [{1, 2, 3, 40}, {5}, set()]
-    # every second block: 16 runs per buffer and phase -- far more than 10 ranges
+    # every second block: 16 runs per buffer and phase -- far more than 24 ranges
     spread = batch_of(lay, [np.arange(0, 32, 2) * T + 7] * 3, 64)
     bad = batch_of(lay, [[9, 10, lay.capacity + 1, 1 << 40], [3 * T + 1], [5]], 8)
     good = batch_of(lay, [[2 * T + 1, 9 * T + 5], [5 * T + 2, 6 * T], [T + 1]], 8)
-    p = DevicePlanner(lay, 0, max_indices=256, max_ranges=10)
+    p = DevicePlanner(lay, 0, max_indices=256, max_ranges=24)
     p.set_resident(before)
     f = flags | capi.RT_PLAN_EVICT
 
