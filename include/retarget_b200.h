@@ -60,7 +60,15 @@ typedef enum rt_status {
     RT_ERR_COMPLETED_COUNT = -27,   /* experiments/cache_window.py:53-54 */
     /* experiments/slot_placement.py:60-64 */
     RT_ERR_BUDGET_DIVISIBLE = -28,
-    RT_ERR_BLOCK_PAGE = -29
+    RT_ERR_BLOCK_PAGE = -29,
+    /* controllers: experiments/cache_window.py:79-87,105-107 and slot_placement.py:28-34,74-75 */
+    RT_ERR_METRICS_MISSING = -30,      /* a completed-token counter is not in the scrape          */
+    RT_ERR_METRICS_INVALID = -31,      /* a completed-token counter is negative or not finite     */
+    RT_ERR_METRICS_KEY_RUNNING = -32,  /* sglang:num_running_reqs was needed and is not there     */
+    RT_ERR_METRICS_KEY_QUEUE = -33,    /* sglang:num_queue_reqs was needed and is not there       */
+    RT_ERR_LAYOUT_MISMATCH = -34,      /* not allocation_count allocations of allocation_bytes    */
+    RT_ERR_SLOT_SPEC = -35,            /* a SlotPlacementSpec field is out of range               */
+    RT_ERR_FEEDBACK_IDENTITY = -36     /* snapshot of another process or another block size       */
 } rt_status;
 
 const char *rt_strerror(int status);
@@ -127,7 +135,7 @@ int rt_encode_runs(const int64_t *values, size_t n, int64_t *runs_out, size_t ca
                    size_t *n_runs);
 
 /* ------------------------------------------------------------------ */
-/* Plan-command expansion: host, no GPU                                 */
+/* The two scheduler-facing controllers: host state machines            */
 /* ------------------------------------------------------------------ */
 
 /* One registry entry, select.cpp:23770-23778 (ctx and pointer omitted). */
@@ -137,6 +145,184 @@ typedef struct rt_alloc_info {
     int32_t device;
     int32_t concurrent;
 } rt_alloc_info;
+
+/* The serving engine's counters and gauges the window policy reads
+ * (experiments/cache_window.py:80,98-99).  Bit k of `present` says that field k
+ * (in declaration order) was in the scrape: the reference fails differently on
+ * a missing name than on a bad value. */
+typedef struct rt_metrics {
+    double prompt_tokens_total;        /* sglang:prompt_tokens_total      */
+    double generation_tokens_total;    /* sglang:generation_tokens_total  */
+    double num_running_reqs;           /* sglang:num_running_reqs         */
+    double num_queue_reqs;             /* sglang:num_queue_reqs           */
+    uint32_t present;
+    uint32_t reserved;
+} rt_metrics;
+
+/* What one window update decided; the fields of the result dictionary of
+ * CacheWindowController.update, experiments/cache_window.py:133-140. */
+typedef struct rt_window_update {
+    int32_t full;                      /* "initial"                                   */
+    int32_t refresh;                   /* "full_cache_refresh"                        */
+    uint64_t old_window[2];            /* RT_INITIAL twice when full                  */
+    uint64_t new_window[2];
+    uint64_t generation;
+    uint64_t cache_count;              /* also set when RT_ERR_LAYOUT_MISMATCH        */
+    uint64_t gpu_bytes;                /* requested_gpu_bytes                         */
+    uint64_t cpu_bytes;                /* requested_cpu_bytes                         */
+    double completed_highwater;
+} rt_window_update;
+
+typedef struct rt_window_state {
+    int32_t has_current;
+    int32_t has_signature;
+    uint64_t current[2];
+    double last_update;
+    double completed_highwater;
+    uint64_t signature_count;
+} rt_window_state;
+
+/* CacheWindowController, experiments/cache_window.py:71-148, as a state machine.
+ * An update is cut where the reference talks to the control socket:
+ *
+ *   rt_window_controller_begin   counters, window, gates (:90-100); 1 = go on
+ *   (caller: wait_idle, list)
+ *   rt_window_controller_plan    cache filter, signature, full / incremental /
+ *                                refresh, the command line, byte accounting
+ *                                (:102-113,122-131)
+ *   (caller: send the command, wait for the job)
+ *   rt_window_controller_commit  (:132)   or   rt_window_controller_fail (:115-118)
+ *
+ * rt_window_controller_due is `due` (:142-148): 1, 0 or a negative status. */
+typedef struct rt_window_controller rt_window_controller;
+int rt_window_controller_create(const rt_window_spec *spec, rt_window_controller **out);
+int rt_window_controller_destroy(rt_window_controller *c);
+int rt_window_controller_due(rt_window_controller *c, const rt_metrics *metrics, double now);
+int rt_window_controller_begin(rt_window_controller *c, const rt_metrics *metrics, double now, int initial);
+int rt_window_controller_plan(rt_window_controller *c, const rt_alloc_info *allocations, size_t n,
+                              uint64_t generation, char *command, size_t cap, rt_window_update *out);
+int rt_window_controller_commit(rt_window_controller *c, double now);
+int rt_window_controller_fail(rt_window_controller *c);
+/* State access for bindings that expose `current`, `signature`, `last_update`
+ * and `completed_highwater` like the reference's attributes.
+ * rt_window_controller_get_signature returns 1 when no signature is on record. */
+int rt_window_controller_get(const rt_window_controller *c, rt_window_state *out);
+int rt_window_controller_set(rt_window_controller *c, const rt_window_state *in);
+int rt_window_controller_get_signature(const rt_window_controller *c, rt_alloc_info *out, size_t cap, size_t *n);
+int rt_window_controller_set_signature(rt_window_controller *c, const rt_alloc_info *sig, size_t n, int known);
+
+/* SlotPlacementSpec, experiments/slot_placement.py:18-26. */
+typedef struct rt_slot_spec {
+    uint64_t block_tokens;
+    uint64_t lookahead_tokens;
+    double min_update_seconds;
+    uint64_t max_blocks_per_update;
+    double active_seconds;
+    double refresh_seconds;
+    double max_feedback_lag_seconds;
+} rt_slot_spec;
+
+/* SlotPlacementSpec.__post_init__, experiments/slot_placement.py:28-34; on
+ * RT_ERR_SLOT_SPEC *bad_field gets the field's index in declaration order. */
+int rt_slot_spec_check(const rt_slot_spec *spec, int *bad_field);
+
+typedef struct rt_block_stamp {
+    uint32_t block;
+    uint32_t reserved;
+    double t;
+} rt_block_stamp;
+
+/* The fields of a feedback snapshot document (experiments/slot_feedback.py:86-91)
+ * that the controller reads.  Lists keep the document's order. */
+typedef struct rt_snapshot_doc {
+    uint64_t pid;
+    uint64_t epoch;
+    uint64_t block_tokens;
+    int64_t sequence;
+    double observed_monotonic_s;
+    double published_monotonic_s;
+    const int32_t *block_versions;
+    size_t n_versions;
+    const rt_block_stamp *recent_reads;
+    size_t n_reads;
+    const rt_block_stamp *recent_writes;
+    size_t n_writes;
+    const uint32_t *free_head_blocks;
+    size_t n_free;
+} rt_snapshot_doc;
+
+/* target_blocks, experiments/slot_placement.py:37-44. */
+int rt_target_blocks(const rt_snapshot_doc *snapshot, const rt_slot_spec *spec, uint64_t budget,
+                     double now, uint32_t *out, size_t cap, size_t *n);
+
+typedef struct rt_slot_update {
+    uint64_t generation;
+    uint64_t epoch;                    /* feedback_epoch                 */
+    int64_t sequence;                  /* feedback_sequence              */
+    double observed_monotonic_s;       /* feedback_observed_monotonic_s  */
+    uint64_t cache_count;              /* also set when RT_ERR_LAYOUT_MISMATCH */
+    uint64_t gpu_bytes;                /* requested_gpu_bytes            */
+    uint64_t n_desired;
+    uint64_t n_selected;
+} rt_slot_update;
+
+typedef struct rt_slot_state {
+    int32_t has_epoch;
+    int32_t reserved;
+    uint64_t epoch;
+    double last_attempt;
+    uint64_t committed_count;
+} rt_slot_state;
+
+typedef struct rt_block_commit {
+    uint32_t block;
+    int32_t version;
+    double at;
+} rt_block_commit;
+
+/* SlotPlacementController, experiments/slot_placement.py:55-162.  It extends the
+ * window controller: rt_slot_controller_window() is the window controller
+ * inside it (borrowed; it shares the cache signature).
+ *
+ *   rt_slot_controller_accept   the checks of snapshot() (:74-78): 1 usable,
+ *                               0 too old, RT_ERR_FEEDBACK_IDENTITY
+ *   rt_slot_controller_choose   choose (:83-94)
+ *   rt_slot_controller_due      due (:96-104); snapshot NULL = none to act on
+ *   rt_slot_controller_begin    update (:119-132): stamps the attempt, a new
+ *                               epoch empties the record, chooses; 1 = send
+ *   rt_slot_controller_plan     (:133-139,154): cache filter, a new signature
+ *                               empties the record and chooses again, command
+ *   rt_slot_controller_pending  desired / selected of the update in progress
+ *   rt_slot_controller_commit   (:148-153)   or   rt_slot_controller_fail (:140-147)
+ *   rt_slot_controller_seed     after the initial window plan (:107-118) */
+typedef struct rt_slot_controller rt_slot_controller;
+int rt_slot_controller_create(const rt_window_spec *cache_spec, const rt_slot_spec *slot_spec, uint64_t pid,
+                              rt_slot_controller **out);
+int rt_slot_controller_destroy(rt_slot_controller *c);
+rt_window_controller *rt_slot_controller_window(rt_slot_controller *c);
+uint64_t rt_slot_controller_budget(const rt_slot_controller *c);
+int rt_slot_controller_accept(const rt_slot_controller *c, const rt_snapshot_doc *snapshot);
+int rt_slot_controller_choose(const rt_slot_controller *c, const rt_snapshot_doc *snapshot, double now,
+                              uint32_t *desired, size_t cap_desired, size_t *n_desired, uint32_t *selected,
+                              size_t cap_selected, size_t *n_selected);
+int rt_slot_controller_due(const rt_slot_controller *c, const rt_snapshot_doc *snapshot, double now);
+int rt_slot_controller_attempt_allowed(const rt_slot_controller *c, double now);
+int rt_slot_controller_begin(rt_slot_controller *c, const rt_snapshot_doc *snapshot, double now);
+int rt_slot_controller_plan(rt_slot_controller *c, const rt_alloc_info *allocations, size_t n,
+                            uint64_t generation, char *command, size_t cap, rt_slot_update *out);
+int rt_slot_controller_pending(const rt_slot_controller *c, uint32_t *desired, size_t cap_desired,
+                               uint32_t *selected, size_t cap_selected);
+int rt_slot_controller_commit(rt_slot_controller *c, double commit_time);
+int rt_slot_controller_fail(rt_slot_controller *c);
+int rt_slot_controller_seed(rt_slot_controller *c, const rt_snapshot_doc *snapshot, double commit_time);
+int rt_slot_controller_get(const rt_slot_controller *c, rt_slot_state *out);
+int rt_slot_controller_set(rt_slot_controller *c, const rt_slot_state *in);
+int rt_slot_controller_get_committed(const rt_slot_controller *c, rt_block_commit *out, size_t cap, size_t *n);
+int rt_slot_controller_set_committed(rt_slot_controller *c, const rt_block_commit *in, size_t n);
+
+/* ------------------------------------------------------------------ */
+/* Plan-command expansion: host, no GPU                                 */
+/* ------------------------------------------------------------------ */
 
 /* One migration request, select.cpp:23779-23784. */
 typedef struct rt_id_range {

@@ -43,6 +43,15 @@ RT_ERR_PLAN = -11
 RT_ERR_TIMEOUT = -12
 RT_ERR_SPEC_POSITIVE = -20
 RT_ERR_COMPLETED_COUNT = -27
+RT_ERR_BUDGET_DIVISIBLE = -28
+RT_ERR_BLOCK_PAGE = -29
+RT_ERR_METRICS_MISSING = -30
+RT_ERR_METRICS_INVALID = -31
+RT_ERR_METRICS_KEY_RUNNING = -32
+RT_ERR_METRICS_KEY_QUEUE = -33
+RT_ERR_LAYOUT_MISMATCH = -34
+RT_ERR_SLOT_SPEC = -35
+RT_ERR_FEEDBACK_IDENTITY = -36
 
 UPDATE_MODES = ("incremental", "initial_only", "full_cache")
 
@@ -64,6 +73,60 @@ class WindowSpecStruct(C.Structure):
 class AllocInfo(C.Structure):
     _fields_ = [("id", C.c_uint64), ("bytes", C.c_uint64), ("device", C.c_int32),
                 ("concurrent", C.c_int32)]
+
+
+class Metrics(C.Structure):
+    _fields_ = [("prompt_tokens_total", C.c_double), ("generation_tokens_total", C.c_double),
+                ("num_running_reqs", C.c_double), ("num_queue_reqs", C.c_double),
+                ("present", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class WindowUpdate(C.Structure):
+    _fields_ = [("full", C.c_int32), ("refresh", C.c_int32), ("old_window", C.c_uint64 * 2),
+                ("new_window", C.c_uint64 * 2), ("generation", C.c_uint64), ("cache_count", C.c_uint64),
+                ("gpu_bytes", C.c_uint64), ("cpu_bytes", C.c_uint64), ("completed_highwater", C.c_double)]
+
+
+class WindowState(C.Structure):
+    _fields_ = [("has_current", C.c_int32), ("has_signature", C.c_int32), ("current", C.c_uint64 * 2),
+                ("last_update", C.c_double), ("completed_highwater", C.c_double),
+                ("signature_count", C.c_uint64)]
+
+
+class SlotSpecStruct(C.Structure):
+    _fields_ = [("block_tokens", C.c_uint64), ("lookahead_tokens", C.c_uint64),
+                ("min_update_seconds", C.c_double), ("max_blocks_per_update", C.c_uint64),
+                ("active_seconds", C.c_double), ("refresh_seconds", C.c_double),
+                ("max_feedback_lag_seconds", C.c_double)]
+
+
+class BlockStamp(C.Structure):
+    _fields_ = [("block", C.c_uint32), ("reserved", C.c_uint32), ("t", C.c_double)]
+
+
+class SnapshotDoc(C.Structure):
+    _fields_ = [("pid", C.c_uint64), ("epoch", C.c_uint64), ("block_tokens", C.c_uint64),
+                ("sequence", C.c_int64), ("observed_monotonic_s", C.c_double),
+                ("published_monotonic_s", C.c_double),
+                ("block_versions", C.POINTER(C.c_int32)), ("n_versions", C.c_size_t),
+                ("recent_reads", C.POINTER(BlockStamp)), ("n_reads", C.c_size_t),
+                ("recent_writes", C.POINTER(BlockStamp)), ("n_writes", C.c_size_t),
+                ("free_head_blocks", C.POINTER(C.c_uint32)), ("n_free", C.c_size_t)]
+
+
+class SlotUpdate(C.Structure):
+    _fields_ = [("generation", C.c_uint64), ("epoch", C.c_uint64), ("sequence", C.c_int64),
+                ("observed_monotonic_s", C.c_double), ("cache_count", C.c_uint64), ("gpu_bytes", C.c_uint64),
+                ("n_desired", C.c_uint64), ("n_selected", C.c_uint64)]
+
+
+class SlotState(C.Structure):
+    _fields_ = [("has_epoch", C.c_int32), ("reserved", C.c_int32), ("epoch", C.c_uint64),
+                ("last_attempt", C.c_double), ("committed_count", C.c_uint64)]
+
+
+class BlockCommit(C.Structure):
+    _fields_ = [("block", C.c_uint32), ("version", C.c_int32), ("at", C.c_double)]
 
 
 class IdRange(C.Structure):
@@ -151,6 +214,45 @@ def _load():
         "rt_plan_from_bitmaps": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p,
                                            C.c_uint32, C.c_void_p, C.c_void_p]),
         "rt_plan_sync": (C.c_int, [C.c_void_p]),
+        # controllers
+        "rt_window_controller_create": (C.c_int, [C.POINTER(WindowSpecStruct), C.POINTER(C.c_void_p)]),
+        "rt_window_controller_destroy": (C.c_int, [C.c_void_p]),
+        "rt_window_controller_due": (C.c_int, [C.c_void_p, C.POINTER(Metrics), C.c_double]),
+        "rt_window_controller_begin": (C.c_int, [C.c_void_p, C.POINTER(Metrics), C.c_double, C.c_int]),
+        "rt_window_controller_plan": (C.c_int, [C.c_void_p, C.POINTER(AllocInfo), C.c_size_t, C.c_uint64,
+                                                C.c_char_p, C.c_size_t, C.POINTER(WindowUpdate)]),
+        "rt_window_controller_commit": (C.c_int, [C.c_void_p, C.c_double]),
+        "rt_window_controller_fail": (C.c_int, [C.c_void_p]),
+        "rt_window_controller_get": (C.c_int, [C.c_void_p, C.POINTER(WindowState)]),
+        "rt_window_controller_set": (C.c_int, [C.c_void_p, C.POINTER(WindowState)]),
+        "rt_window_controller_get_signature": (C.c_int, [C.c_void_p, C.POINTER(AllocInfo), C.c_size_t,
+                                                         C.POINTER(C.c_size_t)]),
+        "rt_window_controller_set_signature": (C.c_int, [C.c_void_p, C.POINTER(AllocInfo), C.c_size_t, C.c_int]),
+        "rt_slot_spec_check": (C.c_int, [C.POINTER(SlotSpecStruct), C.POINTER(C.c_int)]),
+        "rt_target_blocks": (C.c_int, [C.POINTER(SnapshotDoc), C.POINTER(SlotSpecStruct), C.c_uint64, C.c_double,
+                                       u32p, C.c_size_t, C.POINTER(C.c_size_t)]),
+        "rt_slot_controller_create": (C.c_int, [C.POINTER(WindowSpecStruct), C.POINTER(SlotSpecStruct), C.c_uint64,
+                                                C.POINTER(C.c_void_p)]),
+        "rt_slot_controller_destroy": (C.c_int, [C.c_void_p]),
+        "rt_slot_controller_window": (C.c_void_p, [C.c_void_p]),
+        "rt_slot_controller_budget": (C.c_uint64, [C.c_void_p]),
+        "rt_slot_controller_accept": (C.c_int, [C.c_void_p, C.POINTER(SnapshotDoc)]),
+        "rt_slot_controller_choose": (C.c_int, [C.c_void_p, C.POINTER(SnapshotDoc), C.c_double, u32p, C.c_size_t,
+                                                C.POINTER(C.c_size_t), u32p, C.c_size_t, C.POINTER(C.c_size_t)]),
+        "rt_slot_controller_due": (C.c_int, [C.c_void_p, C.POINTER(SnapshotDoc), C.c_double]),
+        "rt_slot_controller_attempt_allowed": (C.c_int, [C.c_void_p, C.c_double]),
+        "rt_slot_controller_begin": (C.c_int, [C.c_void_p, C.POINTER(SnapshotDoc), C.c_double]),
+        "rt_slot_controller_plan": (C.c_int, [C.c_void_p, C.POINTER(AllocInfo), C.c_size_t, C.c_uint64,
+                                              C.c_char_p, C.c_size_t, C.POINTER(SlotUpdate)]),
+        "rt_slot_controller_pending": (C.c_int, [C.c_void_p, u32p, C.c_size_t, u32p, C.c_size_t]),
+        "rt_slot_controller_commit": (C.c_int, [C.c_void_p, C.c_double]),
+        "rt_slot_controller_fail": (C.c_int, [C.c_void_p]),
+        "rt_slot_controller_seed": (C.c_int, [C.c_void_p, C.POINTER(SnapshotDoc), C.c_double]),
+        "rt_slot_controller_get": (C.c_int, [C.c_void_p, C.POINTER(SlotState)]),
+        "rt_slot_controller_set": (C.c_int, [C.c_void_p, C.POINTER(SlotState)]),
+        "rt_slot_controller_get_committed": (C.c_int, [C.c_void_p, C.POINTER(BlockCommit), C.c_size_t,
+                                                       C.POINTER(C.c_size_t)]),
+        "rt_slot_controller_set_committed": (C.c_int, [C.c_void_p, C.POINTER(BlockCommit), C.c_size_t]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -52,6 +52,14 @@ const char *rt_strerror(int status) {
         // messages of experiments/slot_placement.py:60-64
         case RT_ERR_BUDGET_DIVISIBLE: return "KV budget must be divisible by block_tokens";
         case RT_ERR_BLOCK_PAGE: return "slot blocks must be page aligned";
+        // messages of experiments/cache_window.py:82-85,105-107 and slot_placement.py:75
+        case RT_ERR_METRICS_MISSING: return "cache-window policy requires SGLang completed-token counters";
+        case RT_ERR_METRICS_INVALID: return "invalid SGLang completed-token counters";
+        case RT_ERR_METRICS_KEY_RUNNING: return "sglang:num_running_reqs";
+        case RT_ERR_METRICS_KEY_QUEUE: return "sglang:num_queue_reqs";
+        case RT_ERR_LAYOUT_MISMATCH: return "cache layout mismatch";
+        case RT_ERR_SLOT_SPEC: return "slot placement field out of range";
+        case RT_ERR_FEEDBACK_IDENTITY: return "slot feedback identity or geometry mismatch";
         default: return "unknown status";
     }
 }
