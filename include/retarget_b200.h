@@ -655,6 +655,46 @@ int rt_uvm_wait(uint64_t job_id, double timeout_s, int *cuda_error);
 /* Path the listener is bound to ("" when not listening).  Returns its length. */
 int rt_uvm_socket_path(char *out, size_t cap);
 
+/* ------------------------------------------------------------------ */
+/* Client side of the control socket                                    */
+/* ------------------------------------------------------------------ */
+
+/* One command over the control socket of another process
+ * (UvmController.command, experiments/control.py:427-460): connects to
+ * `socket_path`, sends `line` (no terminator; at most 510 bytes, no CR / LF) and
+ * collects the reply up to its newline into `reply`.  One deadline of
+ * `timeout_s` covers connect, send and receive.  Returns the reply's length;
+ * RT_ERR_IO with the errno in *os_error (ETIMEDOUT when the deadline passed);
+ * RT_ERR_CAPACITY for a reply beyond `cap` or 1 MiB. */
+int rt_uvm_client_command(const char *socket_path, const char *line, double timeout_s, char *reply,
+                          size_t cap, int *os_error);
+
+/* The fields of a `status` reply, select.cpp:24058-24068
+ * (UvmStatus, experiments/control.py:53-83). */
+typedef struct rt_uvm_status {
+    uint64_t pid;
+    uint64_t managed_bytes;
+    uint64_t allocation_count;
+    uint64_t allocation_generation;
+    int32_t busy;
+    int32_t last_error;
+    uint64_t job_id;
+    uint64_t completed_job;
+    uint64_t completed_cpu_bytes;
+    uint64_t completed_gpu_bytes;
+    uint64_t job_completed_bytes;
+} rt_uvm_status;
+
+/* Parses a status reply.  RT_ERR_PLAN when the reply says ok:false,
+ * RT_ERR_INVALID_ARGUMENT when a field is missing. */
+int rt_uvm_parse_status(const char *reply, rt_uvm_status *out);
+
+/* What a client checks before it trusts a PID (experiments/control.py:403-425):
+ * the start time of the process (clock ticks since boot; another value later
+ * means the PID was reused) and the uid that owns it. */
+int rt_process_start_time(uint64_t pid, uint64_t *ticks, int *os_error);
+int rt_process_owner(uint64_t pid, uint32_t *uid, int *os_error);
+
 #ifdef __cplusplus
 }
 #endif

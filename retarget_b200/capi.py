@@ -39,6 +39,7 @@ RT_ERR_NO_DEVICE = -2
 RT_ERR_CAPACITY = -5
 RT_ERR_ALIGNMENT = -6
 RT_ERR_SLOT_RANGE = -7
+RT_ERR_IO = -10
 RT_ERR_PLAN = -11
 RT_ERR_TIMEOUT = -12
 RT_ERR_SPEC_POSITIVE = -20

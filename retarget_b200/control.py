@@ -1,17 +1,25 @@
 """Client side of the UVM control socket.
 
-Same wire behaviour as the reference's ``UvmController.command/status/
-_allocation_snapshot/wait_idle/_wait_job`` (experiments/control.py:403-544): one
-ASCII line per connection (shorter than 512 bytes), one JSON line back, 50 ms
-polling while a job runs, and refusal to talk to a PID that has been replaced.
-The prefix plans of the trainer side are here too: ``aligned_uvm_target``,
-``set_target`` and ``retarget`` with their result records
-(experiments/control.py:379-400,488-654).
-The shared-memory registry, the message-queue doorbell and the timeslice
-controls of that file belong to the scheduler's control path and are not part
-of this package.
+The wire behaviour is the reference's (experiments/control.py:403-544): one
+ASCII line per connection, shorter than 512 bytes; one JSON line back; a status
+poll every 50 ms while a job runs; no talking to a PID that has been replaced.
+How it is done is this package's own:
 
-``LocalUvm`` is the in-process twin: it hands the same lines straight to
+* the transport, the status parser and the two identity checks (owner and start
+  time of the PID) are native (``rt_uvm_client_command``, ``rt_uvm_parse_status``,
+  ``rt_process_start_time``, ``rt_process_owner``);
+* everything that waits goes through one poller (``_Protocol._poll``): a
+  condition on the status, a deadline, and what to say when it passes;
+* the prefix plans of the trainer side (``aligned_uvm_target``, ``set_target``,
+  ``retarget``, experiments/control.py:379-400,488-654) keep the placement they
+  last established as one record and fall back to a full target whenever it
+  does not describe the registry any more.
+
+The shared-memory registry, the message-queue doorbell and the timeslice
+controls of the reference's file belong to the scheduler's control path and
+are not part of this package.
+
+``LocalUvm`` is the in-process twin: the same lines go straight to
 ``rt_uvm_command`` of the library loaded in this process, for callers that own
 the GPU process themselves (tests, the benchmark, an embedded scheduler).
 """
@@ -19,23 +27,52 @@ from __future__ import annotations
 
 import ctypes as C
 import dataclasses
+import errno
 import json
 import os
-import pathlib
-import socket
 import time
-from typing import Any
+from typing import Any, Callable
 
 from . import capi
+
+_REPLY_BYTES = 1 << 20
+POLL_SECONDS = 0.05
 
 
 class ControlError(RuntimeError):
     """The controlled process cannot be driven safely (experiments/control.py:29)."""
 
 
+class _StatusStruct(C.Structure):
+    _fields_ = [("pid", C.c_uint64), ("managed_bytes", C.c_uint64), ("allocation_count", C.c_uint64),
+                ("allocation_generation", C.c_uint64), ("busy", C.c_int32), ("last_error", C.c_int32),
+                ("job_id", C.c_uint64), ("completed_job", C.c_uint64), ("completed_cpu_bytes", C.c_uint64),
+                ("completed_gpu_bytes", C.c_uint64), ("job_completed_bytes", C.c_uint64)]
+
+
+def _bind():
+    lib = capi.lib
+    lib.rt_uvm_client_command.restype = C.c_int
+    lib.rt_uvm_client_command.argtypes = [C.c_char_p, C.c_char_p, C.c_double, C.c_char_p, C.c_size_t,
+                                          C.POINTER(C.c_int)]
+    lib.rt_uvm_parse_status.restype = C.c_int
+    lib.rt_uvm_parse_status.argtypes = [C.c_char_p, C.POINTER(_StatusStruct)]
+    lib.rt_process_start_time.restype = C.c_int
+    lib.rt_process_start_time.argtypes = [C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(C.c_int)]
+    lib.rt_process_owner.restype = C.c_int
+    lib.rt_process_owner.argtypes = [C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_int)]
+    lib.rt_uvm_command.restype = C.c_int
+    lib.rt_uvm_command.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t]
+    return lib
+
+
+_lib = _bind()
+
+
 @dataclasses.dataclass(frozen=True)
 class UvmStatus:
-    """experiments/control.py:53-83"""
+    """A `status` reply; field names are the reply's (experiments/control.py:53-83),
+    because result dictionaries carry ``dataclasses.asdict(status)``."""
     pid: int
     managed_bytes: int
     allocation_count: int
@@ -50,11 +87,17 @@ class UvmStatus:
 
     @classmethod
     def from_reply(cls, reply: dict[str, Any]) -> "UvmStatus":
-        if not reply.get("ok"):
+        """Parsed by the library from the reply's JSON text."""
+        raw = _StatusStruct()
+        status = _lib.rt_uvm_parse_status(json.dumps(reply, separators=(",", ":")).encode(), C.byref(raw))
+        if status == capi.RT_ERR_PLAN:
             raise ControlError(f"UVM status failed: {reply}")
-        fields = {f.name: reply.get(f.name, 0) if f.name == "allocation_generation" else reply[f.name]
-                  for f in dataclasses.fields(cls)}
-        return cls(**{k: (bool(v) if k == "busy" else int(v)) for k, v in fields.items()})
+        if status:
+            missing = next((f.name for f in dataclasses.fields(cls)
+                            if f.name not in reply and f.name != "allocation_generation"), "?")
+            raise KeyError(missing)
+        return cls(**{f.name: (bool(raw.busy) if f.name == "busy" else int(getattr(raw, f.name)))
+                      for f in dataclasses.fields(cls)})
 
 
 @dataclasses.dataclass(frozen=True)
@@ -103,21 +146,39 @@ class _Placement:
 
 
 def process_start_time(pid: int) -> int:
-    """Field 22 of /proc/<pid>/stat; guards against PID reuse."""
+    """Start time of ``pid`` in clock ticks since boot; guards against PID reuse."""
+    ticks, err = C.c_uint64(), C.c_int()
+    status = _lib.rt_process_start_time(pid, C.byref(ticks), C.byref(err))
+    if status == capi.RT_ERR_IO:
+        raise ControlError(f"cannot read process {pid}: {OSError(err.value, os.strerror(err.value))}")
+    if status:
+        raise ControlError(f"malformed /proc/{pid}/stat starttime")
+    return ticks.value
+
+
+def _wire_form(command: str) -> bytes:
+    """The line as it goes out, without its terminator."""
+    if any(c in command for c in "\0\n\r"):
+        raise ValueError("UVM command must be one line without terminators")
+    wire = command.encode("ascii")
+    if len(wire) + 1 >= 512:
+        raise ValueError("UVM command is too long")
+    return wire
+
+
+def _reply_object(raw: bytes, pid: int) -> dict[str, Any]:
     try:
-        text = pathlib.Path(f"/proc/{pid}/stat").read_text()
-    except OSError as exc:
-        raise ControlError(f"cannot read process {pid}: {exc}") from exc
-    tail = text[text.rfind(")") + 2:].split()
-    try:
-        return int(tail[19])
-    except (IndexError, ValueError) as exc:
-        raise ControlError(f"malformed /proc/{pid}/stat starttime") from exc
+        reply = json.loads(raw)
+    except json.JSONDecodeError as exc:
+        raise ControlError(f"invalid UVM response from PID {pid}: {raw!r}") from exc
+    if not isinstance(reply, dict):
+        raise ControlError(f"unexpected UVM response from PID {pid}: {reply!r}")
+    return reply
 
 
 class _Protocol:
-    """Everything above the transport: what the reference client derives from
-    command()."""
+    """Everything above the transport.  A subclass supplies ``command(line) ->
+    reply dictionary`` and ``pid``."""
 
     pid: int
     # prefix plans: the placement the process is known to be in (None: unknown, the
@@ -136,62 +197,67 @@ class _Protocol:
     def _pending_job(self):
         return self._in_flight[0] if self._in_flight else None
 
+    # ---- queries ----
     def status(self) -> UvmStatus:
-        status = UvmStatus.from_reply(self.command("status"))
-        if status.pid != self.pid:
-            raise ControlError(f"UVM socket identity mismatch: expected {self.pid}, got {status.pid}")
-        return status
+        answer = UvmStatus.from_reply(self.command("status"))
+        if answer.pid != self.pid:
+            raise ControlError(f"UVM socket identity mismatch: expected {self.pid}, got {answer.pid}")
+        return answer
 
     def _allocation_snapshot(self) -> tuple[int, list[dict[str, int]]]:
         reply = self.command("list")
         if not reply.get("ok"):
             raise ControlError(f"UVM list failed: {reply}")
-        allocations = [{"id": int(a["id"]), "bytes": int(a["bytes"]), "device": int(a["device"])}
-                       for a in reply.get("allocations", [])]
-        return int(reply.get("allocation_generation", 0)), allocations
+        rows = [{key: int(entry[key]) for key in ("id", "bytes", "device")}
+                for entry in reply.get("allocations", [])]
+        return int(reply.get("allocation_generation", 0)), rows
 
     def allocations(self) -> list[dict[str, int]]:
         return self._allocation_snapshot()[1]
 
-    def wait_idle(self, timeout: float = 120.0, poll_seconds: float = 0.05) -> UvmStatus:
-        deadline = time.monotonic() + timeout
-        while True:
-            status = self.status()
-            if not status.busy:
-                self._settle_in_flight(status)
-                return status
-            if time.monotonic() >= deadline:
-                raise ControlError(f"UVM worker for PID {self.pid} remained busy")
+    # ---- waiting ----
+    def _poll(self, settled: Callable[[UvmStatus], bool], timeout: float, poll_seconds: float,
+              gave_up: str) -> UvmStatus:
+        """Status polls until ``settled(status)``; ControlError(gave_up) once
+        ``timeout`` seconds have passed without it."""
+        give_up_at = time.monotonic() + timeout
+        answer = self.status()
+        while not settled(answer):
+            if time.monotonic() >= give_up_at:
+                raise ControlError(gave_up)
             time.sleep(poll_seconds)
+            answer = self.status()
+        return answer
 
-    def _settle_in_flight(self, status: UvmStatus) -> None:
-        """An idle worker settles a job that was submitted without waiting
-        (experiments/control.py:488-513)."""
-        if self._in_flight is None:
-            return
-        job_id, placement = self._in_flight
-        if status.completed_job < job_id:
-            raise ControlError(f"UVM worker for PID {self.pid} became idle before job {job_id} completed")
-        self._in_flight = None
-        if status.last_error != 0:
-            self._placed = None
-            raise ControlError(f"UVM job {job_id} for PID {self.pid} failed with CUDA error "
-                               f"{status.last_error}")
-        self._placed = placement
+    def _job_error(self, job_id: int, answer: UvmStatus) -> ControlError | None:
+        if answer.last_error == 0:
+            return None
+        return ControlError(f"UVM job {job_id} for PID {self.pid} failed with CUDA error {answer.last_error}")
 
-    def _wait_job(self, job_id: int, timeout: float = 120.0, poll_seconds: float = 0.05) -> UvmStatus:
-        deadline = time.monotonic() + timeout
-        while True:
-            status = self.status()
-            if not status.busy and status.completed_job >= job_id:
-                if status.last_error != 0:
-                    raise ControlError(f"UVM job {job_id} for PID {self.pid} failed with CUDA error "
-                                       f"{status.last_error}")
-                return status
-            if time.monotonic() >= deadline:
-                raise ControlError(f"timed out waiting for UVM job {job_id}")
-            time.sleep(poll_seconds)
+    def wait_idle(self, timeout: float = 120.0, poll_seconds: float = POLL_SECONDS) -> UvmStatus:
+        answer = self._poll(lambda s: not s.busy, timeout, poll_seconds,
+                            f"UVM worker for PID {self.pid} remained busy")
+        if self._in_flight is not None:
+            # an idle worker settles the job that was submitted without waiting
+            job_id, placement = self._in_flight
+            if answer.completed_job < job_id:
+                raise ControlError(f"UVM worker for PID {self.pid} became idle before job {job_id} completed")
+            self._in_flight = None
+            failure = self._job_error(job_id, answer)
+            self._placed = None if failure else placement
+            if failure:
+                raise failure
+        return answer
 
+    def _wait_job(self, job_id: int, timeout: float = 120.0, poll_seconds: float = POLL_SECONDS) -> UvmStatus:
+        answer = self._poll(lambda s: not s.busy and s.completed_job >= job_id, timeout, poll_seconds,
+                            f"timed out waiting for UVM job {job_id}")
+        failure = self._job_error(job_id, answer)
+        if failure:
+            raise failure
+        return answer
+
+    # ---- prefix plans ----
     def _registry(self, status: UvmStatus, *targets: int):
         """Generation, signature and the page-aligned form of each target, clamped
         to what is managed."""
@@ -266,66 +332,38 @@ class _Protocol:
         return self._wait_job(int(reply["job_id"]), timeout=timeout)
 
 
-def _check_line(command: str) -> bytes:
-    if "\0" in command or "\n" in command or "\r" in command:
-        raise ValueError("UVM command must be one line without terminators")
-    wire = (command + "\n").encode("ascii")
-    if len(wire) >= 512:
-        raise ValueError("UVM command is too long")
-    return wire
-
-
-def _parse_reply(raw: bytes, pid: int) -> dict[str, Any]:
-    try:
-        reply = json.loads(raw)
-    except json.JSONDecodeError as exc:
-        raise ControlError(f"invalid UVM response from PID {pid}: {raw!r}") from exc
-    if not isinstance(reply, dict):
-        raise ControlError(f"unexpected UVM response from PID {pid}: {reply!r}")
-    return reply
-
-
 class UvmController(_Protocol):
-    """One-command-per-connection client for the control socket of another
-    (or this) process."""
+    """Client for the control socket of another (or this) process: one command
+    per connection, through the library's transport."""
 
     def __init__(self, pid: int, timeout: float = 2.0, path: str | None = None):
         if pid <= 0:
             raise ValueError("pid must be positive")
-        try:
-            owner = pathlib.Path(f"/proc/{pid}").stat().st_uid
-        except OSError as exc:
-            raise ControlError(f"cannot stat process {pid}: {exc}") from exc
-        if owner != os.getuid():
+        owner, err = C.c_uint32(), C.c_int()
+        if _lib.rt_process_owner(pid, C.byref(owner), C.byref(err)):
+            raise ControlError(f"cannot stat process {pid}: {OSError(err.value, os.strerror(err.value))}")
+        if owner.value != os.getuid():
             raise ControlError(f"PID {pid} is owned by another user")
         self.pid = pid
-        self._start_time = process_start_time(pid)
+        self._born = process_start_time(pid)
         self.timeout = timeout
         self.path = path or f"/tmp/select-uvm-{os.getuid()}-{pid}.sock"
+        self._reply = C.create_string_buffer(_REPLY_BYTES + 2)
 
     def command(self, command: str) -> dict[str, Any]:
-        if process_start_time(self.pid) != self._start_time:
+        if process_start_time(self.pid) != self._born:
             raise ControlError(f"PID {self.pid} was replaced; refusing stale UVM control")
-        wire = _check_line(command)
-        chunks, total = [], 0
-        with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as client:
-            client.settimeout(self.timeout)
-            try:
-                client.connect(self.path)
-                client.sendall(wire)
-                while True:
-                    chunk = client.recv(4096)
-                    if not chunk:
-                        break
-                    chunks.append(chunk)
-                    total += len(chunk)
-                    if total > 1024 * 1024:
-                        raise ControlError("oversized UVM response")
-                    if b"\n" in chunk:
-                        break
-            except OSError as exc:
-                raise ControlError(f"UVM command to PID {self.pid} failed: {exc}") from exc
-        return _parse_reply(b"".join(chunks).split(b"\n", 1)[0], self.pid)
+        wire = _wire_form(command)
+        err = C.c_int()
+        n = _lib.rt_uvm_client_command(self.path.encode(), wire, float(self.timeout), self._reply,
+                                       len(self._reply), C.byref(err))
+        if n == capi.RT_ERR_CAPACITY:
+            raise ControlError("oversized UVM response")
+        if n == capi.RT_ERR_IO:
+            why = "timed out" if err.value == errno.ETIMEDOUT else str(OSError(err.value, os.strerror(err.value)))
+            raise ControlError(f"UVM command to PID {self.pid} failed: {why}")
+        capi.check(n, "rt_uvm_client_command")
+        return _reply_object(self._reply.raw[:n], self.pid)
 
 
 class LocalUvm(_Protocol):
@@ -333,12 +371,9 @@ class LocalUvm(_Protocol):
 
     def __init__(self):
         self.pid = os.getpid()
-        self._buf = C.create_string_buffer(1 << 20)
-        capi.lib.rt_uvm_command.restype = C.c_int
-        capi.lib.rt_uvm_command.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t]
+        self._reply = C.create_string_buffer(_REPLY_BYTES)
 
     def command(self, command: str) -> dict[str, Any]:
-        wire = _check_line(command)
-        n = capi.lib.rt_uvm_command(wire[:-1], self._buf, len(self._buf))
+        n = _lib.rt_uvm_command(_wire_form(command), self._reply, len(self._reply))
         capi.check(n, "rt_uvm_command")
-        return _parse_reply(self._buf.raw[:n], self.pid)
+        return _reply_object(self._reply.raw[:n], self.pid)

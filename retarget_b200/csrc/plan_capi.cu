@@ -19,7 +19,7 @@ cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid,
                                  bool chained);
 cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream_t stream);
 cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plain_blocks_per_sm,
-                                int *tma_blocks_per_sm);
+                                int *tma_blocks_per_sm, int *table_blocks_per_sm);
 }  // namespace rt
 
 struct rt_plan {
@@ -28,6 +28,7 @@ struct rt_plan {
     int sm_count = 0;
     int plain_blocks_per_sm = 1;
     int tma_blocks_per_sm = 1;
+    int table_blocks_per_sm = 1;
     uint32_t n_blocks = 0;
     uint32_t block_tokens = 0;
     int shift = -1;
@@ -245,8 +246,9 @@ int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, ui
     do {
         if ((e = cudaDeviceGetAttribute(&pl->sm_count, cudaDevAttrMultiProcessorCount, device))) { fail(e); break; }
         if ((e = rt::scan_plan_occupancy(L.n_groups, L.n_buffers, &pl->plain_blocks_per_sm,
-                                         &pl->tma_blocks_per_sm))) { fail(e); break; }
+                                         &pl->tma_blocks_per_sm, &pl->table_blocks_per_sm))) { fail(e); break; }
         if (pl->plain_blocks_per_sm < 1) pl->plain_blocks_per_sm = 1;
+        if (pl->table_blocks_per_sm < 1) pl->table_blocks_per_sm = 1;
         if (pl->tma_blocks_per_sm < 1) pl->tma_blocks_per_sm = 1;
         if ((e = cudaStreamCreateWithFlags(&pl->stream, cudaStreamNonBlocking))) { fail(e); break; }
         size_t gbytes = 2 * sizeof(rt::GroupScratch) * L.n_groups;
@@ -392,8 +394,7 @@ int step_table_impl(rt_plan *pl, const void *d_table, bool ids32, const int32_t 
     // Work is dealt by row segment.  One segment per row is best when there are
     // several rows for every CTA; a table of few, long rows is cut into segments
     // of at least 4096 ids so that every CTA still gets a share.
-    const int per_sm = pl->plain_blocks_per_sm;
-    const unsigned long long ctas = (unsigned long long)pl->sm_count * per_sm;
+    const unsigned long long ctas = (unsigned long long)pl->sm_count * pl->table_blocks_per_sm;   // one wave
     unsigned long long segs = 1;
     if (n_rows < 4 * ctas) {
         segs = (4 * ctas + n_rows - 1) / n_rows;

@@ -473,7 +473,7 @@ __device__ __forceinline__ void fetch_table_batch(const Id *slots, const TableSh
 }
 
 template <bool kPow2, typename Id>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kScanThreads, 4)
 scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
     constexpr int kPer = IdTraits<Id>::kPer;
     extern __shared__ __align__(16) unsigned char tail_mem[];
@@ -827,7 +827,7 @@ cudaError_t launch_scan_plan_tma(const ScanArgs &a, const PlanArgs &p, int grid,
 // Opt in to the dynamic shared memory the kernels need and report how many CTAs
 // of each streaming kernel fit on one SM for this plan's geometry.
 cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plain_blocks_per_sm,
-                                int *tma_blocks_per_sm) {
+                                int *tma_blocks_per_sm, int *table_blocks_per_sm) {
     const int tail = (int)tail_smem_bytes(n_groups, n_buffers);
     const int tma = kStages * kStageBytes;
     // The attribute belongs to the kernel, not to a plan: it is set to what the
@@ -853,6 +853,9 @@ cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plai
     RT_SET_SMEM(plan_tail_kernel, tail_max)
 #undef RT_SET_SMEM
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(plain_blocks_per_sm, scan_plan_kernel<true, long long>,
+                                                      kScanThreads, tail);
+    if (e != cudaSuccess) return e;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(table_blocks_per_sm, scan_table_kernel<true, int>,
                                                       kScanThreads, tail);
     if (e != cudaSuccess) return e;
     return cudaOccupancyMaxActiveBlocksPerMultiprocessor(tma_blocks_per_sm, scan_plan_tma_kernel<true>,

@@ -8,6 +8,7 @@
 #include <errno.h>
 #include <poll.h>
 #include <pthread.h>
+#include <sys/eventfd.h>
 #include <sys/socket.h>
 #include <sys/stat.h>
 #include <sys/un.h>
@@ -57,6 +58,7 @@ struct Server {
     uint32_t n_streams = 4;
     std::thread worker, listener;
     int listen_fd = -1, client_fd = -1;
+    int stop_fd = -1;                    // eventfd: wakes the listener for a stop
     std::string socket_path;
     dev_t socket_dev = 0;
     ino_t socket_ino = 0;
@@ -300,68 +302,124 @@ std::string handle_line(const char *line) {
 }
 
 // ---------------------------------------------------------------------------
-// socket listener (select.cpp:24330-24376): one command per connection
+// control socket (the protocol of select.cpp:24330-24445): one command per
+// connection, one JSON line back
 // ---------------------------------------------------------------------------
-void send_all(int fd, const std::string &text) {
-    const char *s = text.data();
-    size_t left = text.size();
-    while (left) {
-        ssize_t n = send(fd, s, left, MSG_NOSIGNAL);
-        if (n < 0 && errno == EINTR) continue;
-        if (n <= 0) return;
-        s += n;
-        left -= (size_t)n;
-    }
+// The listener thread sleeps in poll() on the listening socket and on an
+// eventfd that rt_uvm_stop() writes to, so it neither wakes up periodically nor
+// needs a connection shut down under it to notice a stop.  A connection is
+// served against ONE deadline (a second, as the protocol allows a client) that
+// covers reading the line and writing the reply; the line is collected from
+// whatever recv() returns, not byte by byte.
+
+double monotonic_now() {
+    return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 
-void listener_main() {
+enum class Ready { yes, stop, timeout, error };
+
+// Sleeps until `fd` is ready for `events`, the stop event fires or the deadline
+// passes (deadline < 0: no deadline).
+Ready wait_fd(int fd, short events, int stop_fd, double deadline) {
     for (;;) {
-        struct pollfd pfd = {g.listen_fd, POLLIN, 0};
-        int ready = poll(&pfd, 1, 200);
-        {
-            std::lock_guard<std::mutex> st(g.state);
-            if (g.stop) break;
+        int ms = -1;
+        if (deadline >= 0) {
+            const double left = deadline - monotonic_now();
+            if (left <= 0) return Ready::timeout;
+            ms = (int)(left * 1e3) + 1;
         }
-        if (ready <= 0 || !(pfd.revents & POLLIN)) continue;
-        int fd = accept4(g.listen_fd, nullptr, nullptr, SOCK_CLOEXEC);
-        if (fd < 0) continue;
-        bool stopping;
-        {
-            std::lock_guard<std::mutex> st(g.state);
-            g.client_fd = fd;
-            stopping = g.stop;
+        pollfd fds[2] = {{fd, events, 0}, {stop_fd, POLLIN, 0}};
+        const int n = poll(fds, 2, ms);
+        if (n < 0) {
+            if (errno == EINTR) continue;
+            return Ready::error;
         }
-        struct ucred peer;
-        socklen_t size = sizeof(peer);
-        if (!stopping && getsockopt(fd, SOL_SOCKET, SO_PEERCRED, &peer, &size) == 0 &&
-            size == sizeof(peer) && peer.uid == getuid()) {
-            // a partial line cannot hold the listener for more than a second
-            struct timeval timeout = {1, 0};
-            setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &timeout, sizeof(timeout));
-            setsockopt(fd, SOL_SOCKET, SO_SNDTIMEO, &timeout, sizeof(timeout));
-            char line[512];
-            size_t used = 0;
-            bool complete = false, invalid = false;
-            while (used + 1 < sizeof(line)) {
-                char c;
-                ssize_t n = recv(fd, &c, 1, 0);
-                if (n < 0 && errno == EINTR) continue;
-                if (n != 1) break;
-                if (c == '\n') { complete = true; break; }
-                if (!c) { invalid = true; break; }
-                line[used++] = c;
-            }
-            line[used] = 0;
-            send_all(fd, (complete && !invalid ? handle_line(line) : error_reply("invalid_line")) + "\n");
-        }
-        {
-            std::lock_guard<std::mutex> st(g.state);
-            g.client_fd = -1;
-            close(fd);
-        }
+        if (fds[1].revents) return Ready::stop;
+        if (fds[0].revents) return Ready::yes;
     }
 }
 
+constexpr size_t kLineBytes = 512;              // a command is shorter than this, terminator included
+
+enum class Line { ok, invalid };
+
+// One '\n'-terminated command without NUL bytes, shorter than kLineBytes.
+// Anything else -- end of stream, a stalled or over-long line, a NUL -- is
+// `invalid` (the protocol's invalid_line).
+Line read_line(int fd, int stop_fd, double deadline, std::string *line) {
+    char buf[kLineBytes];
+    size_t used = 0;
+    while (used + 1 < sizeof(buf)) {
+        const ssize_t n = recv(fd, buf + used, sizeof(buf) - 1 - used, MSG_DONTWAIT);
+        if (n > 0) {
+            const char *chunk = buf + used;
+            const char *nl = static_cast<const char *>(memchr(chunk, '\n', (size_t)n));
+            const size_t fresh = nl ? (size_t)(nl - chunk) : (size_t)n;
+            if (memchr(chunk, 0, fresh)) return Line::invalid;
+            used += fresh;
+            if (nl) {
+                line->assign(buf, used);
+                return Line::ok;
+            }
+        } else if (n == 0) {
+            return Line::invalid;
+        } else if (errno == EAGAIN || errno == EWOULDBLOCK) {
+            if (wait_fd(fd, POLLIN, stop_fd, deadline) != Ready::yes) return Line::invalid;
+        } else if (errno != EINTR) {
+            return Line::invalid;
+        }
+    }
+    return Line::invalid;
+}
+
+void write_reply(int fd, int stop_fd, double deadline, const std::string &text) {
+    size_t sent = 0;
+    while (sent < text.size()) {
+        const ssize_t n = send(fd, text.data() + sent, text.size() - sent, MSG_NOSIGNAL | MSG_DONTWAIT);
+        if (n > 0) sent += (size_t)n;
+        else if (n < 0 && (errno == EAGAIN || errno == EWOULDBLOCK)) {
+            if (wait_fd(fd, POLLOUT, stop_fd, deadline) != Ready::yes) return;
+        } else if (n < 0 && errno == EINTR) continue;
+        else return;
+    }
+}
+
+bool peer_is_us(int fd) {
+    ucred peer;
+    socklen_t size = sizeof(peer);
+    return getsockopt(fd, SOL_SOCKET, SO_PEERCRED, &peer, &size) == 0 && size == sizeof(peer) &&
+           peer.uid == getuid();
+}
+
+void serve_connection(int fd, int stop_fd) {
+    if (!peer_is_us(fd)) return;                // another user's process gets no answer at all
+    const double deadline = monotonic_now() + 1.0;
+    std::string line;
+    const std::string reply = read_line(fd, stop_fd, deadline, &line) == Line::ok ? handle_line(line.c_str())
+                                                                                   : error_reply("invalid_line");
+    write_reply(fd, stop_fd, deadline, reply + "\n");
+}
+
+void listener_main(int listen_fd, int stop_fd) {
+    while (wait_fd(listen_fd, POLLIN, stop_fd, -1) == Ready::yes) {
+        const int fd = accept4(listen_fd, nullptr, nullptr, SOCK_CLOEXEC);
+        if (fd < 0) continue;
+        {
+            std::lock_guard<std::mutex> st(g.state);
+            g.client_fd = fd;                   // the fork handler closes it in a child
+        }
+        serve_connection(fd, stop_fd);
+        std::lock_guard<std::mutex> st(g.state);
+        g.client_fd = -1;
+        close(fd);
+    }
+}
+
+// The socket file belongs to us only if WE created it: bind() fails on a path
+// that exists, and nothing here ever removes a path first (a socket left behind
+// by a dead process with the same PID is somebody else's to clean up).  What
+// was created is remembered by device and inode and removed only while the
+// path still names that very file.
 void unlink_owned_socket() {
     std::string path;
     dev_t dev;
@@ -373,42 +431,43 @@ void unlink_owned_socket() {
         ino = g.socket_ino;
         g.socket_ino = 0;
     }
-    struct stat st;
-    if (ino && lstat(path.c_str(), &st) == 0 && S_ISSOCK(st.st_mode) && st.st_uid == getuid() &&
-        st.st_dev == dev && st.st_ino == ino)
+    struct stat now;
+    if (!ino || lstat(path.c_str(), &now) != 0) return;
+    if (S_ISSOCK(now.st_mode) && now.st_uid == getuid() && now.st_dev == dev && now.st_ino == ino)
         unlink(path.c_str());
 }
 
-int open_socket(const char *path) {
-    struct sockaddr_un address = {};
+int open_socket(const char *requested) {
+    std::string path = requested ? requested
+                                 : "/tmp/select-uvm-" + std::to_string((unsigned long)getuid()) + "-" +
+                                       std::to_string((long)getpid()) + ".sock";
+    sockaddr_un address = {};
     address.sun_family = AF_UNIX;
-    char def[sizeof(address.sun_path)];
-    if (!path) {
-        snprintf(def, sizeof(def), "/tmp/select-uvm-%lu-%ld.sock", (unsigned long)getuid(), (long)getpid());
-        path = def;
-    }
-    if (strlen(path) >= sizeof(address.sun_path)) return RT_ERR_INVALID_ARGUMENT;
-    strcpy(address.sun_path, path);
-    int fd = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC | SOCK_NONBLOCK, 0);
+    if (path.size() >= sizeof(address.sun_path)) return RT_ERR_INVALID_ARGUMENT;
+    memcpy(address.sun_path, path.c_str(), path.size() + 1);
+    const int fd = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC | SOCK_NONBLOCK, 0);
     if (fd < 0) return RT_ERR_IO;
-    // never remove a path that already exists, even if it looks stale
-    if (bind(fd, (struct sockaddr *)&address, sizeof(address)) != 0) { close(fd); return RT_ERR_IO; }
-    struct stat st;
-    if (lstat(path, &st) != 0) { close(fd); return RT_ERR_IO; }
-    {
-        // status readers look at these under `state`
-        std::lock_guard<std::mutex> lock(g.state);
-        g.socket_path = path;
-        g.socket_dev = st.st_dev;
-        g.socket_ino = st.st_ino;
+    struct stat made;
+    if (bind(fd, reinterpret_cast<sockaddr *>(&address), sizeof(address)) != 0 || lstat(path.c_str(), &made) != 0) {
+        close(fd);
+        return RT_ERR_IO;
     }
-    if (chmod(path, 0600) != 0 || listen(fd, 16) != 0) {
+    {
+        std::lock_guard<std::mutex> lock(g.state);    // status readers look at these under `state`
+        g.socket_path = path;
+        g.socket_dev = made.st_dev;
+        g.socket_ino = made.st_ino;
+    }
+    const int stop_fd = eventfd(0, EFD_CLOEXEC | EFD_NONBLOCK);
+    if (stop_fd < 0 || chmod(path.c_str(), 0600) != 0 || listen(fd, 16) != 0) {
+        if (stop_fd >= 0) close(stop_fd);
         close(fd);
         unlink_owned_socket();
         return RT_ERR_IO;
     }
     std::lock_guard<std::mutex> lock(g.state);
     g.listen_fd = fd;
+    g.stop_fd = stop_fd;
     return RT_OK;
 }
 
@@ -452,6 +511,7 @@ int rt_uvm_start(const rt_uvm_config *config) {
         g.owner = getpid();
         g.stop = false;
         g.listen_fd = -1;
+        g.stop_fd = -1;
         g.socket_path.clear();
     }
     if (cfg.listen) {
@@ -459,12 +519,13 @@ int rt_uvm_start(const rt_uvm_config *config) {
         if (st != RT_OK) return st;
     }
     g.worker = std::thread(rt::worker_main);
-    bool listening;
+    int listen_fd, stop_fd;
     {
         std::lock_guard<std::mutex> st(g.state);
-        listening = g.listen_fd >= 0;
+        listen_fd = g.listen_fd;
+        stop_fd = g.stop_fd;
     }
-    if (listening) g.listener = std::thread(rt::listener_main);
+    if (listen_fd >= 0) g.listener = std::thread(rt::listener_main, listen_fd, stop_fd);
     std::lock_guard<std::mutex> st(g.state);
     g.running = true;
     return RT_OK;
@@ -476,7 +537,10 @@ int rt_uvm_stop(void) {
         std::lock_guard<std::mutex> st(g.state);
         if (!g.running) return RT_ERR_NOT_RUNNING;
         g.stop = true;
-        if (g.client_fd >= 0) shutdown(g.client_fd, SHUT_RDWR);
+        if (g.stop_fd >= 0) {
+            const uint64_t one = 1;                    // wakes the listener wherever it sleeps
+            if (write(g.stop_fd, &one, sizeof(one)) < 0) { /* the counter is saturated: it is awake */ }
+        }
         g.wake.notify_all();
     }
     if (g.listener.joinable()) g.listener.join();
@@ -485,7 +549,8 @@ int rt_uvm_stop(void) {
     std::lock_guard<std::mutex> life(g.life);
     std::lock_guard<std::mutex> st(g.state);
     if (g.listen_fd >= 0) close(g.listen_fd);
-    g.listen_fd = -1;
+    if (g.stop_fd >= 0) close(g.stop_fd);
+    g.listen_fd = g.stop_fd = -1;
     g.running = false;
     g.busy = false;
     g.job.clear();
@@ -709,7 +774,8 @@ void uvm_fork_child() {
     // no mutex and no CUDA call is safe here; the path still belongs to the parent
     if (g.listen_fd >= 0) close(g.listen_fd);
     if (g.client_fd >= 0) close(g.client_fd);
-    g.listen_fd = g.client_fd = -1;
+    if (g.stop_fd >= 0) close(g.stop_fd);
+    g.listen_fd = g.client_fd = g.stop_fd = -1;
 }
 
 }  // namespace rt
