@@ -2,7 +2,7 @@
 """Placement-plan benchmark.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
-                    [--launch graph|stream] [--tma] [--no-cpu] [--no-variants]
+                    [--launch graph|stream] [--unchained] [--tma] [--no-cpu] [--no-extras]
 
 One step = one placement plan for one decode step of the headline workload:
 40 layers (80 KV buffers of 512 MiB), 256 requests, a 262,144-slot pool, and per
@@ -11,27 +11,37 @@ history draws -- 22.3 M int64 slot ids (178 MB) per step.  Two different
 batches alternate, so every step re-reads more than the L2 holds; one lives in
 the lower half of every buffer and one in the upper half, so every plan evicts
 one run and adds one run per buffer (160 ranges per step, the shape of the
-reference's incremental window update).  `variants` reports the same step when
-nothing moves (0 ranges), when the whole budget is replaced in single-block
-runs (6080 ranges) and when the ids are int32.
+reference's incremental window update).
 
-`value`  device time per step, slot ids already in HBM (two CUDA events on the
-         launching stream around the K steps, max over ranks); the steps are
-         issued as CUDA-graph replays (--launch graph, default) or one by one
---workload feedback  the event-driven path (device-resident feedback state)
-         on an incremental decode trace, beside the Python chain on one core
-`e2e`    the same plan through the host-buffer C-ABI call: pinned host ids are
-         copied to the device, planned, and the range list is copied back
+The JSON line (rank 0) carries every term of the metric:
+
+`value`      device time per step, slot ids already in HBM: two CUDA events on
+             the launching stream around the timed steps, max over ranks.  The
+             steps go out as replays of a CUDA graph of chained steps; the graph
+             is replayed until the timed region lasts at least 50 ms, so that
+             `--steps 20` does not end up timing 0.6 ms (`timed_steps` says how
+             many steps were timed; `steps` stays the number asked for)
+`roofline`   slot-scan GB/s of that step against the measured HBM copy peak
+`e2e`        the same plan through the host-buffer C-ABI call: pinned host ids
+             are copied to the device, planned, the range list comes back
+`prefetch`   GB/s of the prefetch executor on managed memory against the pinned
+             host link, measured in the same run (one GPU)
+`feedback`   the event-driven path (device-resident feedback state) on an
+             incremental decode trace, beside the Python chain on one core
+`configs`    the other stated configurations (full refresh, sparse feedback,
+             one tensor-parallel shard): us, GB/s, fraction of the peak
+`tp_shard_us`  (every N) the tensor-parallel shard configuration per rank
+
 --impl reference  times the CPU restatement of the reference's Python path on
-         the host cores (a bounded sample of layers per step, scaled up)
-
-Prints one JSON line (rank 0).
+             the host cores: every step runs all layers, one process per core
 """
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import dataclasses
 import json
+import math
 import multiprocessing as mp
 import os
 import statistics
@@ -48,6 +58,8 @@ sys.path.insert(0, str(ROOT))
 METRIC = "placement_plan_us_per_decode_step"
 UNIT = "us/step"
 FALLBACK_HBM_GBS = 6650.0
+MIN_TIMED_MS = 50.0
+MIB, GIB = 1 << 20, 1 << 30
 
 
 def make_batches(name: str):
@@ -71,28 +83,41 @@ def make_workload(name: str, seed: int):
     raise SystemExit(f"unknown workload {name}")
 
 
-def algorithmic_bytes(batch, n_ranges: int) -> int:
+def algorithmic_bytes(batch, n_ranges: int, id_bytes: int = 8) -> int:
     """Bytes one step must move: every slot id once, the group offsets, the
     resident words read and written, the ranges and the result record."""
     G = batch.layout.n_groups
-    return 8 * batch.n_idx + 8 * (G + 1) + 2 * 4 * 32 * G + 24 * n_ranges + 64
+    return id_bytes * batch.n_idx + 8 * (G + 1) + 2 * 4 * 32 * G + 24 * n_ranges + 64
 
 
-def workload_config(batch, extra=None) -> dict:
+def workload_config(batch, args) -> dict:
+    """Describes the workload and how its steps are issued.  Both arms print the
+    same dictionary for the same command line."""
     lay = batch.layout
     name = batch.name
     for tag, text in ((", lower half", ", steps alternate between the lower and upper half of every buffer"),
                       (", even blocks", ", steps alternate between even and odd blocks")):
         if name.endswith(tag):
             name = name[:-len(tag)] + text
-    cfg = {"workload": name, "layers": lay.layers, "kv_buffers": lay.n_buffers,
-           "alloc_bytes": lay.alloc_bytes, "pool_slots": lay.pool_slots,
-           "bytes_per_slot": lay.bytes_per_slot, "uvm_block_bytes": lay.block_bytes,
-           "bitmaps": lay.n_groups, "blocks_per_bitmap": lay.n_blocks,
-           "budget_blocks": batch.budget_blocks, "slot_ids_per_step": batch.n_idx,
-           "slot_id_bytes_per_step": 8 * batch.n_idx, "index_dtype": "int64"}
-    cfg.update(extra or {})
-    return cfg
+    world = args.gpus
+    launch = ("CUDA graph of up to 20 steps, replayed until the timed region lasts >= 50 ms"
+              if args.launch == "graph" else "one launch per step on the stream, >= 50 ms of steps")
+    if not args.unchained:
+        launch += "; steps chained (programmatic dependent launch): the scan of step i+1 runs over the tail of step i"
+    return {"workload": name, "layers": lay.layers, "kv_buffers": lay.n_buffers,
+            "alloc_bytes": lay.alloc_bytes, "pool_slots": lay.pool_slots,
+            "bytes_per_slot": lay.bytes_per_slot, "uvm_block_bytes": lay.block_bytes,
+            "bitmaps": lay.n_groups, "blocks_per_bitmap": lay.n_blocks,
+            "budget_blocks": batch.budget_blocks, "slot_ids_per_step": batch.n_idx,
+            "slot_id_bytes_per_step": 8 * batch.n_idx, "index_dtype": "int64",
+            "parallelism": f"{world} independent per-GPU planners (one KV shard each), no collective on the data path",
+            "l2": f"{8 * batch.n_idx / 1e6:.0f} MB of ids per step, two batches alternate"
+                  + (" (> 126 MB L2)" if 8 * batch.n_idx > 126e6 else " (fits the L2: a latency figure)"),
+            "staging": "cp.async.bulk (TMA) -> shared" if args.tma else "ld.global 128-bit, two register sets",
+            "gpu_arm_launch": launch,
+            "reference_arm": "CPU restatement of the reference's Python chain, all layers of every step, "
+                             "one process per host core",
+            "evict": True}
 
 
 # --------------------------------------------------------------------------
@@ -152,7 +177,6 @@ def _cpu_layer(args):
     """Worker: the literal reference chain on one layer of one batch."""
     which, layer, resident_blocks = args
     from oracle import compose
-    import dataclasses
     b = _CPU["batches"][which]
     lay = dataclasses.replace(b.layout, layers=1, shared_bitmap=True)
     lo, hi = int(b.group_off[layer]), int(b.group_off[layer + 1])
@@ -167,26 +191,23 @@ def _cpu_layer(args):
     return time.perf_counter() - t, len(out), layer, sorted(resident[0])
 
 
-def cpu_python_port(batches, sample_layers: int, procs: int, steps: int, warmup: int):
-    """Times the Python restatement of the reference path on `sample_layers`
-    layers per step (spread over `procs` processes) and scales to all layers.
-    Returns per-step seconds for the whole workload."""
-    L = batches[0].layout.n_groups
+def cpu_python_port(batches, layers, procs: int, steps: int, warmup: int):
+    """The Python restatement of the reference path on the given layers of every
+    step, spread over `procs` processes.  Returns the wall seconds of each timed
+    step (for those layers; nothing is scaled here)."""
     _CPU["batches"] = batches
     resident = {}
-    layers = list(range(min(sample_layers, L)))
     ctx = mp.get_context("fork")
     times = []
     with ctx.Pool(procs) as pool:
         for step in range(warmup + steps):
             t = time.perf_counter()
-            res = pool.map(_cpu_layer, [(step % 2, l, resident.get(l, ())) for l in layers],
-                           chunksize=1)
+            res = pool.map(_cpu_layer, [(step % 2, l, resident.get(l, ())) for l in layers], chunksize=1)
             dt = time.perf_counter() - t
             for _, _, layer, blocks in res:
                 resident[layer] = blocks
             if step >= warmup:
-                times.append(dt * L / len(layers))
+                times.append(dt)
     return times
 
 
@@ -195,316 +216,199 @@ def cpu_c_port(batches, reps: int):
     co = c_oracle.COracle(batches[0].layout)
     threads = min(co.max_threads, os.cpu_count() or 1)
     times = []
-    for i in range(reps + 1):
+    for i in range(reps + 2):
         b = batches[i % 2]
         t = time.perf_counter()
         co.step(b.slots, b.group_off, b.budget_blocks, True, threads)
-        if i:
+        if i >= 2:
             times.append(time.perf_counter() - t)
     return statistics.median(times), threads
 
 
 def run_reference(args):
-    """The reference arm: CPU only, rank 0 only."""
+    """The reference arm: CPU only, rank 0 only.  Every step plans ALL layers."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     batches = make_batches(args.workload)
     cores = os.cpu_count() or 1
     L = batches[0].layout.n_groups
-    sample = min(L, max(1, cores))
-    times = cpu_python_port(batches, sample, min(cores, sample), args.steps, args.warmup)
+    procs = max(1, min(cores, L))
+    t0 = time.perf_counter()
+    times = cpu_python_port(batches, list(range(L)), procs, args.steps, args.warmup)
+    wall = time.perf_counter() - t0
     per_step = statistics.mean(times)
     us = per_step * 1e6
-    sample_text = (f"{sample} of {L} layers per step through the Python restatement of "
-                   f"encode_runs->blocks->target_blocks->choose->blocksv, {min(cores, sample)} "
-                   f"processes, scaled x{L / sample:.2f}")
+    sample_text = (f"all {L} layers of every step through the Python restatement of "
+                   f"encode_runs->blocks->target_blocks->choose->blocksv, {procs} processes; "
+                   f"{args.steps} timed steps, nothing scaled")
     line = {"impl": "reference", "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
             "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
-            "data": "synthetic", "config": workload_config(batches[0]),
-            "cpu_baseline": {"value": us, "unit": UNIT, "cores": min(cores, sample), "kind": "port",
-                             "sample": sample_text},
+            "data": "synthetic", "config": workload_config(batches[0], args),
+            "cpu_baseline": {"value": us, "unit": UNIT, "cores": procs, "kind": "port", "sample": sample_text},
             "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+            "gpu_launches": 0, "wall_s": wall}
     emit(line)
 
 
 # --------------------------------------------------------------------------
-# GPU arm
+# GPU arm: helpers
 # --------------------------------------------------------------------------
-def run_ours(args):
-    import torch
-    from retarget_b200.multirank import Ranks
+class StepTimer:
+    """Times back-to-back steps of one planner on one stream."""
+
+    def __init__(self, torch, planner, stream, d_out, d_res, flags):
+        self.torch, self.planner, self.stream = torch, planner, stream
+        self.d_out, self.d_res, self.flags = d_out, d_res, flags
+
+    def step(self, tensors, pair, i, handle=None, flags=None):
+        b = pair[i % 2]
+        self.planner.step_device(tensors[i % 2], b.group_off, b.budget_blocks,
+                                 self.flags if flags is None else flags, self.d_out, self.d_res,
+                                 handle if handle is not None else self.stream.cuda_stream)
+
+    def result(self):
+        from retarget_b200.planner import result_from_tensor
+        r = result_from_tensor(self.d_res)
+        if r["flags"]:
+            raise SystemExit(f"bench.py: planner reported flags {r['flags']}")
+        return r
+
+    def timed(self, tensors, pair, *, min_steps, launch="graph", warm=4, min_ms=MIN_TIMED_MS, flags=None):
+        """(us per step, steps timed, ranges of the last step).  Graph mode captures
+        an even number of steps once and replays it."""
+        torch = self.torch
+        for i in range(warm):
+            self.step(tensors, pair, i, flags=flags)
+        torch.cuda.synchronize()
+        self.result()
+        per = 0
+        graph = None
+        if launch == "graph":
+            per = max(2, min(20, min_steps - min_steps % 2))
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=self.stream, capture_error_mode="thread_local"):
+                for i in range(per):
+                    self.step(tensors, pair, warm + i, torch.cuda.current_stream().cuda_stream, flags=flags)
+            graph.replay()                    # untimed: first replay of a new graph
+            torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+
+        def run(n):
+            ev[0].record(self.stream)
+            if graph is not None:
+                for _ in range(n // per):
+                    graph.replay()
+            else:
+                for i in range(n):
+                    self.step(tensors, pair, warm + i, flags=flags)
+            ev[1].record(self.stream)
+            torch.cuda.synchronize()
+            return ev[0].elapsed_time(ev[1])
+
+        unit = per if graph is not None else 2
+        n = max(unit, -(-min_steps // unit) * unit)
+        probe = run(n)                         # sizes the timed region, then it is measured afresh
+        want = max(n, int(math.ceil(min_ms / max(probe / n, 1e-6))))
+        n = -(-want // unit) * unit
+        return n, run, graph
+
+
+def upload(torch, dev, batches, dtype=None):
+    return [torch.from_numpy(b.slots if dtype is None else b.slots.astype(dtype)).to(dev) for b in batches]
+
+
+class UvmConfig(C.Structure):
+    _fields_ = [("socket_path", C.c_char_p), ("chunk_bytes", C.c_uint64), ("batch_bytes", C.c_uint64),
+                ("streams", C.c_uint32), ("listen", C.c_int32)]
+
+
+def prefetch_leg(torch, dev, gib: int = 4):
+    """Prefetched GB/s against the host link: `gib` x 1 GiB managed buffers,
+    registered with the in-process UVM server, moved as a whole to the CPU and
+    back by the executor (64 MiB chunks on 4 side streams, one wait per GiB);
+    the yardstick is a pinned host -> device copy measured just before."""
+    from cuda.bindings import driver as cu
+    from cuda.bindings import runtime as cudart
     from retarget_b200 import capi
-    from retarget_b200.planner import DevicePlanner, result_from_tensor
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    batches = make_batches(args.workload)
-    lay = batches[0].layout
-    # CPU baseline first: its worker processes are forked before CUDA is initialised
-    cpu_lines = {}
-    if rank == 0 and world == 1 and not args.no_cpu:
-        sample = 2
-        L = lay.n_groups
-        py = cpu_python_port(batches, sample, 1, 2, 1)
-        c_s, c_threads = cpu_c_port(batches, 3)
-        cpu_lines["cpu_baseline"] = {
-            "value": statistics.mean(py) * 1e6, "unit": UNIT, "cores": 1, "kind": "port",
-            "sample": f"{min(sample, L)} of {L} layers per step through the Python restatement of "
-                      f"the reference chain, 1 process, scaled x{L / min(sample, L):.0f}"}
-        cpu_lines["cpu_baseline_native"] = {
-            "value": c_s * 1e6, "unit": UNIT, "cores": c_threads, "kind": "port",
-            "sample": "full step, C restatement with OpenMP over layers"}
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; retarget_b200 has no CPU path to fall back to")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    ranks = Ranks("nccl").start(dev)
-    flags = capi.RT_PLAN_EVICT | (capi.RT_PLAN_TMA if args.tma else 0)
-    # back-to-back steps of one plan: each may scan under the tail of the one before
-    if not args.unchained:
-        flags |= capi.RT_PLAN_CHAINED
-    planner = DevicePlanner(lay, local, max_indices=max(b.n_idx for b in batches) + 8,
-                            max_ranges=1 << 16)
-    d_slots = [torch.from_numpy(b.slots).to(dev) for b in batches]
-    h_slots = [torch.from_numpy(b.slots).pin_memory() for b in batches]
-    d_out = torch.zeros((1 << 16) * 24, dtype=torch.uint8, device=dev)
-    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
-    # a stream of our own: handle 0 would select the planner's internal stream
-    stream = torch.cuda.Stream(device=dev)
-    torch.cuda.set_stream(stream)
-    K, W = args.steps, args.warmup
-
-    def barrier():
-        ranks.barrier()
-        torch.cuda.synchronize()
-
-    def device_step(i):
-        b = batches[i % 2]
-        planner.step_device(d_slots[i % 2], b.group_off, b.budget_blocks, flags, d_out, d_res,
-                            stream.cuda_stream)
-
-    # clocks are sampled from the warm-up to the end of the end-to-end loop: the
-    # device-timed region alone lasts only a few milliseconds
-    sampler = ClockSampler(local) if rank == 0 else None
-    for i in range(W):
-        device_step(i)
+    from retarget_b200.control import LocalUvm
+    lib = capi.lib
+    err, concurrent = cudart.cudaDeviceGetAttribute(cudart.cudaDeviceAttr.cudaDevAttrConcurrentManagedAccess,
+                                                    dev.index or 0)
+    if int(err) != 0 or not concurrent:
+        return {"unavailable": "device has no concurrent managed access"}
+    n = 1 << 30
+    host = torch.empty(n, dtype=torch.uint8).pin_memory()
+    devbuf = torch.empty(n, dtype=torch.uint8, device=dev)
+    devbuf.copy_(host, non_blocking=True)
     torch.cuda.synchronize()
-    n_ranges = result_from_tensor(d_res)["n_ranges"]
-
-    # The K launches go out the way a serving engine issues its decode step: as
-    # nodes of a CUDA graph (--launch graph, the default; an even number of steps
-    # is captured once and replayed, what does not fill a replay is launched
-    # plainly) or one by one on the stream (--launch stream).  One event on either
-    # side of the K launches: an event between every two launches is measurement
-    # overhead on the stream (about 2.5 us each here).
-    graph, per_replay = None, 0
-    if args.launch == "graph" and K >= 2:
-        per_replay = min(20, K - K % 2)
-        graph = torch.cuda.CUDAGraph()
-        # thread-local capture mode: the process group's watchdog thread may query events meanwhile
-        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
-            for i in range(per_replay):
-                b = batches[(W + i) % 2]
-                planner.step_device(d_slots[(W + i) % 2], b.group_off, b.budget_blocks, flags, d_out,
-                                    d_res, torch.cuda.current_stream().cuda_stream)
-        graph.replay()                        # untimed: first replay of a new graph
-        torch.cuda.synchronize()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    barrier()
-    ev[0].record(stream)
-    done = 0
-    if graph is not None:
-        for _ in range(K // per_replay):
-            graph.replay()
-        done = K // per_replay * per_replay
-    for i in range(done, K):
-        device_step(W + i)
-    ev[1].record(stream)
-    barrier()
-    total_ms = ev[0].elapsed_time(ev[1])
-    last = result_from_tensor(d_res)
-    if last["flags"]:
-        raise SystemExit(f"bench.py: planner reported flags {last['flags']}")
-
-    # the same step under other conditions (headline workload, one GPU only)
-    variants = {}
-    if args.workload == "target" and world == 1 and not args.no_variants:
-        def timed(slot_tensors, pair, n=50):
-            def one(i):
-                planner.step_device(slot_tensors[i % 2], pair[i % 2].group_off,
-                                    pair[i % 2].budget_blocks, flags, d_out, d_res, stream.cuda_stream)
-            for i in range(4):
-                one(i)
-            torch.cuda.synchronize()
-            t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-            t[0].record(stream)
-            for i in range(n):
-                one(i)
-            t[1].record(stream)
-            torch.cuda.synchronize()
-            r = result_from_tensor(d_res)
-            if r["flags"]:
-                raise SystemExit(f"bench.py: planner reported flags {r['flags']}")
-            return t[0].elapsed_time(t[1]) * 1e3 / n, r["n_ranges"], n
-
-        from retarget_b200 import workloads
-        us, nr, n = timed(d_slots, batches)
-        variants["stream_launches"] = {"us_per_step": us, "ranges_per_step": nr, "steps": n,
-                                       "gbs": algorithmic_bytes(batches[0], nr) / us / 1e3}
-        for kind in ("steady", "fragmented"):
-            pair = workloads.target_pair(kind)
-            tensors = [torch.from_numpy(b.slots).to(dev) for b in pair]
-            us, nr, n = timed(tensors, pair)
-            variants[kind] = {"us_per_step": us, "ranges_per_step": nr, "steps": n,
-                              "gbs": algorithmic_bytes(pair[0], nr) / us / 1e3}
-            del tensors
-        tensors = [torch.from_numpy(b.slots.astype(np.int32)).to(dev) for b in batches]
-        us, nr, n = timed(tensors, batches)
-        variants["int32_ids"] = {"us_per_step": us, "ranges_per_step": nr, "steps": n,
-                                 "gbs": (algorithmic_bytes(batches[0], nr) - 4 * batches[0].n_idx) / us / 1e3}
-        del tensors
-        # the padded-table entry point (the serving engine's req_to_token layout) on the same ids as
-        # int32: one row per (layer, request), one bitmap for all buffers
-        rows = batches[0].n_idx // 2176
-        if rows * 2176 == batches[0].n_idx:
-            shared = dataclasses.replace(lay, shared_bitmap=True)
-            table_planner = DevicePlanner(shared, local)
-            tables = [torch.from_numpy(b.slots.astype(np.int32).reshape(rows, 2176)).to(dev) for b in batches]
-            lens = torch.full((rows,), 2176, dtype=torch.int32, device=dev)
-            for i in range(4):
-                table_planner.step_table(tables[i % 2], lens, batches[0].budget_blocks, flags, d_out, d_res,
-                                         stream.cuda_stream)
-            torch.cuda.synchronize()
-            t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-            t[0].record(stream)
-            for i in range(50):
-                table_planner.step_table(tables[i % 2], lens, batches[0].budget_blocks, flags, d_out, d_res,
-                                         stream.cuda_stream)
-            t[1].record(stream)
-            torch.cuda.synchronize()
-            us = t[0].elapsed_time(t[1]) * 1e3 / 50
-            variants["table_int32_one_bitmap"] = {"us_per_step": us, "rows": rows, "stride": 2176, "steps": 50,
-                                                  "ranges_per_step": result_from_tensor(d_res)["n_ranges"],
-                                                  "gbs": 4 * batches[0].n_idx / us / 1e3}
-            table_planner.close()
-            del tables
-        for i in range(2):      # leave the resident state as the main workload left it
-            device_step(W + K + i)
-        torch.cuda.synchronize()
-
-    # end to end through the host-buffer call: pinned ids -> device -> plan -> ranges on the host
-    out_host = np.empty(1 << 16, dtype=capi.RANGE_DTYPE)
-    e2e_ranges = 0
-    for i in range(W):
-        planner.step_host(h_slots[i % 2].numpy(), batches[i % 2].group_off,
-                          batches[i % 2].budget_blocks, flags, out=out_host)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(K):
-        b = batches[(W + i) % 2]
-        got, res = planner.step_host(h_slots[(W + i) % 2].numpy(), b.group_off, b.budget_blocks,
-                                     flags, out=out_host)
-        e2e_ranges = res.n_ranges
+    t = time.perf_counter()
+    for _ in range(3):
+        devbuf.copy_(host, non_blocking=True)
     torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / K
-    plan = out_host[:e2e_ranges].copy()      # the last timed plan, compared across ranks below
-    if variants:
-        # the host-buffer call on int32 ids: half the bytes over the host link
-        h32 = [torch.from_numpy(b.slots.astype(np.int32)).pin_memory() for b in batches]
-        n32 = 20
-        for i in range(2):
-            planner.step_host(h32[i].numpy(), batches[i].group_off, batches[i].budget_blocks, flags,
-                              out=out_host)
-        t0 = time.perf_counter()
-        for i in range(n32):
-            b = batches[i % 2]
-            planner.step_host(h32[i % 2].numpy(), b.group_off, b.budget_blocks, flags, out=out_host)
-        torch.cuda.synchronize()
-        variants["int32_ids_host_call"] = {"us_per_step": (time.perf_counter() - t0) / n32 * 1e6,
-                                           "steps": n32, "h2d_bytes_per_step": 4 * batches[0].n_idx}
-        del h32
-        for i in range(2):      # back to the main pair's resident state
-            planner.step_host(h_slots[(W + K + i) % 2].numpy(), batches[(W + K + i) % 2].group_off,
-                              batches[(W + K + i) % 2].budget_blocks, flags, out=out_host)
-    clocks = sampler.stop() if sampler else None
+    h2d = 3 * n / (time.perf_counter() - t) / 1e9
+    del host, devbuf
+    err, ctx = cu.cuCtxGetCurrent()
+    ptrs = []
+    for _ in range(gib):
+        err, p = cudart.cudaMallocManaged(GIB, cudart.cudaMemAttachGlobal)
+        if int(err) != 0:
+            for q in ptrs:
+                cudart.cudaFree(q)
+            return {"unavailable": f"cudaMallocManaged failed: {err}"}
+        ptrs.append(int(p))
+        cudart.cudaMemset(p, 0x11, GIB)
+    torch.cuda.synchronize()
+    lib.rt_uvm_register.argtypes = [C.c_uint64, C.c_uint64, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_uint64)]
+    lib.rt_uvm_unregister_ptr.argtypes = [C.c_uint64]
+    for p in ptrs:
+        capi.check(lib.rt_uvm_register(p, GIB, C.c_void_p(int(ctx)), dev.index or 0, 1, None), "rt_uvm_register")
+    total = gib * GIB
+    uvm = LocalUvm()
+    cfg = UvmConfig(None, 64 * MIB, 1024 * MIB, 4, 0)
+    capi.check(lib.rt_uvm_start(C.byref(cfg)), "rt_uvm_start")
+    try:
+        gen = uvm.status().allocation_generation
 
-    ms_per_step, e2e_ms = ranks.max_over_ranks([total_ms / K, e2e_s * 1e3])
-    launch_ms = ms_per_step           # one launch per step, nothing else on the stream
-    # every rank planned from the same slot table: the plans must agree
-    # (dst names the rank's own GPU; the rest must agree)
-    plans_agree = ranks.same_everywhere(b"".join(plan[k].tobytes() for k in ("buffer", "offset", "bytes")))
+        def job(line):
+            t0 = time.perf_counter()
+            reply = uvm.command(line)
+            assert reply.get("ok"), reply
+            done = uvm._wait_job(reply["job_id"], timeout=600, poll_seconds=0.0005)
+            return time.perf_counter() - t0, done
 
-    if rank == 0:
-        peaks_path = ROOT / "MEASURED_PEAKS.json"
-        if peaks_path.exists():
-            peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured"
-        else:
-            peak, peak_src = FALLBACK_HBM_GBS, "fallback"
-        bytes_step = algorithmic_bytes(batches[0], n_ranges)
-        achieved = bytes_step / (launch_ms * 1e-3) / 1e9
-        line = {
-            "metric": METRIC, "value": ms_per_step * 1e3, "unit": UNIT, "n_gpus": world,
-            "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": False,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-            "config": workload_config(batches[0], {
-                "parallelism": f"{world} independent per-GPU planners (one KV shard each), no collective on the data path",
-                "l2": "178 MB of ids per step (> 126 MB L2); two batches alternate",
-                "staging": "cp.async.bulk (TMA) -> shared" if args.tma else "ld.global 128-bit, two register sets",
-                "launch": (f"CUDA graph of {per_replay} steps, replayed" if graph is not None
-                           else "one launch per step on the stream") +
-                          ("" if args.unchained else "; steps chained (programmatic dependent launch): "
-                           "the scan of step i+1 runs over the tail of step i"),
-                "evict": True}),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak,
-                         "traffic": PROFILED_TRAFFIC_BYTES.get((args.workload, bool(args.tma))),
-                         "peak_source": peak_src, "algorithmic_bytes_per_launch": bytes_step,
-                         "launch_ms": launch_ms, "kernel": "scan_plan_tma_kernel" if args.tma else "scan_plan_kernel"},
-            "e2e": {"value": e2e_ms * 1e3, "unit": UNIT,
-                    "h2d_bytes_per_step": 8 * batches[0].n_idx,
-                    "d2h_bytes_per_step": 24 * e2e_ranges + 64},
-            "gpu_launches": K,
-            "clocks": clocks,
-            "slot_scan_gbs_aggregate": world * achieved,
-            "plans_per_s_aggregate": world / (ms_per_step * 1e-3),
-            "ranges_per_step": n_ranges,
-            "plans_agree_across_ranks": plans_agree,
-        }
-        if variants:
-            line["variants"] = variants
-            line["variants_launch"] = "one launch per step on the stream, 50 steps between two events"
-        if cpu_lines:
-            line.update(cpu_lines)
-        emit(line)
-    planner.close()
-    ranks.stop()
+        job(f"targetv {gen} {total}")
+        to_cpu, _ = job(f"targetv {gen} 0")
+        to_gpu, done = job(f"targetv {gen} {total}")
+        out = {"h2d_link_gbs": h2d, "to_gpu_gbs": total / to_gpu / 1e9, "frac_of_link": total / to_gpu / 1e9 / h2d,
+               "to_cpu_gbs": total / to_cpu / 1e9, "bytes_moved_each_way": total,
+               "job_completed_bytes": done.job_completed_bytes,
+               "executor": "64 MiB chunks on 4 side streams, one wait per GiB",
+               "link_yardstick": "pinned host -> device copy of 1 GiB, same process, measured just before"}
+    finally:
+        capi.check(lib.rt_uvm_stop(), "rt_uvm_stop")
+        for p in ptrs:
+            lib.rt_uvm_unregister_ptr(p)
+            cudart.cudaFree(p)
+    return out
 
 
-# --------------------------------------------------------------------------
-# event-driven path: device-resident feedback state, one plan per decode step
-# --------------------------------------------------------------------------
-def run_feedback(args):
-    """--workload feedback: the incremental decode trace (65,536-slot pool, 40
-    layers, Poisson arrivals, one token per live request per step) through
-    rt_feedback_alloc / rt_feedback_attention / rt_feedback_plan, every index
+def feedback_leg(torch, dev, stream, steps=100, warm=8, cpu=True):
+    """The event-driven path on the incremental decode trace (65,536-slot pool,
+    40 layers, Poisson arrivals, one token per live request per step):
+    rt_feedback_alloc / rt_feedback_attention / rt_feedback_plan with every index
     tensor already in HBM; beside it the Python restatement of
-    SlotFeedback.consume -> publish -> target_blocks -> choose -> blocksv on one
-    host core.  One GPU only."""
-    import torch
+    SlotFeedback.consume -> publish -> target_blocks -> choose -> blocksv on one core."""
     from retarget_b200 import capi, workloads
     from retarget_b200.feedback import DeviceFeedback
     from retarget_b200.planner import DevicePlanner, result_from_tensor
-
-    K, W = args.steps, args.warmup
     layout = workloads.Layout(40, 2048, 65536)
-    trace = workloads.decode_trace(0, steps=W + K, initial_requests=48)
+    trace = workloads.decode_trace(0, steps=warm + steps, initial_requests=48)
     budget, max_blocks, active, refresh = 16, 16, 2.0, 10.0
     times = [100.0 + 0.03 * i for i in range(len(trace))]
-    cpu = None
-    if not args.no_cpu:
+    out = {}
+    cpu_ranges = None
+    if cpu:
         from oracle import compose
         from oracle import ref_policy as rp
         spec = rp.SlotSpec(block_tokens=layout.block_tokens, max_blocks_per_update=max_blocks,
@@ -516,20 +420,13 @@ def run_feedback(args):
             if len(ev.alloc_slots):
                 session.alloc(ev.alloc_slots, ev.free_head, times[i] - 0.002)
             session.attention(ev.read_slots, ev.write_slots, times[i])
-            out, _ = session.plan(times[i] + 0.001)
-            if i >= W:
+            got, _ = session.plan(times[i] + 0.001)
+            if i >= warm:
                 t_cpu += time.perf_counter() - t0
-                cpu_ranges += len(out)
-        cpu = {"value": t_cpu / K * 1e6, "unit": UNIT, "cores": 1, "kind": "port",
-               "sample": f"all {K} timed steps through the Python restatement of the reference's "
-                         f"event-driven chain", "ranges": cpu_ranges}
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; retarget_b200 has no CPU path to fall back to")
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(0)
-    stream = torch.cuda.Stream(device=dev)
-    torch.cuda.set_stream(stream)
-    planner = DevicePlanner(layout, 0)
+                cpu_ranges += len(got)
+        out["cpu_us_per_step"] = t_cpu / steps * 1e6
+        out["cpu"] = "Python restatement of the reference's event-driven chain, 1 core, all timed steps"
+    planner = DevicePlanner(layout, dev.index or 0)
     fb = DeviceFeedback(planner, pid=0)
     up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
     d_steps = [(up(ev.alloc_slots) if len(ev.alloc_slots) else None,
@@ -538,10 +435,8 @@ def run_feedback(args):
     d_out = torch.zeros((1 << 14) * 24, dtype=torch.uint8, device=dev)
     d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
     h = stream.cuda_stream
-    launches = 0
 
     def step(i):
-        nonlocal launches
         a, head, r, w = d_steps[i]
         if a is not None:
             fb.alloc(a, times[i] - 0.002, head, h)
@@ -549,49 +444,33 @@ def run_feedback(args):
         fb.plan(times[i] + 0.001, budget=budget, max_blocks_per_update=max_blocks, active_seconds=active,
                 refresh_seconds=refresh, flags=capi.RT_PLAN_EVICT, d_out=d_out, d_result=d_res, stream=h)
 
-    sampler = ClockSampler(0)
-    for i in range(W):
+    for i in range(warm):
         step(i)
     torch.cuda.synchronize()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     ev[0].record(stream)
-    gpu_ranges = 0
-    for i in range(W, W + K):
+    for i in range(warm, warm + steps):
         step(i)
     ev[1].record(stream)
     torch.cuda.synchronize()
-    us = ev[0].elapsed_time(ev[1]) * 1e3 / K
-    # same trace again, synchronising every step, to count the ranges and to
-    # get the latency a caller sees (launch + run + read-back of the result)
+    out["us_per_step"] = ev[0].elapsed_time(ev[1]) * 1e3 / steps
+    # the same trace again, one step at a time, to count the ranges
     fb.clear(99.0, h)
     planner.set_resident([set()])
-    t_sync = 0.0
-    for i in range(W + K):
-        t0 = time.perf_counter()
+    gpu_ranges = 0
+    for i in range(warm + steps):
         step(i)
         stream.synchronize()
-        n = result_from_tensor(d_res)["n_ranges"]
-        if i >= W:
-            t_sync += time.perf_counter() - t0
-            gpu_ranges += n
-    clocks = sampler.stop()
-    ids = sum(len(e.alloc_slots) + len(e.read_slots) + len(e.write_slots) for e in trace[W:]) / K
-    line = {"metric": "feedback_plan_us_per_decode_step", "value": us, "unit": UNIT, "n_gpus": 1, "steps": K,
-            "warmup": W, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-            "config": {"workload": "incremental decode trace L40 S65536, event-driven feedback state",
-                       "layers": 40, "pool_slots": 65536, "blocks_per_bitmap": layout.n_blocks,
-                       "budget_blocks": budget, "event_ids_per_step": ids,
-                       "live_requests_last_step": trace[-1].live},
-            "e2e": {"value": t_sync / K * 1e6, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 64,
-                    "note": "ids already on the device; launch + run + result read-back, one step at a time"},
-            "ranges_total": gpu_ranges, "clocks": clocks}
-    if cpu:
-        line["cpu_baseline"] = cpu
-        line["ranges_match_cpu"] = cpu["ranges"] == gpu_ranges
-    emit(line)
+        if i >= warm:
+            gpu_ranges += result_from_tensor(d_res)["n_ranges"]
+    ids = sum(len(e.alloc_slots) + len(e.read_slots) + len(e.write_slots) for e in trace[warm:]) / steps
+    out.update(steps=steps, event_ids_per_step=ids, launches_per_step=sum(2 + (a is not None) for a, *_ in d_steps[warm:]) / steps,
+               ranges_total=gpu_ranges, workload="incremental decode trace L40 S65536, event-driven feedback state")
+    if cpu_ranges is not None:
+        out["ranges_match_cpu"] = cpu_ranges == gpu_ranges
     fb.close()
     planner.close()
+    return out
 
 
 # DRAM bytes per launch of the scan kernel from the ncu captures summarised under
@@ -601,6 +480,287 @@ PROFILED_TRAFFIC_BYTES = {
     ("target", False): 181_694_000,   # 178.35 MB read + 3.35 MB written
     ("target", True): 182_228_000,    # 178.34 MB read + 3.89 MB written
 }
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    from retarget_b200.multirank import Ranks
+    from retarget_b200 import capi, workloads
+    from retarget_b200.planner import DevicePlanner
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    single = world == 1
+    batches = make_batches(args.workload)
+    lay = batches[0].layout
+    # CPU baselines first: their worker processes are forked before CUDA is initialised
+    cpu_lines = {}
+    if rank == 0 and single and not args.no_cpu:
+        c_s, c_threads = cpu_c_port(batches, 5)
+        cpu_lines["cpu_baseline"] = {
+            "value": c_s * 1e6, "unit": UNIT, "cores": c_threads, "kind": "port",
+            "sample": "full step (all layers), C restatement of the reference chain with OpenMP over layers, "
+                      "median of 5 steps"}
+        sample = 2
+        py = cpu_python_port(batches, list(range(sample)), 1, 2, 1)
+        cpu_lines["cpu_baseline_python"] = {
+            "value": statistics.mean(py) * 1e6, "unit": "us per step for the sampled layers", "cores": 1,
+            "kind": "port", "layers_in_sample": sample, "layers_per_step": lay.n_groups,
+            "sample": f"{sample} of {lay.n_groups} layers per step through the Python restatement of the "
+                      f"reference chain, 1 process (the reference arm times all layers)"}
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; retarget_b200 has no CPU path to fall back to")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    ranks = Ranks("nccl").start(dev)
+    base = capi.RT_PLAN_EVICT | (capi.RT_PLAN_TMA if args.tma else 0)
+    # back-to-back steps of one plan: each may scan under the tail of the one before
+    flags = base | (0 if args.unchained else capi.RT_PLAN_CHAINED)
+    planner = DevicePlanner(lay, local, max_indices=max(b.n_idx for b in batches) + 8, max_ranges=1 << 16)
+    d_slots = upload(torch, dev, batches)
+    h_slots = [torch.from_numpy(b.slots).pin_memory() for b in batches]
+    d_out = torch.zeros((1 << 16) * 24, dtype=torch.uint8, device=dev)
+    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
+    # a stream of our own: handle 0 would select the planner's internal stream
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    K, W = args.steps, args.warmup
+    timer = StepTimer(torch, planner, stream, d_out, d_res, flags)
+
+    def barrier():
+        ranks.barrier()
+        torch.cuda.synchronize()
+
+    # clocks are sampled from the warm-up to the end of the end-to-end loop
+    sampler = ClockSampler(local) if rank == 0 else None
+
+    # ---- headline: device time per step ----
+    n_timed, run, graph = timer.timed(d_slots, batches, min_steps=K, launch=args.launch, warm=W)
+    n_timed = int(ranks.max_over_ranks([n_timed])[0])       # every rank times the same number of steps
+    barrier()
+    total_ms = run(n_timed)
+    barrier()
+    n_ranges = timer.result()["n_ranges"]
+
+    # ---- config 4 on every rank: one tensor-parallel shard per GPU ----
+    tp_pair = [workloads.tp_shard(0), workloads.tp_shard(1)]
+    tp_planner = DevicePlanner(tp_pair[0].layout, local)
+    tp_timer = StepTimer(torch, tp_planner, stream, d_out, d_res, flags)
+    tp_slots = upload(torch, dev, tp_pair)
+    tp_n, tp_run, _ = tp_timer.timed(tp_slots, tp_pair, min_steps=200, launch=args.launch, min_ms=20.0)
+    tp_n = int(ranks.max_over_ranks([tp_n])[0])
+    barrier()
+    tp_ms = tp_run(tp_n)
+    barrier()
+    tp_ranges = tp_timer.result()["n_ranges"]
+
+    extras = {}
+    if rank == 0 and single and not args.no_extras:
+        def leg(pair, tensors, *, launch=args.launch, f=None, id_bytes=8, min_ms=20.0, p=None):
+            t = timer if p is None else StepTimer(torch, p, stream, d_out, d_res, flags)
+            n, go, _ = t.timed(tensors, pair, min_steps=50, launch=launch, min_ms=min_ms, flags=f)
+            ms = go(n)
+            nr = t.result()["n_ranges"]
+            us = ms * 1e3 / n
+            gbs = algorithmic_bytes(pair[0], nr, id_bytes) / us / 1e3
+            return {"us_per_step": us, "ranges_per_step": nr, "steps": n, "gbs": gbs}
+
+        # per-launch kernel durations: an event pair around every launch, fully serialised launches
+        dur = []
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
+        for i, (a, b) in enumerate(evs):
+            a.record(stream)
+            timer.step(d_slots, batches, i, flags=base)
+            b.record(stream)
+        torch.cuda.synchronize()
+        dur = sorted(a.elapsed_time(b) * 1e3 for a, b in evs)
+        extras["per_launch_us"] = {"launches": len(dur), "min": dur[0], "median": dur[len(dur) // 2],
+                                   "p95": dur[int(len(dur) * 0.95)],
+                                   "how": "one CUDA event pair around every launch, launches not chained"}
+        variants = {}
+        if args.workload == "target":
+            variants["stream_launches"] = leg(batches, d_slots, launch="stream")
+            variants["unchained_graph"] = leg(batches, d_slots, f=base)
+            for kind in ("steady", "fragmented"):
+                pair = workloads.target_pair(kind)
+                tensors = upload(torch, dev, pair)
+                variants[kind] = leg(pair, tensors)
+                del tensors
+            tensors = upload(torch, dev, batches, np.int32)
+            variants["int32_ids"] = leg(batches, tensors, id_bytes=4)
+            del tensors
+            if not args.tma:
+                variants["tma_staging"] = leg(batches, d_slots, f=flags | capi.RT_PLAN_TMA)
+            # the padded-table entry point (the serving engine's req_to_token layout) on the same ids:
+            # one row per (layer, request), one bitmap for all buffers
+            rows = batches[0].n_idx // 2176
+            if rows * 2176 == batches[0].n_idx:
+                shared = dataclasses.replace(lay, shared_bitmap=True)
+                for name, dtype, width in (("table_int32_one_bitmap", np.int32, 4), ("table_int64_one_bitmap", np.int64, 8)):
+                    tp = DevicePlanner(shared, local)
+                    tables = [torch.from_numpy(b.slots.astype(dtype).reshape(rows, 2176)).to(dev) for b in batches]
+                    lens = torch.full((rows,), 2176, dtype=torch.int32, device=dev)
+
+                    def table_step(i):
+                        tp.step_table(tables[i % 2], lens, batches[0].budget_blocks, flags, d_out, d_res,
+                                      stream.cuda_stream)
+                    for i in range(4):
+                        table_step(i)
+                    torch.cuda.synchronize()
+                    n = 400
+                    t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                    t[0].record(stream)
+                    for i in range(n):
+                        table_step(i)
+                    t[1].record(stream)
+                    torch.cuda.synchronize()
+                    us = t[0].elapsed_time(t[1]) * 1e3 / n
+                    variants[name] = {"us_per_step": us, "rows": rows, "stride": 2176, "steps": n,
+                                      "ranges_per_step": timer.result()["n_ranges"],
+                                      "gbs": width * batches[0].n_idx / us / 1e3}
+                    tp.close()
+                    del tables
+            for i in range(2):      # leave the resident state as the main workload left it
+                timer.step(d_slots, batches, W + n_timed + i)
+            torch.cuda.synchronize()
+        extras["variants"] = variants
+        # the other stated configurations
+        configs = {}
+        for name in ("full_refresh", "sparse"):
+            pair = [make_workload(name, 0), make_workload(name, 1)]
+            p = DevicePlanner(pair[0].layout, local)
+            tensors = upload(torch, dev, pair)
+            configs[name] = leg(pair, tensors, p=p)
+            configs[name]["slot_ids_per_step"] = pair[0].n_idx
+            p.close()
+            del tensors
+        extras["configs"] = configs
+        extras["feedback"] = feedback_leg(torch, dev, stream, cpu=not args.no_cpu)
+        try:
+            extras["prefetch"] = prefetch_leg(torch, dev)
+        except Exception as exc:                        # the headline must not die with a side measurement
+            extras["prefetch"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+
+    # ---- end to end through the host-buffer call: pinned ids -> device -> plan -> ranges on the host ----
+    out_host = np.empty(1 << 16, dtype=capi.RANGE_DTYPE)
+
+    def host_loop(tensors, steps):
+        last = 0
+        for i in range(2):
+            planner.step_host(tensors[i % 2].numpy(), batches[i % 2].group_off, batches[i % 2].budget_blocks,
+                              base, out=out_host)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            b = batches[i % 2]
+            _, res = planner.step_host(tensors[i % 2].numpy(), b.group_off, b.budget_blocks, base, out=out_host)
+            last = res.n_ranges
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / steps, last
+
+    e2e_s, e2e_ranges = host_loop(h_slots, max(K, 10))
+    plan = out_host[:e2e_ranges].copy()      # the last timed plan, compared across ranks below
+    # the same call on the engine's own 32-bit ids: half the bytes over the host link
+    h32 = [torch.from_numpy(b.slots.astype(np.int32)).pin_memory() for b in batches]
+    e2e32_s, _ = host_loop(h32, max(K, 10))
+    del h32
+    # ceiling of the host-buffer call: every rank doing nothing but its pinned copy
+    stage = torch.empty_like(d_slots[0])
+    for i in range(2):
+        stage.copy_(h_slots[i], non_blocking=True)
+    barrier()
+    t0 = time.perf_counter()
+    n_copy = 10
+    for i in range(n_copy):
+        stage.copy_(h_slots[i % 2], non_blocking=True)
+    torch.cuda.synchronize()
+    copy_s = (time.perf_counter() - t0) / n_copy
+    del stage
+    host_loop(h_slots, 2)                    # back to the main pair's resident state
+    clocks = sampler.stop() if sampler else None
+
+    ms_per_step, tp_ms_per_step, e2e_ms, e2e32_ms, copy_ms = ranks.max_over_ranks(
+        [total_ms / n_timed, tp_ms / tp_n, e2e_s * 1e3, e2e32_s * 1e3, copy_s * 1e3])
+    # every rank planned from the same slot table: the plans must agree
+    # (dst names the rank's own GPU; the rest must agree)
+    plans_agree = ranks.same_everywhere(b"".join(plan[k].tobytes() for k in ("buffer", "offset", "bytes")))
+
+    if rank == 0:
+        peaks_path = ROOT / "MEASURED_PEAKS.json"
+        if peaks_path.exists():
+            peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured"
+        else:
+            peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+        bytes_step = algorithmic_bytes(batches[0], n_ranges)
+        achieved = bytes_step / (ms_per_step * 1e-3) / 1e9
+        tp_bytes = algorithmic_bytes(tp_pair[0], tp_ranges)
+        line = {
+            "metric": METRIC, "value": ms_per_step * 1e3, "unit": UNIT, "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+            "config": workload_config(batches[0], args),
+            "timed_steps": n_timed, "timed_region_ms": ms_per_step * n_timed,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak,
+                         "traffic": PROFILED_TRAFFIC_BYTES.get((args.workload, bool(args.tma))),
+                         "peak_source": peak_src, "algorithmic_bytes_per_launch": bytes_step,
+                         "launch_ms": ms_per_step,
+                         "kernel": "scan_plan_tma_kernel" if args.tma else "scan_plan_kernel"},
+            "e2e": {"value": e2e_ms * 1e3, "unit": UNIT,
+                    "h2d_bytes_per_step": 8 * batches[0].n_idx,
+                    "d2h_bytes_per_step": 24 * e2e_ranges + 64,
+                    "int32_ids_us": e2e32_ms * 1e3, "int32_h2d_bytes_per_step": 4 * batches[0].n_idx,
+                    "h2d_copy_only_us": copy_ms * 1e3,
+                    "frac_of_h2d_ceiling": copy_ms / e2e_ms,
+                    "limiter": "the pinned host -> device copy of the slot ids (PCIe and, with several "
+                               "ranks, the one host NUMA node all GPUs copy from)"},
+            "gpu_launches": n_timed,
+            "clocks": clocks,
+            "slot_scan_gbs_aggregate": world * achieved,
+            "plans_per_s_aggregate": world / (ms_per_step * 1e-3),
+            "ranges_per_step": n_ranges,
+            "plans_agree_across_ranks": plans_agree,
+            "tp_shard_us": tp_ms_per_step * 1e3,
+            "tp_shard": {"us_per_step": tp_ms_per_step * 1e3, "steps": tp_n, "ranges_per_step": tp_ranges,
+                         "slot_ids_per_step": tp_pair[0].n_idx,
+                         "gbs": tp_bytes / (tp_ms_per_step * 1e-3) / 1e9,
+                         "frac": tp_bytes / (tp_ms_per_step * 1e-3) / 1e9 / peak,
+                         "workload": "48 layers, one KV head per rank (256 B slots), 262,144-slot pool, "
+                                     "256 requests; every rank plans its own shard"},
+        }
+        for name, cfg in extras.get("configs", {}).items():
+            cfg["frac"] = cfg["gbs"] / peak
+        line.update(extras)
+        line.update(cpu_lines)
+        emit(line)
+    tp_planner.close()
+    planner.close()
+    ranks.stop()
+
+
+# --------------------------------------------------------------------------
+# event-driven path alone
+# --------------------------------------------------------------------------
+def run_feedback(args):
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; retarget_b200 has no CPU path to fall back to")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    sampler = ClockSampler(0)
+    got = feedback_leg(torch, dev, stream, steps=args.steps, warm=max(args.warmup, 3), cpu=not args.no_cpu)
+    line = {"metric": "feedback_plan_us_per_decode_step", "value": got["us_per_step"], "unit": UNIT, "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": got["us_per_step"] / 1e3,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
+            "data": "synthetic", "config": {"workload": got["workload"]}, "feedback": got,
+            "clocks": sampler.stop()}
+    emit(line)
 
 
 # Libraries under us (NCCL's version banner, for one) write to stdout.  The
@@ -638,10 +798,13 @@ def main():
                     help="how the timed launches are issued: CUDA graph replays or one by one")
     ap.add_argument("--unchained", action="store_true",
                     help="launch every step fully serialised after the one before it (no RT_PLAN_CHAINED)")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-variants", action="store_true", help="skip the secondary measurements")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--no-extras", "--no-variants", dest="no_extras", action="store_true",
+                    help="skip the secondary measurements (variants, configs, feedback, prefetch)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "ours":
+        args.warmup = max(args.warmup, 3)
+        args.steps = max(args.steps, 2)
     quiet_stdout()
     if args.workload == "feedback":
         run_feedback(args)

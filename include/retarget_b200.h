@@ -607,6 +607,23 @@ int rt_paged_read(const void *const *d_buffers, uint32_t n_buffers, uint32_t byt
                   const int64_t *d_slots, uint64_t n_slots, uint64_t capacity_slots,
                   uint64_t *d_sums, void *stream);
 
+/* Synthetic paged bf16 decode attention: for every request r and every layer,
+ * out = softmax(q . K^T / sqrt(128)) . V over the K and V rows of the request's
+ * slots d_slots[d_req_off[r] .. d_req_off[r+1]) (slot 0 and ids outside
+ * 1..capacity_slots are skipped).  A layer's K and V buffers are
+ * [pool_slots][n_kv_heads][128] bf16 (n_kv_heads <= 8); d_q is
+ * [n_requests][n_layers][n_kv_heads][128] bf16, d_out the same shape in fp32
+ * (bf16 inputs, fp32 accumulation).  d_k_buffers / d_v_buffers are DEVICE arrays
+ * of n_layers base pointers; d_slots and d_req_off are device arrays.
+ * No reference counterpart: it stands in for the serving engine's decode
+ * attention in the end-to-end prefetch experiment, where the point is that real
+ * arithmetic waits for the KV pages a plan did or did not bring in.  Runs on
+ * the current device, asynchronously on `stream` (NULL: legacy default stream). */
+int rt_paged_attention(const void *const *d_k_buffers, const void *const *d_v_buffers, uint32_t n_layers,
+                       uint32_t n_kv_heads, const void *d_q, const int64_t *d_slots,
+                       const int64_t *d_req_off, uint32_t n_requests, uint64_t capacity_slots,
+                       float *d_out, void *stream);
+
 /* ------------------------------------------------------------------ */
 /* UVM control server + prefetch executor (process-wide singleton)      */
 /* ------------------------------------------------------------------ */

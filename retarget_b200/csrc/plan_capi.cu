@@ -110,16 +110,20 @@ void next_scratch(rt_plan *pl, rt::PlanArgs &p) {
 
 // CSR work-unit table.  Every group gets at least one unit so that its tail
 // runs even when it has no ids this step.
-// ids of one 16-byte load and of one 16 KiB work unit, by id width
+// ids of one 16-byte load, by id width, and of one work unit: 4 KiB (a vector
+// per thread) for the register-staged kernel, 16 KiB (one staging buffer) for
+// the bulk-copy kernel
 inline long long ids_per_vec(bool ids32) { return ids32 ? 4 : 2; }
-inline long long ids_per_unit(bool ids32) { return ids32 ? 2 * rt::kChunkElems : rt::kChunkElems; }
+inline long long ids_per_unit(bool ids32, bool tma) {
+    return tma ? rt::kChunkElems : rt::kScanThreads * ids_per_vec(ids32);
+}
 
 int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const void *d_slots,
-                       const int64_t *group_off, bool ids32) {
+                       const int64_t *group_off, bool ids32, bool tma = false) {
     const uint32_t G = pl->layout.n_groups;
     // int32 ids: a negative id must never look like a valid large one
     if (ids32 && pl->layout.capacity_slots > 0x7fffffffull) return RT_ERR_INVALID_ARGUMENT;
-    const long long per_vec = ids_per_vec(ids32), per_unit = ids_per_unit(ids32);
+    const long long per_vec = ids_per_vec(ids32), per_unit = ids_per_unit(ids32, tma);
     a.slots = reinterpret_cast<const long long *>(d_slots);
     a.lens = nullptr;
     a.stride = 0;
@@ -335,7 +339,8 @@ int step_device_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t
     if (!d_slots && group_off[pl->layout.n_groups] > 0) return RT_ERR_INVALID_ARGUMENT;
     DeviceGuard guard(pl->device);
     rt::ScanArgs a;
-    int st = fill_scan_args_csr(pl, a, d_slots, group_off, ids32);
+    const bool tma = !ids32 && want_tma(flags);      // the bulk-copy kernel reads int64 ids only
+    int st = fill_scan_args_csr(pl, a, d_slots, group_off, ids32, tma);
     if (st != RT_OK) return st;
     rt::PlanArgs p;
     fill_plan_args(pl, p, budget, flags, out, cap, result);
@@ -343,7 +348,6 @@ int step_device_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t
     next_scratch(pl, p);
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
     const bool chained = (flags & RT_PLAN_CHAINED) != 0;
-    bool tma = !ids32 && want_tma(flags);      // the bulk-copy kernel reads int64 ids only
     int grid = grid_for(pl, a.n_units, tma);
     RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s, chained)
                 : rt::launch_scan_plan(a, p, false, ids32, grid, s, chained));
@@ -391,14 +395,16 @@ int step_table_impl(rt_plan *pl, const void *d_table, bool ids32, const int32_t 
     a.lens = d_lens;
     a.stride = (long long)stride;
     if (stride > (1ull << 40)) return RT_ERR_INVALID_ARGUMENT;
-    // Work is dealt by row segment.  One segment per row is best when there are
-    // several rows for every CTA; a table of few, long rows is cut into segments
-    // of at least 4096 ids so that every CTA still gets a share.
+    // Work is dealt by row segment: to warps (8 per CTA) when rows are long enough
+    // for a warp each, else to CTAs.  Rows are cut into segments of at least 1024
+    // ids until there are about four segments per worker, so that the last round
+    // of the round-robin leaves few workers idle.
     const unsigned long long ctas = (unsigned long long)pl->sm_count * pl->table_blocks_per_sm;   // one wave
+    const unsigned long long workers = stride >= 1024 ? ctas * (rt::kScanThreads / 32) : ctas;
     unsigned long long segs = 1;
-    if (n_rows < 4 * ctas) {
-        segs = (4 * ctas + n_rows - 1) / n_rows;
-        const unsigned long long most = (stride + 4095) / 4096;
+    if (n_rows < 4 * workers) {
+        segs = (4 * workers + n_rows - 1) / n_rows;
+        const unsigned long long most = stride / 1024 ? stride / 1024 : 1;
         if (segs > most) segs = most;
     }
     unsigned long long seg_ids = (stride + segs - 1) / segs;

@@ -84,6 +84,12 @@ template <> struct IdTraits<int> {
 template <typename Id>
 constexpr int kChunkIds = kScanThreads * IdTraits<Id>::kPer * kUnroll;
 static_assert(kChunkIds<long long> == kChunkElems, "unit size mismatch");
+// The register-staged kernel deals out work in units of ONE vector per thread
+// (4 KiB), a quarter of what it loads at a time: with a few hundred CTAs and a
+// few thousand 16 KiB chunks per launch, whole chunks would leave some CTAs a
+// chunk short of the others for the last microsecond and a half of the launch.
+template <typename Id>
+constexpr int kSubIds = kScanThreads * IdTraits<Id>::kPer;
 template <typename Id>
 constexpr uint32_t kAllIdsOf = (1u << (IdTraits<Id>::kPer * kUnroll)) - 1u;
 constexpr uint32_t kAllIds = kAllIdsOf<long long>;
@@ -220,8 +226,10 @@ struct GroupSpan {
     long long e0;            // even start index of unit q_lo
 };
 
+// `unit_ids`: ids per work unit, the granularity the host counted units in.
 template <typename Id = long long>
-__device__ __forceinline__ GroupSpan group_span(const ScanArgs &a, uint32_t g, int q_begin, int q_end) {
+__device__ __forceinline__ GroupSpan group_span(const ScanArgs &a, uint32_t g, int q_begin, int q_end,
+                                                int unit_ids = kChunkIds<Id>) {
     GroupSpan s;
     const int uf = a.unit_first[g], ul = a.unit_first[g + 1];
     s.q_lo = q_begin > uf ? q_begin : uf;
@@ -229,7 +237,7 @@ __device__ __forceinline__ GroupSpan group_span(const ScanArgs &a, uint32_t g, i
     s.units_in_group = ul - uf;
     s.lo = a.group_off[g];
     s.hi = a.group_off[g + 1];
-    s.e0 = (s.lo & ~(long long)(IdTraits<Id>::kPer - 1)) + (long long)(s.q_lo - uf) * kChunkIds<Id>;
+    s.e0 = (s.lo & ~(long long)(IdTraits<Id>::kPer - 1)) + (long long)(s.q_lo - uf) * unit_ids;
     return s;
 }
 
@@ -331,10 +339,10 @@ __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, Ha
 // --------------------------------------------------------------------------
 // kernel: CSR input, plain 128-bit loads, register double buffering
 // --------------------------------------------------------------------------
-// Every CTA owns one contiguous span of work units, walks it bitmap by bitmap,
-// keeps its shared block map across the units of a bitmap and hands over once
-// per (CTA, bitmap).  Inside a bitmap the next unit's loads are issued before
-// the current unit is marked.
+// Every CTA owns one contiguous span of work units (4 KiB each), walks it bitmap
+// by bitmap, keeps its shared block map across a bitmap's part of the span and
+// hands over once per (CTA, bitmap).  Inside a bitmap it streams 16 KiB chunks;
+// the next chunk's loads are issued before the current chunk is marked.
 #ifdef RT_MIN_CTAS
 #define RT_SCAN_BOUNDS __launch_bounds__(kScanThreads, RT_MIN_CTAS)
 #else
@@ -357,21 +365,23 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
     clear_map(s_map);
     __syncthreads();
     for (uint32_t g = first_group(a, q_begin);; ++g) {
-        const GroupSpan sp = group_span<Id>(a, g, q_begin, q_end);
-        int q = sp.q_lo;
+        const GroupSpan sp = group_span<Id>(a, g, q_begin, q_end, kSubIds<Id>);
+        // this CTA's part of the bitmap's ids: [begin, end), read from the 16-byte
+        // aligned index e0 <= begin on
         long long e0 = sp.e0;
+        const long long span_end = sp.e0 + (long long)(sp.q_hi - sp.q_lo) * kSubIds<Id>;
+        const long long begin = e0 > sp.lo ? e0 : sp.lo, end = span_end < sp.hi ? span_end : sp.hi;
         const Id *mine = slots + e0 + kPer * (int)threadIdx.x;
-        // ragged first unit of the bitmap (start index not on a 16-byte boundary)
-        if (q < sp.q_hi && e0 < sp.lo) {
+        // ragged first chunk of the bitmap (its first id is not on a 16-byte boundary)
+        if (e0 < begin && begin < end) {
             Chunk<Id> ch;
-            load_chunk<Id>(mine, e0, sp.lo, sp.hi, ch);
+            load_chunk<Id>(mine, e0, begin, end, ch);
             mark_chunk<kPow2, Id>(ch, a, s_map, c);
-            ++q; e0 += kChunk; mine += kChunk;
+            e0 += kChunk; mine += kChunk;
         }
-        // whole units: two register sets alternate, so the loads of one unit are
+        // whole chunks: two register sets alternate, so the loads of one chunk are
         // in flight while the other is marked, with no copies between them
-        int n_whole = (int)((sp.hi - e0) / kChunk);
-        if (n_whole > sp.q_hi - q) n_whole = sp.q_hi - q;
+        const int n_whole = end > e0 ? (int)((end - e0) / kChunk) : 0;
         if (n_whole > 0) {
             Vec va[kUnroll], vb[kUnroll];
 #pragma unroll
@@ -396,13 +406,12 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
                 mark_full<kPow2>(va, a, s_map, c);
                 mine += kChunk;
             }
-            q += n_whole;
             e0 += (long long)n_whole * kChunk;
         }
-        // ragged last unit
-        if (q < sp.q_hi) {
+        // what is left of the part: less than a chunk
+        if (e0 < end) {
             Chunk<Id> ch;
-            load_chunk<Id>(mine, e0, sp.lo, sp.hi, ch);
+            load_chunk<Id>(mine, e0, begin, end, ch);
             mark_chunk<kPow2, Id>(ch, a, s_map, c);
         }
         leave_group<0>(p, g, s_map, c);
@@ -416,15 +425,24 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
 // --------------------------------------------------------------------------
 // Row r holds lens[r] valid ids at table[r * stride ..]; the rest of the row is
 // padding that is never read.  Work is dealt by ROW SEGMENT (seg_ids ids of one
-// row; one segment per row unless the table has few, long rows), round-robin
-// over the CTAs.  A CTA first turns its segments into a list of 16-byte vectors:
-// per segment the first vector and the number of vectors that hold valid ids,
-// with an exclusive prefix sum over the list in shared memory.  It then streams
-// the flattened vector list exactly like the CSR kernel streams a span -- 256
-// threads x kUnroll independent 128-bit loads, the next batch in flight while
-// this one is marked -- so short rows (2176 ids = 8.5 KiB) cost no idle lanes
-// and no dependent load per row.  All ids feed bitmap 0.
+// row).  All ids feed bitmap 0.  Two ways to walk the segments, chosen by the
+// host from the segment length:
+//
+//   kWarpSegs   segments of a few hundred ids or more (the serving engine's
+//               request rows): one WARP per segment, segments dealt round-robin
+//               over all warps of the grid.  A lane takes every 32nd 16-byte
+//               vector, kUnroll of them in flight with the next kUnroll issued
+//               before these are marked; the next segment's length is fetched
+//               while this one streams, so no dependent load sits between rows.
+//   otherwise   short rows: segments are dealt round-robin over the CTAs.  A CTA
+//               first turns its segments into a list of 16-byte vectors (per
+//               segment the number of vectors that hold valid ids, exclusive
+//               prefix sum in shared memory) and streams the flattened list --
+//               256 threads x kUnroll loads per batch, each thread finding its
+//               vector's segment with a cursor that only moves forward -- so
+//               rows of a few ids still fill every lane.
 constexpr int kSegsPerPass = 1024;
+constexpr int kWarpSegVectors = 64;     // shortest segment (in 16-byte vectors) that gets a warp of its own
 
 struct TableSeg {
     long long lo, hi;        // valid ids of the segment: flat indices [lo, hi)
@@ -472,20 +490,125 @@ __device__ __forceinline__ void fetch_table_batch(const Id *slots, const TableSh
     }
 }
 
-template <bool kPow2, typename Id>
+// Valid ids [lo, hi) of segment v (flat indices into the table).
+__device__ __forceinline__ void table_segment(const ScanArgs &a, unsigned long long v, long long len,
+                                              long long &lo, long long &hi) {
+    const uint32_t row = (uint32_t)(a.segs_per_row == 1 ? v : v / a.segs_per_row);
+    const uint32_t seg = (uint32_t)(v - (unsigned long long)row * a.segs_per_row);
+    if (len < 0) len = 0;
+    if (len > a.stride) len = a.stride;
+    const long long row_lo = (long long)row * a.stride;
+    lo = row_lo + (long long)seg * a.seg_ids;
+    hi = lo + a.seg_ids;
+    if (hi > row_lo + len) hi = row_lo + len;
+    if (hi < lo) hi = lo;
+}
+
+// A warp's walk over its segments (kWarpSegs).  The segments of a warp, laid end
+// to end, form one sequence of 16-byte vectors; lane l takes vectors l, l + 32,
+// ... of that sequence, so every batch of 32 * kUnroll vectors is full whatever
+// the segment lengths are.  Each lane keeps its own cursor (all lanes walk the
+// same segments, a few vectors apart); the length of the segment after the
+// current one is always already on its way.
+struct SegCursor {
+    unsigned long long v;        // current segment
+    unsigned long long first;    // index of its first vector in the warp's sequence
+    long long lo, hi, i0;        // its valid ids [lo, hi); its first vector starts at flat index i0
+    long long n_vec;             // vectors in it
+    long long len_next;          // valid ids of the row of segment v + n_warps
+    bool done;
+};
+
+template <typename Id>
+__device__ __forceinline__ void enter_segment(const ScanArgs &a, unsigned long long n_virtual,
+                                              unsigned long long n_warps, SegCursor &c) {
+    constexpr int kPer = IdTraits<Id>::kPer;
+    table_segment(a, c.v, c.len_next, c.lo, c.hi);
+    c.i0 = c.lo & ~(long long)(kPer - 1);
+    c.n_vec = c.hi > c.lo ? (c.hi - c.i0 + kPer - 1) / kPer : 0;
+    const unsigned long long nv = c.v + n_warps;
+    c.len_next = nv < n_virtual ? (long long)__ldg(a.lens + (a.segs_per_row == 1 ? nv : nv / a.segs_per_row)) : 0;
+}
+
+// Vectors base + lane + 32 u (u < kUnroll) of the warp's sequence.
+template <typename Id>
+__device__ __forceinline__ void fetch_warp_batch(const Id *slots, const ScanArgs &a, unsigned long long n_virtual,
+                                                 unsigned long long n_warps, unsigned long long base,
+                                                 uint32_t lane, SegCursor &c, Chunk<Id> &ch) {
+    using Vec = typename IdTraits<Id>::Vec;
+    constexpr int kPer = IdTraits<Id>::kPer;
+    constexpr uint32_t kWhole = (1u << kPer) - 1u;
+    ch.mask = 0;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        const unsigned long long vi = base + lane + 32u * (unsigned)u;
+        while (!c.done && vi >= c.first + (unsigned long long)c.n_vec) {
+            c.first += (unsigned long long)c.n_vec;
+            c.v += n_warps;
+            if (c.v >= n_virtual) c.done = true;
+            else enter_segment<Id>(a, n_virtual, n_warps, c);
+        }
+        if (c.done) continue;
+        const long long at = c.i0 + (long long)(vi - c.first) * kPer;
+        if (at >= c.lo && at + kPer <= c.hi) {
+            ch.v[u] = RT_LOAD(reinterpret_cast<const Vec *>(slots + at));
+            ch.mask |= kWhole << (kPer * u);
+        } else {
+            // first or last vector of a segment: only the ids inside it are read
+#pragma unroll
+            for (int k = 0; k < kPer; ++k) {
+                Id x = 0;
+                if (at + k >= c.lo && at + k < c.hi) {
+                    x = RT_LOAD(slots + at + k);
+                    ch.mask |= 1u << (kPer * u + k);
+                }
+                vec_set(ch.v[u], k, x);
+            }
+        }
+    }
+}
+
+template <bool kPow2, typename Id, bool kWarpSegs>
 __global__ void __launch_bounds__(kScanThreads, 4)
 scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
     constexpr int kPer = IdTraits<Id>::kPer;
     extern __shared__ __align__(16) unsigned char tail_mem[];
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
-    __shared__ TableShared sh;
     const Id *slots = reinterpret_cast<const Id *>(a.slots);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     ScanCounters c = {0, 0};
     clear_map(s_map);
-    // this CTA's segments: blockIdx.x, blockIdx.x + gridDim.x, ...
     const unsigned long long n_virtual = (unsigned long long)a.n_rows * a.segs_per_row;
+    if (kWarpSegs) {
+        __syncthreads();                         // the map is clear before any warp marks
+        // this warp's segments: its global index, then every n_warps-th
+        const unsigned long long n_warps = (unsigned long long)gridDim.x * (kScanThreads / 32);
+        SegCursor cur;
+        cur.v = (unsigned long long)blockIdx.x * (kScanThreads / 32) + warp;
+        cur.first = 0;
+        cur.done = cur.v >= n_virtual;
+        cur.lo = cur.hi = cur.i0 = cur.n_vec = 0;
+        cur.len_next = cur.done ? 0 : (long long)__ldg(a.lens + (a.segs_per_row == 1 ? cur.v : cur.v / a.segs_per_row));
+        if (!cur.done) enter_segment<Id>(a, n_virtual, n_warps, cur);
+        constexpr unsigned long long kWarpBatch = 32ull * kUnroll;
+        Chunk<Id> now, nxt;
+        unsigned long long base = 0;
+        fetch_warp_batch<Id>(slots, a, n_virtual, n_warps, base, lane, cur, now);
+        // the next batch is in flight while this one is marked; a batch that is
+        // empty in every lane is past the warp's last vector
+        while (__any_sync(0xffffffffu, now.mask != 0)) {
+            base += kWarpBatch;
+            fetch_warp_batch<Id>(slots, a, n_virtual, n_warps, base, lane, cur, nxt);
+            if (now.mask) mark_chunk<kPow2, Id>(now, a, s_map, c);
+            now = nxt;
+        }
+        leave_group<0>(p, 0, s_map, c);
+        finish_cta<0>(p, 1u, hs, tail_mem);
+        return;
+    }
+    __shared__ TableShared sh;
+    // this CTA's segments: blockIdx.x, blockIdx.x + gridDim.x, ...
     const unsigned long long mine =
         n_virtual > blockIdx.x ? (n_virtual - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     for (unsigned long long pass = 0; pass < mine; pass += kSegsPerPass) {
@@ -499,14 +622,8 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
             cnt[e] = 0;
             if (k < n_segs) {
                 const unsigned long long v = blockIdx.x + (pass + k) * gridDim.x;
-                const uint32_t row = (uint32_t)(v / a.segs_per_row), seg = (uint32_t)(v - (unsigned long long)row * a.segs_per_row);
-                long long len = __ldg(a.lens + row);
-                if (len < 0) len = 0;
-                if (len > a.stride) len = a.stride;
-                const long long row_lo = (long long)row * a.stride;
-                long long lo = row_lo + (long long)seg * a.seg_ids, hi = lo + a.seg_ids;
-                if (hi > row_lo + len) hi = row_lo + len;
-                if (hi < lo) hi = lo;
+                long long lo, hi;
+                table_segment(a, v, (long long)__ldg(a.lens + (a.segs_per_row == 1 ? v : v / a.segs_per_row)), lo, hi);
                 const long long v0 = lo / kPer, v1 = (hi + kPer - 1) / kPer;
                 sh.seg[k].lo = lo;
                 sh.seg[k].hi = hi;
@@ -798,11 +915,14 @@ cudaError_t launch_scan_plan(const ScanArgs &a, const PlanArgs &p, bool table, b
     const bool pow2 = a.shift >= 0;
     const size_t smem = tail_smem_bytes(p.n_groups, p.n_buffers);
     if (table) {
-        if (ids32)
-            return pow2 ? launch_scan(scan_table_kernel<true, int>, grid, kScanThreads, smem, stream, chained, a, p)
-                        : launch_scan(scan_table_kernel<false, int>, grid, kScanThreads, smem, stream, chained, a, p);
-        return pow2 ? launch_scan(scan_table_kernel<true, long long>, grid, kScanThreads, smem, stream, chained, a, p)
-                    : launch_scan(scan_table_kernel<false, long long>, grid, kScanThreads, smem, stream, chained, a, p);
+        // one warp per segment when a segment holds at least kWarpSegVectors 16-byte vectors
+        const bool warps = a.seg_ids / (ids32 ? 4 : 2) >= kWarpSegVectors;
+#define RT_TABLE(P, T)                                                                                        \
+    (warps ? launch_scan(scan_table_kernel<P, T, true>, grid, kScanThreads, smem, stream, chained, a, p)      \
+           : launch_scan(scan_table_kernel<P, T, false>, grid, kScanThreads, smem, stream, chained, a, p))
+        if (ids32) return pow2 ? RT_TABLE(true, int) : RT_TABLE(false, int);
+        return pow2 ? RT_TABLE(true, long long) : RT_TABLE(false, long long);
+#undef RT_TABLE
     }
     if (ids32)
         return pow2 ? launch_scan(scan_plan_kernel<true, int>, grid, kScanThreads, smem, stream, chained, a, p)
@@ -846,16 +966,21 @@ cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plai
     RT_SET_SMEM((scan_plan_kernel<false, long long>), tail_max)
     RT_SET_SMEM((scan_plan_kernel<true, int>), tail_max)
     RT_SET_SMEM((scan_plan_kernel<false, int>), tail_max)
-    RT_SET_SMEM((scan_table_kernel<true, long long>), tail_max)
-    RT_SET_SMEM((scan_table_kernel<false, long long>), tail_max)
-    RT_SET_SMEM((scan_table_kernel<true, int>), tail_max)
-    RT_SET_SMEM((scan_table_kernel<false, int>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<true, long long, true>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<false, long long, true>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<true, int, true>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<false, int, true>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<true, long long, false>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<false, long long, false>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<true, int, false>), tail_max)
+    RT_SET_SMEM((scan_table_kernel<false, int, false>), tail_max)
     RT_SET_SMEM(plan_tail_kernel, tail_max)
 #undef RT_SET_SMEM
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(plain_blocks_per_sm, scan_plan_kernel<true, long long>,
                                                       kScanThreads, tail);
     if (e != cudaSuccess) return e;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(table_blocks_per_sm, scan_table_kernel<true, int>,
+    // (the list-building form has the larger footprint of the two)
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(table_blocks_per_sm, scan_table_kernel<true, int, false>,
                                                       kScanThreads, tail);
     if (e != cudaSuccess) return e;
     return cudaOccupancyMaxActiveBlocksPerMultiprocessor(tma_blocks_per_sm, scan_plan_tma_kernel<true>,
