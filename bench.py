@@ -32,6 +32,11 @@ The JSON line (rank 0) carries every term of the metric:
              one tensor-parallel shard): us, GB/s, fraction of the peak
 `tp_shard_us`  (every N) the tensor-parallel shard configuration per rank
 
+--workload e2e_prefetch  the end-to-end loop on managed memory: every decode step
+             plans from that step's slot table, hands the ranges to the prefetch
+             executor and runs a paged decode-attention reader; with the plan,
+             with evictions only, and with everything resident
+
 --impl reference  times the CPU restatement of the reference's Python path on
              the host cores: every step runs all layers, one process per core
 """
@@ -763,6 +768,224 @@ def run_feedback(args):
     emit(line)
 
 
+# --------------------------------------------------------------------------
+# end to end: plan -> prefetch -> paged decode attention, every decode step
+# --------------------------------------------------------------------------
+def run_e2e_prefetch(args):
+    """--workload e2e_prefetch: the oversubscribed end-to-end configuration at the
+    largest size that is safe on a shared host.
+
+    K and V of every layer live in managed memory registered with the in-process
+    UVM server; a managed ballast (co-resident training tensors) is touched every
+    step.  An incremental decode trace runs for `--steps` steps.  Each step, arm
+    by arm:
+
+      plan         the device planner turns THAT step's slot table into ranges
+                   (evictions first), rt_uvm_submit_ranges hands them to the
+                   executor on its side streams, then the attention reader runs
+      no_prefetch  the same evictions are executed (same residency pressure) but
+                   nothing is brought in ahead: the reader's first touch of a new
+                   block faults it in
+      resident     everything on the GPU, no plan: the floor of the reader
+
+    The footprint is scaled down (the full 160 GiB + 20 GiB would need as much
+    host memory again on a machine shared with other jobs): a GPU share limit is
+    emulated by the plan's own evictions instead of by real oversubscription, and
+    pages are handed out in address order so that the live set is a region a
+    bounded plan can follow.  UVM fault counts: unavailable (CUPTI's
+    unified-memory counters cannot be enabled with this toolkit and driver)."""
+    import torch
+    from cuda.bindings import driver as cu
+    from cuda.bindings import runtime as cudart
+    from retarget_b200 import capi, workloads
+    from retarget_b200.control import LocalUvm
+    from retarget_b200.planner import DevicePlanner, ranges_from_tensor, result_from_tensor
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; retarget_b200 has no CPU path to fall back to")
+    K, W = max(args.steps, 64), max(args.warmup, 3)
+    lib = capi.lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    torch.zeros(1, device=dev)
+    err, concurrent = cudart.cudaDeviceGetAttribute(cudart.cudaDeviceAttr.cudaDevAttrConcurrentManagedAccess, 0)
+    if int(err) != 0 or not concurrent:
+        emit({"metric": "e2e_decode_step_ms", "unavailable": "device has no concurrent managed access"})
+        return
+    # ---- sizes: at most a quarter of the host memory that is available right now ----
+    layers, heads, bytes_per_slot = 40, 8, 2048
+    avail = 0
+    for text in Path("/proc/meminfo").read_text().splitlines():
+        if text.startswith("MemAvailable:"):
+            avail = int(text.split()[1]) * 1024
+    pool_slots = 131072                                       # 256 MiB per buffer, 20 GiB of K + V
+    while pool_slots > 8192 and 2 * layers * pool_slots * bytes_per_slot * 1.1 > avail / 4:
+        pool_slots //= 2
+    alloc = pool_slots * bytes_per_slot
+    total = 2 * layers * alloc
+    ballast_bytes = max(64 * MIB, total // 8 // (2 * MIB) * (2 * MIB))     # 20 GiB : 160 GiB in the full configuration
+    layout = workloads.Layout(layers, bytes_per_slot, pool_slots)        # one bitmap for all buffers
+    budget = layout.n_blocks // 2
+    # requests sized so that the live set stays well inside the pool
+    median = max(256, pool_slots // 96)
+    trace = workloads.decode_trace(0, steps=W + K, pool_slots=pool_slots, arrival_rate=0.25, median=median,
+                                   mean_output=256, initial_requests=24, shuffle_pages=False)
+    err, ctx = cu.cuCtxGetCurrent()
+    ptrs = []
+    def release():
+        for q in ptrs:
+            lib.rt_uvm_unregister_ptr(q)
+            cudart.cudaFree(q)
+    for _ in range(2 * layers + 1):
+        size = alloc if len(ptrs) < 2 * layers else ballast_bytes
+        err, p = cudart.cudaMallocManaged(size, cudart.cudaMemAttachGlobal)
+        if int(err) != 0:
+            release()
+            emit({"metric": "e2e_decode_step_ms", "unavailable": f"cudaMallocManaged failed: {err}"})
+            return
+        ptrs.append(int(p))
+        cudart.cudaMemset(p, 0x3c if len(ptrs) % 2 else 0x3d, size)       # bf16 values near 0.01 / 0.05
+    torch.cuda.synchronize()
+    lib.rt_uvm_register.argtypes = [C.c_uint64, C.c_uint64, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_uint64)]
+    lib.rt_uvm_unregister_ptr.argtypes = [C.c_uint64]
+    lib.rt_uvm_submit_ranges.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.POINTER(C.c_uint64)]
+    lib.rt_uvm_wait.argtypes = [C.c_uint64, C.c_double, C.POINTER(C.c_int)]
+    lib.rt_paged_attention.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p,
+                                       C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p]
+    lib.rt_paged_read.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64,
+                                  C.c_void_p, C.c_void_p]
+    ids = []
+    for k, p in enumerate(ptrs):
+        i = C.c_uint64()
+        capi.check(lib.rt_uvm_register(p, alloc if k < 2 * layers else ballast_bytes, C.c_void_p(int(ctx)), 0, 1,
+                                       C.byref(i)), "rt_uvm_register")
+        ids.append(i.value)
+    kv_ids = (C.c_uint64 * (2 * layers))(*ids[:2 * layers])
+    uvm = LocalUvm()
+    cfg = UvmConfig(None, 64 * MIB, 1024 * MIB, 4, 0)
+    capi.check(lib.rt_uvm_start(C.byref(cfg)), "rt_uvm_start")
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    h = stream.cuda_stream
+    # yardstick for the prefetch rate
+    host = torch.empty(256 * MIB, dtype=torch.uint8).pin_memory()
+    devbuf = torch.empty(256 * MIB, dtype=torch.uint8, device=dev)
+    devbuf.copy_(host, non_blocking=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(4):
+        devbuf.copy_(host, non_blocking=True)
+    torch.cuda.synchronize()
+    h2d = 4 * 256 * MIB / (time.perf_counter() - t0) / 1e9
+    del host, devbuf
+    # device-side inputs of the reader
+    max_live = max(t.live for t in trace)
+    d_k = torch.tensor(ptrs[:layers], dtype=torch.int64, device=dev)             # K buffers first, then V
+    d_v = torch.tensor(ptrs[layers:2 * layers], dtype=torch.int64, device=dev)
+    q = (torch.randn(max_live, layers, heads, 128, device=dev) * 0.5).to(torch.bfloat16)
+    out = torch.zeros(max_live, layers, heads, 128, dtype=torch.float32, device=dev)
+    d_steps = [(torch.from_numpy(t.read_slots).to(dev), torch.from_numpy(t.req_off).to(dev), t.live) for t in trace]
+    d_ballast = torch.tensor([ptrs[-1]], dtype=torch.int64, device=dev)
+    ballast_rows = ballast_bytes // bytes_per_slot
+    touch = torch.arange(1, min(ballast_rows, 32768), dtype=torch.int64, device=dev)    # 64 MiB of the ballast
+    d_sum = torch.zeros(1, dtype=torch.int64, device=dev)
+    d_out = torch.zeros((1 << 14) * 24, dtype=torch.uint8, device=dev)
+    d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
+    planner = DevicePlanner(layout, 0)
+    sampler = ClockSampler(0)
+
+    def migrate(line):
+        reply = uvm.command(line)
+        assert reply.get("ok"), reply
+        uvm._wait_job(reply["job_id"], timeout=600, poll_seconds=0.0005)
+
+    def read(i):
+        slots, off, live = d_steps[i]
+        capi.check(lib.rt_paged_read(d_ballast.data_ptr(), 1, bytes_per_slot, touch.data_ptr(), touch.numel(),
+                                     ballast_rows - 1, d_sum.data_ptr(), h), "rt_paged_read")
+        capi.check(lib.rt_paged_attention(d_k.data_ptr(), d_v.data_ptr(), layers, heads, q.data_ptr(),
+                                          slots.data_ptr(), off.data_ptr(), live, layout.capacity,
+                                          out.data_ptr(), h), "rt_paged_attention")
+        stream.synchronize()
+
+    def arm(kind):
+        gen = uvm.status().allocation_generation
+        kv_total = 2 * layers * alloc
+        # start: K and V on the CPU (plan / no_prefetch) or everything on the GPU (resident)
+        migrate(f"targetv {gen} {kv_total + ballast_bytes if kind == 'resident' else 0}")
+        if kind != "resident":
+            migrate(f"prefetch {ids[-1]} 0 {ballast_bytes} gpu")
+        planner.set_resident([set()])
+        t_step = t_plan = t_move = t_read = 0.0
+        moved = to_gpu = 0
+        n_ranges = 0
+        for i in range(W + K):
+            slots, off, live = d_steps[i]
+            a = time.perf_counter()
+            b = c = a
+            if kind != "resident":
+                planner.step_device(slots, np.array([0, slots.numel()], np.int64), budget, capi.RT_PLAN_EVICT,
+                                    d_out, d_res, h)
+                stream.synchronize()
+                res = result_from_tensor(d_res)
+                if res["flags"]:
+                    raise SystemExit(f"bench.py: planner reported flags {res['flags']}")
+                ranges = ranges_from_tensor(d_out, res["n_ranges"])
+                if kind == "no_prefetch":
+                    ranges = ranges[:res["n_cpu_ranges"]]           # the evictions only
+                b = time.perf_counter()
+                if len(ranges):
+                    job, cuda_err = C.c_uint64(), C.c_int()
+                    keep = np.ascontiguousarray(ranges)
+                    capi.check(lib.rt_uvm_submit_ranges(keep.ctypes.data, len(keep), kv_ids, 2 * layers,
+                                                        C.byref(job)), "rt_uvm_submit_ranges")
+                    capi.check(lib.rt_uvm_wait(job.value, 600.0, C.byref(cuda_err)), "rt_uvm_wait")
+                    if cuda_err.value:
+                        raise SystemExit(f"bench.py: prefetch job failed with CUDA error {cuda_err.value}")
+                c = time.perf_counter()
+            read(i)
+            d = time.perf_counter()
+            if i >= W:
+                t_step += d - a; t_plan += b - a; t_move += c - b; t_read += d - c
+                if kind != "resident":
+                    n_ranges += len(ranges)
+                    moved += int(ranges["bytes"].sum())
+                    to_gpu += int(ranges["bytes"][ranges["dst"] >= 0].sum())
+        rec = {"step_ms": t_step / K * 1e3, "plan_ms": t_plan / K * 1e3, "prefetch_ms": t_move / K * 1e3,
+               "reader_ms": t_read / K * 1e3, "ranges_per_step": n_ranges / K,
+               "bytes_moved_per_step": moved / K, "bytes_to_gpu_per_step": to_gpu / K}
+        if kind == "plan" and t_move > 0:
+            rec["prefetch_gbs_while_moving"] = moved / t_move / 1e9
+            rec["prefetch_frac_of_link"] = moved / t_move / 1e9 / h2d
+        return rec
+
+    try:
+        arms = {kind: arm(kind) for kind in ("resident", "no_prefetch", "plan")}
+    finally:
+        capi.check(lib.rt_uvm_stop(), "rt_uvm_stop")
+        planner.close()
+        release()
+    live_slots = statistics.mean(int(s.numel()) for s, _, _ in d_steps[W:])
+    line = {"metric": "e2e_decode_step_ms", "value": arms["plan"]["step_ms"], "unit": "ms/step", "n_gpus": 1,
+            "steps": K, "warmup": W, "ms_per_step": arms["plan"]["step_ms"], "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 rows, fp32 accumulate (reader); int64 ids (plan)",
+            "data": "synthetic",
+            "config": {"workload": "incremental decode trace over managed K/V: plan -> prefetch -> paged decode "
+                                   "attention, every step", "layers": layers, "kv_buffers": 2 * layers,
+                       "alloc_bytes": alloc, "kv_bytes_total": total, "ballast_bytes": ballast_bytes,
+                       "pool_slots": pool_slots, "blocks_per_bitmap": layout.n_blocks, "budget_blocks": budget,
+                       "live_slots_mean": live_slots, "live_requests_max": max_live,
+                       "reader_bytes_per_step": live_slots * 2 * layers * bytes_per_slot,
+                       "host_memory_available_bytes": avail,
+                       "host_memory_margin": "K + V + ballast sized to at most a quarter of MemAvailable",
+                       "page_order": "address order (the live set is a moving region)"},
+            "arms": arms, "h2d_link_gbs": h2d,
+            "um_fault_counts": "unavailable: CUPTI's unified-memory counter activity cannot be enabled with this "
+                               "toolkit and driver",
+            "clocks": sampler.stop()}
+    emit(line)
+
+
 # Libraries under us (NCCL's version banner, for one) write to stdout.  The
 # result line must be the only thing there: everything else goes to stderr.
 _RESULT_FD = None
@@ -792,7 +1015,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="target",
-                    choices=["target", "steady", "fragmented", "sparse", "full_refresh", "tp_shard", "feedback"])
+                    choices=["target", "steady", "fragmented", "sparse", "full_refresh", "tp_shard", "feedback",
+                             "e2e_prefetch"])
     ap.add_argument("--tma", action="store_true", help="stage ids with bulk async copies (TMA)")
     ap.add_argument("--launch", default="graph", choices=["graph", "stream"],
                     help="how the timed launches are issued: CUDA graph replays or one by one")
@@ -808,6 +1032,8 @@ def main():
     quiet_stdout()
     if args.workload == "feedback":
         run_feedback(args)
+    elif args.workload == "e2e_prefetch":
+        run_e2e_prefetch(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

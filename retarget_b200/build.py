@@ -95,25 +95,6 @@ def build(force: bool = False, verbose: bool = False) -> dict:
             _run([nvcc(), "-shared", "-o", str(pre), *map(str, pre_objs), *map(str, objs),
                   "-cudart", "static", "-lpthread", "-ldl", "-lrt"])
         out["preload"] = pre
-    # optional: unified-memory counters through CUPTI, a library of its own
-    um_src = CSRC / "um_counters.cpp"
-    cuda_root = Path(nvcc()).resolve().parent.parent
-    cupti_dirs = [cuda_root / "targets" / "x86_64-linux" / "lib", cuda_root / "extras" / "CUPTI" / "lib64",
-                  cuda_root / "lib64"]
-    cupti_lib = next((d for d in cupti_dirs if (d / "libcupti.so").exists()), None)
-    cupti_inc = next((d for d in (cuda_root / "targets" / "x86_64-linux" / "include",
-                                  cuda_root / "extras" / "CUPTI" / "include", cuda_root / "include")
-                      if (d / "cupti.h").exists()), None)
-    if um_src.exists() and cupti_lib and cupti_inc:
-        um = PKG / "libretarget_umcount.so"
-        if force or _stale(um, [um_src]):
-            try:
-                _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", f"-I{cupti_inc}", f"-I{cuda_include()}",
-                      str(um_src), "-o", str(um), f"-L{cupti_lib}", "-lcupti", f"-Wl,-rpath,{cupti_lib}"])
-            except RuntimeError:
-                um = None                   # the experiment reports the counters as unavailable
-        if um:
-            out["umcount"] = um
     if verbose:
         print("".join(log))
     return out

@@ -110,20 +110,16 @@ void next_scratch(rt_plan *pl, rt::PlanArgs &p) {
 
 // CSR work-unit table.  Every group gets at least one unit so that its tail
 // runs even when it has no ids this step.
-// ids of one 16-byte load, by id width, and of one work unit: 4 KiB (a vector
-// per thread) for the register-staged kernel, 16 KiB (one staging buffer) for
-// the bulk-copy kernel
+// ids of one 16-byte load and of one 16 KiB work unit, by id width
 inline long long ids_per_vec(bool ids32) { return ids32 ? 4 : 2; }
-inline long long ids_per_unit(bool ids32, bool tma) {
-    return tma ? rt::kChunkElems : rt::kScanThreads * ids_per_vec(ids32);
-}
+inline long long ids_per_unit(bool ids32) { return ids32 ? 2 * rt::kChunkElems : rt::kChunkElems; }
 
 int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const void *d_slots,
-                       const int64_t *group_off, bool ids32, bool tma = false) {
+                       const int64_t *group_off, bool ids32) {
     const uint32_t G = pl->layout.n_groups;
     // int32 ids: a negative id must never look like a valid large one
     if (ids32 && pl->layout.capacity_slots > 0x7fffffffull) return RT_ERR_INVALID_ARGUMENT;
-    const long long per_vec = ids_per_vec(ids32), per_unit = ids_per_unit(ids32, tma);
+    const long long per_vec = ids_per_vec(ids32), per_unit = ids_per_unit(ids32);
     a.slots = reinterpret_cast<const long long *>(d_slots);
     a.lens = nullptr;
     a.stride = 0;
@@ -340,7 +336,7 @@ int step_device_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t
     DeviceGuard guard(pl->device);
     rt::ScanArgs a;
     const bool tma = !ids32 && want_tma(flags);      // the bulk-copy kernel reads int64 ids only
-    int st = fill_scan_args_csr(pl, a, d_slots, group_off, ids32, tma);
+    int st = fill_scan_args_csr(pl, a, d_slots, group_off, ids32);
     if (st != RT_OK) return st;
     rt::PlanArgs p;
     fill_plan_args(pl, p, budget, flags, out, cap, result);
@@ -394,7 +390,7 @@ int step_table_impl(rt_plan *pl, const void *d_table, bool ids32, const int32_t 
     a.slots = reinterpret_cast<const long long *>(d_table);
     a.lens = d_lens;
     a.stride = (long long)stride;
-    if (stride > (1ull << 40)) return RT_ERR_INVALID_ARGUMENT;
+    if (stride > (1ull << 40) || n_rows > 0x7fffffffu) return RT_ERR_INVALID_ARGUMENT;
     // Work is dealt by row segment: to warps (8 per CTA) when rows are long enough
     // for a warp each, else to CTAs.  Rows are cut into segments of at least 1024
     // ids until there are about four segments per worker, so that the last round

@@ -84,12 +84,6 @@ template <> struct IdTraits<int> {
 template <typename Id>
 constexpr int kChunkIds = kScanThreads * IdTraits<Id>::kPer * kUnroll;
 static_assert(kChunkIds<long long> == kChunkElems, "unit size mismatch");
-// The register-staged kernel deals out work in units of ONE vector per thread
-// (4 KiB), a quarter of what it loads at a time: with a few hundred CTAs and a
-// few thousand 16 KiB chunks per launch, whole chunks would leave some CTAs a
-// chunk short of the others for the last microsecond and a half of the launch.
-template <typename Id>
-constexpr int kSubIds = kScanThreads * IdTraits<Id>::kPer;
 template <typename Id>
 constexpr uint32_t kAllIdsOf = (1u << (IdTraits<Id>::kPer * kUnroll)) - 1u;
 constexpr uint32_t kAllIds = kAllIdsOf<long long>;
@@ -226,10 +220,8 @@ struct GroupSpan {
     long long e0;            // even start index of unit q_lo
 };
 
-// `unit_ids`: ids per work unit, the granularity the host counted units in.
 template <typename Id = long long>
-__device__ __forceinline__ GroupSpan group_span(const ScanArgs &a, uint32_t g, int q_begin, int q_end,
-                                                int unit_ids = kChunkIds<Id>) {
+__device__ __forceinline__ GroupSpan group_span(const ScanArgs &a, uint32_t g, int q_begin, int q_end) {
     GroupSpan s;
     const int uf = a.unit_first[g], ul = a.unit_first[g + 1];
     s.q_lo = q_begin > uf ? q_begin : uf;
@@ -237,7 +229,7 @@ __device__ __forceinline__ GroupSpan group_span(const ScanArgs &a, uint32_t g, i
     s.units_in_group = ul - uf;
     s.lo = a.group_off[g];
     s.hi = a.group_off[g + 1];
-    s.e0 = (s.lo & ~(long long)(IdTraits<Id>::kPer - 1)) + (long long)(s.q_lo - uf) * unit_ids;
+    s.e0 = (s.lo & ~(long long)(IdTraits<Id>::kPer - 1)) + (long long)(s.q_lo - uf) * kChunkIds<Id>;
     return s;
 }
 
@@ -339,10 +331,13 @@ __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, Ha
 // --------------------------------------------------------------------------
 // kernel: CSR input, plain 128-bit loads, register double buffering
 // --------------------------------------------------------------------------
-// Every CTA owns one contiguous span of work units (4 KiB each), walks it bitmap
-// by bitmap, keeps its shared block map across a bitmap's part of the span and
-// hands over once per (CTA, bitmap).  Inside a bitmap it streams 16 KiB chunks;
-// the next chunk's loads are issued before the current chunk is marked.
+// Every CTA owns one contiguous span of work units (16 KiB each), walks it
+// bitmap by bitmap, keeps its shared block map across a bitmap's part of the
+// span and hands over once per (CTA, bitmap).  Inside a bitmap the next unit's
+// loads are issued before the current unit is marked.  (Dealing the work out in
+// 4 KiB units instead, so that no CTA is a whole unit short of the others,
+// measured 1.5-5 % slower: the launch is bound by HBM, not by its slowest CTA,
+// and the part-units at both ends of every span cost more than they save.)
 #ifdef RT_MIN_CTAS
 #define RT_SCAN_BOUNDS __launch_bounds__(kScanThreads, RT_MIN_CTAS)
 #else
@@ -365,11 +360,11 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
     clear_map(s_map);
     __syncthreads();
     for (uint32_t g = first_group(a, q_begin);; ++g) {
-        const GroupSpan sp = group_span<Id>(a, g, q_begin, q_end, kSubIds<Id>);
+        const GroupSpan sp = group_span<Id>(a, g, q_begin, q_end);
         // this CTA's part of the bitmap's ids: [begin, end), read from the 16-byte
         // aligned index e0 <= begin on
         long long e0 = sp.e0;
-        const long long span_end = sp.e0 + (long long)(sp.q_hi - sp.q_lo) * kSubIds<Id>;
+        const long long span_end = sp.e0 + (long long)(sp.q_hi - sp.q_lo) * kChunk;
         const long long begin = e0 > sp.lo ? e0 : sp.lo, end = span_end < sp.hi ? span_end : sp.hi;
         const Id *mine = slots + e0 + kPer * (int)threadIdx.x;
         // ragged first chunk of the bitmap (its first id is not on a 16-byte boundary)
@@ -490,11 +485,9 @@ __device__ __forceinline__ void fetch_table_batch(const Id *slots, const TableSh
     }
 }
 
-// Valid ids [lo, hi) of segment v (flat indices into the table).
-__device__ __forceinline__ void table_segment(const ScanArgs &a, unsigned long long v, long long len,
+// Valid ids [lo, hi) of segment `seg` of row `row` (flat indices into the table).
+__device__ __forceinline__ void table_segment(const ScanArgs &a, uint32_t row, uint32_t seg, long long len,
                                               long long &lo, long long &hi) {
-    const uint32_t row = (uint32_t)(a.segs_per_row == 1 ? v : v / a.segs_per_row);
-    const uint32_t seg = (uint32_t)(v - (unsigned long long)row * a.segs_per_row);
     if (len < 0) len = 0;
     if (len > a.stride) len = a.stride;
     const long long row_lo = (long long)row * a.stride;
@@ -509,47 +502,60 @@ __device__ __forceinline__ void table_segment(const ScanArgs &a, unsigned long l
 // ... of that sequence, so every batch of 32 * kUnroll vectors is full whatever
 // the segment lengths are.  Each lane keeps its own cursor (all lanes walk the
 // same segments, a few vectors apart); the length of the segment after the
-// current one is always already on its way.
+// current one is always already on its way.  Segment numbers advance by the
+// number of warps in the grid; (row, segment-in-row) are stepped along with
+// precomputed quotient and remainder, so the walk contains no division.
 struct SegCursor {
-    unsigned long long v;        // current segment
-    unsigned long long first;    // index of its first vector in the warp's sequence
+    uint32_t row, seg;           // current segment
+    uint32_t row_next, seg_next; // the one after it
+    uint32_t first;              // index of the current segment's first vector in the warp's sequence
+    uint32_t n_vec;              // vectors in it
     long long lo, hi, i0;        // its valid ids [lo, hi); its first vector starts at flat index i0
-    long long n_vec;             // vectors in it
-    long long len_next;          // valid ids of the row of segment v + n_warps
+    long long len_next;          // valid ids of row_next
     bool done;
 };
 
+struct SegStride {
+    uint32_t rows, segs;         // advance of (row, segment-in-row) from one of a warp's segments to the next
+};
+
 template <typename Id>
-__device__ __forceinline__ void enter_segment(const ScanArgs &a, unsigned long long n_virtual,
-                                              unsigned long long n_warps, SegCursor &c) {
+__device__ __forceinline__ void enter_segment(const ScanArgs &a, const SegStride &step, SegCursor &c) {
     constexpr int kPer = IdTraits<Id>::kPer;
-    table_segment(a, c.v, c.len_next, c.lo, c.hi);
+    c.row = c.row_next;
+    c.seg = c.seg_next;
+    table_segment(a, c.row, c.seg, c.len_next, c.lo, c.hi);
     c.i0 = c.lo & ~(long long)(kPer - 1);
-    c.n_vec = c.hi > c.lo ? (c.hi - c.i0 + kPer - 1) / kPer : 0;
-    const unsigned long long nv = c.v + n_warps;
-    c.len_next = nv < n_virtual ? (long long)__ldg(a.lens + (a.segs_per_row == 1 ? nv : nv / a.segs_per_row)) : 0;
+    c.n_vec = c.hi > c.lo ? (uint32_t)((c.hi - c.i0 + kPer - 1) / kPer) : 0u;
+    c.seg_next = c.seg + step.segs;
+    c.row_next = c.row + step.rows;
+    if (c.seg_next >= a.segs_per_row) {
+        c.seg_next -= a.segs_per_row;
+        ++c.row_next;
+    }
+    // (a row number past the table marks the end; rows * segments is below 2^32 * 2^32, the sum cannot wrap
+    //  before it passes n_rows because step.rows < n_rows whenever a warp has a second segment)
+    c.len_next = c.row_next < a.n_rows ? (long long)__ldg(a.lens + c.row_next) : 0;
 }
 
 // Vectors base + lane + 32 u (u < kUnroll) of the warp's sequence.
 template <typename Id>
-__device__ __forceinline__ void fetch_warp_batch(const Id *slots, const ScanArgs &a, unsigned long long n_virtual,
-                                                 unsigned long long n_warps, unsigned long long base,
-                                                 uint32_t lane, SegCursor &c, Chunk<Id> &ch) {
+__device__ __forceinline__ void fetch_warp_batch(const Id *slots, const ScanArgs &a, const SegStride &step,
+                                                 uint32_t base, uint32_t lane, SegCursor &c, Chunk<Id> &ch) {
     using Vec = typename IdTraits<Id>::Vec;
     constexpr int kPer = IdTraits<Id>::kPer;
     constexpr uint32_t kWhole = (1u << kPer) - 1u;
     ch.mask = 0;
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-        const unsigned long long vi = base + lane + 32u * (unsigned)u;
-        while (!c.done && vi >= c.first + (unsigned long long)c.n_vec) {
-            c.first += (unsigned long long)c.n_vec;
-            c.v += n_warps;
-            if (c.v >= n_virtual) c.done = true;
-            else enter_segment<Id>(a, n_virtual, n_warps, c);
+        const uint32_t vi = base + lane + 32u * (unsigned)u;
+        while (!c.done && vi - c.first >= c.n_vec) {
+            c.first += c.n_vec;
+            if (c.row_next >= a.n_rows) c.done = true;
+            else enter_segment<Id>(a, step, c);
         }
         if (c.done) continue;
-        const long long at = c.i0 + (long long)(vi - c.first) * kPer;
+        const long long at = c.i0 + (long long)((vi - c.first) * (uint32_t)kPer);
         if (at >= c.lo && at + kPer <= c.hi) {
             ch.v[u] = RT_LOAD(reinterpret_cast<const Vec *>(slots + at));
             ch.mask |= kWhole << (kPer * u);
@@ -584,22 +590,27 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
         __syncthreads();                         // the map is clear before any warp marks
         // this warp's segments: its global index, then every n_warps-th
         const unsigned long long n_warps = (unsigned long long)gridDim.x * (kScanThreads / 32);
+        const unsigned long long mine0 = (unsigned long long)blockIdx.x * (kScanThreads / 32) + warp;
+        SegStride step;
+        step.rows = (uint32_t)(n_warps / a.segs_per_row);
+        step.segs = (uint32_t)(n_warps % a.segs_per_row);
         SegCursor cur;
-        cur.v = (unsigned long long)blockIdx.x * (kScanThreads / 32) + warp;
-        cur.first = 0;
-        cur.done = cur.v >= n_virtual;
-        cur.lo = cur.hi = cur.i0 = cur.n_vec = 0;
-        cur.len_next = cur.done ? 0 : (long long)__ldg(a.lens + (a.segs_per_row == 1 ? cur.v : cur.v / a.segs_per_row));
-        if (!cur.done) enter_segment<Id>(a, n_virtual, n_warps, cur);
-        constexpr unsigned long long kWarpBatch = 32ull * kUnroll;
+        cur.row = cur.seg = cur.first = cur.n_vec = 0;
+        cur.lo = cur.hi = cur.i0 = 0;
+        cur.row_next = (uint32_t)(mine0 / a.segs_per_row);
+        cur.seg_next = (uint32_t)(mine0 % a.segs_per_row);
+        cur.done = mine0 >= n_virtual;
+        cur.len_next = cur.done ? 0 : (long long)__ldg(a.lens + cur.row_next);
+        if (!cur.done) enter_segment<Id>(a, step, cur);
+        constexpr uint32_t kWarpBatch = 32u * kUnroll;
         Chunk<Id> now, nxt;
-        unsigned long long base = 0;
-        fetch_warp_batch<Id>(slots, a, n_virtual, n_warps, base, lane, cur, now);
+        uint32_t base = 0;
+        fetch_warp_batch<Id>(slots, a, step, base, lane, cur, now);
         // the next batch is in flight while this one is marked; a batch that is
         // empty in every lane is past the warp's last vector
         while (__any_sync(0xffffffffu, now.mask != 0)) {
             base += kWarpBatch;
-            fetch_warp_batch<Id>(slots, a, n_virtual, n_warps, base, lane, cur, nxt);
+            fetch_warp_batch<Id>(slots, a, step, base, lane, cur, nxt);
             if (now.mask) mark_chunk<kPow2, Id>(now, a, s_map, c);
             now = nxt;
         }
@@ -622,8 +633,10 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
             cnt[e] = 0;
             if (k < n_segs) {
                 const unsigned long long v = blockIdx.x + (pass + k) * gridDim.x;
+                const uint32_t row = (uint32_t)(a.segs_per_row == 1 ? v : v / a.segs_per_row);
+                const uint32_t seg = (uint32_t)(v - (unsigned long long)row * a.segs_per_row);
                 long long lo, hi;
-                table_segment(a, v, (long long)__ldg(a.lens + (a.segs_per_row == 1 ? v : v / a.segs_per_row)), lo, hi);
+                table_segment(a, row, seg, (long long)__ldg(a.lens + row), lo, hi);
                 const long long v0 = lo / kPer, v1 = (hi + kPer - 1) / kPer;
                 sh.seg[k].lo = lo;
                 sh.seg[k].hi = hi;

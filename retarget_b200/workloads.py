@@ -66,9 +66,12 @@ class Layout:
 class PagePool:
     """FIFO free list of 16-slot pages, seeded order, page 0 withheld."""
 
-    def __init__(self, pool_slots: int, rng: np.random.Generator):
+    def __init__(self, pool_slots: int, rng: np.random.Generator, shuffle: bool = True):
         pages = pool_slots // PAGE_SLOTS
-        order = rng.permutation(pages)
+        # shuffle=False: pages go out in address order, the way a freshly started
+        # allocator hands them out (the live set is then a region that moves
+        # through the pool, which is what a bounded window can follow)
+        order = rng.permutation(pages) if shuffle else np.arange(pages)
         self.free = deque(int(p) for p in order if p != 0)
 
     def take(self, n_pages: int) -> list[int]:
@@ -248,15 +251,16 @@ class TraceStep:
     completed_tokens: int      # cumulative prompt + generated tokens after the step
     live: int
     free_head: np.ndarray | None = None   # first 4096 free slots, sampled on even steps
+    req_off: np.ndarray | None = None     # request r of the live batch owns read_slots[req_off[r]:req_off[r+1]]
 
 
 def decode_trace(seed=0, *, steps=256, pool_slots=65536, arrival_rate=0.5, median=1024,
-                 mean_output=256, initial_requests=0) -> list[TraceStep]:
+                 mean_output=256, initial_requests=0, shuffle_pages=True) -> list[TraceStep]:
     """Poisson arrivals, log-normal prompts, geometric output lengths; every
     live request appends one token per step and finished requests return their
     pages to the tail of the free list."""
     rng = np.random.default_rng(seed)
-    pool = PagePool(pool_slots, rng)
+    pool = PagePool(pool_slots, rng, shuffle_pages)
     live: list[dict] = []
     completed = 0
     trace = []
@@ -293,6 +297,7 @@ def decode_trace(seed=0, *, steps=256, pool_slots=65536, arrival_rate=0.5, media
             read_slots=np.concatenate(reads) if reads else np.zeros(0, np.int64),
             write_slots=np.array(writes, dtype=np.int64),
             completed_tokens=completed, live=len(live),
+            req_off=np.concatenate([[0], np.cumsum([len(x) for x in reads])]).astype(np.int64),
             free_head=(page_slots(list(pool.free)[:4096 // PAGE_SLOTS], 4096)[:len(pool.free) * PAGE_SLOTS]
                        if step % 2 == 0 else None)))
         done = [r for r in live if r["left"] <= 0]
