@@ -825,7 +825,7 @@ def run_e2e_prefetch(args):
     total = 2 * layers * alloc
     ballast_bytes = max(64 * MIB, total // 8 // (2 * MIB) * (2 * MIB))     # 20 GiB : 160 GiB in the full configuration
     layout = workloads.Layout(layers, bytes_per_slot, pool_slots)        # one bitmap for all buffers
-    budget = layout.n_blocks // 2
+    budget = layout.n_blocks * 3 // 4                                    # the GPU share the plan may fill
     # requests sized so that the live set stays well inside the pool
     median = max(256, pool_slots // 96)
     trace = workloads.decode_trace(0, steps=W + K, pool_slots=pool_slots, arrival_rate=0.25, median=median,

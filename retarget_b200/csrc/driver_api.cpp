@@ -63,6 +63,7 @@ void load() {
     bind(g_api.primary_release_v2, "cuDevicePrimaryCtxRelease_v2");
     bind(g_api.primary_reset_v1, "cuDevicePrimaryCtxReset");
     bind(g_api.primary_reset_v2, "cuDevicePrimaryCtxReset_v2");
+    bind(g_api.primary_get_state, "cuDevicePrimaryCtxGetState");
     bind(g_api.get_proc_address_v1, "cuGetProcAddress");
     bind(g_api.get_proc_address_v2, "cuGetProcAddress_v2");
     g_ok = true;

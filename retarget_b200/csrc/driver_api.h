@@ -28,6 +28,7 @@ struct DriverApi {
     CUresult (*primary_release_v2)(CUdevice) = nullptr;
     CUresult (*primary_reset_v1)(CUdevice) = nullptr;
     CUresult (*primary_reset_v2)(CUdevice) = nullptr;
+    CUresult (*primary_get_state)(CUdevice, unsigned int *, int *) = nullptr;
     CUresult (*get_proc_address_v1)(const char *, void **, int, cuuint64_t) = nullptr;
     CUresult (*get_proc_address_v2)(const char *, void **, int, cuuint64_t,
                                     CUdriverProcAddressQueryResult *) = nullptr;

@@ -63,8 +63,13 @@ struct Server {
     dev_t socket_dev = 0;
     ino_t socket_ino = 0;
     pid_t owner = 0;
-    // side streams, per context, owned by the worker thread
-    std::map<CUcontext, std::vector<CUstream>> streams;
+    // side streams, per context (with the device the context belongs to), used by
+    // the worker thread under `life`
+    struct SideStreams {
+        int device = -1;
+        std::vector<CUstream> list;
+    };
+    std::map<CUcontext, SideStreams> streams;
 };
 
 Server g;
@@ -87,10 +92,12 @@ struct Pending {
     int dst;
 };
 
-CUresult streams_for(const DriverApi &api, CUcontext ctx, std::vector<CUstream> **out) {
+CUresult streams_for(const DriverApi &api, CUcontext ctx, int device, std::vector<CUstream> **out) {
     auto it = g.streams.find(ctx);
     if (it == g.streams.end()) {
-        std::vector<CUstream> made;
+        Server::SideStreams made_for;
+        made_for.device = device;
+        std::vector<CUstream> &made = made_for.list;
         for (uint32_t i = 0; i < g.n_streams; ++i) {
             CUstream s = nullptr;
             CUresult r = api.stream_create(&s, CU_STREAM_NON_BLOCKING);
@@ -100,10 +107,29 @@ CUresult streams_for(const DriverApi &api, CUcontext ctx, std::vector<CUstream> 
             }
             made.push_back(s);
         }
-        it = g.streams.emplace(ctx, std::move(made)).first;
+        it = g.streams.emplace(ctx, std::move(made_for)).first;
     }
-    *out = &it->second;
+    *out = &it->second.list;
     return CUDA_SUCCESS;
+}
+
+// Forgets the side streams of the contexts of `device` (any device when < 0).
+// `alive`: the contexts still exist, so the streams are destroyed properly;
+// otherwise they went away with their context and only the handles are dropped.
+// Caller holds `life`.
+void drop_streams_locked(int device, bool alive) {
+    const DriverApi *api = alive ? driver_api() : nullptr;
+    for (auto it = g.streams.begin(); it != g.streams.end();) {
+        if (device >= 0 && it->second.device != device) {
+            ++it;
+            continue;
+        }
+        if (api && api->ctx_set_current && api->stream_destroy && api->ctx_set_current(it->first) == CUDA_SUCCESS) {
+            for (CUstream s : it->second.list) api->stream_destroy(s);
+            api->ctx_set_current(nullptr);
+        }
+        it = g.streams.erase(it);
+    }
 }
 
 // Issues up to `batch` bytes starting at (*range, *done) and waits for them.
@@ -125,11 +151,12 @@ CUresult run_batch(const DriverApi &api, const std::vector<rt_id_range> &job, si
         if ((r.dst < 0) != batch_dst_is_cpu) break;      // phase boundary: wait first
         CUdeviceptr ptr = 0;
         CUcontext ctx = nullptr;
+        int device = -1;
         bool found = false, stopping;
         {
             std::lock_guard<std::mutex> st(g.state);
             for (const Allocation &a : g.allocations)
-                if (a.id == r.id) { ptr = a.ptr + r.offset + *done_in_range; ctx = a.ctx; found = true; break; }
+                if (a.id == r.id) { ptr = a.ptr + r.offset + *done_in_range; ctx = a.ctx; device = a.device; found = true; break; }
             stopping = g.stop;
         }
         if (stopping) { result = CUDA_ERROR_DEINITIALIZED; break; }
@@ -142,7 +169,7 @@ CUresult run_batch(const DriverApi &api, const std::vector<rt_id_range> &job, si
             have_ctx = true;
         }
         std::vector<CUstream> *streams = nullptr;
-        result = streams_for(api, ctx, &streams);
+        result = streams_for(api, ctx, device, &streams);
         if (result != CUDA_SUCCESS) break;
         uint64_t bytes = r.bytes - *done_in_range;
         if (bytes > g.chunk) bytes = g.chunk;
@@ -554,7 +581,7 @@ int rt_uvm_stop(void) {
     g.running = false;
     g.busy = false;
     g.job.clear();
-    g.streams.clear();       // streams die with their contexts / the process
+    rt::drop_streams_locked(-1, true);       // the contexts live on: give their streams back
     g.done.notify_all();
     return RT_OK;
 }
@@ -605,8 +632,9 @@ int rt_uvm_unregister_device(int device) {
     // the device goes, explicit-context records included
     int n = remove_where([](const rt::Allocation &a, const void *k) { return a.device == *(const int *)k; },
                          &device);
+    // (the caller says the device's contexts are gone: nothing left to destroy)
     std::lock_guard<std::mutex> life(g.life);
-    g.streams.clear();
+    rt::drop_streams_locked(device, false);
     return n;
 }
 
@@ -751,6 +779,7 @@ CUresult uvm_tracked_ctx_destroy(CUcontext ctx) {
 
 CUresult uvm_tracked_primary(CUdevice device, CUresult (*real)(CUdevice), const char *name) {
     if (!real) return CUDA_ERROR_NOT_SUPPORTED;
+    const bool is_reset = strstr(name, "Reset") != nullptr;
     uint64_t removed = 0;
     CUresult result;
     {
@@ -759,7 +788,16 @@ CUresult uvm_tracked_primary(CUdevice device, CUresult (*real)(CUdevice), const 
         if (result == CUDA_SUCCESS) {
             removed = forget_locked([](const Allocation &a, const void *k) { return a.device == *(const int *)k; },
                                     &device);
-            g.streams.clear();
+            // Side streams of THIS device only.  A reset destroys the context and
+            // its streams with it; a release usually leaves the context alive (other
+            // holders), and then its streams are destroyed properly instead of
+            // being leaked and made anew by the next job.
+            const DriverApi *api = driver_api();
+            unsigned int flags = 0;
+            int active = 0;
+            const bool alive = !is_reset && api && api->primary_get_state &&
+                               api->primary_get_state(device, &flags, &active) == CUDA_SUCCESS && active;
+            drop_streams_locked((int)device, alive);
         }
     }
     if (removed)

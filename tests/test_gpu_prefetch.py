@@ -88,11 +88,13 @@ def test_executor_moves_managed_ranges(managed):
         gen, allocs = uvm._allocation_snapshot()
         assert [a["bytes"] for a in allocs] == [size] * 4
         big = (1 << 64) - 1
+        before = uvm.status()                  # the byte counters run for the life of the process
         reply = uvm.command(f"windowv {gen} {size} 4 {big} {big} {2 * MIB} {6 * MIB}")
         assert reply["ok"], reply
         st = uvm._wait_job(reply["job_id"], timeout=60, poll_seconds=0.002)
         assert st.last_error == 0
-        assert st.completed_gpu_bytes == 4 * 4 * MIB and st.completed_cpu_bytes == 4 * 4 * MIB
+        assert st.completed_gpu_bytes - before.completed_gpu_bytes == 4 * 4 * MIB
+        assert st.completed_cpu_bytes - before.completed_cpu_bytes == 4 * 4 * MIB
         for p in ptrs:
             assert last_location(cudart, p, 2 * MIB) == -1                     # cudaCpuDeviceId
             assert last_location(cudart, p + 2 * MIB, 4 * MIB) == 0

@@ -325,3 +325,38 @@ def test_device_planner_ranges_can_be_submitted_directly(server):
     bad = ranges.copy()
     bad[1] = (0, 0, 4 * MIB, 200 * MIB)
     assert env.lib.rt_uvm_submit_ranges(bad.ctypes.data, 3, ids, 4, C.byref(job)) == -1
+
+
+def test_side_streams_are_tracked_per_device(server):
+    """Dropping one device's records leaves the other contexts' side streams in
+    place: the next job on them creates no new streams, and none are destroyed
+    that belong to a context the caller says is gone."""
+    env = server
+    ctx0, ctx1 = 0xC000, 0xC001                  # the stub driver's primary contexts of devices 0 and 1
+
+    def register(ptr, ctx, device):
+        out = C.c_uint64()
+        assert env.lib.rt_uvm_register(ptr, 4 * MIB, C.c_void_p(ctx), device, 1, C.byref(out)) == 0
+        return out.value
+
+    def prefetch(rid):
+        env.fake.fake_cuda_reset()
+        reply = env.local.command(f"prefetch {rid} 0 {4 * MIB} gpu")
+        assert reply["ok"], reply
+        env.local._wait_job(reply["job_id"], timeout=10, poll_seconds=0.002)
+        lines = env.log()
+        return sum(l.startswith("stream_create") for l in lines), sum(l.startswith("stream_destroy") for l in lines)
+
+    a = register(0x7f1000000000, ctx0, 0)
+    b = register(0x7f2000000000, ctx1, 1)
+    assert prefetch(a) == (3, 0) and prefetch(b) == (3, 0)       # three side streams per context, made on first use
+    assert prefetch(a) == (0, 0)                                 # ... and kept
+    env.lib.rt_uvm_unregister_device.argtypes = [C.c_int]
+    env.fake.fake_cuda_reset()
+    assert env.lib.rt_uvm_unregister_device(1) == 1
+    assert not any(l.startswith("stream_destroy") for l in env.log())     # that context is gone: handles dropped
+    b2 = register(0x7f3000000000, ctx1, 1)
+    assert prefetch(a) == (0, 0)                                 # device 0 kept its streams
+    assert prefetch(b2) == (3, 0)                                # device 1 starts over
+    for ptr in (0x7f1000000000, 0x7f3000000000):
+        assert env.lib.rt_uvm_unregister_ptr(ptr) == 1
