@@ -83,23 +83,21 @@ paged_attention_kernel(AttentionArgs a) {
     const long long lo = a.req_off[req], hi = a.req_off[req + 1];
     float m = -INFINITY, l = 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    // the rows of the next kSlotsInFlight slots are loaded before the current ones are used
-    auto fetch = [&](long long i, Frag (&k)[kSlotsInFlight], Frag (&v)[kSlotsInFlight], uint32_t &live) {
-        live = 0;
+    for (long long i = lo; i < hi; i += kSlotsInFlight) {
+        Frag k[kSlotsInFlight], v[kSlotsInFlight];
+        bool live[kSlotsInFlight];
 #pragma unroll
         for (int u = 0; u < kSlotsInFlight; ++u) {
             const long long s = i + u < hi ? a.slots[i + u] : 0;
-            if ((unsigned long long)(s - 1) < a.capacity) {             // slot 0 is padding; ids outside the pool are skipped
-                live |= 1u << u;
+            live[u] = (unsigned long long)(s - 1) < a.capacity;       // slot 0 is padding; ids outside the pool are skipped
+            if (live[u]) {
                 k[u] = load_frag(kbuf + (size_t)s * row_bytes, lane);
                 v[u] = load_frag(vbuf + (size_t)s * row_bytes, lane);
             }
         }
-    };
-    auto consume = [&](const Frag (&k)[kSlotsInFlight], const Frag (&v)[kSlotsInFlight], uint32_t live) {
 #pragma unroll
         for (int u = 0; u < kSlotsInFlight; ++u) {
-            if (!(live & (1u << u))) continue;                          // uniform over the warp
+            if (!live[u]) continue;                                    // uniform over the warp
             const float score =
                 warp_total(q.x[0] * k[u].x[0] + q.x[1] * k[u].x[1] + q.x[2] * k[u].x[2] + q.x[3] * k[u].x[3]);
             const float m_new = fmaxf(m, score);
@@ -109,17 +107,6 @@ paged_attention_kernel(AttentionArgs a) {
             for (int d = 0; d < 4; ++d) acc[d] = acc[d] * keep + w * v[u].x[d];
             m = m_new;
         }
-    };
-    Frag ka[kSlotsInFlight], va[kSlotsInFlight], kb[kSlotsInFlight], vb[kSlotsInFlight];
-    uint32_t live_a = 0, live_b = 0;
-    if (lo < hi) fetch(lo, ka, va, live_a);
-    for (long long i = lo; i < hi; i += 2 * kSlotsInFlight) {
-        if (i + kSlotsInFlight < hi) fetch(i + kSlotsInFlight, kb, vb, live_b);
-        else live_b = 0;
-        consume(ka, va, live_a);
-        if (i + 2 * kSlotsInFlight < hi) fetch(i + 2 * kSlotsInFlight, ka, va, live_a);
-        else live_a = 0;
-        consume(kb, vb, live_b);
     }
     const float inv = l > 0.f ? 1.f / l : 0.f;
     float4 o = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
