@@ -519,7 +519,10 @@ int rt_plan_sync(rt_plan *plan);
  * (NULL here is the legacy default stream).  The first call on a device also
  * looks up the array's device address; make that first call before any stream
  * capture.  All calls on a device share the array: calls that overlap on the GPU
- * race, so keep them on one stream or otherwise serialised. */
+ * race, so keep them on one stream or otherwise serialised.  The address is kept
+ * for the life of the process: after cudaDeviceReset (or any other destruction
+ * of the device's primary context) it is stale and this entry point must not be
+ * called again in that process. */
 #define RT_STATIC_MAX_GROUPS 64u
 int rt_scan_slots_static(const int64_t *d_slots, const int64_t *group_off, uint32_t n_groups,
                          uint64_t capacity_slots, uint32_t block_tokens, uint32_t n_blocks,

@@ -85,6 +85,7 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
     p.buffer_group = pl->d_buffer_group;
     p.group_size = pl->d_group_size;
     p.n_units = 0;
+    p.launch_no = 0;
     p.bitmaps_out = nullptr;
     p.out = out;
     p.result = result;
@@ -101,9 +102,11 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
     p.block_bytes = pl->layout.block_bytes;
 }
 
-// Scan launches alternate between the plan's two scratch sets (plan_device.cuh).
+// Scan launches are numbered from 2 and alternate between the plan's two scratch
+// sets (plan_device.cuh): launch n uses set n & 1 once launch n - 2 has cleaned it.
 void next_scratch(rt_plan *pl, rt::PlanArgs &p) {
-    const uint32_t set = pl->scans++ & 1u;
+    const uint32_t n = pl->scans++ + 2u, set = n & 1u;
+    p.launch_no = n;
     p.groups = pl->d_groups + (size_t)set * pl->layout.n_groups;
     p.global = pl->d_global + set;
 }
@@ -256,6 +259,11 @@ int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, ui
         if ((e = cudaMemset(pl->d_groups, 0, gbytes))) { fail(e); break; }
         if ((e = cudaMalloc(&pl->d_global, 2 * sizeof(rt::GlobalScratch)))) { fail(e); break; }
         if ((e = cudaMemset(pl->d_global, 0, 2 * sizeof(rt::GlobalScratch)))) { fail(e); break; }
+        {
+            // "launches 0 and 1" have left the two sets clean
+            const uint32_t one = 1;
+            if ((e = cudaMemcpy(&pl->d_global[1].cleaned, &one, sizeof(one), cudaMemcpyHostToDevice))) { fail(e); break; }
+        }
         size_t rbytes = sizeof(uint32_t) * rt::kWords * L.n_groups;
         if ((e = cudaMalloc(&pl->d_resident, rbytes))) { fail(e); break; }
         if ((e = cudaMemset(pl->d_resident, 0, rbytes))) { fail(e); break; }

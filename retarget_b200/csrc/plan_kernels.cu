@@ -12,12 +12,18 @@
 // out does the tail"), so nothing in here can hang.
 //
 // Chained launches (RT_PLAN_CHAINED): the kernel is launched with programmatic
-// stream serialization.  Its scanning CTAs need nothing from the launch before
-// it, so they start as soon as that launch has finished SCANNING; only the CTA
-// that ends up running the tail executes griddepcontrol.wait (the previous
-// launch has completed: its resident words, ranges and result are final) and
-// then griddepcontrol.launch_dependents (the next launch may start).  The tail
-// of step i thus runs under the scan of step i+1.
+// stream serialization and every CTA executes griddepcontrol.launch_dependents
+// as its first instruction, so the next launch's CTAs move onto an SM as soon as
+// this launch's CTAs leave it: the ramp of step i+1 overlaps the drain of step i,
+// and the tail of step i (one CTA) runs under the scan of step i+1.  What a
+// launch needs from its predecessors it waits for where it needs it:
+//   * its scratch set (shared with the launch two before it) before its first
+//     write to it: a flag that launch's tail sets, read at kernel start and
+//     polled a bounded time only if that early read came too soon (SetGate);
+//   * the resident words, in the one CTA that runs the tail:
+//     griddepcontrol.wait (the launch before this one has completed).
+// No CTA waits for a CTA that might not be running: a launch can only start once
+// every CTA of the launch before it has started, so all older tails are resident.
 //
 // The path is index arithmetic bound by HBM reads; there is no contraction in
 // it and no tensor-core work.
@@ -248,6 +254,7 @@ __device__ __forceinline__ uint32_t first_group(const ScanArgs &a, int q) {
 // --------------------------------------------------------------------------
 struct HandoverShared {
     int last;      // this CTA retired the last work unit of the launch
+    int gate_ok;   // the scratch set was seen clean in time
 };
 
 // Programmatic dependent launch.  Both are no-ops in a kernel that was launched
@@ -257,6 +264,50 @@ __device__ __forceinline__ void griddep_wait() {
 }
 __device__ __forceinline__ void griddep_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ unsigned long long gate_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t load_cleaned(const PlanArgs &p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(&p.global->cleaned) : "memory");
+    return v;
+}
+
+// Before a CTA's first write to its launch's scratch set, the launch that used
+// the set last (two launches back) must have left it clean.
+#ifndef RT_GATE_NS
+#define RT_GATE_NS 20000000ull      // a tail takes microseconds; 20 ms means it is not coming
+#endif
+struct SetGate {
+    uint32_t seen;      // thread 0: the set's `cleaned` word as read at kernel start
+    bool open;          // the CTA has been through the gate
+};
+__device__ __forceinline__ void gate_begin(const PlanArgs &p, SetGate &g) {
+    g.open = false;
+    g.seen = threadIdx.x == 0 ? load_cleaned(p) : 0u;
+}
+template <int kBar>
+__device__ __forceinline__ void gate_pass(const PlanArgs &p, SetGate &g, HandoverShared &hs) {
+    if (g.open) return;
+    g.open = true;
+    if (threadIdx.x == 0) {
+        const uint32_t need = p.launch_no - 2u;
+        uint32_t v = g.seen;
+        if ((int32_t)(v - need) < 0) {
+            const unsigned long long until = gate_ns() + RT_GATE_NS;
+            do v = load_cleaned(p);
+            while ((int32_t)(v - need) < 0 && gate_ns() < until);
+        }
+        hs.gate_ok = (int32_t)(v - need) >= 0;
+    }
+    cta_sync<kBar, kScanThreads>();
+    // never seen clean: go on all the same (nothing may hang), but the launch is
+    // marked failed, so whatever its tail makes of the set is not committed
+    if (!hs.gate_ok && threadIdx.x == 0) atomicOr(&p.global->error_flags, RT_RESULT_TIMEOUT);
 }
 
 template <int kBar>
@@ -292,8 +343,9 @@ __device__ __forceinline__ void flush_map(const PlanArgs &p, uint32_t g, const u
 // The CTA leaves bitmap g: publish its bits and counters, start a clean map.
 template <int kBar>
 __device__ __forceinline__ void leave_group(const PlanArgs &p, uint32_t g, uint8_t *s_map,
-                                            ScanCounters &c) {
+                                            ScanCounters &c, SetGate &gate, HandoverShared &hs) {
     cta_sync<kBar, kScanThreads>();
+    gate_pass<kBar>(p, gate, hs);
     flush_map(p, g, s_map);
     flush_counters<kBar>(p, c);
     clear_map(s_map);
@@ -315,15 +367,10 @@ __device__ __forceinline__ void finish_cta(const PlanArgs &p, uint32_t count, Ha
         hs.last = prev + count == p.n_units;
     }
     cta_sync<kBar, kScanThreads>();
-    if (!hs.last) return;                 // (a CTA that exits counts as having let the next launch go)
+    if (!hs.last) return;
     __threadfence();
-    // Order matters.  First: the launch before this one has completed, so what its
-    // tail wrote (resident words, its scratch set cleaned) is final.  Then: the
-    // next launch may start scanning.  It uses the other scratch set, and the one
-    // after it cannot start before that one's tail CTA has come through here,
-    // i.e. before THIS launch has completed -- so two launches never share a set.
+    // the launch before this one has completed: its resident words, ranges and result are final
     griddep_wait();
-    griddep_launch_dependents();
     if (tail_mem_unsafe) tail_abort(p);
     else plan_tail<kBar>(p, &p.groups[0].want[0], true, tail_mem);
 }
@@ -352,11 +399,14 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
     extern __shared__ __align__(16) unsigned char tail_mem[];
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
+    griddep_launch_dependents();
     const int q_begin = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
     const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
     if (q_begin >= q_end) return;
     const Id *slots = reinterpret_cast<const Id *>(a.slots);
     ScanCounters c = {0, 0};
+    SetGate gate;
+    gate_begin(p, gate);
     clear_map(s_map);
     __syncthreads();
     for (uint32_t g = first_group(a, q_begin);; ++g) {
@@ -409,7 +459,7 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
             load_chunk<Id>(mine, e0, begin, end, ch);
             mark_chunk<kPow2, Id>(ch, a, s_map, c);
         }
-        leave_group<0>(p, g, s_map, c);
+        leave_group<0>(p, g, s_map, c, gate, hs);
         if (sp.q_hi >= q_end) break;
     }
     finish_cta<0>(p, (uint32_t)(q_end - q_begin), hs, tail_mem);
@@ -583,7 +633,10 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
     __shared__ HandoverShared hs;
     const Id *slots = reinterpret_cast<const Id *>(a.slots);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    griddep_launch_dependents();
     ScanCounters c = {0, 0};
+    SetGate gate;
+    gate_begin(p, gate);
     clear_map(s_map);
     const unsigned long long n_virtual = (unsigned long long)a.n_rows * a.segs_per_row;
     if (kWarpSegs) {
@@ -614,7 +667,7 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
             if (now.mask) mark_chunk<kPow2, Id>(now, a, s_map, c);
             now = nxt;
         }
-        leave_group<0>(p, 0, s_map, c);
+        leave_group<0>(p, 0, s_map, c, gate, hs);
         finish_cta<0>(p, 1u, hs, tail_mem);
         return;
     }
@@ -671,7 +724,7 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
             now = nxt;
         }
     }
-    leave_group<0>(p, 0, s_map, c);
+    leave_group<0>(p, 0, s_map, c, gate, hs);
     finish_cta<0>(p, 1u, hs, tail_mem);
 }
 
@@ -775,6 +828,7 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
     const int tid = threadIdx.x;
+    griddep_launch_dependents();
     const int q_begin = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
     const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
     if (q_begin >= q_end) return;
@@ -828,6 +882,8 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
 
     // ---- consumer warps ----
     ScanCounters c = {0, 0};
+    SetGate gate;
+    gate_begin(p, gate);
     bool gave_up = false;
     int i = 0;
     for (uint32_t g = g0;; ++g) {
@@ -873,7 +929,7 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
             if (mask == kAllIds) mark_full<kPow2>(v, a, s_map, c);
             else mark_masked<kPow2>(v, mask, a, s_map, c);
         }
-        leave_group<kConsumerBar>(p, g, s_map, c);
+        leave_group<kConsumerBar>(p, g, s_map, c, gate, hs);
         if (sp.q_hi >= q_end) break;
     }
     // (one thread's wait running out means the whole CTA stops trusting its ring)
