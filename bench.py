@@ -521,7 +521,8 @@ def run_ours(args):
         raise SystemExit("bench.py: no CUDA device; retarget_b200 has no CPU path to fall back to")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    ranks = Ranks("nccl").start(dev)
+    # RETARGET_RANKS=file: rendezvous through files, no process group (a diagnostic)
+    ranks = Ranks(os.environ.get("RETARGET_RANKS", "nccl")).start(dev)
     base = capi.RT_PLAN_EVICT | (capi.RT_PLAN_TMA if args.tma else 0)
     # back-to-back steps of one plan: each may scan under the tail of the one before
     flags = base | (0 if args.unchained else capi.RT_PLAN_CHAINED)

@@ -85,7 +85,6 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
     p.buffer_group = pl->d_buffer_group;
     p.group_size = pl->d_group_size;
     p.n_units = 0;
-    p.launch_no = 0;
     p.bitmaps_out = nullptr;
     p.out = out;
     p.result = result;
@@ -102,11 +101,9 @@ void fill_plan_args(const rt_plan *pl, rt::PlanArgs &p, uint32_t budget, uint32_
     p.block_bytes = pl->layout.block_bytes;
 }
 
-// Scan launches are numbered from 2 and alternate between the plan's two scratch
-// sets (plan_device.cuh): launch n uses set n & 1 once launch n - 2 has cleaned it.
+// Scan launches alternate between the plan's two scratch sets (plan_device.cuh).
 void next_scratch(rt_plan *pl, rt::PlanArgs &p) {
-    const uint32_t n = pl->scans++ + 2u, set = n & 1u;
-    p.launch_no = n;
+    const uint32_t set = pl->scans++ & 1u;
     p.groups = pl->d_groups + (size_t)set * pl->layout.n_groups;
     p.global = pl->d_global + set;
 }
@@ -153,10 +150,13 @@ int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const void *d_slots,
     return RT_OK;
 }
 
-// One wave: every CTA is resident from the start and owns one contiguous span.
+// Worker CTAs of a launch.  One wave: every CTA is resident from the start and
+// owns one contiguous span; one slot of the wave is left for the gatekeeper CTA
+// the launcher adds.
 int grid_for(const rt_plan *pl, int units, bool tma) {
     const int per_sm = tma ? pl->tma_blocks_per_sm : pl->plain_blocks_per_sm;
-    long long slots = (long long)pl->sm_count * per_sm;
+    long long slots = (long long)pl->sm_count * per_sm - 1;
+    if (slots < 1) slots = 1;
     return (int)(units < slots ? units : slots);
 }
 
@@ -259,11 +259,6 @@ int rt_plan_create(const rt_layout *layout, int device, uint64_t max_indices, ui
         if ((e = cudaMemset(pl->d_groups, 0, gbytes))) { fail(e); break; }
         if ((e = cudaMalloc(&pl->d_global, 2 * sizeof(rt::GlobalScratch)))) { fail(e); break; }
         if ((e = cudaMemset(pl->d_global, 0, 2 * sizeof(rt::GlobalScratch)))) { fail(e); break; }
-        {
-            // "launches 0 and 1" have left the two sets clean
-            const uint32_t one = 1;
-            if ((e = cudaMemcpy(&pl->d_global[1].cleaned, &one, sizeof(one), cudaMemcpyHostToDevice))) { fail(e); break; }
-        }
         size_t rbytes = sizeof(uint32_t) * rt::kWords * L.n_groups;
         if ((e = cudaMalloc(&pl->d_resident, rbytes))) { fail(e); break; }
         if ((e = cudaMemset(pl->d_resident, 0, rbytes))) { fail(e); break; }
@@ -403,7 +398,7 @@ int step_table_impl(rt_plan *pl, const void *d_table, bool ids32, const int32_t 
     // for a warp each, else to CTAs.  Rows are cut into segments of at least 1024
     // ids until there are about four segments per worker, so that the last round
     // of the round-robin leaves few workers idle.
-    const unsigned long long ctas = (unsigned long long)pl->sm_count * pl->table_blocks_per_sm;   // one wave
+    const unsigned long long ctas = (unsigned long long)pl->sm_count * pl->table_blocks_per_sm - 1;   // one wave, less the gatekeeper
     const unsigned long long workers = stride >= 1024 ? ctas * (rt::kScanThreads / 32) : ctas;
     unsigned long long segs = 1;
     if (n_rows < 4 * workers) {

@@ -19,13 +19,12 @@ constexpr int kChunkElems = kScanThreads * 2 * kUnroll;   // 2048 slot ids = 16 
 // zeroes them after reading, so back-to-back launches need no memset.
 //
 // A plan owns TWO sets of scratch (words + counters) and its scan launches use
-// them in turn: launch number n (counted by the host from 2) uses set n & 1.
-// A chained launch (RT_PLAN_CHAINED) may start scanning while the launches
-// before it are still running; the set it uses was last used by launch n - 2,
-// whose tail writes its own number into the set's `cleaned` word when it has
-// left the set clean.  A CTA of launch n reads that word when it starts and
-// looks at it again (a bounded number of times) before its first write to the
-// set; in steady state the first read already says n - 2.
+// them in turn.  A chained launch (RT_PLAN_CHAINED) may run while the launch
+// before it is still running, but never while the launch two before it is: one
+// CTA of every launch does nothing but wait for the launch before it to
+// complete and only then lets the next launch start (the gatekeeper in
+// plan_kernels.cu).  So at most two consecutive launches are in flight at any
+// time, and they use different sets.
 struct GroupScratch {
     uint32_t want[kWords];
 };
@@ -35,8 +34,6 @@ struct GlobalScratch {
     unsigned long long ignored_slots;
     uint32_t units_done;          // arrival counter of scanned work units
     uint32_t error_flags;
-    uint32_t cleaned;             // number of the last launch whose tail left this set clean
-    uint32_t reserved;
 };
 
 // Kernel arguments, passed by value (about 1.7 KiB + 0.1 KiB): no per-step upload.
@@ -75,7 +72,6 @@ struct PlanArgs {
     int scan_only;
     int explicit_sets;                        // `want` holds [evict | add] words per bitmap
     uint32_t n_units;                         // work units of this launch (scan kernels)
-    uint32_t launch_no;                       // scan launches: this launch's number (set = launch_no & 1)
     unsigned long long alloc_bytes;
     unsigned long long block_bytes;
     const uint8_t *buffer_group;              // device: bitmap of every buffer, registry order

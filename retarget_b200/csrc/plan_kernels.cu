@@ -12,18 +12,18 @@
 // out does the tail"), so nothing in here can hang.
 //
 // Chained launches (RT_PLAN_CHAINED): the kernel is launched with programmatic
-// stream serialization and every CTA executes griddepcontrol.launch_dependents
-// as its first instruction, so the next launch's CTAs move onto an SM as soon as
-// this launch's CTAs leave it: the ramp of step i+1 overlaps the drain of step i,
-// and the tail of step i (one CTA) runs under the scan of step i+1.  What a
-// launch needs from its predecessors it waits for where it needs it:
-//   * its scratch set (shared with the launch two before it) before its first
-//     write to it: a flag that launch's tail sets, read at kernel start and
-//     polled a bounded time only if that early read came too soon (SetGate);
-//   * the resident words, in the one CTA that runs the tail:
-//     griddepcontrol.wait (the launch before this one has completed).
-// No CTA waits for a CTA that might not be running: a launch can only start once
-// every CTA of the launch before it has started, so all older tails are resident.
+// stream serialization.  Its scanning CTAs need nothing from the launch before
+// it, so each of them executes griddepcontrol.launch_dependents as its first
+// instruction.  CTA 0 of every launch is a GATEKEEPER: it scans nothing, it
+// executes griddepcontrol.wait (the launch before this one has completed), then
+// griddepcontrol.launch_dependents, and exits.  The next launch can therefore
+// start once this launch's CTAs are all running AND the launch before this one
+// has completed: its CTAs move onto an SM as soon as this launch's CTAs leave it
+// (the ramp of step i+1 overlaps the drain of step i, and the one-CTA tail of
+// step i runs under the scan of step i+1), yet no more than two consecutive
+// launches are ever in flight, which is what lets them alternate between two
+// scratch sets.  The CTA that runs a tail executes griddepcontrol.wait before it
+// reads the resident words.  Nothing polls, nothing spins.
 //
 // The path is index arithmetic bound by HBM reads; there is no contraction in
 // it and no tensor-core work.
@@ -254,7 +254,6 @@ __device__ __forceinline__ uint32_t first_group(const ScanArgs &a, int q) {
 // --------------------------------------------------------------------------
 struct HandoverShared {
     int last;      // this CTA retired the last work unit of the launch
-    int gate_ok;   // the scratch set was seen clean in time
 };
 
 // Programmatic dependent launch.  Both are no-ops in a kernel that was launched
@@ -266,48 +265,17 @@ __device__ __forceinline__ void griddep_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-__device__ __forceinline__ unsigned long long gate_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ uint32_t load_cleaned(const PlanArgs &p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(&p.global->cleaned) : "memory");
-    return v;
-}
-
-// Before a CTA's first write to its launch's scratch set, the launch that used
-// the set last (two launches back) must have left it clean.
-#ifndef RT_GATE_NS
-#define RT_GATE_NS 20000000ull      // a tail takes microseconds; 20 ms means it is not coming
-#endif
-struct SetGate {
-    uint32_t seen;      // thread 0: the set's `cleaned` word as read at kernel start
-    bool open;          // the CTA has been through the gate
-};
-__device__ __forceinline__ void gate_begin(const PlanArgs &p, SetGate &g) {
-    g.open = false;
-    g.seen = threadIdx.x == 0 ? load_cleaned(p) : 0u;
-}
-template <int kBar>
-__device__ __forceinline__ void gate_pass(const PlanArgs &p, SetGate &g, HandoverShared &hs) {
-    if (g.open) return;
-    g.open = true;
-    if (threadIdx.x == 0) {
-        const uint32_t need = p.launch_no - 2u;
-        uint32_t v = g.seen;
-        if ((int32_t)(v - need) < 0) {
-            const unsigned long long until = gate_ns() + RT_GATE_NS;
-            do v = load_cleaned(p);
-            while ((int32_t)(v - need) < 0 && gate_ns() < until);
-        }
-        hs.gate_ok = (int32_t)(v - need) >= 0;
+// First statement of every scan kernel.  Returns true in the gatekeeper CTA,
+// which has then done all it is there for; the others continue as worker
+// number blockIdx.x - 1 of gridDim.x - 1.
+__device__ __forceinline__ bool gatekeeper() {
+    if (blockIdx.x != 0) {
+        griddep_launch_dependents();
+        return false;
     }
-    cta_sync<kBar, kScanThreads>();
-    // never seen clean: go on all the same (nothing may hang), but the launch is
-    // marked failed, so whatever its tail makes of the set is not committed
-    if (!hs.gate_ok && threadIdx.x == 0) atomicOr(&p.global->error_flags, RT_RESULT_TIMEOUT);
+    griddep_wait();                 // the launch before this one has completed ...
+    griddep_launch_dependents();    // ... so the one after this one may use its scratch set
+    return true;
 }
 
 template <int kBar>
@@ -343,9 +311,8 @@ __device__ __forceinline__ void flush_map(const PlanArgs &p, uint32_t g, const u
 // The CTA leaves bitmap g: publish its bits and counters, start a clean map.
 template <int kBar>
 __device__ __forceinline__ void leave_group(const PlanArgs &p, uint32_t g, uint8_t *s_map,
-                                            ScanCounters &c, SetGate &gate, HandoverShared &hs) {
+                                            ScanCounters &c) {
     cta_sync<kBar, kScanThreads>();
-    gate_pass<kBar>(p, gate, hs);
     flush_map(p, g, s_map);
     flush_counters<kBar>(p, c);
     clear_map(s_map);
@@ -399,14 +366,13 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
     extern __shared__ __align__(16) unsigned char tail_mem[];
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
-    griddep_launch_dependents();
-    const int q_begin = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
-    const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
+    if (gatekeeper()) return;
+    const uint32_t worker = blockIdx.x - 1, n_workers = gridDim.x - 1;
+    const int q_begin = (int)((long long)a.n_units * worker / n_workers);
+    const int q_end = (int)((long long)a.n_units * (worker + 1) / n_workers);
     if (q_begin >= q_end) return;
     const Id *slots = reinterpret_cast<const Id *>(a.slots);
     ScanCounters c = {0, 0};
-    SetGate gate;
-    gate_begin(p, gate);
     clear_map(s_map);
     __syncthreads();
     for (uint32_t g = first_group(a, q_begin);; ++g) {
@@ -459,7 +425,7 @@ scan_plan_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pla
             load_chunk<Id>(mine, e0, begin, end, ch);
             mark_chunk<kPow2, Id>(ch, a, s_map, c);
         }
-        leave_group<0>(p, g, s_map, c, gate, hs);
+        leave_group<0>(p, g, s_map, c);
         if (sp.q_hi >= q_end) break;
     }
     finish_cta<0>(p, (uint32_t)(q_end - q_begin), hs, tail_mem);
@@ -633,17 +599,16 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
     __shared__ HandoverShared hs;
     const Id *slots = reinterpret_cast<const Id *>(a.slots);
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    griddep_launch_dependents();
+    if (gatekeeper()) return;
+    const uint32_t worker = blockIdx.x - 1, n_workers = gridDim.x - 1;
     ScanCounters c = {0, 0};
-    SetGate gate;
-    gate_begin(p, gate);
     clear_map(s_map);
     const unsigned long long n_virtual = (unsigned long long)a.n_rows * a.segs_per_row;
     if (kWarpSegs) {
         __syncthreads();                         // the map is clear before any warp marks
         // this warp's segments: its global index, then every n_warps-th
-        const unsigned long long n_warps = (unsigned long long)gridDim.x * (kScanThreads / 32);
-        const unsigned long long mine0 = (unsigned long long)blockIdx.x * (kScanThreads / 32) + warp;
+        const unsigned long long n_warps = (unsigned long long)n_workers * (kScanThreads / 32);
+        const unsigned long long mine0 = (unsigned long long)worker * (kScanThreads / 32) + warp;
         SegStride step;
         step.rows = (uint32_t)(n_warps / a.segs_per_row);
         step.segs = (uint32_t)(n_warps % a.segs_per_row);
@@ -667,14 +632,13 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
             if (now.mask) mark_chunk<kPow2, Id>(now, a, s_map, c);
             now = nxt;
         }
-        leave_group<0>(p, 0, s_map, c, gate, hs);
+        leave_group<0>(p, 0, s_map, c);
         finish_cta<0>(p, 1u, hs, tail_mem);
         return;
     }
     __shared__ TableShared sh;
-    // this CTA's segments: blockIdx.x, blockIdx.x + gridDim.x, ...
-    const unsigned long long mine =
-        n_virtual > blockIdx.x ? (n_virtual - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // this CTA's segments: worker, worker + n_workers, ...
+    const unsigned long long mine = n_virtual > worker ? (n_virtual - worker + n_workers - 1) / n_workers : 0;
     for (unsigned long long pass = 0; pass < mine; pass += kSegsPerPass) {
         const int n_segs = (int)(mine - pass < (unsigned long long)kSegsPerPass ? mine - pass : kSegsPerPass);
         __syncthreads();                         // the previous pass is done with the lists
@@ -685,7 +649,7 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
             const int k = (int)tid * 4 + e;
             cnt[e] = 0;
             if (k < n_segs) {
-                const unsigned long long v = blockIdx.x + (pass + k) * gridDim.x;
+                const unsigned long long v = worker + (pass + k) * n_workers;
                 const uint32_t row = (uint32_t)(a.segs_per_row == 1 ? v : v / a.segs_per_row);
                 const uint32_t seg = (uint32_t)(v - (unsigned long long)row * a.segs_per_row);
                 long long lo, hi;
@@ -724,7 +688,7 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
             now = nxt;
         }
     }
-    leave_group<0>(p, 0, s_map, c, gate, hs);
+    leave_group<0>(p, 0, s_map, c);
     finish_cta<0>(p, 1u, hs, tail_mem);
 }
 
@@ -828,9 +792,10 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
     __shared__ __align__(16) uint8_t s_map[RT_MAX_BLOCKS];
     __shared__ HandoverShared hs;
     const int tid = threadIdx.x;
-    griddep_launch_dependents();
-    const int q_begin = (int)((long long)a.n_units * blockIdx.x / gridDim.x);
-    const int q_end = (int)((long long)a.n_units * (blockIdx.x + 1) / gridDim.x);
+    if (gatekeeper()) return;
+    const uint32_t worker = blockIdx.x - 1, n_workers = gridDim.x - 1;
+    const int q_begin = (int)((long long)a.n_units * worker / n_workers);
+    const int q_end = (int)((long long)a.n_units * (worker + 1) / n_workers);
     if (q_begin >= q_end) return;
     const long long copy_limit = a.group_off[a.n_groups] & ~1LL;
     if (tid == 0) {
@@ -861,9 +826,9 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
                     }
                     const long long n = copy_end_of(e0, sp.hi, copy_limit) - e0;
 #ifdef RT_TEST_STALL
-                    // test build only: CTA 0 "loses" its first copy, so that the
+                    // test build only: the first worker "loses" its first copy, so that the
                     // consumers' bounded wait runs out (nothing faults, nothing hangs)
-                    if (blockIdx.x == 0 && i == 0) continue;
+                    if (blockIdx.x == 1 && i == 0) continue;
 #endif
                     if (n > 0) {
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -882,8 +847,6 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
 
     // ---- consumer warps ----
     ScanCounters c = {0, 0};
-    SetGate gate;
-    gate_begin(p, gate);
     bool gave_up = false;
     int i = 0;
     for (uint32_t g = g0;; ++g) {
@@ -929,7 +892,7 @@ scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__
             if (mask == kAllIds) mark_full<kPow2>(v, a, s_map, c);
             else mark_masked<kPow2>(v, mask, a, s_map, c);
         }
-        leave_group<kConsumerBar>(p, g, s_map, c, gate, hs);
+        leave_group<kConsumerBar>(p, g, s_map, c);
         if (sp.q_hi >= q_end) break;
     }
     // (one thread's wait running out means the whole CTA stops trusting its ring)
@@ -967,7 +930,7 @@ template <typename Kernel>
 static cudaError_t launch_scan(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t stream,
                                bool chained, const ScanArgs &a, const PlanArgs &p) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
+    cfg.gridDim = dim3((unsigned)grid + 1u);          // the workers and, as CTA 0, the gatekeeper
     cfg.blockDim = dim3((unsigned)threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;

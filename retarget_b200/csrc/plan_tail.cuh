@@ -321,17 +321,6 @@ __device__ __forceinline__ void pass_a(const PassA &in, const TailShared &sh, ui
     }
 }
 
-// The launch's scratch set is clean again: say so to launch_no + 2, which may
-// already be running.  Call with the whole CTA, after the last write to the set.
-__device__ __forceinline__ void release_set(const PlanArgs &p) {
-    if (!p.launch_no) return;                 // not a scan launch: it owns no set
-    asm volatile("bar.sync 2, %0;" ::"n"(kScanThreads) : "memory");   // every thread's clean-up stores are done
-    if (threadIdx.x == 0) {
-        __threadfence();
-        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(&p.global->cleaned), "r"(p.launch_no) : "memory");
-    }
-}
-
 // --------------------------------------------------------------------------
 // tail of a launch whose scan failed in the CTA that would plan: no plan, the
 // resident words stay as they are, the scratch is cleaned for the next launch
@@ -352,7 +341,6 @@ __device__ __forceinline__ void tail_abort(const PlanArgs &p) {
         gl.units_done = 0;
         gl.error_flags = 0;
     }
-    release_set(p);
 }
 
 // --------------------------------------------------------------------------
@@ -548,7 +536,6 @@ __device__ bool plan_tail(const PlanArgs &p, uint32_t *want, bool consume, unsig
         gl.units_done = 0;
         gl.error_flags = 0;
     }
-    release_set(p);
     return delivered;
 }
 

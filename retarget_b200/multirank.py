@@ -6,7 +6,10 @@ the slot table, so ranks never trade data.  What they do share is bookkeeping:
 a rendezvous, a barrier around timed regions, the maximum of per-rank timings,
 and (as a consistency check) a digest of each rank's plan, which must be the
 same everywhere because the slot ids are.  This module holds exactly that, on
-top of ``torch.distributed`` -- NCCL on GPUs, gloo on CPU-only hosts.
+top of ``torch.distributed`` -- NCCL on GPUs, gloo on CPU-only hosts -- or, with
+backend ``"file"``, on nothing but files in a directory all ranks can see (no
+process group, no communicator threads: used to tell what a process group costs
+the timed region).
 """
 from __future__ import annotations
 
@@ -29,6 +32,14 @@ class Ranks:
         """Joins the process group (no-op for a single process)."""
         if self.world == 1:
             return self
+        if self.backend == "file":
+            import tempfile
+            # all ranks of one launch have the same parent (the launcher): its PID makes the directory theirs
+            tag = os.environ.get("MASTER_PORT", "0") + "-" + str(os.getppid())
+            self._dir = os.path.join(tempfile.gettempdir(), f"retarget-ranks-{tag}")
+            os.makedirs(self._dir, exist_ok=True)
+            self._round = 0
+            return self
         import torch
         import torch.distributed as dist
         backend = self.backend or ("nccl" if device is not None else "gloo")
@@ -43,12 +54,38 @@ class Ranks:
             self._dist.destroy_process_group()
             self._dist = None
 
+    # ---- file rendezvous: every rank writes <round>.<rank>, then waits for all of them ----
+    def _exchange(self, payload: bytes) -> list[bytes]:
+        import time
+        self._round += 1
+        mine = os.path.join(self._dir, f"{self._round}.{self.rank}")
+        with open(mine + ".tmp", "wb") as f:
+            f.write(payload)
+        os.replace(mine + ".tmp", mine)
+        out = []
+        deadline = time.monotonic() + 600
+        for r in range(self.world):
+            path = os.path.join(self._dir, f"{self._round}.{r}")
+            while not os.path.exists(path):
+                if time.monotonic() > deadline:
+                    raise RuntimeError(f"rank {r} never reached rendezvous {self._round}")
+                time.sleep(0.0005)
+            with open(path, "rb") as f:
+                out.append(f.read())
+        return out
+
     def barrier(self):
-        if self._dist is not None:
+        if getattr(self, "_dir", None):
+            self._exchange(b"")
+        elif self._dist is not None:
             self._dist.barrier()
 
     def max_over_ranks(self, values):
         """Element-wise maximum of a list of floats over all ranks."""
+        if getattr(self, "_dir", None):
+            rows = [np.frombuffer(x, dtype=np.float64) for x in
+                    self._exchange(np.asarray(list(values), dtype=np.float64).tobytes())]
+            return [float(v) for v in np.max(np.stack(rows), axis=0)]
         if self._dist is None:
             return [float(v) for v in values]
         import torch
@@ -58,6 +95,8 @@ class Ranks:
 
     def same_everywhere(self, payload: bytes) -> bool:
         """True when every rank holds the same bytes (compared by digest)."""
+        if getattr(self, "_dir", None):
+            return len(set(self._exchange(hashlib.sha256(payload).digest()))) == 1
         if self._dist is None:
             return True
         import torch

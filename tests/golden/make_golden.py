@@ -293,6 +293,78 @@ def controller_vectors(cw, sp, sf, ctl):
     return out
 
 
+class FailingUvm(RecordingUvm):
+    """RecordingUvm whose next command is rejected, or whose next job fails."""
+
+    def __init__(self, ctl, allocations, generation=7):
+        super().__init__(ctl, allocations, generation)
+        self.reject_next = False
+        self.fail_next_job = False
+
+    def command(self, line):
+        if self.reject_next:
+            self.reject_next = False
+            self.commands.append(line)
+            return {"ok": False, "error": "busy"}
+        return super().command(line)
+
+    def _wait_job(self, job_id, timeout=0):
+        if self.fail_next_job:
+            self.fail_next_job = False
+            raise self.ctl.ControlError(f"UVM job {job_id} for PID 1234 failed with CUDA error 700")
+        return super()._wait_job(job_id, timeout)
+
+
+def controller_failure_vectors(cw, sp, sf, ctl):
+    """How the window controller reacts to metrics it cannot use, a command the
+    socket rejects and a job that fails: the exception (type, text), the command
+    lines sent, and the state afterwards."""
+    kw = dict(allocation_bytes=134217728, allocation_count=8, bytes_per_token=2048,
+              width_tokens=16384, lookahead_tokens=8192, quantum_tokens=1024,
+              min_update_seconds=1.0, idle_only=True)
+    allocs = [dict(id=i + 1, bytes=134217728, device=0) for i in range(8)] + [dict(id=20, bytes=1 << 20, device=0)]
+    c = cw.CacheWindowController(cw.CacheWindowSpec(**kw))
+    uvm = FailingUvm(ctl, allocs)
+    full = {"sglang:prompt_tokens_total": 100.0, "sglang:generation_tokens_total": 0.0,
+            "sglang:num_running_reqs": 0.0, "sglang:num_queue_reqs": 0.0}
+    inf, nan = float("inf"), float("nan")
+    script = [
+        ("update", dict(full), 10.0, True, None),
+        ("due", {k: v for k, v in full.items() if "prompt" not in k}, 12.0, False, None),
+        ("update", {k: v for k, v in full.items() if "generation" not in k}, 12.0, False, None),
+        ("update", dict(full, **{"sglang:prompt_tokens_total": -1.0}), 12.0, False, None),
+        ("due", dict(full, **{"sglang:generation_tokens_total": inf}), 12.0, False, None),
+        ("update", dict(full, **{"sglang:prompt_tokens_total": nan}), 12.0, False, None),
+        # the gauges are looked up only when the window moved and the interval has passed
+        ("due", {k: v for k, v in dict(full, **{"sglang:prompt_tokens_total": 9000.0}).items() if "running" not in k},
+         12.0, False, None),
+        ("update", {k: v for k, v in dict(full, **{"sglang:prompt_tokens_total": 9000.0}).items() if "queue" not in k},
+         12.0, False, None),
+        ("due", {k: v for k, v in full.items() if "running" not in k}, 12.0, False, None),      # window unchanged
+        ("update", dict(full, **{"sglang:prompt_tokens_total": 9000.0}), 12.0, False, "reject"),
+        ("update", dict(full, **{"sglang:prompt_tokens_total": 9000.0}), 12.5, False, "fail_job"),
+        ("update", dict(full, **{"sglang:prompt_tokens_total": 9000.0}), 13.0, False, None),    # state was dropped: full plan
+        ("update", dict(full, **{"sglang:prompt_tokens_total": 30000.0}), 15.0, False, None),
+    ]
+    log = []
+    for op, m, now, initial, trouble in script:
+        uvm.reject_next, uvm.fail_next_job = trouble == "reject", trouble == "fail_job"
+        before = len(uvm.commands)
+        entry = dict(op=op, metrics={k: (repr(v) if v != v or v in (inf, -inf) else v) for k, v in m.items()},
+                     now=now, initial=initial, trouble=trouble)
+        try:
+            got = c.due(m, now) if op == "due" else strip_times(c.update(uvm, m, now, initial=initial))
+            entry["result"] = got
+        except Exception as e:                                   # noqa: BLE001 -- the type is the datum
+            entry["error"] = [type(e).__name__, str(e) if not isinstance(e, KeyError) else e.args[0]]
+        entry["commands"] = uvm.commands[before:]
+        entry["current"] = list(c.current) if c.current else None
+        entry["signature_known"] = c.signature is not None
+        entry["highwater"] = c.completed_highwater
+        log.append(entry)
+    return dict(spec=kw, allocations=allocs, generation=7, log=log)
+
+
 def placement_controller_vectors(cw, sp, sf, ctl):
     """SlotPlacementController.choose/update against hand-built snapshots."""
     kw = dict(allocation_bytes=16 * 2097152, allocation_count=4, bytes_per_token=2048,
@@ -573,6 +645,7 @@ def main():
         runs=run_vectors(probe, sp),
         feedback=feedback_vectors(sf, sp, probe),
         window_controller=controller_vectors(cw, sp, sf, ctl),
+        controller_failures=controller_failure_vectors(cw, sp, sf, ctl),
         placement_controller=placement_controller_vectors(cw, sp, sf, ctl),
         placement_chain=placement_chain_vectors(cw, sp, sf, ctl, probe),
         targets=target_vectors(ctl),

@@ -90,6 +90,56 @@ def test_window_controller_replay(golden):
             assert (list(ctl.current) if ctl.current else None) == step["current"]
 
 
+class FailingUvm(RecordingUvm):
+    def __init__(self, allocations, generation):
+        super().__init__(allocations, generation)
+        self.reject_next = self.fail_next_job = False
+
+    def command(self, line):
+        if self.reject_next:
+            self.reject_next = False
+            self.commands.append(line)
+            return {"ok": False, "error": "busy"}
+        return super().command(line)
+
+    def _wait_job(self, job_id, timeout=0):
+        if self.fail_next_job:
+            self.fail_next_job = False
+            raise ControlError(f"UVM job {job_id} for PID 1234 failed with CUDA error 700")
+        return super()._wait_job(job_id, timeout)
+
+
+def test_window_controller_failures_replay(golden):
+    """Metrics the policy cannot use (a counter missing, negative, infinite, NaN; a
+    gauge missing when it is needed), a command the socket rejects and a job that
+    fails: same exception type and text, same lines on the wire and same state
+    afterwards as the reference controller."""
+    block = golden["controller_failures"]
+    ctl = cw.CacheWindowController(cw.CacheWindowSpec(**block["spec"]))
+    uvm = FailingUvm(block["allocations"], block["generation"])
+    kinds = {"ControlError": ControlError, "KeyError": KeyError, "ValueError": ValueError}
+    for step in block["log"]:
+        metrics = {k: (float(v.strip("'")) if isinstance(v, str) else v) for k, v in step["metrics"].items()}
+        uvm.reject_next, uvm.fail_next_job = step["trouble"] == "reject", step["trouble"] == "fail_job"
+        before = len(uvm.commands)
+
+        def call():
+            if step["op"] == "due":
+                return ctl.due(metrics, step["now"])
+            return _strip(ctl.update(uvm, metrics, step["now"], initial=step["initial"]))
+        if "error" in step:
+            kind, text = step["error"]
+            with pytest.raises(kinds[kind]) as e:
+                call()
+            assert (e.value.args[0] if kind == "KeyError" else str(e.value)) == text, step
+        else:
+            assert call() == step["result"], step
+        assert uvm.commands[before:] == step["commands"]
+        assert (list(ctl.current) if ctl.current else None) == step["current"]
+        assert (ctl.signature is not None) == step["signature_known"]
+        assert ctl.completed_highwater == step["highwater"]
+
+
 def test_placement_controller_replay(golden, tmp_path, monkeypatch):
     block = golden["placement_controller"]
     monkeypatch.setenv("RETARGET_SLOT_FEEDBACK_DIR", str(tmp_path))

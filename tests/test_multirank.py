@@ -17,7 +17,7 @@ WORKER = textwrap.dedent("""
     from retarget_b200 import workloads
     from retarget_b200.multirank import Ranks
     from oracle import c_oracle
-    r = Ranks("gloo").start()
+    r = Ranks({backend!r}).start()
     assert r.world == 2
     batch = workloads.tp_shard(0, requests=32)          # the same slot table on every rank
     co = c_oracle.COracle(batch.layout, device=r.local_rank)
@@ -36,12 +36,16 @@ WORKER = textwrap.dedent("""
 """)
 
 
-def test_two_ranks_plan_independently_and_agree(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("backend", ["gloo", "file"])
+def test_two_ranks_plan_independently_and_agree(tmp_path, backend):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     script = tmp_path / "worker.py"
-    script.write_text(WORKER.format(root=str(ROOT)))
+    script.write_text(WORKER.format(root=str(ROOT), backend=backend))
     procs = []
     for rank in range(2):
         env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE="2",
