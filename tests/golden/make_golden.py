@@ -429,6 +429,85 @@ def placement_controller_vectors(cw, sp, sf, ctl):
     return dict(cache_spec=kw, slot_spec=sspec, allocations=allocs, generation=7, pid=4242, log=log)
 
 
+def placement_failure_vectors(cw, sp, sf, ctl):
+    """SlotPlacementController when things go wrong: no snapshot file, a snapshot
+    of another process or geometry, a stale one, a rejected command, a failed
+    job, another set of cache allocations, too few of them."""
+    kw = dict(allocation_bytes=16 * 2097152, allocation_count=4, bytes_per_token=2048,
+              width_tokens=4096, lookahead_tokens=1024, quantum_tokens=1024)
+    allocs = [dict(id=i + 1, bytes=16 * 2097152, device=0) for i in range(4)] + [dict(id=9, bytes=4096, device=0)]
+    sspec = dict(block_tokens=1024, lookahead_tokens=4096, min_update_seconds=.25,
+                 max_blocks_per_update=2, active_seconds=2.0, refresh_seconds=10.0,
+                 max_feedback_lag_seconds=1.0)
+    log = []
+    clock = {"now": 0.0}
+
+    class ScriptedTime:
+        @staticmethod
+        def monotonic():
+            return clock["now"]
+    real_time = sp.time
+    sp.time = ScriptedTime
+    try:
+        with tempfile.TemporaryDirectory() as tmp:
+            os.environ["RETARGET_SLOT_FEEDBACK_DIR"] = tmp
+            c = sp.SlotPlacementController(cw.CacheWindowSpec(**kw), sp.SlotPlacementSpec(**sspec), 4242)
+            c.signature = tuple((a["id"], a["bytes"], a["device"]) for a in allocs[:4])
+            c.epoch = 1
+            uvm = FailingUvm(ctl, allocs)
+            path = Path(tmp) / "4242.json"
+
+            def doc(now, reads, free, **over):
+                d = dict(version=1, pid=4242, epoch=1, sequence=0, observed_monotonic_s=now,
+                         published_monotonic_s=now, capacity_tokens=16383, block_tokens=1024,
+                         block_versions=[0] * 16, recent_reads=reads, recent_writes=[], free_head_blocks=free)
+                d.update(over)
+                return d
+            steps = [
+                (50.0, None, None, None),                                                   # no file yet
+                (50.5, doc(50.5, [[3, 50.4]], [], pid=7), None, None),                       # another process
+                (51.0, doc(51.0, [[3, 50.9]], [], block_tokens=256), None, None),            # another geometry
+                (51.5, doc(51.5, [[3, 51.4]], [], observed_monotonic_s=49.0), None, None),   # published late
+                (52.0, doc(52.0, [[3, 51.9], [5, 51.8]], [7]), "reject", None),
+                (52.5, doc(52.5, [[3, 52.4], [5, 52.3]], [7]), "fail_job", None),
+                (53.0, doc(53.0, [[3, 52.9], [5, 52.8]], [7]), None, None),                  # record was dropped: again
+                (53.5, doc(53.5, [[3, 53.4], [5, 53.3]], [7]), None, None),
+                (54.0, doc(54.0, [[3, 53.9], [5, 53.8], [6, 53.7]], [7]), None, "renumber"),  # other allocation ids
+                (54.5, doc(54.5, [[3, 54.4], [5, 54.3], [6, 54.2], [8, 54.1]], [7]), None, "drop_one"),
+            ]
+            for now, snapshot, trouble, registry in steps:
+                clock["now"] = now
+                if snapshot is None:
+                    if path.exists():
+                        path.unlink()
+                else:
+                    path.write_text(json.dumps(snapshot))
+                if registry == "renumber":
+                    uvm.allocs = [dict(a, id=a["id"] + 40) for a in allocs]
+                elif registry == "drop_one":
+                    uvm.allocs = uvm.allocs[1:]
+                uvm.reject_next, uvm.fail_next_job = trouble == "reject", trouble == "fail_job"
+                m = {"sglang:prompt_tokens_total": 0.0, "sglang:generation_tokens_total": 0.0}
+                entry = dict(now=now, snapshot=snapshot, trouble=trouble, registry=registry)
+                before = len(uvm.commands)
+                for op in ("due", "update"):
+                    try:
+                        got = c.due(m, now) if op == "due" else c.update(uvm, m, now)
+                        if op == "update" and got is not None:
+                            got = {k: got[k] for k in ("desired_blocks", "gpu_blocks", "committed_blocks",
+                                                       "requested_gpu_bytes")}
+                        entry[op] = got
+                    except Exception as e:                       # noqa: BLE001 -- the type is the datum
+                        entry[op + "_error"] = [type(e).__name__, str(e)]
+                entry["commands"] = uvm.commands[before:]
+                entry["committed"] = sorted(c.committed)
+                entry["last_attempt"] = c.last_attempt
+                log.append(entry)
+    finally:
+        sp.time = real_time
+    return dict(cache_spec=kw, slot_spec=sspec, allocations=allocs, generation=7, pid=4242, log=log)
+
+
 def placement_chain_vectors(cw, sp, sf, ctl, probe):
     """The whole event-driven chain of the reference, unmodified: event rows ->
     SlotFeedback.consume/publish (snapshot file) -> SlotPlacementController.update,
@@ -647,6 +726,7 @@ def main():
         window_controller=controller_vectors(cw, sp, sf, ctl),
         controller_failures=controller_failure_vectors(cw, sp, sf, ctl),
         placement_controller=placement_controller_vectors(cw, sp, sf, ctl),
+        placement_failures=placement_failure_vectors(cw, sp, sf, ctl),
         placement_chain=placement_chain_vectors(cw, sp, sf, ctl, probe),
         targets=target_vectors(ctl),
     )

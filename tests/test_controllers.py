@@ -175,6 +175,56 @@ def test_placement_controller_replay(golden, tmp_path, monkeypatch):
     assert ctl2.choose(ctl2.snapshot(50.0), 50.0) == ([3, 7, 9, 12], [3, 7])
 
 
+def test_placement_controller_failures_replay(golden, tmp_path, monkeypatch):
+    """No snapshot file, a snapshot of another process or geometry, a stale one, a
+    rejected command, a failed job, renumbered allocations, a missing allocation:
+    same answers, exceptions, lines and record as the reference controller."""
+    block = golden["placement_failures"]
+    monkeypatch.setenv("RETARGET_SLOT_FEEDBACK_DIR", str(tmp_path))
+    clock = {"now": 0.0}
+
+    class Scripted:
+        @staticmethod
+        def monotonic():
+            return clock["now"]
+    monkeypatch.setattr(sp, "time", Scripted)
+    ctl = sp.SlotPlacementController(cw.CacheWindowSpec(**block["cache_spec"]),
+                                     sp.SlotPlacementSpec(**block["slot_spec"]), block["pid"])
+    ctl.signature = tuple((a["id"], a["bytes"], a["device"]) for a in block["allocations"][:4])
+    ctl.epoch = 1
+    uvm = FailingUvm(block["allocations"], block["generation"])
+    path = tmp_path / f"{block['pid']}.json"
+    keys = ("desired_blocks", "gpu_blocks", "committed_blocks", "requested_gpu_bytes")
+    for step in block["log"]:
+        clock["now"] = now = step["now"]
+        if step["snapshot"] is None:
+            path.unlink(missing_ok=True)
+        else:
+            path.write_text(json.dumps(step["snapshot"]))
+        if step["registry"] == "renumber":
+            uvm.allocs = [dict(a, id=a["id"] + 40) for a in block["allocations"]]
+        elif step["registry"] == "drop_one":
+            uvm.allocs = uvm.allocs[1:]
+        uvm.reject_next, uvm.fail_next_job = step["trouble"] == "reject", step["trouble"] == "fail_job"
+        metrics = {"sglang:prompt_tokens_total": 0.0, "sglang:generation_tokens_total": 0.0}
+        before = len(uvm.commands)
+        for op in ("due", "update"):
+            def call():
+                if op == "due":
+                    return ctl.due(metrics, now)
+                got = ctl.update(uvm, metrics, now)
+                return None if got is None else {k: got[k] for k in keys}
+            if op + "_error" in step:
+                with pytest.raises(ControlError) as e:
+                    call()
+                assert [type(e.value).__name__, str(e.value)] == step[op + "_error"], (now, op)
+            else:
+                assert call() == step[op], (now, op)
+        assert uvm.commands[before:] == step["commands"], now
+        assert sorted(ctl.committed) == step["committed"], now
+        assert ctl.last_attempt == step["last_attempt"], now
+
+
 def test_budget_rules():
     with pytest.raises(ValueError, match="KV budget must be divisible by block_tokens"):
         sp.SlotPlacementController(cw.CacheWindowSpec(16 * 2097152, 4, 2048, 4096, 1024, 1024),
