@@ -632,6 +632,30 @@ def run_ours(args):
                                       "gbs": width * batches[0].n_idx / us / 1e3}
                     tp.close()
                     del tables
+            # the allocation-free scan (scratch in a static device array, scan only, 64-bit ids)
+            fn = capi.lib.rt_scan_slots_static
+            fn.restype = C.c_int
+            fn.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p,
+                           C.c_void_p, C.c_void_p]
+            d_bits = torch.zeros(lay.n_groups * 32, dtype=torch.int32, device=dev)
+
+            def static_scan(i):
+                b = batches[i % 2]
+                capi.check(fn(d_slots[i % 2].data_ptr(), b.group_off.ctypes.data, lay.n_groups, lay.capacity,
+                              lay.block_tokens, lay.n_blocks, d_bits.data_ptr(), d_res.data_ptr(),
+                              stream.cuda_stream), "rt_scan_slots_static")
+            for i in range(4):
+                static_scan(i)
+            torch.cuda.synchronize()
+            t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            t[0].record(stream)
+            for i in range(200):
+                static_scan(i)
+            t[1].record(stream)
+            torch.cuda.synchronize()
+            us = t[0].elapsed_time(t[1]) * 1e3 / 200
+            variants["static_scan_only"] = {"us_per_step": us, "steps": 200, "gbs": 8 * batches[0].n_idx / us / 1e3,
+                                            "note": "rt_scan_slots_static: a memset of its scratch + one launch per call"}
             for i in range(2):      # leave the resident state as the main workload left it
                 timer.step(d_slots, batches, W + n_timed + i)
             torch.cuda.synchronize()

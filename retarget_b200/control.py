@@ -69,56 +69,46 @@ def _bind():
 _lib = _bind()
 
 
-@dataclasses.dataclass(frozen=True)
-class UvmStatus:
-    """A `status` reply; field names are the reply's (experiments/control.py:53-83),
-    because result dictionaries carry ``dataclasses.asdict(status)``."""
-    pid: int
-    managed_bytes: int
-    allocation_count: int
-    allocation_generation: int
-    busy: bool
-    job_id: int
-    completed_job: int
-    last_error: int
-    completed_cpu_bytes: int
-    completed_gpu_bytes: int
-    job_completed_bytes: int
-
-    @classmethod
-    def from_reply(cls, reply: dict[str, Any]) -> "UvmStatus":
-        """Parsed by the library from the reply's JSON text."""
-        raw = _StatusStruct()
-        status = _lib.rt_uvm_parse_status(json.dumps(reply, separators=(",", ":")).encode(), C.byref(raw))
-        if status == capi.RT_ERR_PLAN:
-            raise ControlError(f"UVM status failed: {reply}")
-        if status:
-            missing = next((f.name for f in dataclasses.fields(cls)
-                            if f.name not in reply and f.name != "allocation_generation"), "?")
-            raise KeyError(missing)
-        return cls(**{f.name: (bool(raw.busy) if f.name == "busy" else int(getattr(raw, f.name)))
-                      for f in dataclasses.fields(cls)})
+# The fields of a `status` reply in the order the server writes them
+# (select.cpp:24058-24068); `busy` is the one boolean.  The record type is made
+# from this list so that it, the native parser's structure and the reply cannot
+# drift apart; result dictionaries carry ``dataclasses.asdict(status)``.
+STATUS_FIELDS = ("pid", "managed_bytes", "allocation_count", "allocation_generation", "busy", "job_id",
+                 "completed_job", "last_error", "completed_cpu_bytes", "completed_gpu_bytes",
+                 "job_completed_bytes")
+assert set(STATUS_FIELDS) == {name for name, _ in _StatusStruct._fields_}
 
 
-@dataclasses.dataclass(frozen=True)
-class UvmTargetResult:
-    """What ``set_target`` did: the request, the request clamped to the managed
-    bytes, and the page-aligned target that was sent."""
-    requested_bytes: int
-    clamped_bytes: int
-    submitted_bytes: int
-    status: UvmStatus
+def _status_from_reply(cls, reply: dict[str, Any]):
+    """Builds the record from a reply dictionary; the parsing is the library's."""
+    raw = _StatusStruct()
+    status = _lib.rt_uvm_parse_status(json.dumps(reply, separators=(",", ":")).encode(), C.byref(raw))
+    if status == capi.RT_ERR_PLAN:
+        raise ControlError(f"UVM status failed: {reply}")
+    if status:
+        raise KeyError(next((n for n in STATUS_FIELDS if n not in reply and n != "allocation_generation"), "?"))
+    return cls(*((bool(raw.busy) if n == "busy" else int(getattr(raw, n))) for n in STATUS_FIELDS))
 
 
-@dataclasses.dataclass(frozen=True)
-class UvmRetargetResult:
-    """What ``retarget`` did, with the previous target it moved away from."""
-    previous_requested_bytes: int
-    previous_submitted_bytes: int
-    requested_bytes: int
-    clamped_bytes: int
-    submitted_bytes: int
-    status: UvmStatus
+UvmStatus = dataclasses.make_dataclass(
+    "UvmStatus", [(n, bool if n == "busy" else int) for n in STATUS_FIELDS], frozen=True,
+    namespace={"from_reply": classmethod(_status_from_reply),
+               "__doc__": "A `status` reply (the reference's UvmStatus, experiments/control.py:53-83)."})
+UvmStatus.__module__ = __name__
+
+
+# What a prefix plan did: the request, the request clamped to the managed bytes,
+# the page-aligned target that was sent, the status after the job.  A retarget
+# also says which target it moved away from.  (Field names are the reference's:
+# its callers read them, experiments/control.py:85-104.)
+_TARGET_FIELDS = ("requested_bytes", "clamped_bytes", "submitted_bytes")
+UvmTargetResult = dataclasses.make_dataclass(
+    "UvmTargetResult", [*((n, int) for n in _TARGET_FIELDS), ("status", UvmStatus)], frozen=True)
+UvmRetargetResult = dataclasses.make_dataclass(
+    "UvmRetargetResult", [*(("previous_" + n, int) for n in _TARGET_FIELDS[::2]),
+                          *((n, int) for n in _TARGET_FIELDS), ("status", UvmStatus)], frozen=True)
+for _record in (UvmTargetResult, UvmRetargetResult):
+    _record.__module__ = __name__
 
 
 def aligned_uvm_target(allocation_sizes, desired_bytes: int, page_size: int) -> int:
@@ -197,6 +187,13 @@ class _Protocol:
     def _pending_job(self):
         return self._in_flight[0] if self._in_flight else None
 
+    def _accepted(self, line: str, refusal: str) -> dict[str, Any]:
+        """Sends one line; a reply that is not ok becomes ControlError(refusal + reply)."""
+        reply = self.command(line)
+        if not reply.get("ok"):
+            raise ControlError(f"{refusal}: {reply}")
+        return reply
+
     # ---- queries ----
     def status(self) -> UvmStatus:
         answer = UvmStatus.from_reply(self.command("status"))
@@ -205,12 +202,10 @@ class _Protocol:
         return answer
 
     def _allocation_snapshot(self) -> tuple[int, list[dict[str, int]]]:
-        reply = self.command("list")
-        if not reply.get("ok"):
-            raise ControlError(f"UVM list failed: {reply}")
+        listing = self._accepted("list", "UVM list failed")
         rows = [{key: int(entry[key]) for key in ("id", "bytes", "device")}
-                for entry in reply.get("allocations", [])]
-        return int(reply.get("allocation_generation", 0)), rows
+                for entry in listing.get("allocations", [])]
+        return int(listing.get("allocation_generation", 0)), rows
 
     def allocations(self) -> list[dict[str, int]]:
         return self._allocation_snapshot()[1]
@@ -269,10 +264,7 @@ class _Protocol:
         return generation, signature, clamped, [aligned_uvm_target(sizes, c, page) for c in clamped]
 
     def _submit_prefix_plan(self, line: str, what: str, placement: _Placement, wait: bool, timeout: float):
-        reply = self.command(line)
-        if not reply.get("ok"):
-            raise ControlError(f"UVM {what} for PID {self.pid} failed: {reply}")
-        job_id = int(reply["job_id"])
+        job_id = int(self._accepted(line, f"UVM {what} for PID {self.pid} failed")["job_id"])
         if not wait:
             self._in_flight = (job_id, placement)
             return job_id, None
@@ -326,9 +318,7 @@ class _Protocol:
                  timeout: float = 120.0) -> UvmStatus:
         if where not in ("cpu", "gpu"):
             raise ValueError("where must be 'cpu' or 'gpu'")
-        reply = self.command(f"prefetch {allocation_id} {offset} {length} {where}")
-        if not reply.get("ok"):
-            raise ControlError(f"UVM prefetch rejected: {reply}")
+        reply = self._accepted(f"prefetch {allocation_id} {offset} {length} {where}", "UVM prefetch rejected")
         return self._wait_job(int(reply["job_id"]), timeout=timeout)
 
 
