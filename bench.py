@@ -401,8 +401,9 @@ def prefetch_leg(torch, dev, gib: int = 4):
 def feedback_leg(torch, dev, stream, steps=100, warm=8, cpu=True):
     """The event-driven path on the incremental decode trace (65,536-slot pool,
     40 layers, Poisson arrivals, one token per live request per step):
-    rt_feedback_alloc / rt_feedback_attention / rt_feedback_plan with every index
-    tensor already in HBM; beside it the Python restatement of
+    rt_feedback_step (allocation event + attention event + plan in one launch) with
+    every index tensor already in HBM, launched step by step and as one captured
+    graph, and the same steps as the three separate calls; beside it the Python restatement of
     SlotFeedback.consume -> publish -> target_blocks -> choose -> blocksv on one core."""
     from retarget_b200 import capi, workloads
     from retarget_b200.feedback import DeviceFeedback
@@ -441,35 +442,63 @@ def feedback_leg(torch, dev, stream, steps=100, warm=8, cpu=True):
     d_res = torch.zeros(64, dtype=torch.uint8, device=dev)
     h = stream.cuda_stream
 
-    def step(i):
+    policy = dict(budget=budget, max_blocks_per_update=max_blocks, active_seconds=active, refresh_seconds=refresh,
+                  flags=capi.RT_PLAN_EVICT, d_out=d_out, d_result=d_res, stream=h)
+
+    def three_calls(i):
         a, head, r, w = d_steps[i]
         if a is not None:
             fb.alloc(a, times[i] - 0.002, head, h)
         fb.attention(r, w, times[i], h)
-        fb.plan(times[i] + 0.001, budget=budget, max_blocks_per_update=max_blocks, active_seconds=active,
-                refresh_seconds=refresh, flags=capi.RT_PLAN_EVICT, d_out=d_out, d_result=d_res, stream=h)
+        fb.plan(times[i] + 0.001, **policy)
 
-    for i in range(warm):
-        step(i)
-    torch.cuda.synchronize()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    ev[0].record(stream)
-    for i in range(warm, warm + steps):
-        step(i)
-    ev[1].record(stream)
-    torch.cuda.synchronize()
-    out["us_per_step"] = ev[0].elapsed_time(ev[1]) * 1e3 / steps
+    def one_launch(i):
+        a, head, r, w = d_steps[i]
+        fb.step(d_allocated=a, t_allocated=times[i] - 0.002, d_free_head=head, d_read=r, d_written=w,
+                t_attention=times[i], now=times[i] + 0.001, **policy)
+
+    def restart():
+        fb.clear(99.0, h)
+        planner.set_resident([set()])
+
+    def timed(step, graph=False):
+        """The trace from the start: `warm` untimed steps, then `steps` timed ones --
+        launched one by one, or (graph) captured once and replayed as one graph."""
+        restart()
+        for i in range(warm):
+            step(i)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        if graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(warm, warm + steps):
+                    step(i)
+            ev[0].record(stream)
+            g.replay()
+        else:
+            ev[0].record(stream)
+            for i in range(warm, warm + steps):
+                step(i)
+        ev[1].record(stream)
+        torch.cuda.synchronize()
+        return ev[0].elapsed_time(ev[1]) * 1e3 / steps
+
+    out["three_calls_us_per_step"] = timed(three_calls)
+    out["one_launch_us_per_step"] = timed(one_launch)
+    out["one_launch_graph_us_per_step"] = timed(one_launch, graph=True)
+    out["us_per_step"] = out["one_launch_us_per_step"]
     # the same trace again, one step at a time, to count the ranges
-    fb.clear(99.0, h)
-    planner.set_resident([set()])
+    restart()
     gpu_ranges = 0
     for i in range(warm + steps):
-        step(i)
+        one_launch(i)
         stream.synchronize()
         if i >= warm:
             gpu_ranges += result_from_tensor(d_res)["n_ranges"]
     ids = sum(len(e.alloc_slots) + len(e.read_slots) + len(e.write_slots) for e in trace[warm:]) / steps
-    out.update(steps=steps, event_ids_per_step=ids, launches_per_step=sum(2 + (a is not None) for a, *_ in d_steps[warm:]) / steps,
+    out.update(steps=steps, event_ids_per_step=ids, launches_per_step=1,
+               three_calls_launches_per_step=sum(2 + (a is not None) for a, *_ in d_steps[warm:]) / steps,
                ranges_total=gpu_ranges, workload="incremental decode trace L40 S65536, event-driven feedback state")
     if cpu_ranges is not None:
         out["ranges_match_cpu"] = cpu_ranges == gpu_ranges

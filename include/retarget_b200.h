@@ -594,6 +594,33 @@ typedef struct rt_feedback_policy {
 int rt_feedback_plan(rt_feedback *fb, const rt_feedback_policy *policy, double at, double now,
                      rt_range *out, uint32_t cap, rt_plan_result *result, void *stream);
 
+/* One decode step's events, as the serving engine produces them: the slots
+ * the allocator handed out (with the new free-list head, or null), then the
+ * slots attention read and wrote.  All pointers are DEVICE pointers, int64 for
+ * rt_feedback_step, int32 for rt_feedback_step_i32. */
+typedef struct rt_feedback_step_ids {
+    const void *d_allocated;         /* may be null with n_allocated == 0: no allocation this step */
+    uint64_t n_allocated;
+    const void *d_free_head;         /* null: derive the head from the known one */
+    uint32_t n_free;
+    uint32_t reserved;
+    double t_allocated;
+    const void *d_read;
+    uint64_t n_read;
+    const void *d_written;
+    uint64_t n_written;
+    double t_attention;
+} rt_feedback_step_ids;
+
+/* rt_feedback_alloc + rt_feedback_attention + rt_feedback_plan (at =
+ * t_attention) as ONE kernel launch, with the same results as the three calls
+ * in that order: the hooks of one decode step (slot_feedback.py:49-79) and the
+ * controller's update that follows them (slot_placement.py:83-94,150-153). */
+int rt_feedback_step(rt_feedback *fb, const rt_feedback_step_ids *ids, const rt_feedback_policy *policy,
+                     double now, rt_range *out, uint32_t cap, rt_plan_result *result, void *stream);
+int rt_feedback_step_i32(rt_feedback *fb, const rt_feedback_step_ids *ids, const rt_feedback_policy *policy,
+                         double now, rt_range *out, uint32_t cap, rt_plan_result *result, void *stream);
+
 /* ------------------------------------------------------------------ */
 /* Synthetic paged KV reader                                            */
 /* ------------------------------------------------------------------ */

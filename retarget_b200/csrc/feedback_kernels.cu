@@ -32,7 +32,8 @@ struct FeedbackState {
     double *commit_time;       // [n_blocks]
     long long *free_head;      // [kFreeHeadMax] slot ids, queue order
     int32_t *free_count;       // [1]
-    uint32_t *event_blocks;    // [2 * kWords] scratch: blocks touched by the current event's two lists
+    uint32_t *event_blocks;    // [3 * kWords] scratch: blocks touched by the current event's lists
+                               //   (one event: [a | b]; a whole step: [allocated | read | written])
     uint32_t *arrivals;        // [1] scratch: CTAs of the current event that have finished marking
     uint32_t *slot_marks;      // [(capacity + 32) / 32] scratch: slots of the current alloc event
     unsigned long long *bad;   // [2] invalid / ignored ids seen so far
@@ -100,6 +101,7 @@ __device__ __forceinline__ void mark_ids(const Id *ids, long long n, const Geome
 // Byte map -> the event's words (call between two CTA barriers).
 __device__ __forceinline__ void flush_event_map(const uint8_t *s_map, uint32_t *words) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (warp >= 8) return;                      // eight warps x four words cover the map
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         uint32_t word = warp * 4 + k;
@@ -149,12 +151,49 @@ __device__ void update_free_head(const FeedbackState &st, const Id *fresh, int n
     if (tid == 0) *st.free_count = *s_base;
 }
 
+// What needs a whole allocation event, by the CTA that arrived last:
+// versions[b] = max(generations[b*T .. (b+1)*T)) and write_seen = t for every
+// touched block (slot_feedback.py:59-62), the free-list head, and the clean-up
+// of the slot marks.  `words`: the event's touched-block words.
+template <typename Id>
+__device__ void finish_alloc_event(const EventArgs &ev, const Geometry &geo, const FeedbackState &st,
+                                   const uint32_t *words, int *s_warp, int *s_base) {
+    const Id *ids_a = static_cast<const Id *>(ev.ids_a);
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t b = warp; b < geo.n_blocks; b += blockDim.x >> 5) {          // a warp per touched block
+        if (!((__ldcg(&words[b >> 5]) >> (b & 31)) & 1u)) continue;             // uniform over the warp
+        unsigned long long lo = (unsigned long long)b * geo.block_tokens;
+        unsigned long long hi = lo + geo.block_tokens;
+        if (hi > geo.capacity + 1) hi = geo.capacity + 1;
+        int best = 0;
+        for (unsigned long long s = lo + lane; s < hi; s += 32) best = max(best, __ldcg(&st.generations[s]));
+        best = __reduce_max_sync(0xffffffffu, best);
+        if (lane == 0) { st.versions[b] = best; st.write_seen[b] = ev.t; }
+    }
+    update_free_head(st, static_cast<const Id *>(ev.fresh), ev.n_fresh, geo.capacity, s_warp, s_base);
+    __syncthreads();
+    // the slot marks served the free-head filter: clear them again
+    for (long long i = threadIdx.x; i < ev.n_a; i += blockDim.x) {
+        long long s = (long long)ids_a[i];
+        if ((unsigned long long)s <= geo.capacity) st.slot_marks[(uint32_t)s >> 5] = 0;
+    }
+}
+
+// read_seen = t (slot_feedback.py:72-73), write_seen = t (:74-75)
+__device__ __forceinline__ void finish_attention_event(double t, const Geometry &geo, const FeedbackState &st,
+                                                       const uint32_t *read_words, const uint32_t *write_words) {
+    for (uint32_t b = threadIdx.x; b < geo.n_blocks; b += blockDim.x) {
+        if ((__ldcg(&read_words[b >> 5]) >> (b & 31)) & 1u) st.read_seen[b] = t;
+        if ((__ldcg(&write_words[b >> 5]) >> (b & 31)) & 1u) st.write_seen[b] = t;
+    }
+}
+
 template <typename Id>
 __global__ void __launch_bounds__(256)
 feedback_event_kernel(EventArgs ev, Geometry geo, FeedbackState st) {
     const Id *ids_a = static_cast<const Id *>(ev.ids_a), *ids_b = static_cast<const Id *>(ev.ids_b);
     __shared__ uint8_t s_map[2][RT_MAX_BLOCKS];
-    __shared__ int s_warp[8], s_base, s_last;
+    __shared__ int s_warp[32], s_base, s_last;
     reinterpret_cast<uint32_t *>(s_map[0])[threadIdx.x] = 0;
     reinterpret_cast<uint32_t *>(s_map[1])[threadIdx.x] = 0;
     __syncthreads();
@@ -164,7 +203,7 @@ feedback_event_kernel(EventArgs ev, Geometry geo, FeedbackState st) {
     __syncthreads();
     flush_event_map(s_map[0], st.event_blocks);
     if (ev.n_b) flush_event_map(s_map[1], st.event_blocks + kWords);
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
     uint32_t inv = warp_sum(invalid), ign = warp_sum(ignored);
     if (lane == 0) {
         if (inv) atomicAdd(&st.bad[0], (unsigned long long)inv);
@@ -177,33 +216,8 @@ feedback_event_kernel(EventArgs ev, Geometry geo, FeedbackState st) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    if (!ev.alloc) {
-        // read_seen = t (slot_feedback.py:72-73), write_seen = t (:74-75)
-        for (uint32_t b = threadIdx.x; b < geo.n_blocks; b += blockDim.x) {
-            if ((__ldcg(&st.event_blocks[b >> 5]) >> (b & 31)) & 1u) st.read_seen[b] = ev.t;
-            if ((__ldcg(&st.event_blocks[kWords + (b >> 5)]) >> (b & 31)) & 1u) st.write_seen[b] = ev.t;
-        }
-    } else {
-        // versions[b] = max(generations[b*T .. (b+1)*T)), write_seen = t (slot_feedback.py:59-62):
-        // a warp per touched block
-        for (uint32_t b = warp; b < geo.n_blocks; b += blockDim.x >> 5) {
-            if (!((__ldcg(&st.event_blocks[b >> 5]) >> (b & 31)) & 1u)) continue;      // uniform over the warp
-            unsigned long long lo = (unsigned long long)b * geo.block_tokens;
-            unsigned long long hi = lo + geo.block_tokens;
-            if (hi > geo.capacity + 1) hi = geo.capacity + 1;
-            int best = 0;
-            for (unsigned long long s = lo + lane; s < hi; s += 32) best = max(best, __ldcg(&st.generations[s]));
-            best = __reduce_max_sync(0xffffffffu, best);
-            if (lane == 0) { st.versions[b] = best; st.write_seen[b] = ev.t; }
-        }
-        update_free_head(st, static_cast<const Id *>(ev.fresh), ev.n_fresh, geo.capacity, s_warp, &s_base);
-        __syncthreads();
-        // the slot marks served the free-head filter: clear them again
-        for (long long i = threadIdx.x; i < ev.n_a; i += blockDim.x) {
-            long long s = (long long)ids_a[i];
-            if ((unsigned long long)s <= geo.capacity) st.slot_marks[(uint32_t)s >> 5] = 0;
-        }
-    }
+    if (!ev.alloc) finish_attention_event(ev.t, geo, st, st.event_blocks, st.event_blocks + kWords);
+    else finish_alloc_event<Id>(ev, geo, st, st.event_blocks, s_warp, &s_base);
     __syncthreads();
     if (threadIdx.x < 2 * kWords) st.event_blocks[threadIdx.x] = 0;
     if (threadIdx.x == 0) *st.arrivals = 0;
@@ -271,14 +285,22 @@ static_assert(2 * 2 * kRankThreads * sizeof(unsigned long long) >= tail_smem_byt
 // (experiments/slot_placement.py:131-132), so a committed block that drops out
 // of the desired set for a while is not sent again when it comes back with its
 // version unchanged.
-__global__ void __launch_bounds__(kRankThreads)
-feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *resident, uint32_t *sets,
-                     const __grid_constant__ PlanArgs tail) {
-    __shared__ __align__(16) unsigned long long s_swap[2][2][kRankThreads];   // [buffer][hi|lo][thread]
-    __shared__ int s_free_pos[kRankThreads];
-    __shared__ uint32_t s_warp[32];
-    __shared__ uint8_t s_sel[kRankThreads], s_des[kRankThreads];
-    __shared__ int s_delivered;
+struct RankShared {
+    unsigned long long swap[2][2][kRankThreads];   // [buffer][hi|lo][thread]
+    int free_pos[kRankThreads];
+    uint32_t warp[32];
+    uint8_t sel[kRankThreads], des[kRankThreads];
+    int delivered;
+};
+
+__device__ void rank_and_plan(const Geometry &geo, const FeedbackState &st, const RankPolicy &pol, uint32_t *resident,
+                              uint32_t *sets, const PlanArgs &tail, RankShared &sh) {
+    auto &s_swap = sh.swap;
+    auto &s_free_pos = sh.free_pos;
+    auto &s_warp = sh.warp;
+    auto &s_sel = sh.sel;
+    auto &s_des = sh.des;
+    int &s_delivered = sh.delivered;
     const uint32_t b = threadIdx.x, lane = b & 31, warp = b >> 5, n_threads = blockDim.x;
     s_free_pos[b] = 0x7fffffff;
     __syncthreads();
@@ -386,6 +408,72 @@ feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *r
     if (lane == 0) resident[warp] = new_word;
 }
 
+__global__ void __launch_bounds__(kRankThreads)
+feedback_rank_kernel(Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *resident, uint32_t *sets,
+                     const __grid_constant__ PlanArgs tail) {
+    __shared__ __align__(16) RankShared sh;
+    rank_and_plan(geo, st, pol, resident, sets, tail, sh);
+}
+
+// --------------------------------------------------------------------------
+// one launch per decode step: allocation event + attention event + plan
+// --------------------------------------------------------------------------
+// What a serving engine does every decode step -- hand out pages, run
+// attention, ask for a plan -- folded into ONE launch.  Every CTA marks its
+// share of the three id lists (allocated, read, written); the CTA that arrives
+// last then does, in the order the separate calls would have: the allocation
+// event's finishing work, the attention event's stamps, the ranking and the
+// plan.  blockDim is the ranking's (a power of two covering the blocks).
+struct StepArgs {
+    EventArgs alloc;           // n_a == 0 and no fresh head: no allocation event this step
+    EventArgs attention;
+};
+
+template <typename Id>
+__global__ void __launch_bounds__(kRankThreads)
+feedback_step_kernel(StepArgs ev, Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *resident,
+                     uint32_t *sets, const __grid_constant__ PlanArgs tail) {
+    __shared__ __align__(16) RankShared sh;
+    __shared__ int s_base, s_last;
+    // the three byte maps live in the sort buffers until the ranking needs them
+    uint8_t(*s_map)[RT_MAX_BLOCKS] = reinterpret_cast<uint8_t(*)[RT_MAX_BLOCKS]>(&sh.swap[0][0][0]);
+    static_assert(sizeof(sh.swap) >= 3 * RT_MAX_BLOCKS, "sort buffers too small for the byte maps");
+    for (uint32_t i = threadIdx.x; i < 3 * RT_MAX_BLOCKS / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t *>(&s_map[0][0])[i] = 0;
+    __syncthreads();
+    const bool has_alloc = ev.alloc.n_a > 0 || ev.alloc.fresh != nullptr;
+    uint32_t invalid = 0, ignored = 0;
+    mark_ids(static_cast<const Id *>(ev.alloc.ids_a), ev.alloc.n_a, geo, st, 1, s_map[0], invalid, ignored);
+    mark_ids(static_cast<const Id *>(ev.attention.ids_a), ev.attention.n_a, geo, st, 0, s_map[1], invalid, ignored);
+    mark_ids(static_cast<const Id *>(ev.attention.ids_b), ev.attention.n_b, geo, st, 0, s_map[2], invalid, ignored);
+    __syncthreads();
+    if (ev.alloc.n_a) flush_event_map(s_map[0], st.event_blocks);
+    if (ev.attention.n_a) flush_event_map(s_map[1], st.event_blocks + kWords);
+    if (ev.attention.n_b) flush_event_map(s_map[2], st.event_blocks + 2 * kWords);
+    const uint32_t lane = threadIdx.x & 31;
+    uint32_t inv = warp_sum(invalid), ign = warp_sum(ignored);
+    if (lane == 0) {
+        if (inv) atomicAdd(&st.bad[0], (unsigned long long)inv);
+        if (ign) atomicAdd(&st.bad[1], (unsigned long long)ign);
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(st.arrivals, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (has_alloc) {
+        finish_alloc_event<Id>(ev.alloc, geo, st, st.event_blocks, reinterpret_cast<int *>(sh.warp), &s_base);
+        __syncthreads();
+    }
+    finish_attention_event(ev.attention.t, geo, st, st.event_blocks + kWords, st.event_blocks + 2 * kWords);
+    __syncthreads();
+    if (threadIdx.x < 3 * kWords) st.event_blocks[threadIdx.x] = 0;
+    if (threadIdx.x == 0) *st.arrivals = 0;
+    __syncthreads();                       // the state is final; the maps are no longer needed
+    rank_and_plan(geo, st, pol, resident, sets, tail, sh);
+}
+
 }  // namespace rt
 
 // --------------------------------------------------------------------------
@@ -473,7 +561,7 @@ int rt_feedback_create(rt_plan *plan, rt_feedback **out) {
     auto take = [&](size_t bytes) { size_t at = off; off += align_up(bytes); return at; };
     size_t o_gen = take(4 * (cap + 1)), o_ver = take(4 * nb), o_rs = take(8 * nb), o_ws = take(8 * nb),
            o_cv = take(4 * nb), o_ct = take(8 * nb), o_fh = take(8 * rt::kFreeHeadMax), o_fc = take(4),
-           o_eb = take(4 * 2 * rt::kWords), o_arr = take(4), o_sm = take(4 * ((cap + 32) / 32 + 1)), o_bad = take(16),
+           o_eb = take(4 * 3 * rt::kWords), o_arr = take(4), o_sm = take(4 * ((cap + 32) / 32 + 1)), o_bad = take(16),
            o_sets = take(4 * 3 * rt::kWords);
     fb->block_bytes = off;
     cudaError_t e = cudaMalloc(&fb->block, off);
@@ -588,11 +676,86 @@ int rt_feedback_snapshot(rt_feedback *fb, int32_t *versions, double *read_seen, 
     return RT_OK;
 }
 
+static bool policy_ok(const rt_feedback_policy *policy) {
+    return policy && policy->active_seconds > 0 && policy->refresh_seconds > 0;
+}
+
+static rt::RankPolicy rank_policy(const rt_feedback_policy *policy, double at, double now) {
+    rt::RankPolicy pol;
+    pol.budget = policy->budget;
+    pol.max_blocks = policy->max_blocks_per_update;
+    pol.flags = policy->flags;
+    pol.at = at;
+    pol.now = now;
+    pol.commit = now;
+    pol.active_seconds = policy->active_seconds;
+    pol.refresh_seconds = policy->refresh_seconds;
+    return pol;
+}
+
+// one thread per block id, a power of two for the sorting network, and at
+// least the CTA the tail part needs
+static uint32_t rank_threads(const rt_feedback *fb) {
+    uint32_t threads = rt::kScanThreads;
+    while (threads < fb->geo.n_blocks) threads <<= 1;
+    return threads;
+}
+
+static int feedback_step(rt_feedback *fb, const rt_feedback_step_ids *ids, const rt_feedback_policy *policy,
+                         double now, rt_range *out, uint32_t cap, rt_plan_result *result, void *stream,
+                         bool ids32) {
+    if (!fb || !ids || !policy_ok(policy) || !result || (!out && cap) || (!ids->d_allocated && ids->n_allocated) ||
+        (!ids->d_free_head && ids->n_free) || (!ids->d_read && ids->n_read) || (!ids->d_written && ids->n_written))
+        return RT_ERR_INVALID_ARGUMENT;
+    if (ids32 && fb->geo.capacity > 0x7fffffffull) return RT_ERR_INVALID_ARGUMENT;
+    FbDevice guard(fb->view.device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : fb->view.stream;
+    rt::StepArgs ev = {};
+    ev.alloc.ids_a = ids->d_allocated;
+    ev.alloc.n_a = (long long)ids->n_allocated;
+    ev.alloc.fresh = ids->d_free_head;
+    ev.alloc.n_fresh = (int)ids->n_free;
+    ev.alloc.alloc = 1;
+    ev.alloc.t = ids->t_allocated;
+    ev.attention.ids_a = ids->d_read;
+    ev.attention.n_a = (long long)ids->n_read;
+    ev.attention.ids_b = ids->d_written;
+    ev.attention.n_b = (long long)ids->n_written;
+    ev.attention.t = ids->t_attention;
+    rt::RankPolicy pol = rank_policy(policy, ids->t_attention, now);
+    rt::PlanArgs p;
+    rt::plan_fill_args(fb->plan, p, RT_MAX_BLOCKS, policy->flags | RT_PLAN_DRY_RUN, out, cap, result);
+    p.explicit_sets = 1;
+    const uint32_t threads = rank_threads(fb);
+    // a CTA per `threads` ids of the longest list, at most one wave of the device
+    uint64_t longest = ids->n_allocated > ids->n_read ? ids->n_allocated : ids->n_read;
+    if (ids->n_written > longest) longest = ids->n_written;
+    uint64_t want = (longest + threads - 1) / threads;
+    const uint64_t wave = (uint64_t)fb->view.sm_count * (2048 / threads);
+    int grid = (int)(want < 1 ? 1 : want < wave ? want : wave);
+    if (ids32)
+        rt::feedback_step_kernel<int><<<grid, threads, 0, s>>>(ev, fb->geo, fb->st, pol, fb->view.d_resident,
+                                                               fb->d_sets, p);
+    else
+        rt::feedback_step_kernel<long long><<<grid, threads, 0, s>>>(ev, fb->geo, fb->st, pol,
+                                                                     fb->view.d_resident, fb->d_sets, p);
+    FB_CUDA(cudaGetLastError());
+    return RT_OK;
+}
+
+int rt_feedback_step(rt_feedback *fb, const rt_feedback_step_ids *ids, const rt_feedback_policy *policy, double now,
+                     rt_range *out, uint32_t cap, rt_plan_result *result, void *stream) {
+    return feedback_step(fb, ids, policy, now, out, cap, result, stream, false);
+}
+
+int rt_feedback_step_i32(rt_feedback *fb, const rt_feedback_step_ids *ids, const rt_feedback_policy *policy,
+                         double now, rt_range *out, uint32_t cap, rt_plan_result *result, void *stream) {
+    return feedback_step(fb, ids, policy, now, out, cap, result, stream, true);
+}
+
 int rt_feedback_plan(rt_feedback *fb, const rt_feedback_policy *policy, double at, double now, rt_range *out,
                      uint32_t cap, rt_plan_result *result, void *stream) {
-    if (!fb || !policy || !result || (!out && cap) || !(policy->active_seconds > 0) ||
-        !(policy->refresh_seconds > 0))
-        return RT_ERR_INVALID_ARGUMENT;
+    if (!fb || !policy_ok(policy) || !result || (!out && cap)) return RT_ERR_INVALID_ARGUMENT;
     FbDevice guard(fb->view.device);
     cudaStream_t s = stream ? (cudaStream_t)stream : fb->view.stream;
     rt::RankPolicy pol;

@@ -191,6 +191,7 @@ void plan_view(const rt_plan *pl, PlanView *v) {
     v->shift = pl->shift;
     v->magic = pl->magic;
     v->magic_shift = pl->magic_shift;
+    v->sm_count = pl->sm_count;
 }
 void plan_fill_args(const rt_plan *pl, PlanArgs &p, uint32_t budget, uint32_t flags, rt_range *out,
                     uint32_t cap, rt_plan_result *result) {

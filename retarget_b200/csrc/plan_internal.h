@@ -16,6 +16,7 @@ struct PlanView {
     uint32_t n_blocks, block_tokens;
     int shift;
     uint32_t magic, magic_shift;
+    int sm_count;
 };
 
 void plan_view(const rt_plan *pl, PlanView *v);

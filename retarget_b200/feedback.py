@@ -30,6 +30,13 @@ class FeedbackPolicy(C.Structure):
                 ("reserved", C.c_uint32), ("active_seconds", C.c_double), ("refresh_seconds", C.c_double)]
 
 
+class StepIds(C.Structure):
+    _fields_ = [("d_allocated", C.c_void_p), ("n_allocated", C.c_uint64), ("d_free_head", C.c_void_p),
+                ("n_free", C.c_uint32), ("reserved", C.c_uint32), ("t_allocated", C.c_double),
+                ("d_read", C.c_void_p), ("n_read", C.c_uint64), ("d_written", C.c_void_p),
+                ("n_written", C.c_uint64), ("t_attention", C.c_double)]
+
+
 def _bind():
     lib = capi.lib
     vp = C.c_void_p
@@ -44,6 +51,9 @@ def _bind():
                                          C.POINTER(C.c_uint64)]
     lib.rt_feedback_plan.argtypes = [vp, C.POINTER(FeedbackPolicy), C.c_double, C.c_double, vp, C.c_uint32,
                                      vp, vp]
+    lib.rt_feedback_step.argtypes = [vp, C.POINTER(StepIds), C.POINTER(FeedbackPolicy), C.c_double, vp,
+                                     C.c_uint32, vp, vp]
+    lib.rt_feedback_step_i32.argtypes = lib.rt_feedback_step.argtypes
     return lib
 
 
@@ -104,6 +114,29 @@ class DeviceFeedback:
         cap = d_out.numel() * d_out.element_size() // capi.RANGE_DTYPE.itemsize
         capi.check(self.lib.rt_feedback_plan(self._h, C.byref(pol), float(self.at), float(now), _ptr(d_out),
                                              cap, _ptr(d_result), stream), "rt_feedback_plan")
+
+    def step(self, *, d_allocated, t_allocated, d_read, d_written, t_attention, now, budget,
+             max_blocks_per_update, active_seconds, refresh_seconds, flags, d_out, d_result, d_free_head=None,
+             stream=None):
+        """One decode step in one launch: ``alloc`` (skipped when ``d_allocated`` is
+        None), ``attention`` and ``plan``, with the results of the three calls in
+        that order."""
+        lists = [x for x in (d_allocated, d_free_head, d_read, d_written) if x is not None]
+        narrow = _is_i32(d_read)
+        if any(_is_i32(x) != narrow for x in lists):
+            raise TypeError("the id lists of one step must have the same dtype")
+        if d_allocated is not None:
+            self._event(t_allocated)
+        self._event(t_attention)
+        n_free = 0 if d_free_head is None else min(int(d_free_head.numel()), FREE_HEAD_MAX)
+        ids = StepIds(_ptr(d_allocated), 0 if d_allocated is None else int(d_allocated.numel()),
+                      _ptr(d_free_head), n_free, 0, float(t_allocated), _ptr(d_read), int(d_read.numel()),
+                      _ptr(d_written), int(d_written.numel()), float(t_attention))
+        pol = FeedbackPolicy(budget, max_blocks_per_update, flags, 0, active_seconds, refresh_seconds)
+        cap = d_out.numel() * d_out.element_size() // capi.RANGE_DTYPE.itemsize
+        fn = self.lib.rt_feedback_step_i32 if narrow else self.lib.rt_feedback_step
+        capi.check(fn(self._h, C.byref(ids), C.byref(pol), float(now), _ptr(d_out), cap, _ptr(d_result), stream),
+                   "rt_feedback_step")
 
     def arrays(self):
         nb = self.layout.n_blocks

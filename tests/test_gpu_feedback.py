@@ -28,7 +28,9 @@ def canonical(snapshot):
 
 
 def run_trace(layout, trace, *, budget, max_blocks, active, refresh, evict, dt=0.03, clear_at=None,
-              dtype=np.int64):
+              dtype=np.int64, fused=False):
+    """`fused`: the step's three calls (alloc, attention, plan) as the one-launch
+    `step()`; the oracle is driven the same either way."""
     dev = torch.device("cuda:0")
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)
@@ -51,15 +53,22 @@ def run_trace(layout, trace, *, budget, max_blocks, active, refresh, evict, dt=0
         if clear_at is not None and step == clear_at:
             fb.clear(t - 0.004, h)
             oracle.clear(t - 0.004)
-        if len(ev.alloc_slots):
-            head = None if ev.free_head is None else up(ev.free_head)
-            fb.alloc(up(ev.alloc_slots), t - 0.002, head, h)
-            oracle.alloc(ev.alloc_slots, ev.free_head, t - 0.002)
-        fb.attention(up(ev.read_slots), up(ev.write_slots), t, h)
-        oracle.attention(ev.read_slots, ev.write_slots, t)
         now = t + 0.001
-        fb.plan(now, budget=budget, max_blocks_per_update=max_blocks, active_seconds=active,
-                refresh_seconds=refresh, flags=flags, d_out=d_out, d_result=d_res, stream=h)
+        policy = dict(budget=budget, max_blocks_per_update=max_blocks, active_seconds=active,
+                      refresh_seconds=refresh, flags=flags, d_out=d_out, d_result=d_res, stream=h)
+        head = None if ev.free_head is None or not len(ev.alloc_slots) else up(ev.free_head)
+        if fused:
+            fb.step(d_allocated=up(ev.alloc_slots) if len(ev.alloc_slots) else None, t_allocated=t - 0.002,
+                    d_free_head=head, d_read=up(ev.read_slots), d_written=up(ev.write_slots), t_attention=t,
+                    now=now, **policy)
+        else:
+            if len(ev.alloc_slots):
+                fb.alloc(up(ev.alloc_slots), t - 0.002, head, h)
+            fb.attention(up(ev.read_slots), up(ev.write_slots), t, h)
+            fb.plan(now, **policy)
+        if len(ev.alloc_slots):
+            oracle.alloc(ev.alloc_slots, ev.free_head, t - 0.002)
+        oracle.attention(ev.read_slots, ev.write_slots, t)
         want, info = oracle.plan(now)
         torch.cuda.synchronize()
         res = result_from_tensor(d_res)
@@ -76,16 +85,21 @@ def run_trace(layout, trace, *, budget, max_blocks, active, refresh, evict, dt=0
     return moved
 
 
-def test_incremental_trace_config():
+FUSED = pytest.mark.parametrize("fused", [False, True], ids=["three-calls", "one-launch"])
+
+
+@FUSED
+def test_incremental_trace_config(fused):
     """40 layers, 65,536-slot pool, Poisson arrivals, 25 % budget, every step planned."""
     layout = workloads.Layout(40, 2048, 65536)
     trace = workloads.decode_trace(0, steps=256, initial_requests=12)
-    moved = run_trace(layout, trace, budget=16, max_blocks=16, active=2.0, refresh=10.0, evict=True)
+    moved = run_trace(layout, trace, budget=16, max_blocks=16, active=2.0, refresh=10.0, evict=True, fused=fused)
     assert moved > 0
 
 
+@FUSED
 @pytest.mark.parametrize("dtype", [np.int64, np.int32], ids=["i64", "i32"])
-def test_reference_update_limits_refresh_and_allocator_clear(dtype):
+def test_reference_update_limits_refresh_and_allocator_clear(dtype, fused):
     """The reference's own policy values (4 new blocks per update), a short
     refresh period so that due-for-refresh blocks are re-sent, no eviction, and an
     allocator clear in the middle.  Once with 64-bit and once with 32-bit ids."""
@@ -93,17 +107,19 @@ def test_reference_update_limits_refresh_and_allocator_clear(dtype):
     trace = workloads.decode_trace(3, steps=120, pool_slots=32768, arrival_rate=1.0, median=256,
                                    mean_output=24, initial_requests=6)
     moved = run_trace(layout, trace, budget=8, max_blocks=4, active=2.0, refresh=0.5, evict=False,
-                      clear_at=70, dtype=dtype)
+                      clear_at=70, dtype=dtype, fused=fused)
     assert moved > 0
 
 
-def test_small_blocks_wide_bitmap():
+@FUSED
+def test_small_blocks_wide_bitmap(fused):
     """1000 blocks of 6 slots: the multiply-shift division and a bitmap that
     fills every lane of the ranking kernel."""
     layout = workloads.Layout(2, 2048, 6001, 12288)
     trace = workloads.decode_trace(5, steps=60, pool_slots=5984, arrival_rate=0.7, median=200,
                                    mean_output=30, initial_requests=3)
-    moved = run_trace(layout, trace, budget=300, max_blocks=300, active=0.2, refresh=5.0, evict=True)
+    moved = run_trace(layout, trace, budget=300, max_blocks=300, active=0.2, refresh=5.0, evict=True,
+                      fused=fused)
     assert moved > 0
 
 
