@@ -77,16 +77,17 @@ struct EventArgs {
 
 template <typename Id>
 __device__ __forceinline__ void mark_ids(const Id *ids, long long n, const Geometry &geo,
-                                         const FeedbackState &st, int alloc, uint8_t *s_map, uint32_t &invalid,
-                                         uint32_t &ignored) {
+                                         const FeedbackState &st, int alloc, uint8_t *s_map, int *s_ver,
+                                         uint32_t &invalid, uint32_t &ignored) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (long long)gridDim.x * blockDim.x) {
         long long s = (long long)__ldcs(ids + i);
         if ((unsigned long long)(s - 1) < geo.capacity) {
-            uint32_t v = (uint32_t)s;
-            s_map[block_of_slot(v, geo)] = 1;
+            const uint32_t v = (uint32_t)s, block = block_of_slot(v, geo);
+            s_map[block] = 1;
             if (alloc) {
-                atomicAdd(&st.generations[v], 1);
+                // the slot's new generation is a candidate for its block's version
+                atomicMax(&s_ver[block], atomicAdd(&st.generations[v], 1) + 1);
                 atomicOr(&st.slot_marks[v >> 5], 1u << (v & 31));
             }
         } else if (s < 1) {
@@ -110,13 +111,28 @@ __device__ __forceinline__ void flush_event_map(const uint8_t *s_map, uint32_t *
     }
 }
 
+// Allocation events: a block's version is the largest generation among its
+// slots (slot_feedback.py:61).  Generations only ever grow, and only in the
+// slots an event allocates, so the largest generation of a touched block after
+// the event is the larger of its version before and the new generations of the
+// slots just allocated: no slot of the block has to be read again.
+__device__ __forceinline__ void flush_versions(const uint8_t *s_map, const int *s_ver, const FeedbackState &st) {
+    for (uint32_t b = threadIdx.x; b < (uint32_t)RT_MAX_BLOCKS; b += blockDim.x)
+        if (s_map[b]) atomicMax(&st.versions[b], s_ver[b]);
+}
+
 // Free-list head, by one CTA.  With a fresh head the event replaces it
 // (slot_feedback.py:63-64); without, the slots this event allocated are dropped
-// from the known head, order kept (slot_feedback.py:65-70).
+// from the known head, order kept (slot_feedback.py:65-70).  One pass: every
+// thread takes a contiguous piece of the head into registers (all its loads in
+// flight together), a CTA-wide prefix sum places what it keeps.
+constexpr int kHeadPerThread = kFreeHeadMax / 256;       // CTAs have at least 256 threads
+static_assert(kWords == 32, "a lane per bitmap word");
+
 template <typename Id>
 __device__ void update_free_head(const FeedbackState &st, const Id *fresh, int n_fresh,
-                                 unsigned long long capacity, int *s_warp, int *s_base) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+                                 unsigned long long capacity, int *s_warp) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (fresh) {
         int n = n_fresh < kFreeHeadMax ? n_fresh : kFreeHeadMax;
         for (int i = tid; i < n; i += blockDim.x) st.free_head[i] = (long long)fresh[i];
@@ -124,53 +140,50 @@ __device__ void update_free_head(const FeedbackState &st, const Id *fresh, int n
         return;
     }
     const int n = *st.free_count;
-    if (tid == 0) *s_base = 0;
-    __syncthreads();
-    for (int start = 0; start < n; start += blockDim.x) {
-        int i = start + tid;
-        long long slot = i < n ? st.free_head[i] : 0;
-        bool keep = i < n;
-        if (keep && (unsigned long long)slot <= capacity)
-            keep = !((__ldcg(&st.slot_marks[(uint32_t)slot >> 5]) >> ((uint32_t)slot & 31)) & 1u);
-        uint32_t mask = __ballot_sync(0xffffffffu, keep);
-        if (lane == 0) s_warp[warp] = __popc(mask);
-        __syncthreads();
-        int before = *s_base;
-        for (int w = 0; w < warp; ++w) before += s_warp[w];
-        int pos = before + __popc(mask & ((1u << lane) - 1u));
-        __syncthreads();                       // everyone has read its slot before anyone writes
-        if (keep) st.free_head[pos] = slot;
-        __syncthreads();
-        if (tid == 0) {
-            int total = 0;
-            for (int w = 0; w < n_warps; ++w) total += s_warp[w];
-            *s_base += total;
-        }
-        __syncthreads();
+    const int per = (n + (int)blockDim.x - 1) / (int)blockDim.x;      // <= kHeadPerThread
+    const int first = tid * per;
+    long long slot[kHeadPerThread];
+    uint32_t keep = 0;
+#pragma unroll
+    for (int k = 0; k < kHeadPerThread; ++k)
+        slot[k] = (k < per && first + k < n) ? __ldcg(&st.free_head[first + k]) : -1;
+#pragma unroll
+    for (int k = 0; k < kHeadPerThread; ++k) {
+        if (!(k < per && first + k < n)) continue;
+        bool stays = true;
+        if ((unsigned long long)slot[k] <= capacity)
+            stays = !((__ldcg(&st.slot_marks[(uint32_t)slot[k] >> 5]) >> ((uint32_t)slot[k] & 31)) & 1u);
+        keep |= (uint32_t)stays << k;
     }
-    if (tid == 0) *st.free_count = *s_base;
+    // exclusive prefix of the kept counts over the CTA
+    const int mine = __popc(keep);
+    int incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();                            // every thread has read its piece of the head
+    int before = incl - mine;
+    for (int w = 0; w < warp; ++w) before += s_warp[w];
+#pragma unroll
+    for (int k = 0; k < kHeadPerThread; ++k)
+        if ((keep >> k) & 1u) st.free_head[before++] = slot[k];
+    if (tid == (int)blockDim.x - 1) *st.free_count = before;
 }
 
 // What needs a whole allocation event, by the CTA that arrived last:
-// versions[b] = max(generations[b*T .. (b+1)*T)) and write_seen = t for every
-// touched block (slot_feedback.py:59-62), the free-list head, and the clean-up
-// of the slot marks.  `words`: the event's touched-block words.
+// write_seen = t for every touched block (slot_feedback.py:62), the free-list
+// head, and the clean-up of the slot marks.  `words`: the event's touched-block
+// words.  (The versions were brought up to date while the ids were marked.)
 template <typename Id>
 __device__ void finish_alloc_event(const EventArgs &ev, const Geometry &geo, const FeedbackState &st,
-                                   const uint32_t *words, int *s_warp, int *s_base) {
+                                   const uint32_t *words, int *s_warp) {
     const Id *ids_a = static_cast<const Id *>(ev.ids_a);
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (uint32_t b = warp; b < geo.n_blocks; b += blockDim.x >> 5) {          // a warp per touched block
-        if (!((__ldcg(&words[b >> 5]) >> (b & 31)) & 1u)) continue;             // uniform over the warp
-        unsigned long long lo = (unsigned long long)b * geo.block_tokens;
-        unsigned long long hi = lo + geo.block_tokens;
-        if (hi > geo.capacity + 1) hi = geo.capacity + 1;
-        int best = 0;
-        for (unsigned long long s = lo + lane; s < hi; s += 32) best = max(best, __ldcg(&st.generations[s]));
-        best = __reduce_max_sync(0xffffffffu, best);
-        if (lane == 0) { st.versions[b] = best; st.write_seen[b] = ev.t; }
-    }
-    update_free_head(st, static_cast<const Id *>(ev.fresh), ev.n_fresh, geo.capacity, s_warp, s_base);
+    for (uint32_t b = threadIdx.x; b < geo.n_blocks; b += blockDim.x)
+        if ((__ldcg(&words[b >> 5]) >> (b & 31)) & 1u) st.write_seen[b] = ev.t;
+    update_free_head(st, static_cast<const Id *>(ev.fresh), ev.n_fresh, geo.capacity, s_warp);
     __syncthreads();
     // the slot marks served the free-head filter: clear them again
     for (long long i = threadIdx.x; i < ev.n_a; i += blockDim.x) {
@@ -193,14 +206,17 @@ __global__ void __launch_bounds__(256)
 feedback_event_kernel(EventArgs ev, Geometry geo, FeedbackState st) {
     const Id *ids_a = static_cast<const Id *>(ev.ids_a), *ids_b = static_cast<const Id *>(ev.ids_b);
     __shared__ uint8_t s_map[2][RT_MAX_BLOCKS];
-    __shared__ int s_warp[32], s_base, s_last;
+    __shared__ int s_ver[RT_MAX_BLOCKS], s_warp[32], s_last;
     reinterpret_cast<uint32_t *>(s_map[0])[threadIdx.x] = 0;
     reinterpret_cast<uint32_t *>(s_map[1])[threadIdx.x] = 0;
+    if (ev.alloc)
+        for (uint32_t b = threadIdx.x; b < (uint32_t)RT_MAX_BLOCKS; b += blockDim.x) s_ver[b] = 0;
     __syncthreads();
     uint32_t invalid = 0, ignored = 0;
-    mark_ids(ids_a, ev.n_a, geo, st, ev.alloc, s_map[0], invalid, ignored);
-    mark_ids(ids_b, ev.n_b, geo, st, 0, s_map[1], invalid, ignored);
+    mark_ids(ids_a, ev.n_a, geo, st, ev.alloc, s_map[0], s_ver, invalid, ignored);
+    mark_ids(ids_b, ev.n_b, geo, st, 0, s_map[1], nullptr, invalid, ignored);
     __syncthreads();
+    if (ev.alloc) flush_versions(s_map[0], s_ver, st);
     flush_event_map(s_map[0], st.event_blocks);
     if (ev.n_b) flush_event_map(s_map[1], st.event_blocks + kWords);
     const uint32_t lane = threadIdx.x & 31;
@@ -217,7 +233,7 @@ feedback_event_kernel(EventArgs ev, Geometry geo, FeedbackState st) {
     if (!s_last) return;
     __threadfence();
     if (!ev.alloc) finish_attention_event(ev.t, geo, st, st.event_blocks, st.event_blocks + kWords);
-    else finish_alloc_event<Id>(ev, geo, st, st.event_blocks, s_warp, &s_base);
+    else finish_alloc_event<Id>(ev, geo, st, st.event_blocks, s_warp);
     __syncthreads();
     if (threadIdx.x < 2 * kWords) st.event_blocks[threadIdx.x] = 0;
     if (threadIdx.x == 0) *st.arrivals = 0;
@@ -305,6 +321,7 @@ __device__ void rank_and_plan(const Geometry &geo, const FeedbackState &st, cons
     s_free_pos[b] = 0x7fffffff;
     __syncthreads();
     const int n_free = *st.free_count;
+#pragma unroll 4
     for (int i = b; i < n_free; i += n_threads) {
         long long slot = st.free_head[i];
         if (slot >= 0) {
@@ -316,6 +333,12 @@ __device__ void rank_and_plan(const Geometry &geo, const FeedbackState &st, cons
     __syncthreads();
     const bool real = b < geo.n_blocks;
     const double r = real ? st.read_seen[b] : -INFINITY, w = real ? st.write_seen[b] : -INFINITY;
+    // what `choose` will ask about block b if it ends up inside the budget (slot_placement.py:86-93);
+    // none of it depends on the rank, so it is settled here, while thread b still speaks for block b
+    const int32_t version_b = real ? st.versions[b] : 0;
+    const int32_t commit_version_b = real ? st.commit_version[b] : 0;
+    const double commit_time_b = real ? st.commit_time[b] : 0.0;
+    const bool held_b = (resident[b >> 5] >> (b & 31)) & 1u;
     const bool recent_r = isfinite(r) && pol.at - r <= 30.0, recent_w = isfinite(w) && pol.at - w <= 30.0;
     const bool active_r = recent_r && pol.now - r <= pol.active_seconds;
     const bool active_w = recent_w && pol.now - w <= pol.active_seconds;
@@ -328,11 +351,17 @@ __device__ void rank_and_plan(const Geometry &geo, const FeedbackState &st, cons
         const bool use_r = recent_r && (!recent_w || r >= w);
         k = make_key(3, ordered_bits(-(use_r ? r : w)), use_r ? 0u : 1u, b);
     }
+    s_sel[b] = !held_b || commit_version_b != version_b ||
+               (pol.now - commit_time_b >= pol.refresh_seconds && (active_r || active_w));
     // Bitonic sort, one key per thread, keys in registers: partners up to 16
     // lanes away trade by shuffle, farther ones through shared memory (two
-    // buffers in turn, so one barrier per step is enough).
+    // buffers in turn, so one barrier per step is enough).  Only the power of
+    // two that covers the blocks is sorted as a whole; the threads beyond it hold
+    // "never" keys and merely permute them among themselves.
+    uint32_t sort_n = 32;
+    while (sort_n < geo.n_blocks) sort_n <<= 1;
     uint32_t turn = 0;
-    for (uint32_t size = 2; size <= n_threads; size <<= 1) {
+    for (uint32_t size = 2; size <= sort_n; size <<= 1) {
         for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
             RankKey other;
             if (stride < 32) {
@@ -353,15 +382,8 @@ __device__ void rank_and_plan(const Geometry &geo, const FeedbackState &st, cons
     // position b of the sorted order holds block `blk`
     const uint32_t blk = (uint32_t)(k.lo & 1023u);
     const bool desired = (k.hi >> 61) != 7 && b < pol.budget;
-    const bool held = (resident[blk >> 5] >> (blk & 31)) & 1u;
-    bool todo = false;
-    if (desired) {
-        const double rb = st.read_seen[blk], wb = st.write_seen[blk];
-        const bool act = (isfinite(rb) && pol.at - rb <= 30.0 && pol.now - rb <= pol.active_seconds) ||
-                         (isfinite(wb) && pol.at - wb <= 30.0 && pol.now - wb <= pol.active_seconds);
-        todo = !held || st.commit_version[blk] != st.versions[blk] ||
-               (pol.now - st.commit_time[blk] >= pol.refresh_seconds && act);
-    }
+    __syncthreads();                        // s_sel[] of every block is in shared memory (sort_n may be one warp)
+    const bool todo = desired && s_sel[blk];
     // first max_blocks of `todo` in rank order
     uint32_t mask = __ballot_sync(0xffffffffu, todo);
     if (lane == 0) s_warp[warp] = __popc(mask);
@@ -369,13 +391,11 @@ __device__ void rank_and_plan(const Geometry &geo, const FeedbackState &st, cons
     uint32_t before = __popc(mask & ((1u << lane) - 1u));
     for (uint32_t wv = 0; wv < warp; ++wv) before += s_warp[wv];
     const bool selected = todo && before < pol.max_blocks;
-    s_sel[blk] = selected;
+    s_sel[blk] = selected;                  // (every thread read its s_sel[blk] before the barrier above)
     s_des[blk] = desired;
-    const int32_t version_now = selected ? st.versions[blk] : 0;
     __syncthreads();
     // back to block-id order: thread b speaks for block b, warp = bitmap word
     const bool sel_b = s_sel[b], des_b = s_des[b];
-    const bool held_b = (resident[b >> 5] >> (b & 31)) & 1u;
     const bool evict_b = (pol.flags & RT_PLAN_EVICT) && held_b && !des_b;
     const uint32_t add_word = __ballot_sync(0xffffffffu, sel_b);
     const uint32_t evict_word = __ballot_sync(0xffffffffu, evict_b);
@@ -401,9 +421,9 @@ __device__ void rank_and_plan(const Geometry &geo, const FeedbackState &st, cons
     __syncthreads();
     // ---- commit, now that the plan is known to fit the caller's range buffer ----
     if (!s_delivered || !moves || (pol.flags & RT_PLAN_DRY_RUN)) return;
-    if (selected) {
-        st.commit_version[blk] = version_now;
-        st.commit_time[blk] = pol.commit;
+    if (sel_b) {
+        st.commit_version[b] = version_b;
+        st.commit_time[b] = pol.commit;
     }
     if (lane == 0) resident[warp] = new_word;
 }
@@ -434,19 +454,24 @@ __global__ void __launch_bounds__(kRankThreads)
 feedback_step_kernel(StepArgs ev, Geometry geo, FeedbackState st, RankPolicy pol, uint32_t *resident,
                      uint32_t *sets, const __grid_constant__ PlanArgs tail) {
     __shared__ __align__(16) RankShared sh;
-    __shared__ int s_base, s_last;
-    // the three byte maps live in the sort buffers until the ranking needs them
+    __shared__ int s_last;
+    // the three byte maps and the version candidates live in the sort buffers
+    // until the ranking needs them
     uint8_t(*s_map)[RT_MAX_BLOCKS] = reinterpret_cast<uint8_t(*)[RT_MAX_BLOCKS]>(&sh.swap[0][0][0]);
-    static_assert(sizeof(sh.swap) >= 3 * RT_MAX_BLOCKS, "sort buffers too small for the byte maps");
-    for (uint32_t i = threadIdx.x; i < 3 * RT_MAX_BLOCKS / 4; i += blockDim.x)
+    int *s_ver = reinterpret_cast<int *>(&sh.swap[0][0][0]) + 3 * RT_MAX_BLOCKS / 4;
+    static_assert(sizeof(sh.swap) >= 7 * RT_MAX_BLOCKS, "sort buffers too small for the maps");
+    for (uint32_t i = threadIdx.x; i < (ev.alloc.n_a ? 7u : 3u) * RT_MAX_BLOCKS / 4; i += blockDim.x)
         reinterpret_cast<uint32_t *>(&s_map[0][0])[i] = 0;
     __syncthreads();
     const bool has_alloc = ev.alloc.n_a > 0 || ev.alloc.fresh != nullptr;
     uint32_t invalid = 0, ignored = 0;
-    mark_ids(static_cast<const Id *>(ev.alloc.ids_a), ev.alloc.n_a, geo, st, 1, s_map[0], invalid, ignored);
-    mark_ids(static_cast<const Id *>(ev.attention.ids_a), ev.attention.n_a, geo, st, 0, s_map[1], invalid, ignored);
-    mark_ids(static_cast<const Id *>(ev.attention.ids_b), ev.attention.n_b, geo, st, 0, s_map[2], invalid, ignored);
+    mark_ids(static_cast<const Id *>(ev.alloc.ids_a), ev.alloc.n_a, geo, st, 1, s_map[0], s_ver, invalid, ignored);
+    mark_ids(static_cast<const Id *>(ev.attention.ids_a), ev.attention.n_a, geo, st, 0, s_map[1], nullptr, invalid,
+             ignored);
+    mark_ids(static_cast<const Id *>(ev.attention.ids_b), ev.attention.n_b, geo, st, 0, s_map[2], nullptr, invalid,
+             ignored);
     __syncthreads();
+    if (ev.alloc.n_a) flush_versions(s_map[0], s_ver, st);
     if (ev.alloc.n_a) flush_event_map(s_map[0], st.event_blocks);
     if (ev.attention.n_a) flush_event_map(s_map[1], st.event_blocks + kWords);
     if (ev.attention.n_b) flush_event_map(s_map[2], st.event_blocks + 2 * kWords);
@@ -463,7 +488,7 @@ feedback_step_kernel(StepArgs ev, Geometry geo, FeedbackState st, RankPolicy pol
     if (!s_last) return;
     __threadfence();
     if (has_alloc) {
-        finish_alloc_event<Id>(ev.alloc, geo, st, st.event_blocks, reinterpret_cast<int *>(sh.warp), &s_base);
+        finish_alloc_event<Id>(ev.alloc, geo, st, st.event_blocks, reinterpret_cast<int *>(sh.warp));
         __syncthreads();
     }
     finish_attention_event(ev.attention.t, geo, st, st.event_blocks + kWords, st.event_blocks + 2 * kWords);

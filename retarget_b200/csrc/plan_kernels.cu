@@ -712,6 +712,9 @@ scan_table_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ Pl
 #define RT_STAGES 4
 #endif
 constexpr int kStages = RT_STAGES;
+#ifndef RT_TMA_MIN_CTAS
+#define RT_TMA_MIN_CTAS 3
+#endif
 constexpr int kStageBytes = kChunkElems * 8;
 // the staging ring is reused as the tail's working memory once streaming is over
 static_assert((size_t)kStages * kStageBytes >= tail_smem_bytes(RT_MAX_GROUPS, RT_MAX_BUFFERS),
@@ -784,7 +787,7 @@ __device__ __forceinline__ long long copy_end_of(long long e0, long long hi, lon
 }
 
 template <bool kPow2>
-__global__ void __launch_bounds__(kTmaThreads)
+__global__ void __launch_bounds__(kTmaThreads, RT_TMA_MIN_CTAS)
 scan_plan_tma_kernel(const __grid_constant__ ScanArgs a, const __grid_constant__ PlanArgs p) {
     extern __shared__ __align__(128) unsigned char stage_mem[];
     __shared__ __align__(8) uint64_t full_bar[kStages];    // copy landed (tx bytes)

@@ -4,7 +4,8 @@ protocol's 1024 blocks, update limits from one block to the whole budget, active
 and refresh periods shorter and longer than the trace, with and without
 eviction, 64- and 32-bit ids, an allocator clear somewhere in the middle.  Every
 step's range list, counters and resident set, and the snapshot every 16 steps,
-must equal the CPU restatement of the reference's chain exactly."""
+must equal the CPU restatement of the reference's chain exactly.  Odd seeds drive
+the device through the one-launch step, even seeds through the three calls."""
 import os
 
 import numpy as np
@@ -44,4 +45,5 @@ def test_random_policy_and_geometry(seed):
     rng = np.random.default_rng(7100 + seed)
     case = random_case(rng)
     trace = workloads.decode_trace(int(rng.integers(1 << 30)), **case["trace"])
-    run_trace(case["layout"], trace, clear_at=case["clear_at"], dtype=case["dtype"], **case["policy"])
+    run_trace(case["layout"], trace, clear_at=case["clear_at"], dtype=case["dtype"], fused=bool(seed & 1),
+              **case["policy"])
