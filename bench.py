@@ -709,22 +709,30 @@ def run_ours(args):
     # ---- end to end through the host-buffer call: pinned ids -> device -> plan -> ranges on the host ----
     out_host = np.empty(1 << 16, dtype=capi.RANGE_DTYPE)
 
-    def host_loop(tensors, steps):
+    def host_loop(tensors, steps, f=base):
         last = 0
         for i in range(2):
             planner.step_host(tensors[i % 2].numpy(), batches[i % 2].group_off, batches[i % 2].budget_blocks,
-                              base, out=out_host)
+                              f, out=out_host)
         barrier()
         t0 = time.perf_counter()
         for i in range(steps):
             b = batches[i % 2]
-            _, res = planner.step_host(tensors[i % 2].numpy(), b.group_off, b.budget_blocks, base, out=out_host)
+            _, res = planner.step_host(tensors[i % 2].numpy(), b.group_off, b.budget_blocks, f, out=out_host)
             last = res.n_ranges
         torch.cuda.synchronize()
         return (time.perf_counter() - t0) / steps, last
 
+    # the call as a user makes it: 64-bit ids in pinned host memory; the library narrows them to 32 bits
+    # on the host cores and overlaps that with the copy
     e2e_s, e2e_ranges = host_loop(h_slots, max(K, 10))
     plan = out_host[:e2e_ranges].copy()      # the last timed plan, compared across ranks below
+    pack_threads = planner.narrow_threads()
+    narrowed = pack_threads > 0 and lay.capacity < 0x7fffffff and batches[0].n_idx >= 1 << 20 and not args.tma
+    # the same call told to copy the 64-bit ids as they are
+    e2e_wide_s, wide_ranges = host_loop(h_slots, max(K, 10), base | capi.RT_PLAN_WIDE_COPY)
+    if wide_ranges != e2e_ranges or not np.array_equal(out_host[:wide_ranges], plan):
+        raise SystemExit("bench.py: the narrowed and the wide host-buffer calls disagree")
     # the same call on the engine's own 32-bit ids: half the bytes over the host link
     h32 = [torch.from_numpy(b.slots.astype(np.int32)).pin_memory() for b in batches]
     e2e32_s, _ = host_loop(h32, max(K, 10))
@@ -744,8 +752,8 @@ def run_ours(args):
     host_loop(h_slots, 2)                    # back to the main pair's resident state
     clocks = sampler.stop() if sampler else None
 
-    ms_per_step, tp_ms_per_step, e2e_ms, e2e32_ms, copy_ms = ranks.max_over_ranks(
-        [total_ms / n_timed, tp_ms / tp_n, e2e_s * 1e3, e2e32_s * 1e3, copy_s * 1e3])
+    ms_per_step, tp_ms_per_step, e2e_ms, e2e32_ms, copy_ms, e2e_wide_ms = ranks.max_over_ranks(
+        [total_ms / n_timed, tp_ms / tp_n, e2e_s * 1e3, e2e32_s * 1e3, copy_s * 1e3, e2e_wide_s * 1e3])
     # every rank planned from the same slot table: the plans must agree
     # (dst names the rank's own GPU; the rest must agree)
     plans_agree = ranks.same_everywhere(b"".join(plan[k].tobytes() for k in ("buffer", "offset", "bytes")))
@@ -772,13 +780,23 @@ def run_ours(args):
                          "launch_ms": ms_per_step,
                          "kernel": "scan_plan_tma_kernel" if args.tma else "scan_plan_kernel"},
             "e2e": {"value": e2e_ms * 1e3, "unit": UNIT,
-                    "h2d_bytes_per_step": 8 * batches[0].n_idx,
+                    "h2d_bytes_per_step": (4 if narrowed else 8) * batches[0].n_idx,
                     "d2h_bytes_per_step": 24 * e2e_ranges + 64,
+                    "host_id_bytes_per_step": 8 * batches[0].n_idx,
+                    "how": (f"rt_plan_step on 64-bit ids in pinned host memory: narrowed to 32 bits by {pack_threads} "
+                            "host threads in chunks of 2^21 ids, every chunk's copy overlapping the next chunk's "
+                            "narrowing" if narrowed else
+                            "rt_plan_step on 64-bit ids in pinned host memory, copied as they are (too few host "
+                            "CPUs per GPU for narrowing to pay)"),
+                    "host_pack_threads": pack_threads if narrowed else 0,
+                    "wide_copy_us": e2e_wide_ms * 1e3, "wide_h2d_bytes_per_step": 8 * batches[0].n_idx,
                     "int32_ids_us": e2e32_ms * 1e3, "int32_h2d_bytes_per_step": 4 * batches[0].n_idx,
                     "h2d_copy_only_us": copy_ms * 1e3,
-                    "frac_of_h2d_ceiling": copy_ms / e2e_ms,
+                    "frac_of_h2d_ceiling": copy_ms / e2e_wide_ms,
                     "limiter": "the pinned host -> device copy of the slot ids (PCIe and, with several "
-                               "ranks, the one host NUMA node all GPUs copy from)"},
+                               "ranks, the one host NUMA node all GPUs copy from); wide_copy_us is the call "
+                               "that copies all 8 bytes per id, h2d_copy_only_us that copy alone, "
+                               "int32_ids_us the call on ids the caller already holds as 32-bit"},
             "gpu_launches": n_timed,
             "clocks": clocks,
             "slot_scan_gbs_aggregate": world * achieved,

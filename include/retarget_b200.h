@@ -387,6 +387,17 @@ typedef struct rt_layout {
                              /* this step's ids and that kernel itself releases its        */
                              /* dependents early (programmatic dependent launch).  After   */
                              /* any other kind of operation the flag changes nothing.      */
+#define RT_PLAN_WIDE_COPY 16u /* host-buffer call only: copy the 64-bit ids as they are.     */
+                             /* Without it rt_plan_step narrows the ids of a pool with      */
+                             /* fewer than 2^31 - 1 slots to 32 bits on the host cores      */
+                             /* before they cross the host link (same results; ids outside  */
+                             /* 0 .. 2^31 keep their class: negative stays "ignored", large */
+                             /* stays "out of range"), when there are at least 2^20 of them.*/
+                             /* RETARGET_B200_PACK_THREADS sets the number of host threads  */
+                             /* (0: never narrow).  Default: 3/4 of the process's CPUs per  */
+                             /* visible GPU, at most 16; with fewer than 8 the call copies  */
+                             /* the ids as they are (narrowing costs host memory traffic,   */
+                             /* which is what is short when many planners share a host).    */
 
 /* A step whose result carries any of these flags has NOT changed the resident
  * bitmaps: a plan that cannot be delivered in full is not committed (the
@@ -451,10 +462,22 @@ int rt_plan_step_device(rt_plan *plan, const int64_t *d_slots, const int64_t *gr
 
 /* Same step from HOST memory: copies the slot ids to the device, plans, copies
  * the ranges back and waits.  This is the call a scheduler makes when the slot
- * table lives on the host, as in kv_audit_probe.py:54-105. */
+ * table lives on the host, as in kv_audit_probe.py:54-105.  The copy is what
+ * bounds it, so large lists of 64-bit ids cross the link as 32-bit ids (see
+ * RT_PLAN_WIDE_COPY); h_slots may be pageable or pinned memory. */
 int rt_plan_step(rt_plan *plan, const int64_t *h_slots, const int64_t *group_off,
                  uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
                  rt_plan_result *result);
+
+/* Host threads rt_plan_step narrows with for this plan; 0: it copies 64-bit
+ * ids as they are (see RT_PLAN_WIDE_COPY for the rule). */
+int rt_plan_narrow_threads(rt_plan *plan, uint32_t *threads);
+
+/* What rt_plan_step does to 64-bit ids before they cross the host link, as a
+ * host utility: dst[i] = src[i] for ids in [0, 2^31), -1 for ids below zero,
+ * INT32_MAX for ids of 2^31 and above.  `threads` host threads share the work
+ * (0: as many as rt_plan_step would use). */
+int rt_narrow_ids(const int64_t *src, int32_t *dst, uint64_t n, uint32_t threads);
 
 /* Padded request table (the serving engine's req_to_token layout): row r holds
  * lens[r] valid ids in d_table[r*stride ..]; one bitmap for all buffers

@@ -28,6 +28,7 @@ RT_PLAN_EVICT = 1
 RT_PLAN_DRY_RUN = 2
 RT_PLAN_TMA = 4
 RT_PLAN_CHAINED = 8
+RT_PLAN_WIDE_COPY = 16
 
 RT_RESULT_OVERFLOW = 1
 RT_RESULT_SLOT_RANGE = 2

@@ -10,6 +10,7 @@
 #include "plan_device.cuh"
 #include "rt_internal.h"
 #include "plan_internal.h"
+#include "host_pack.h"
 
 namespace rt {
 void division_magic(uint32_t d, uint32_t *magic, uint32_t *shift);
@@ -21,6 +22,8 @@ cudaError_t launch_plan_tail(const uint32_t *want, const PlanArgs &p, cudaStream
 cudaError_t scan_plan_occupancy(uint32_t n_groups, uint32_t n_buffers, int *plain_blocks_per_sm,
                                 int *tma_blocks_per_sm, int *table_blocks_per_sm);
 }  // namespace rt
+
+constexpr unsigned kUnset = ~0u;
 
 struct rt_plan {
     rt_layout layout;
@@ -41,6 +44,8 @@ struct rt_plan {
     uint8_t *d_buffer_group = nullptr;  // bitmap of every buffer, registry order
     uint16_t *d_group_size = nullptr;   // buffers per bitmap
     long long *d_stage = nullptr;      // host-buffer call: slot ids land here
+    int32_t *h_narrow = nullptr;       // host-buffer call: pinned staging for ids narrowed to 32 bits
+    unsigned narrow_threads = kUnset;  // host threads that do the narrowing (0: never narrow)
     uint64_t max_indices = 0;
     rt_range *h_out = nullptr;         // pinned + mapped: the kernel writes ranges here
     rt_plan_result *h_result = nullptr;
@@ -305,6 +310,7 @@ int rt_plan_destroy(rt_plan *pl) {
     cudaFree(pl->d_group_size);
     cudaFree(pl->d_stage);
     if (pl->h_out) cudaFreeHost(pl->h_out);
+    if (pl->h_narrow) cudaFreeHost(pl->h_narrow);
     if (pl->h_result) cudaFreeHost(pl->h_result);
     delete pl;
     return RT_OK;
@@ -354,6 +360,18 @@ int step_device_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t
     return RT_OK;
 }
 
+unsigned plan_narrow_threads(rt_plan *pl) {
+    if (pl->narrow_threads == kUnset) {
+        int devices = 1;
+        if (cudaGetDeviceCount(&devices) != cudaSuccess || devices < 1) devices = 1;
+        pl->narrow_threads = rt::narrow_threads((unsigned)devices);
+    }
+    return pl->narrow_threads;
+}
+
+constexpr int64_t kNarrowMinIds = 1 << 20;       // below this the wide copy takes well under a millisecond
+constexpr size_t kNarrowChunkIds = 1 << 20;      // 8 MiB in, 4 MiB out per chunk
+
 int step_host_impl(rt_plan *pl, const void *h_slots, bool ids32, const int64_t *group_off,
                    uint32_t budget, uint32_t flags, rt_range *out, uint32_t cap,
                    rt_plan_result *result) {
@@ -363,8 +381,39 @@ int step_host_impl(rt_plan *pl, const void *h_slots, bool ids32, const int64_t *
     if (n < 0 || (uint64_t)n > pl->max_indices || group_off[0] < 0) return RT_ERR_CAPACITY;
     if (n && !h_slots) return RT_ERR_INVALID_ARGUMENT;
     DeviceGuard guard(pl->device);
-    if (n) RT_CUDA(cudaMemcpyAsync(pl->d_stage, h_slots, (ids32 ? 4 : 8) * (size_t)n,
-                                   cudaMemcpyHostToDevice, pl->stream));
+    // 64-bit ids of a pool that 32 bits can number cross the host link as 32-bit
+    // ids: narrowed on the host cores into pinned memory, each chunk copied as soon
+    // as it is complete while the chunks after it are being narrowed.  Half the bytes on
+    // the link, which is what bounds this call; the caller's buffer need not be
+    // pinned.  (The bulk-copy kernel has no 32-bit form; short lists are not
+    // worth the hand-over to the worker threads.)
+    bool narrow = !ids32 && !(flags & (RT_PLAN_WIDE_COPY | RT_PLAN_TMA)) && n >= kNarrowMinIds &&
+                  pl->layout.capacity_slots < 0x7fffffffull;
+    narrow = narrow && plan_narrow_threads(pl) > 0;
+    if (narrow) {
+        if (!pl->h_narrow)
+            RT_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&pl->h_narrow), 4 * (size_t)pl->max_indices + 64,
+                                  cudaHostAllocDefault));
+        // every chunk is copied as soon as it is narrowed, while the host threads go on
+        struct Copier {
+            rt_plan *pl;
+            cudaError_t err;
+        } copier = {pl, cudaSuccess};
+        rt::narrow_ids_streamed(
+            static_cast<const int64_t *>(h_slots), pl->h_narrow, (size_t)n, pl->narrow_threads, kNarrowChunkIds,
+            [](void *ctx, size_t first, size_t count) {
+                Copier *c = static_cast<Copier *>(ctx);
+                if (c->err != cudaSuccess) return;
+                c->err = cudaMemcpyAsync(reinterpret_cast<int32_t *>(c->pl->d_stage) + first, c->pl->h_narrow + first,
+                                         4 * count, cudaMemcpyHostToDevice, c->pl->stream);
+            },
+            &copier);
+        RT_CUDA(copier.err);
+        ids32 = true;
+    } else if (n) {
+        RT_CUDA(cudaMemcpyAsync(pl->d_stage, h_slots, (ids32 ? 4 : 8) * (size_t)n, cudaMemcpyHostToDevice,
+                                pl->stream));
+    }
     uint32_t dev_cap = cap < pl->max_ranges ? cap : pl->max_ranges;
     // (the copy precedes the kernel in the stream: nothing to chain to)
     int st = step_device_impl(pl, pl->d_stage, ids32, group_off, budget, flags & ~RT_PLAN_CHAINED,
@@ -476,6 +525,24 @@ int rt_plan_step(rt_plan *pl, const int64_t *h_slots, const int64_t *group_off, 
 int rt_plan_step_i32(rt_plan *pl, const int32_t *h_slots, const int64_t *group_off, uint32_t budget,
                      uint32_t flags, rt_range *out, uint32_t cap, rt_plan_result *result) {
     return step_host_impl(pl, h_slots, true, group_off, budget, flags, out, cap, result);
+}
+
+int rt_plan_narrow_threads(rt_plan *pl, uint32_t *threads) {
+    if (!pl || !threads) return RT_ERR_INVALID_ARGUMENT;
+    *threads = plan_narrow_threads(pl);
+    return RT_OK;
+}
+
+int rt_narrow_ids(const int64_t *src, int32_t *dst, uint64_t n, uint32_t threads) {
+    if ((!src || !dst) && n) return RT_ERR_INVALID_ARGUMENT;
+    if (!threads) {
+        int devices = 1;
+        if (cudaGetDeviceCount(&devices) != cudaSuccess || devices < 1) devices = 1;
+        threads = rt::narrow_threads((unsigned)devices);
+        if (!threads) threads = 1;
+    }
+    rt::narrow_ids_parallel(src, dst, (size_t)n, threads);
+    return RT_OK;
 }
 
 int rt_plan_step_table(rt_plan *pl, const int64_t *d_table, const int32_t *d_lens, uint32_t n_rows,

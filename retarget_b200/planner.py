@@ -87,6 +87,12 @@ class DevicePlanner:
         capi.check(st, "rt_plan_step")
         return out[:min(res.n_ranges, len(out))], res
 
+    def narrow_threads(self) -> int:
+        """Host threads `step_host` narrows 64-bit ids with (0: it copies them as they are)."""
+        t = C.c_uint32()
+        capi.check(capi.lib.rt_plan_narrow_threads(self._h, C.byref(t)), "rt_plan_narrow_threads")
+        return t.value
+
     def step_device(self, d_slots, group_off: np.ndarray, budget: int, flags: int, d_out, d_result,
                     stream=None):
         """Everything already on the device (torch tensors); asynchronous.
