@@ -685,6 +685,35 @@ def run_ours(args):
             us = t[0].elapsed_time(t[1]) * 1e3 / 200
             variants["static_scan_only"] = {"us_per_step": us, "steps": 200, "gbs": 8 * batches[0].n_idx / us / 1e3,
                                             "note": "rt_scan_slots_static: a memset of its scratch + one launch per call"}
+            # what a pure read of the same bytes reaches (same access pattern, nothing done with the ids)
+            probe = capi.lib.rt_read_probe
+            probe.restype = C.c_int
+            probe.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]
+            d_sink = torch.zeros(1, dtype=torch.int64, device=dev)
+            nbytes = 8 * batches[0].n_idx // 16 * 16
+
+            def read_only(i, handle):
+                capi.check(probe(d_slots[i % 2].data_ptr(), nbytes, d_sink.data_ptr(), handle), "rt_read_probe")
+            for i in range(4):
+                read_only(i, stream.cuda_stream)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                for i in range(20):
+                    read_only(i, torch.cuda.current_stream().cuda_stream)
+            g.replay()
+            torch.cuda.synchronize()
+            t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            t[0].record(stream)
+            for _ in range(40):
+                g.replay()
+            t[1].record(stream)
+            torch.cuda.synchronize()
+            us = t[0].elapsed_time(t[1]) * 1e3 / 800
+            variants["read_only_probe"] = {"us_per_step": us, "steps": 800, "gbs": nbytes / us / 1e3,
+                                           "note": "rt_read_probe over the same two id arrays, graph replays, launches "
+                                                   "not chained: the same bytes read and thrown away"}
+            del g
             for i in range(2):      # leave the resident state as the main workload left it
                 timer.step(d_slots, batches, W + n_timed + i)
             torch.cuda.synchronize()

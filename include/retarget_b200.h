@@ -660,6 +660,13 @@ int rt_paged_read(const void *const *d_buffers, uint32_t n_buffers, uint32_t byt
                   const int64_t *d_slots, uint64_t n_slots, uint64_t capacity_slots,
                   uint64_t *d_sums, void *stream);
 
+/* Read-only bandwidth yardstick: reads `bytes` (a multiple of 16, 16-byte
+ * aligned) of device memory once, with the slot scan's access pattern, and
+ * folds them into *d_sink (xor of the 64-bit words, folded; the caller zeroes
+ * it).  No reference counterpart: the bench quotes its GB/s beside the scan's.
+ * Asynchronous on `stream`. */
+int rt_read_probe(const void *d_data, uint64_t bytes, uint64_t *d_sink, void *stream);
+
 /* Synthetic paged bf16 decode attention: for every request r and every layer,
  * out = softmax(q . K^T / sqrt(128)) . V over the K and V rows of the request's
  * slots d_slots[d_req_off[r] .. d_req_off[r+1]) (slot 0 and ids outside

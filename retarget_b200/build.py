@@ -29,7 +29,7 @@ CXX_FLAGS = ["-O2", "-g", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-pthread",
 CORE_CU = ["plan_kernels.cu", "plan_capi.cu"]
 CORE_CPP = ["host_policy.cpp", "uvm_plan.cpp", "controllers.cpp", "uvm_client.cpp", "host_pack.cpp"]
 OPTIONAL_CORE_CPP = ["uvm_server.cpp", "driver_api.cpp"]
-OPTIONAL_CORE_CU = ["feedback_kernels.cu", "paged_reader.cu", "paged_attention.cu", "noalloc_scan.cu"]
+OPTIONAL_CORE_CU = ["feedback_kernels.cu", "paged_reader.cu", "paged_attention.cu", "noalloc_scan.cu", "read_probe.cu"]
 PRELOAD_CPP = ["preload_hooks.cpp"]
 
 
