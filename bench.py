@@ -711,8 +711,8 @@ def run_ours(args):
             torch.cuda.synchronize()
             us = t[0].elapsed_time(t[1]) * 1e3 / 800
             variants["read_only_probe"] = {"us_per_step": us, "steps": 800, "gbs": nbytes / us / 1e3,
-                                           "note": "rt_read_probe over the same two id arrays, graph replays, launches "
-                                                   "not chained: the same bytes read and thrown away"}
+                                           "note": "rt_read_probe over the same two id arrays, graph replays of launches "
+                                                   "that overlap each other: the same bytes read and thrown away"}
             del g
             for i in range(2):      # leave the resident state as the main workload left it
                 timer.step(d_slots, batches, W + n_timed + i)
@@ -1175,7 +1175,8 @@ def emit(line: dict):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed steps (default 200; 20 for --impl reference, whose steps take a second each)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="target",
@@ -1193,6 +1194,8 @@ def main():
     ap.add_argument("--no-extras", "--no-variants", dest="no_extras", action="store_true",
                     help="skip the secondary measurements (variants, configs, feedback, prefetch)")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 20 if args.impl == "reference" else 200
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
         args.steps = max(args.steps, 2)

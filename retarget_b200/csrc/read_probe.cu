@@ -4,7 +4,8 @@
 // with the data but fold it into one word.  No reference counterpart: the bench
 // quotes it beside the scan so that the scan's GB/s can be read against what a
 // pure read of the same bytes reaches on the same device at the same moment
-// (the measured copy peak counts a read AND a write stream).
+// (the measured copy peak counts a read AND a write stream).  Probes issued
+// back to back overlap each other's ramp and drain, as chained scans do.
 #include <cuda_runtime.h>
 
 #include "rt_internal.h"
@@ -16,6 +17,9 @@ constexpr int kVecPerThread = 4;                                  // 4 x 16 B x 
 
 __global__ void __launch_bounds__(kThreads, 4)
 read_probe_kernel(const uint4 *__restrict__ data, unsigned long long n_vec, unsigned long long *sink) {
+    // back-to-back probes do not depend on one another: let the next one start
+    // as soon as this one's CTAs are all running
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const unsigned long long unit_vec = (unsigned long long)kThreads * kVecPerThread;
     const unsigned long long units = n_vec / unit_vec;
     const unsigned long long q0 = units * blockIdx.x / gridDim.x, q1 = units * (blockIdx.x + 1) / gridDim.x;
@@ -68,9 +72,19 @@ extern "C" int rt_read_probe(const void *d_data, uint64_t bytes, uint64_t *d_sin
     int device = 0, sms = 148;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    read_probe_kernel<<<sms * 4, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint4 *>(d_data), bytes / 16, reinterpret_cast<unsigned long long *>(d_sink));
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)sms * 4);
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, read_probe_kernel, static_cast<const uint4 *>(d_data),
+                                       (unsigned long long)(bytes / 16),
+                                       reinterpret_cast<unsigned long long *>(d_sink));
+    if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) { rt::last_cuda_error_set((int)e); return RT_ERR_CUDA; }
     return RT_OK;
 }
