@@ -323,11 +323,6 @@ def upload(torch, dev, batches, dtype=None):
     return [torch.from_numpy(b.slots if dtype is None else b.slots.astype(dtype)).to(dev) for b in batches]
 
 
-class UvmConfig(C.Structure):
-    _fields_ = [("socket_path", C.c_char_p), ("chunk_bytes", C.c_uint64), ("batch_bytes", C.c_uint64),
-                ("streams", C.c_uint32), ("listen", C.c_int32)]
-
-
 def prefetch_leg(torch, dev, gib: int = 4):
     """Prefetched GB/s against the host link: `gib` x 1 GiB managed buffers,
     registered with the in-process UVM server, moved as a whole to the CPU and
@@ -370,7 +365,7 @@ def prefetch_leg(torch, dev, gib: int = 4):
         capi.check(lib.rt_uvm_register(p, GIB, C.c_void_p(int(ctx)), dev.index or 0, 1, None), "rt_uvm_register")
     total = gib * GIB
     uvm = LocalUvm()
-    cfg = UvmConfig(None, 64 * MIB, 1024 * MIB, 4, 0)
+    cfg = capi.UvmConfig(None, 64 * MIB, 1024 * MIB, 4, 0)
     capi.check(lib.rt_uvm_start(C.byref(cfg)), "rt_uvm_start")
     try:
         gen = uvm.status().allocation_generation
@@ -390,6 +385,26 @@ def prefetch_leg(torch, dev, gib: int = 4):
                "job_completed_bytes": done.job_completed_bytes,
                "executor": "64 MiB chunks on 4 side streams, one wait per GiB",
                "link_yardstick": "pinned host -> device copy of 1 GiB, same process, measured just before"}
+        # a window that moves by its own width: half of every buffer goes to the CPU while the other half
+        # comes in, first in the reference's order (all evictions, then all additions), then both at once
+        half = GIB // 2
+        job(f"windowfullv {gen} {GIB} {gib} 0 0 0 {half}")
+        flips = [(0, half, half, GIB), (half, GIB, 0, half)]
+        both = {}
+        for name, overlap in (("in_order", 0), ("overlapped", 1)):
+            capi.check(lib.rt_uvm_stop(), "rt_uvm_stop")
+            cfg = capi.UvmConfig(None, 64 * MIB, 1024 * MIB, 4, 0, overlap)
+            capi.check(lib.rt_uvm_start(C.byref(cfg)), "rt_uvm_start")
+            spent = 0.0
+            for k in range(6):
+                o0, o1, n0, n1 = flips[k % 2]
+                t, _ = job(f"windowv {gen} {GIB} {gib} {o0} {o1} {n0} {n1}")
+                spent += t if k >= 4 else 0.0          # the first flips touch the host pages for the first time
+            both[name + "_gbs"] = 2 * total / spent / 1e9
+        both["bytes_per_plan"] = total
+        both["what"] = ("windowv plans that evict one half of every buffer and bring in the other half: "
+                        "GB/s over both directions together")
+        out["both_ways"] = both
     finally:
         capi.check(lib.rt_uvm_stop(), "rt_uvm_stop")
         for p in ptrs:
@@ -970,7 +985,7 @@ def run_e2e_prefetch(args):
         ids.append(i.value)
     kv_ids = (C.c_uint64 * (2 * layers))(*ids[:2 * layers])
     uvm = LocalUvm()
-    cfg = UvmConfig(None, 64 * MIB, 1024 * MIB, 4, 0)
+    cfg = capi.UvmConfig(None, 64 * MIB, 1024 * MIB, 4, 0)
     capi.check(lib.rt_uvm_start(C.byref(cfg)), "rt_uvm_start")
     stream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(stream)

@@ -700,6 +700,12 @@ typedef struct rt_uvm_config {
     uint64_t batch_bytes;      /* bytes issued between two waits; 0: 256 MiB             */
     uint32_t streams;          /* side streams per context; 0: 4                         */
     int32_t listen;            /* 0: no socket, commands only through rt_uvm_command     */
+    uint32_t overlap_phases;   /* 0: every CPU-bound range has landed before the first   */
+                               /* GPU-bound one is issued (the reference's order).  1:   */
+                               /* the two stretches of a plan move at the same time, one */
+                               /* direction of the host link each; for callers whose     */
+                               /* evictions are not what makes room for the additions    */
+    uint32_t reserved;
 } rt_uvm_config;
 
 int rt_uvm_start(const rt_uvm_config *config);

@@ -58,6 +58,13 @@ RT_ERR_FEEDBACK_IDENTITY = -36
 UPDATE_MODES = ("incremental", "initial_only", "full_cache")
 
 
+class UvmConfig(C.Structure):
+    """rt_uvm_config: how the in-process UVM server and its prefetch executor run."""
+    _fields_ = [("socket_path", C.c_char_p), ("chunk_bytes", C.c_uint64), ("batch_bytes", C.c_uint64),
+                ("streams", C.c_uint32), ("listen", C.c_int32), ("overlap_phases", C.c_uint32),
+                ("reserved", C.c_uint32)]
+
+
 class RtError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(message)

@@ -56,6 +56,7 @@ struct Server {
     std::vector<rt_id_range> job;
     uint64_t chunk = 16ull << 20, batch = 256ull << 20, page = 4096;
     uint32_t n_streams = 4;
+    bool overlap_phases = false;   // run a plan's CPU-bound and GPU-bound stretch at the same time
     std::thread worker, listener;
     int listen_fd = -1, client_fd = -1;
     int stop_fd = -1;                    // eventfd: wakes the listener for a stop
@@ -132,11 +133,21 @@ void drop_streams_locked(int device, bool alive) {
     }
 }
 
-// Issues up to `batch` bytes starting at (*range, *done) and waits for them.
+// A stretch of the job that moves in one direction: ranges [range, end), `done`
+// bytes of the first one already issued.
+struct Lane {
+    size_t range, end;
+    uint64_t done;
+    bool finished() const { return range >= end; }
+};
+
+// Issues up to `batch` bytes, taking chunks from the lanes in turn, and waits for
+// them.  One lane: the job's queue order.  Two lanes (overlapped phases): the
+// CPU-bound and the GPU-bound stretch advance together, each on its own share of
+// the side streams, so that both directions of the host link are busy at once.
 // Holds `life` for the whole batch so that no allocation can be freed under a
 // queued prefetch.
-CUresult run_batch(const DriverApi &api, const std::vector<rt_id_range> &job, size_t *range,
-                   uint64_t *done_in_range) {
+CUresult run_batch(const DriverApi &api, const std::vector<rt_id_range> &job, Lane *lanes, uint32_t n_lanes) {
     std::lock_guard<std::mutex> life(g.life);
     std::vector<Pending> pending;
     std::vector<CUstream> used;
@@ -144,45 +155,52 @@ CUresult run_batch(const DriverApi &api, const std::vector<rt_id_range> &job, si
     bool have_ctx = false;
     CUresult result = CUDA_SUCCESS;
     uint64_t issued = 0;
-    const int batch_dst_is_cpu = job[*range].dst < 0;
-    uint32_t rr = 0;
-    while (*range < job.size() && issued < g.batch && result == CUDA_SUCCESS) {
-        const rt_id_range &r = job[*range];
-        if ((r.dst < 0) != batch_dst_is_cpu) break;      // phase boundary: wait first
-        CUdeviceptr ptr = 0;
-        CUcontext ctx = nullptr;
-        int device = -1;
-        bool found = false, stopping;
-        {
-            std::lock_guard<std::mutex> st(g.state);
-            for (const Allocation &a : g.allocations)
-                if (a.id == r.id) { ptr = a.ptr + r.offset + *done_in_range; ctx = a.ctx; device = a.device; found = true; break; }
-            stopping = g.stop;
-        }
-        if (stopping) { result = CUDA_ERROR_DEINITIALIZED; break; }
-        if (!found) { result = CUDA_ERROR_INVALID_VALUE; break; }
-        if (have_ctx && ctx != current) break;            // one context per batch
-        if (!have_ctx) {
-            result = api.ctx_set_current(ctx);
+    uint32_t rr[2] = {0, 0};
+    bool progressed = true;
+    while (progressed && issued < g.batch && result == CUDA_SUCCESS) {
+        progressed = false;
+        for (uint32_t k = 0; k < n_lanes && issued < g.batch && result == CUDA_SUCCESS; ++k) {
+            Lane &lane = lanes[k];
+            if (lane.finished()) continue;
+            const rt_id_range &r = job[lane.range];
+            CUdeviceptr ptr = 0;
+            CUcontext ctx = nullptr;
+            int device = -1;
+            bool found = false, stopping;
+            {
+                std::lock_guard<std::mutex> st(g.state);
+                for (const Allocation &a : g.allocations)
+                    if (a.id == r.id) { ptr = a.ptr + r.offset + lane.done; ctx = a.ctx; device = a.device; found = true; break; }
+                stopping = g.stop;
+            }
+            if (stopping) { result = CUDA_ERROR_DEINITIALIZED; break; }
+            if (!found) { result = CUDA_ERROR_INVALID_VALUE; break; }
+            if (have_ctx && ctx != current) continue;         // one context per batch: this lane waits for the next
+            if (!have_ctx) {
+                result = api.ctx_set_current(ctx);
+                if (result != CUDA_SUCCESS) break;
+                current = ctx;
+                have_ctx = true;
+            }
+            std::vector<CUstream> *streams = nullptr;
+            result = streams_for(api, ctx, device, &streams);
             if (result != CUDA_SUCCESS) break;
-            current = ctx;
-            have_ctx = true;
+            uint64_t bytes = r.bytes - lane.done;
+            if (bytes > g.chunk) bytes = g.chunk;
+            // lane k of n takes every n-th side stream (all of them when it is alone)
+            const size_t share = streams->size() >= n_lanes ? streams->size() / n_lanes : 1;
+            CUstream s = (*streams)[(k * share + rr[k]++ % share) % streams->size()];
+            result = api.prefetch(ptr, bytes, r.dst, s);
+            if (result != CUDA_SUCCESS) break;
+            bool seen = false;
+            for (CUstream u : used) seen |= u == s;
+            if (!seen) used.push_back(s);
+            pending.push_back({bytes, r.dst});
+            issued += bytes;
+            lane.done += bytes;
+            if (lane.done == r.bytes) { ++lane.range; lane.done = 0; }
+            progressed = true;
         }
-        std::vector<CUstream> *streams = nullptr;
-        result = streams_for(api, ctx, device, &streams);
-        if (result != CUDA_SUCCESS) break;
-        uint64_t bytes = r.bytes - *done_in_range;
-        if (bytes > g.chunk) bytes = g.chunk;
-        CUstream s = (*streams)[rr++ % streams->size()];
-        result = api.prefetch(ptr, bytes, r.dst, s);
-        if (result != CUDA_SUCCESS) break;
-        bool seen = false;
-        for (CUstream u : used) seen |= u == s;
-        if (!seen) used.push_back(s);
-        pending.push_back({bytes, r.dst});
-        issued += bytes;
-        *done_in_range += bytes;
-        if (*done_in_range == r.bytes) { ++*range; *done_in_range = 0; }
     }
     for (CUstream s : used) {
         CUresult r = api.stream_synchronize(s);
@@ -204,6 +222,33 @@ CUresult run_batch(const DriverApi &api, const std::vector<rt_id_range> &job, si
     return result;
 }
 
+// Runs one job.  The ranges are cut into stretches of one direction; a stretch
+// has completed before the next one starts, which is the reference's order
+// (every CPU-bound range has landed before the first GPU-bound one is issued,
+// select.cpp:24231-24240 builds the list that way and 23990-24024 runs it in
+// order).  With `overlap_phases` a job of exactly one CPU-bound stretch followed
+// by one GPU-bound stretch -- every plan the protocol can express -- runs both
+// at once.
+CUresult run_job(const DriverApi &api, const std::vector<rt_id_range> &job, bool overlap) {
+    std::vector<Lane> stretches;
+    for (size_t i = 0; i < job.size(); ++i) {
+        if (stretches.empty() || (job[i].dst < 0) != (job[stretches.back().range].dst < 0))
+            stretches.push_back({i, i + 1, 0});
+        else
+            stretches.back().end = i + 1;
+    }
+    CUresult result = CUDA_SUCCESS;
+    if (overlap && stretches.size() == 2 && job[stretches[0].range].dst < 0) {
+        Lane both[2] = {stretches[0], stretches[1]};
+        while (result == CUDA_SUCCESS && !(both[0].finished() && both[1].finished()))
+            result = run_batch(api, job, both, 2);
+        return result;
+    }
+    for (Lane &lane : stretches)
+        while (result == CUDA_SUCCESS && !lane.finished()) result = run_batch(api, job, &lane, 1);
+    return result;
+}
+
 void worker_main() {
     const DriverApi *api = driver_api();
     std::unique_lock<std::mutex> st(g.state);
@@ -212,12 +257,9 @@ void worker_main() {
         if (g.stop && !g.busy) break;
         std::vector<rt_id_range> job;
         job.swap(g.job);
+        const bool overlap = g.overlap_phases;
         st.unlock();
-        CUresult result = api ? CUDA_SUCCESS : CUDA_ERROR_NOT_INITIALIZED;
-        size_t range = 0;
-        uint64_t done_in_range = 0;
-        while (result == CUDA_SUCCESS && range < job.size())
-            result = run_batch(*api, job, &range, &done_in_range);
+        CUresult result = api ? run_job(*api, job, overlap) : CUDA_ERROR_NOT_INITIALIZED;
         st.lock();
         g.last_error = (int)result;
         g.completed_job = g.job_id;
@@ -535,6 +577,7 @@ int rt_uvm_start(const rt_uvm_config *config) {
         g.batch = cfg.batch_bytes ? cfg.batch_bytes : (256ull << 20);
         if (g.batch < g.chunk) g.batch = g.chunk;
         g.n_streams = cfg.streams ? cfg.streams : 4;
+        g.overlap_phases = cfg.overlap_phases != 0;
         g.owner = getpid();
         g.stop = false;
         g.listen_fd = -1;

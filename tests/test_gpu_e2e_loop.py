@@ -22,9 +22,7 @@ torch = pytest.importorskip("torch")
 MIB = 1 << 20
 
 
-class UvmConfig(C.Structure):
-    _fields_ = [("socket_path", C.c_char_p), ("chunk_bytes", C.c_uint64), ("batch_bytes", C.c_uint64),
-                ("streams", C.c_uint32), ("listen", C.c_int32)]
+from retarget_b200.capi import UvmConfig  # noqa: E402
 
 
 def test_plan_prefetch_attention_every_step():

@@ -28,9 +28,7 @@ def build_fake():
     return FAKE
 
 
-class RtUvmConfig(C.Structure):
-    _fields_ = [("socket_path", C.c_char_p), ("chunk_bytes", C.c_uint64), ("batch_bytes", C.c_uint64),
-                ("streams", C.c_uint32), ("listen", C.c_int32)]
+from retarget_b200.capi import UvmConfig as RtUvmConfig  # noqa: E402
 
 
 @pytest.fixture(scope="module")
@@ -360,3 +358,50 @@ def test_side_streams_are_tracked_per_device(server):
     assert prefetch(b2) == (3, 0)                                # device 1 starts over
     for ptr in (0x7f1000000000, 0x7f3000000000):
         assert env.lib.rt_uvm_unregister_ptr(ptr) == 1
+
+
+def test_overlapped_phases_move_both_ways_at_once(server):
+    """With `overlap_phases` the CPU-bound and the GPU-bound stretch of a plan are
+    issued in turn inside one batch (no wait between them), each on its own side
+    streams; the same chunks are prefetched, the same bytes are accounted."""
+    env = server
+    base = 0x7f4000000000
+    ids = [env.register(128 * MIB, base + k * (1 << 30)) for k in range(4)]
+    gen = env.local.status().allocation_generation
+    n_alloc = sum(1 for a in env.registry if a["bytes"] == 128 * MIB)
+    line = f"windowv {gen} {128 * MIB} {n_alloc} 0 {32 * MIB} {16 * MIB} {48 * MIB}"
+
+    def run():
+        env.fake.fake_cuda_reset()
+        reply = env.local.command(line)
+        assert reply["ok"], reply
+        done = env.local._wait_job(reply["job_id"], timeout=10, poll_seconds=0.002)
+        events = [l.split() for l in env.log() if l.startswith(("prefetch", "sync"))]
+        return events, done
+
+    in_order, done_a = run()
+    assert env.lib.rt_uvm_stop() == 0
+    cfg = RtUvmConfig(env.sock.encode(), 16 * MIB, 64 * MIB, 4, 1, 1)
+    assert env.lib.rt_uvm_start(C.byref(cfg)) == 0
+    try:
+        overlapped, done_b = run()
+    finally:
+        assert env.lib.rt_uvm_stop() == 0
+        cfg = RtUvmConfig(env.sock.encode(), 16 * MIB, 64 * MIB, 3, 1)
+        assert env.lib.rt_uvm_start(C.byref(cfg)) == 0
+    chunks = lambda events: sorted((e[1], int(e[2]), int(e[3])) for e in events if e[0] == "prefetch")
+    assert chunks(in_order) == chunks(overlapped) and done_a.job_completed_bytes == done_b.job_completed_bytes
+    # the reference's order waits between the phases; the overlapped one alternates directions before any wait
+    first_sync = next(i for i, e in enumerate(overlapped) if e[0] == "sync")
+    before = [int(e[3]) for e in overlapped[:first_sync]]
+    assert -1 in before and any(d >= 0 for d in before)
+    assert any(a != b for a, b in zip(before, before[1:]))
+    # each direction keeps to its own streams
+    streams = {}
+    for e in overlapped:
+        if e[0] == "prefetch":
+            streams.setdefault(int(e[3]) < 0, set()).add(e[4])
+    assert not (streams[True] & streams[False])
+    for k in range(4):
+        assert env.lib.rt_uvm_unregister_ptr(base + k * (1 << 30)) == 1
+    env.registry[:] = [a for a in env.registry if a["id"] not in ids]
