@@ -394,10 +394,11 @@ typedef struct rt_layout {
                              /* 0 .. 2^31 keep their class: negative stays "ignored", large */
                              /* stays "out of range"), when there are at least 2^20 of them.*/
                              /* RETARGET_B200_PACK_THREADS sets the number of host threads  */
-                             /* (0: never narrow).  Default: 3/4 of the process's CPUs per  */
-                             /* visible GPU, at most 16; with fewer than 8 the call copies  */
-                             /* the ids as they are (narrowing costs host memory traffic,   */
-                             /* which is what is short when many planners share a host).    */
+                             /* (0: never narrow).  Default: 3/4 of the process's CPUs, at  */
+                             /* most 16, when ONE GPU is visible; with more GPUs visible,   */
+                             /* or fewer than 8 threads, the call copies the ids as they    */
+                             /* are (narrowing costs host memory traffic, which is what is  */
+                             /* short when several planners share a host).                  */
 
 /* A step whose result carries any of these flags has NOT changed the resident
  * bitmaps: a plan that cannot be delivered in full is not committed (the

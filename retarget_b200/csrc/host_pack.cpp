@@ -75,14 +75,17 @@ unsigned narrow_threads(unsigned sharers) {
     cpu_set_t set;
     unsigned cpus = std::thread::hardware_concurrency();
     if (sched_getaffinity(0, sizeof(set), &set) == 0) cpus = (unsigned)CPU_COUNT(&set);
-    // three quarters of this process's share of the CPUs: the rest stays free for the
-    // caller's other threads and the driver's
-    unsigned t = cpus / (sharers ? sharers : 1) * 3 / 4;
+    // Narrowing trades host memory traffic for link traffic: it reads 8 and writes 4
+    // bytes per id to save 4 on the link, and the copy engine reads those 4 again.  It
+    // pays when the link is what is short and the host's memory is not: one planner on
+    // a host.  Two planners narrowing side by side on one host measured slower than two
+    // wide copies (3.98 against 3.60 ms per step), and with fewer than 8 threads the
+    // narrowing is slower than the copy it shortens.
+    if (sharers > 1) return 0;
+    // three quarters of the CPUs: the rest stays free for the caller's other threads
+    // and the driver's
+    unsigned t = cpus * 3 / 4;
     if (t > 16) t = 16;
-    // Narrowing trades host memory traffic for link traffic (it reads 8 and writes 4
-    // bytes per id to save 4 on the link).  With fewer than 8 threads it is slower than
-    // the copy it shortens, and with one planner per GPU on a host whose CPUs are
-    // shared by 4 or 8 of them it is the host memory, not the link, that is short.
     return t >= 8 ? t : 0;
 }
 

@@ -32,9 +32,9 @@ void narrow_ids_streamed(const int64_t *src, int32_t *dst, size_t n, unsigned th
 
 // Threads the host-buffer call narrows with, 0 for "do not narrow".
 // RETARGET_B200_PACK_THREADS decides if set (0 switches narrowing off).  Else:
-// three quarters of the CPUs this process may run on, divided by `sharers`
-// (processes expected to do the same at the same time: one per visible GPU), at
-// most 16 -- and 0 when that leaves fewer than 8.
+// 0 when `sharers` (processes expected to do the same at the same time: one per
+// visible GPU) is more than one; otherwise three quarters of the CPUs this
+// process may run on, at most 16 -- and 0 when that leaves fewer than 8.
 unsigned narrow_threads(unsigned sharers);
 
 }  // namespace rt

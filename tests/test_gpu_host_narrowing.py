@@ -9,6 +9,7 @@ from retarget_b200 import capi, workloads
 from retarget_b200.planner import DevicePlanner, ranges_to_tuples
 
 pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
 
 
 @pytest.fixture(autouse=True)
@@ -73,6 +74,8 @@ def test_thread_rule(monkeypatch):
     monkeypatch.delenv("RETARGET_B200_PACK_THREADS")
     p = DevicePlanner(lay, 0, max_indices=64)
     assert p.narrow_threads() == 0 or 8 <= p.narrow_threads() <= 16
+    if torch.cuda.device_count() > 1:
+        assert p.narrow_threads() == 0          # several GPUs visible: the planners share the host
     p.close()
 
 
