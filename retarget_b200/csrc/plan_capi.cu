@@ -390,10 +390,16 @@ int step_host_impl(rt_plan *pl, const void *h_slots, bool ids32, const int64_t *
     bool narrow = !ids32 && !(flags & (RT_PLAN_WIDE_COPY | RT_PLAN_TMA)) && n >= kNarrowMinIds &&
                   pl->layout.capacity_slots < 0x7fffffffull;
     narrow = narrow && plan_narrow_threads(pl) > 0;
+    if (narrow && !pl->h_narrow &&
+        cudaHostAlloc(reinterpret_cast<void **>(&pl->h_narrow), 4 * (size_t)pl->max_indices + 64,
+                      cudaHostAllocDefault) != cudaSuccess) {
+        // no pinned memory for the staging buffer: this plan copies its ids as they are
+        cudaGetLastError();
+        pl->h_narrow = nullptr;
+        pl->narrow_threads = 0;
+        narrow = false;
+    }
     if (narrow) {
-        if (!pl->h_narrow)
-            RT_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&pl->h_narrow), 4 * (size_t)pl->max_indices + 64,
-                                  cudaHostAllocDefault));
         // every chunk is copied as soon as it is narrowed, while the host threads go on
         struct Copier {
             rt_plan *pl;
