@@ -657,20 +657,26 @@ def run_ours(args):
                     tables = [torch.from_numpy(b.slots.astype(dtype).reshape(rows, 2176)).to(dev) for b in batches]
                     lens = torch.full((rows,), 2176, dtype=torch.int32, device=dev)
 
-                    def table_step(i):
-                        tp.step_table(tables[i % 2], lens, batches[0].budget_blocks, flags, d_out, d_res,
-                                      stream.cuda_stream)
+                    def table_step(i, handle):
+                        tp.step_table(tables[i % 2], lens, batches[0].budget_blocks, flags, d_out, d_res, handle)
                     for i in range(4):
-                        table_step(i)
+                        table_step(i, stream.cuda_stream)
                     torch.cuda.synchronize()
-                    n = 400
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                        for i in range(20):
+                            table_step(i, torch.cuda.current_stream().cuda_stream)
+                    g.replay()
+                    torch.cuda.synchronize()
+                    n = 800
                     t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
                     t[0].record(stream)
-                    for i in range(n):
-                        table_step(i)
+                    for _ in range(n // 20):
+                        g.replay()
                     t[1].record(stream)
                     torch.cuda.synchronize()
                     us = t[0].elapsed_time(t[1]) * 1e3 / n
+                    del g
                     variants[name] = {"us_per_step": us, "rows": rows, "stride": 2176, "steps": n,
                                       "ranges_per_step": timer.result()["n_ranges"],
                                       "gbs": width * batches[0].n_idx / us / 1e3}

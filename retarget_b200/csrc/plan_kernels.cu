@@ -561,6 +561,17 @@ __device__ __forceinline__ void fetch_warp_batch(const Id *slots, const ScanArgs
     using Vec = typename IdTraits<Id>::Vec;
     constexpr int kPer = IdTraits<Id>::kPer;
     constexpr uint32_t kWhole = (1u << kPer) - 1u;
+    // Common case: all of this lane's vectors lie strictly inside the current
+    // segment (neither its first nor its last vector, which may be partly
+    // padding): kUnroll whole-vector loads off one pointer, nothing to test.
+    const uint32_t rel = base + lane - c.first;               // wraps far above n_vec once the segment is behind
+    if (!c.done && rel >= 1u && (unsigned long long)rel + 32u * (kUnroll - 1) + 1u < c.n_vec) {
+        const Vec *src = reinterpret_cast<const Vec *>(slots + c.i0) + rel;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) ch.v[u] = RT_LOAD(src + 32 * u);
+        ch.mask = kAllIdsOf<Id>;
+        return;
+    }
     ch.mask = 0;
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
