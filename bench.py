@@ -17,7 +17,7 @@ The JSON line (rank 0) carries every term of the metric:
 
 `value`      device time per step, slot ids already in HBM: two CUDA events on
              the launching stream around the timed steps, max over ranks.  The
-             steps go out as replays of a CUDA graph of chained steps; the graph
+             steps go out as replays of a CUDA graph of 100 chained steps; the graph
              is replayed until the timed region lasts at least 50 ms, so that
              `--steps 20` does not end up timing 0.6 ms (`timed_steps` says how
              many steps were timed; `steps` stays the number asked for)
@@ -105,8 +105,12 @@ def workload_config(batch, args) -> dict:
         if name.endswith(tag):
             name = name[:-len(tag)] + text
     world = args.gpus
-    launch = ("CUDA graph of up to 20 steps, replayed until the timed region lasts >= 50 ms"
-              if args.launch == "graph" else "one launch per step on the stream, >= 50 ms of steps")
+    if args.launch != "graph":
+        launch = "one launch per step on the stream, >= 50 ms of steps"
+    elif args.min_timed_ms >= 10:
+        launch = f"CUDA graph of 100 steps, replayed until the timed region lasts >= {args.min_timed_ms:g} ms"
+    else:
+        launch = "CUDA graph of at most 20 steps, replayed once"
     if not args.unchained:
         launch += "; steps chained (programmatic dependent launch): the scan of step i+1 runs over the tail of step i"
     return {"workload": name, "layers": lay.layers, "kv_buffers": lay.n_buffers,
@@ -290,7 +294,9 @@ class StepTimer:
         per = 0
         graph = None
         if launch == "graph":
-            per = max(2, min(20, min_steps - min_steps % 2))
+            # a replay's first step cannot chain to the replay before it: long graphs make that rare.
+            # (runs that ask for no minimum time -- profiler captures -- keep the graph as short as the request)
+            per = 100 if min_ms >= 10 else max(2, min(20, min_steps - min_steps % 2))
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=self.stream, capture_error_mode="thread_local"):
                 for i in range(per):
@@ -664,14 +670,14 @@ def run_ours(args):
                     torch.cuda.synchronize()
                     g = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
-                        for i in range(20):
+                        for i in range(100):
                             table_step(i, torch.cuda.current_stream().cuda_stream)
                     g.replay()
                     torch.cuda.synchronize()
-                    n = 800
+                    n = 1000
                     t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
                     t[0].record(stream)
-                    for _ in range(n // 20):
+                    for _ in range(n // 100):
                         g.replay()
                     t[1].record(stream)
                     torch.cuda.synchronize()
@@ -720,18 +726,18 @@ def run_ours(args):
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
-                for i in range(20):
+                for i in range(100):
                     read_only(i, torch.cuda.current_stream().cuda_stream)
             g.replay()
             torch.cuda.synchronize()
             t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
             t[0].record(stream)
-            for _ in range(40):
+            for _ in range(10):
                 g.replay()
             t[1].record(stream)
             torch.cuda.synchronize()
-            us = t[0].elapsed_time(t[1]) * 1e3 / 800
-            variants["read_only_probe"] = {"us_per_step": us, "steps": 800, "gbs": nbytes / us / 1e3,
+            us = t[0].elapsed_time(t[1]) * 1e3 / 1000
+            variants["read_only_probe"] = {"us_per_step": us, "steps": 1000, "gbs": nbytes / us / 1e3,
                                            "note": "rt_read_probe over the same two id arrays, graph replays of launches "
                                                    "that overlap each other: the same bytes read and thrown away"}
             del g

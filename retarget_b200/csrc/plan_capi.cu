@@ -157,10 +157,12 @@ int fill_scan_args_csr(const rt_plan *pl, rt::ScanArgs &a, const void *d_slots,
 
 // Worker CTAs of a launch.  One wave: every CTA is resident from the start and
 // owns one contiguous span; one slot of the wave is left for the gatekeeper CTA
-// the launcher adds.
-int grid_for(const rt_plan *pl, int units, bool tma) {
+// the launcher adds.  A chained launch leaves a second slot free: the one the
+// launch before it is still running its tail in.  Without it one worker starts
+// late by the length of that tail and, the spans being fixed, finishes late.
+int grid_for(const rt_plan *pl, int units, bool tma, bool chained) {
     const int per_sm = tma ? pl->tma_blocks_per_sm : pl->plain_blocks_per_sm;
-    long long slots = (long long)pl->sm_count * per_sm - 1;
+    long long slots = (long long)pl->sm_count * per_sm - 1 - (chained ? 1 : 0);
     if (slots < 1) slots = 1;
     return (int)(units < slots ? units : slots);
 }
@@ -354,7 +356,7 @@ int step_device_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t
     next_scratch(pl, p);
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
     const bool chained = (flags & RT_PLAN_CHAINED) != 0;
-    int grid = grid_for(pl, a.n_units, tma);
+    int grid = grid_for(pl, a.n_units, tma, chained);
     RT_CUDA(tma ? rt::launch_scan_plan_tma(a, p, grid, s, chained)
                 : rt::launch_scan_plan(a, p, false, ids32, grid, s, chained));
     return RT_OK;
@@ -454,7 +456,9 @@ int step_table_impl(rt_plan *pl, const void *d_table, bool ids32, const int32_t 
     // for a warp each, else to CTAs.  Rows are cut into segments of at least 1024
     // ids until there are about four segments per worker, so that the last round
     // of the round-robin leaves few workers idle.
-    const unsigned long long ctas = (unsigned long long)pl->sm_count * pl->table_blocks_per_sm - 1;   // one wave, less the gatekeeper
+    // one wave, less the gatekeeper and, when chained, the slot the previous launch's tail still runs in
+    const unsigned long long ctas = (unsigned long long)pl->sm_count * pl->table_blocks_per_sm - 1 -
+                                    ((flags & RT_PLAN_CHAINED) ? 1 : 0);
     const unsigned long long workers = stride >= 1024 ? ctas * (rt::kScanThreads / 32) : ctas;
     unsigned long long segs = 1;
     if (n_rows < 4 * workers) {
@@ -503,7 +507,7 @@ int scan_slots_impl(rt_plan *pl, const void *d_slots, bool ids32, const int64_t 
     p.bitmaps_out = d_bitmaps;
     next_scratch(pl, p);
     cudaStream_t s = stream ? (cudaStream_t)stream : pl->stream;
-    RT_CUDA(rt::launch_scan_plan(a, p, false, ids32, grid_for(pl, a.n_units, false), s, false));
+    RT_CUDA(rt::launch_scan_plan(a, p, false, ids32, grid_for(pl, a.n_units, false, false), s, false));
     return RT_OK;
 }
 
