@@ -532,8 +532,8 @@ def feedback_leg(torch, dev, stream, steps=100, warm=8, cpu=True):
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, mean of 3 launches), keyed by
 # (workload, tma); a configuration that was not captured reports null.
 PROFILED_TRAFFIC_BYTES = {
-    ("target", False): 182_063_000,   # 178.34 MB read + 3.72 MB written
-    ("target", True): 182_228_000,    # 178.34 MB read + 3.89 MB written
+    ("target", False): 182_136_000,   # 178.34 MB read + 3.79 MB written
+    ("target", True): 183_182_000,    # 178.34 MB read + 4.85 MB written
 }
 
 
