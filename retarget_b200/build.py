@@ -64,6 +64,7 @@ def build(force: bool = False, verbose: bool = False) -> dict:
     headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
     objs = []
     log = []
+    compiled = []                # what this call had to (re)make: empty when everything was up to date
     cu = CORE_CU + [f for f in OPTIONAL_CORE_CU if (CSRC / f).exists()]
     cpp = CORE_CPP + [f for f in OPTIONAL_CORE_CPP if (CSRC / f).exists()]
     for name in cu:
@@ -71,16 +72,19 @@ def build(force: bool = False, verbose: bool = False) -> dict:
         if force or _stale(obj, [src, *headers]):
             log.append(_run([nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []),
                              "-c", str(src), "-o", str(obj)]))
+            compiled.append(name)
         objs.append(obj)
     for name in cpp:
         src, obj = CSRC / name, OBJ / (name + ".o")
         if force or _stale(obj, [src, *headers]):
             log.append(_run(["g++", *CXX_FLAGS, f"-I{cuda_include()}", "-c", str(src), "-o", str(obj)]))
+            compiled.append(name)
         objs.append(obj)
     core = PKG / "libretarget_b200.so"
     if force or _stale(core, objs):
         _run([nvcc(), "-shared", "-o", str(core), *map(str, objs),
               "-cudart", "static", "-Xlinker", "--no-undefined", "-lpthread", "-ldl", "-lrt"])
+        compiled.append(core.name)
     out = {"core": core}
     pre_srcs = [CSRC / f for f in PRELOAD_CPP if (CSRC / f).exists()]
     if pre_srcs:
@@ -89,14 +93,17 @@ def build(force: bool = False, verbose: bool = False) -> dict:
             obj = OBJ / (src.name + ".o")
             if force or _stale(obj, [src, *headers]):
                 _run(["g++", *CXX_FLAGS, f"-I{cuda_include()}", "-c", str(src), "-o", str(obj)])
+                compiled.append(src.name)
             pre_objs.append(obj)
         pre = PKG / "libretarget_preload.so"
         if force or _stale(pre, pre_objs + objs):
             _run([nvcc(), "-shared", "-o", str(pre), *map(str, pre_objs), *map(str, objs),
                   "-cudart", "static", "-lpthread", "-ldl", "-lrt"])
+            compiled.append(pre.name)
         out["preload"] = pre
     if verbose:
         print("".join(log))
+    out["compiled"] = compiled
     return out
 
 
@@ -125,4 +132,5 @@ def build_stall_variant(force: bool = False) -> Path:
 if __name__ == "__main__":
     built = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     for k, v in built.items():
-        print(k, v)
+        if k != "compiled":
+            print(k, v)
