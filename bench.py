@@ -618,149 +618,152 @@ def run_ours(args):
 
     extras = {}
     if rank == 0 and single and not args.no_extras:
-        def leg(pair, tensors, *, launch=args.launch, f=None, id_bytes=8, min_ms=20.0, p=None):
-            t = timer if p is None else StepTimer(torch, p, stream, d_out, d_res, flags)
-            n, go, _ = t.timed(tensors, pair, min_steps=50, launch=launch, min_ms=min_ms, flags=f)
-            ms = go(n)
-            nr = t.result()["n_ranges"]
-            us = ms * 1e3 / n
-            gbs = algorithmic_bytes(pair[0], nr, id_bytes) / us / 1e3
-            return {"us_per_step": us, "ranges_per_step": nr, "steps": n, "gbs": gbs}
-
-        # per-launch kernel durations: an event pair around every launch, fully serialised launches
-        dur = []
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
-        for i, (a, b) in enumerate(evs):
-            a.record(stream)
-            timer.step(d_slots, batches, i, flags=base)
-            b.record(stream)
-        torch.cuda.synchronize()
-        dur = sorted(a.elapsed_time(b) * 1e3 for a, b in evs)
-        extras["per_launch_us"] = {"launches": len(dur), "min": dur[0], "median": dur[len(dur) // 2],
-                                   "p95": dur[int(len(dur) * 0.95)],
-                                   "how": "one CUDA event pair around every launch, launches not chained"}
-        variants = {}
-        if args.workload == "target":
-            variants["stream_launches"] = leg(batches, d_slots, launch="stream")
-            variants["unchained_graph"] = leg(batches, d_slots, f=base)
-            for kind in ("steady", "fragmented"):
-                pair = workloads.target_pair(kind)
-                tensors = upload(torch, dev, pair)
-                variants[kind] = leg(pair, tensors)
-                del tensors
-            tensors = upload(torch, dev, batches, np.int32)
-            variants["int32_ids"] = leg(batches, tensors, id_bytes=4)
-            del tensors
-            if not args.tma:
-                variants["tma_staging"] = leg(batches, d_slots, f=flags | capi.RT_PLAN_TMA)
-            # the padded-table entry point (the serving engine's req_to_token layout) on the same ids:
-            # one row per (layer, request), one bitmap for all buffers
-            rows = batches[0].n_idx // 2176
-            if rows * 2176 == batches[0].n_idx:
-                shared = dataclasses.replace(lay, shared_bitmap=True)
-                for name, dtype, width in (("table_int32_one_bitmap", np.int32, 4), ("table_int64_one_bitmap", np.int64, 8)):
-                    tp = DevicePlanner(shared, local)
-                    tables = [torch.from_numpy(b.slots.astype(dtype).reshape(rows, 2176)).to(dev) for b in batches]
-                    lens = torch.full((rows,), 2176, dtype=torch.int32, device=dev)
-
-                    def table_step(i, handle):
-                        tp.step_table(tables[i % 2], lens, batches[0].budget_blocks, flags, d_out, d_res, handle)
-                    for i in range(4):
-                        table_step(i, stream.cuda_stream)
-                    torch.cuda.synchronize()
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
-                        for i in range(100):
-                            table_step(i, torch.cuda.current_stream().cuda_stream)
-                    g.replay()
-                    torch.cuda.synchronize()
-                    n = 1000
-                    t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-                    t[0].record(stream)
-                    for _ in range(n // 100):
-                        g.replay()
-                    t[1].record(stream)
-                    torch.cuda.synchronize()
-                    us = t[0].elapsed_time(t[1]) * 1e3 / n
-                    del g
-                    variants[name] = {"us_per_step": us, "rows": rows, "stride": 2176, "steps": n,
-                                      "ranges_per_step": timer.result()["n_ranges"],
-                                      "gbs": width * batches[0].n_idx / us / 1e3}
-                    tp.close()
-                    del tables
-            # the allocation-free scan (scratch in a static device array, scan only, 64-bit ids)
-            fn = capi.lib.rt_scan_slots_static
-            fn.restype = C.c_int
-            fn.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p,
-                           C.c_void_p, C.c_void_p]
-            d_bits = torch.zeros(lay.n_groups * 32, dtype=torch.int32, device=dev)
-
-            def static_scan(i):
-                b = batches[i % 2]
-                capi.check(fn(d_slots[i % 2].data_ptr(), b.group_off.ctypes.data, lay.n_groups, lay.capacity,
-                              lay.block_tokens, lay.n_blocks, d_bits.data_ptr(), d_res.data_ptr(),
-                              stream.cuda_stream), "rt_scan_slots_static")
-            for i in range(4):
-                static_scan(i)
-            torch.cuda.synchronize()
-            t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-            t[0].record(stream)
-            for i in range(200):
-                static_scan(i)
-            t[1].record(stream)
-            torch.cuda.synchronize()
-            us = t[0].elapsed_time(t[1]) * 1e3 / 200
-            variants["static_scan_only"] = {"us_per_step": us, "steps": 200, "gbs": 8 * batches[0].n_idx / us / 1e3,
-                                            "note": "rt_scan_slots_static: a memset of its scratch + one launch per call"}
-            # what a pure read of the same bytes reaches (same access pattern, nothing done with the ids)
-            probe = capi.lib.rt_read_probe
-            probe.restype = C.c_int
-            probe.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]
-            d_sink = torch.zeros(1, dtype=torch.int64, device=dev)
-            nbytes = 8 * batches[0].n_idx // 16 * 16
-
-            def read_only(i, handle):
-                capi.check(probe(d_slots[i % 2].data_ptr(), nbytes, d_sink.data_ptr(), handle), "rt_read_probe")
-            for i in range(4):
-                read_only(i, stream.cuda_stream)
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
-                for i in range(100):
-                    read_only(i, torch.cuda.current_stream().cuda_stream)
-            g.replay()
-            torch.cuda.synchronize()
-            t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-            t[0].record(stream)
-            for _ in range(10):
-                g.replay()
-            t[1].record(stream)
-            torch.cuda.synchronize()
-            us = t[0].elapsed_time(t[1]) * 1e3 / 1000
-            variants["read_only_probe"] = {"us_per_step": us, "steps": 1000, "gbs": nbytes / us / 1e3,
-                                           "note": "rt_read_probe over the same two id arrays, graph replays of launches "
-                                                   "that overlap each other: the same bytes read and thrown away"}
-            del g
-            for i in range(2):      # leave the resident state as the main workload left it
-                timer.step(d_slots, batches, W + n_timed + i)
-            torch.cuda.synchronize()
-        extras["variants"] = variants
-        # the other stated configurations
-        configs = {}
-        for name in ("full_refresh", "sparse"):
-            pair = [make_workload(name, 0), make_workload(name, 1)]
-            p = DevicePlanner(pair[0].layout, local)
-            tensors = upload(torch, dev, pair)
-            configs[name] = leg(pair, tensors, p=p)
-            configs[name]["slot_ids_per_step"] = pair[0].n_idx
-            p.close()
-            del tensors
-        extras["configs"] = configs
-        extras["feedback"] = feedback_leg(torch, dev, stream, cpu=not args.no_cpu)
         try:
-            extras["prefetch"] = prefetch_leg(torch, dev)
-        except Exception as exc:                        # the headline must not die with a side measurement
-            extras["prefetch"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+            def leg(pair, tensors, *, launch=args.launch, f=None, id_bytes=8, min_ms=20.0, p=None):
+                t = timer if p is None else StepTimer(torch, p, stream, d_out, d_res, flags)
+                n, go, _ = t.timed(tensors, pair, min_steps=50, launch=launch, min_ms=min_ms, flags=f)
+                ms = go(n)
+                nr = t.result()["n_ranges"]
+                us = ms * 1e3 / n
+                gbs = algorithmic_bytes(pair[0], nr, id_bytes) / us / 1e3
+                return {"us_per_step": us, "ranges_per_step": nr, "steps": n, "gbs": gbs}
+
+            # per-launch kernel durations: an event pair around every launch, fully serialised launches
+            dur = []
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
+            for i, (a, b) in enumerate(evs):
+                a.record(stream)
+                timer.step(d_slots, batches, i, flags=base)
+                b.record(stream)
+            torch.cuda.synchronize()
+            dur = sorted(a.elapsed_time(b) * 1e3 for a, b in evs)
+            extras["per_launch_us"] = {"launches": len(dur), "min": dur[0], "median": dur[len(dur) // 2],
+                                       "p95": dur[int(len(dur) * 0.95)],
+                                       "how": "one CUDA event pair around every launch, launches not chained"}
+            variants = {}
+            if args.workload == "target":
+                variants["stream_launches"] = leg(batches, d_slots, launch="stream")
+                variants["unchained_graph"] = leg(batches, d_slots, f=base)
+                for kind in ("steady", "fragmented"):
+                    pair = workloads.target_pair(kind)
+                    tensors = upload(torch, dev, pair)
+                    variants[kind] = leg(pair, tensors)
+                    del tensors
+                tensors = upload(torch, dev, batches, np.int32)
+                variants["int32_ids"] = leg(batches, tensors, id_bytes=4)
+                del tensors
+                if not args.tma:
+                    variants["tma_staging"] = leg(batches, d_slots, f=flags | capi.RT_PLAN_TMA)
+                # the padded-table entry point (the serving engine's req_to_token layout) on the same ids:
+                # one row per (layer, request), one bitmap for all buffers
+                rows = batches[0].n_idx // 2176
+                if rows * 2176 == batches[0].n_idx:
+                    shared = dataclasses.replace(lay, shared_bitmap=True)
+                    for name, dtype, width in (("table_int32_one_bitmap", np.int32, 4), ("table_int64_one_bitmap", np.int64, 8)):
+                        tp = DevicePlanner(shared, local)
+                        tables = [torch.from_numpy(b.slots.astype(dtype).reshape(rows, 2176)).to(dev) for b in batches]
+                        lens = torch.full((rows,), 2176, dtype=torch.int32, device=dev)
+
+                        def table_step(i, handle):
+                            tp.step_table(tables[i % 2], lens, batches[0].budget_blocks, flags, d_out, d_res, handle)
+                        for i in range(4):
+                            table_step(i, stream.cuda_stream)
+                        torch.cuda.synchronize()
+                        g = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                            for i in range(100):
+                                table_step(i, torch.cuda.current_stream().cuda_stream)
+                        g.replay()
+                        torch.cuda.synchronize()
+                        n = 1000
+                        t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                        t[0].record(stream)
+                        for _ in range(n // 100):
+                            g.replay()
+                        t[1].record(stream)
+                        torch.cuda.synchronize()
+                        us = t[0].elapsed_time(t[1]) * 1e3 / n
+                        del g
+                        variants[name] = {"us_per_step": us, "rows": rows, "stride": 2176, "steps": n,
+                                          "ranges_per_step": timer.result()["n_ranges"],
+                                          "gbs": width * batches[0].n_idx / us / 1e3}
+                        tp.close()
+                        del tables
+                # the allocation-free scan (scratch in a static device array, scan only, 64-bit ids)
+                fn = capi.lib.rt_scan_slots_static
+                fn.restype = C.c_int
+                fn.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p,
+                               C.c_void_p, C.c_void_p]
+                d_bits = torch.zeros(lay.n_groups * 32, dtype=torch.int32, device=dev)
+
+                def static_scan(i):
+                    b = batches[i % 2]
+                    capi.check(fn(d_slots[i % 2].data_ptr(), b.group_off.ctypes.data, lay.n_groups, lay.capacity,
+                                  lay.block_tokens, lay.n_blocks, d_bits.data_ptr(), d_res.data_ptr(),
+                                  stream.cuda_stream), "rt_scan_slots_static")
+                for i in range(4):
+                    static_scan(i)
+                torch.cuda.synchronize()
+                t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                t[0].record(stream)
+                for i in range(200):
+                    static_scan(i)
+                t[1].record(stream)
+                torch.cuda.synchronize()
+                us = t[0].elapsed_time(t[1]) * 1e3 / 200
+                variants["static_scan_only"] = {"us_per_step": us, "steps": 200, "gbs": 8 * batches[0].n_idx / us / 1e3,
+                                                "note": "rt_scan_slots_static: a memset of its scratch + one launch per call"}
+                # what a pure read of the same bytes reaches (same access pattern, nothing done with the ids)
+                probe = capi.lib.rt_read_probe
+                probe.restype = C.c_int
+                probe.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]
+                d_sink = torch.zeros(1, dtype=torch.int64, device=dev)
+                nbytes = 8 * batches[0].n_idx // 16 * 16
+
+                def read_only(i, handle):
+                    capi.check(probe(d_slots[i % 2].data_ptr(), nbytes, d_sink.data_ptr(), handle), "rt_read_probe")
+                for i in range(4):
+                    read_only(i, stream.cuda_stream)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                    for i in range(100):
+                        read_only(i, torch.cuda.current_stream().cuda_stream)
+                g.replay()
+                torch.cuda.synchronize()
+                t = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                t[0].record(stream)
+                for _ in range(10):
+                    g.replay()
+                t[1].record(stream)
+                torch.cuda.synchronize()
+                us = t[0].elapsed_time(t[1]) * 1e3 / 1000
+                variants["read_only_probe"] = {"us_per_step": us, "steps": 1000, "gbs": nbytes / us / 1e3,
+                                               "note": "rt_read_probe over the same two id arrays, graph replays of launches "
+                                                       "that overlap each other: the same bytes read and thrown away"}
+                del g
+                for i in range(2):      # leave the resident state as the main workload left it
+                    timer.step(d_slots, batches, W + n_timed + i)
+                torch.cuda.synchronize()
+            extras["variants"] = variants
+            # the other stated configurations
+            configs = {}
+            for name in ("full_refresh", "sparse"):
+                pair = [make_workload(name, 0), make_workload(name, 1)]
+                p = DevicePlanner(pair[0].layout, local)
+                tensors = upload(torch, dev, pair)
+                configs[name] = leg(pair, tensors, p=p)
+                configs[name]["slot_ids_per_step"] = pair[0].n_idx
+                p.close()
+                del tensors
+            extras["configs"] = configs
+            extras["feedback"] = feedback_leg(torch, dev, stream, cpu=not args.no_cpu)
+            try:
+                extras["prefetch"] = prefetch_leg(torch, dev)
+            except Exception as exc:                        # the headline must not die with a side measurement
+                extras["prefetch"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+        except Exception as exc:                    # the headline must not die with a side measurement
+            extras["extras_error"] = f"{type(exc).__name__}: {exc}"
 
     # ---- end to end through the host-buffer call: pinned ids -> device -> plan -> ranges on the host ----
     out_host = np.empty(1 << 16, dtype=capi.RANGE_DTYPE)
